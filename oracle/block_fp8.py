@@ -1,0 +1,247 @@
+"""Torch/numpy CPU restatement of the reference's block-FP8 W8A8 arithmetic.
+
+TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).  Every function names the reference
+lines it follows.  All tensors live on the CPU; the arithmetic is the reference's own
+torch-native arithmetic, so results are compared bit for bit with the golden files that
+were produced by executing the reference's functions.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0
+
+
+def _align(x: int, a: int) -> int:
+    return (x + a - 1) // a * a
+
+
+# --------------------------------------------------------------------------------------
+# Q: per-token-group quantisation
+# --------------------------------------------------------------------------------------
+def ceil_to_ue8m0(s: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= s, for positive finite fp32 ``s``.
+
+    Follows ``python/sglang/srt/layers/quantization/fp8_utils.py:511-512``
+    (``2 ** ceil(log2(|x|))``) but with exact integer arithmetic on the fp32 exponent, so
+    the answer does not depend on libm's ``log2f`` rounding.
+    """
+    s = s.to(torch.float32).abs()
+    mant, exp = torch.frexp(s)  # s = mant * 2**exp, mant in [0.5, 1)
+    e = torch.where(mant == 0.5, exp - 1, exp)
+    return torch.ldexp(torch.ones_like(s), e)
+
+
+def per_token_group_quant_fp8(x: torch.Tensor, group_size: int = 128, eps: float = 1e-10,
+                              scale_ue8m0: bool = False):
+    """``native_per_token_group_quant_fp8`` (``python/sglang/test/test_block_fp8.py:23-48``).
+
+    amax is taken and clamped in the INPUT dtype (so eps becomes bf16(eps) for bf16 input),
+    then widened to fp32; scale = amax / 448 is an IEEE fp32 division; codes are
+    RNE_e4m3(clamp(x / scale)) with a true fp32 division per element.  With
+    ``scale_ue8m0`` the scale is rounded up to a power of two first (the reference's
+    Blackwell path, ``fp8_kernel.py:441-452`` + ``fp8_utils.py:511-512``).
+
+    Returns (codes e4m3 with x's shape, scales fp32 ``x.shape[:-1] + (K // group_size,)``).
+    """
+    assert x.shape[-1] % group_size == 0 and x.is_contiguous()
+    x_ = x.reshape(x.numel() // group_size, group_size)
+    amax = x_.abs().max(dim=-1, keepdim=True)[0].clamp(min=eps).to(torch.float32)
+    s = amax / FP8_MAX
+    if scale_ue8m0:
+        s = ceil_to_ue8m0(s)
+    q = (x_ / s).clamp(min=-FP8_MAX, max=FP8_MAX).to(FP8)
+    return q.reshape(x.shape), s.reshape(x.shape[:-1] + (x.shape[-1] // group_size,))
+
+
+def pack_scales(s: torch.Tensor, layout: str) -> torch.Tensor:
+    """Lay a logical ``[M, G]`` fp32 scale matrix out the way the reference allocates it
+    (``create_per_token_group_quant_fp8_output_scale``, ``fp8_kernel.py:433-474``).
+
+    layout:
+      "row"     -> contiguous ``[M, G]``
+      "col"     -> shape ``[M, G]``, strides ``(1, M)``
+      "col_tma" -> shape ``[M, G]``, strides ``(1, align(M, 4))``
+      "ue8m0"   -> int32 ``[M, ceil(G/4)]``, strides ``(1, align(M, 4))``; byte ``g % 4`` of
+                   int ``g // 4`` holds the biased exponent of scale g (scales must be
+                   powers of two); unused bytes are zero
+                   (``per_token_group_quant_8bit.cu:54-61,94-97``).
+    Padding rows (M..align(M,4)) are zero-filled here; the kernels leave them untouched.
+    """
+    M, G = s.shape
+    if layout == "row":
+        return s.contiguous()
+    if layout == "col":
+        return s.t().contiguous().t()
+    Ma = _align(M, 4)
+    if layout == "col_tma":
+        buf = torch.zeros(G, Ma, dtype=torch.float32)
+        buf[:, :M] = s.t()
+        return buf.t()[:M, :]
+    if layout == "ue8m0":
+        bits = s.contiguous().view(torch.int32)
+        assert bool(((bits & 0x7FFFFF) == 0).all()), "UE8M0 scales must be powers of two"
+        expo = ((bits >> 23) & 0xFF).to(torch.uint8)  # [M, G]
+        Gp = _align(G, 4)
+        buf = torch.zeros(Gp // 4, Ma, 4, dtype=torch.uint8)
+        e = torch.zeros(M, Gp, dtype=torch.uint8)
+        e[:, :G] = expo
+        buf[:, :M, :] = e.view(M, Gp // 4, 4).permute(1, 0, 2)
+        return buf.view(torch.int32).view(Gp // 4, Ma).t()[:M, :]
+    raise ValueError(layout)
+
+
+# --------------------------------------------------------------------------------------
+# W: 128x128 block quantisation of weights (offline)
+# --------------------------------------------------------------------------------------
+def block_quant_weight(w: torch.Tensor, block=(128, 128)):
+    """Block-quantise ``w [N, K]`` to e4m3 with fp32 scales ``[ceil(N/bn), ceil(K/bk)]``.
+
+    scale = block amax / 448 (1.0 for an all-zero block), code = RNE_e4m3(w / scale), as
+    ``convert_weight`` in ``test/srt/cpu/utils.py:39-87``; ragged edges are zero-padded
+    for the amax and cropped afterwards.
+    """
+    bn, bk = block
+    N, K = w.shape
+    Np, Kp = _align(N, bn), _align(K, bk)
+    wp = torch.zeros(Np, Kp, dtype=torch.float32)
+    wp[:N, :K] = w.to(torch.float32)
+    v = wp.view(Np // bn, bn, Kp // bk, bk)
+    s = v.abs().amax(dim=(1, 3), keepdim=True) / FP8_MAX
+    s = torch.where(s == 0, torch.ones_like(s), s)
+    q = (v / s).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(Np, Kp)[:N, :K].contiguous()
+    return q, s.view(Np // bn, Kp // bk).contiguous()
+
+
+# --------------------------------------------------------------------------------------
+# G: block-scaled GEMM
+# --------------------------------------------------------------------------------------
+def w8a8_block_fp8_matmul(A, B, As, Bs, block_size=(128, 128), output_dtype=torch.bfloat16):
+    """``native_w8a8_block_fp8_matmul`` (``python/sglang/test/test_block_fp8.py:273-325``).
+
+    ``C[:, nb] += (A[:, kb] @ B[nb, kb].T) * (As[:, kb] * Bs[nb, kb])`` in fp32, k-block
+    outer loop, n-block inner loop, then one cast to ``output_dtype``.  A ``[..., K]`` codes
+    (or fp32 values of codes), B ``[N, K]``, As ``[..., ceil(K/bk)]``, Bs ``[ceil(N/bn),
+    ceil(K/bk)]``.
+    """
+    bn, bk = block_size
+    A = A.to(torch.float32)
+    B = B.to(torch.float32)
+    K = A.shape[-1]
+    N = B.shape[0]
+    lead = A.shape[:-1]
+    A = A.reshape(-1, K)
+    As = As.reshape(A.shape[0], -1).to(torch.float32)
+    nt, kt = -(-N // bn), -(-K // bk)
+    assert Bs.shape == (nt, kt) and As.shape[1] == kt
+    C = torch.zeros(A.shape[0], N, dtype=torch.float32)
+    for i in range(kt):
+        a = A[:, i * bk:min((i + 1) * bk, K)]
+        for j in range(nt):
+            b = B[j * bn:min((j + 1) * bn, N), i * bk:min((i + 1) * bk, K)]
+            s = As[:, i:i + 1] * Bs[j][i]
+            C[:, j * bn:min((j + 1) * bn, N)] += torch.matmul(a, b.t()) * s
+    return C.reshape(lead + (N,)).to(output_dtype)
+
+
+# --------------------------------------------------------------------------------------
+# SA / ME: activation and the fused expert MLP
+# --------------------------------------------------------------------------------------
+def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
+    """``SiluAndMul.forward_native`` (``python/sglang/srt/layers/activation.py:68-70``):
+    ``silu(x[..., :d]) * x[..., d:]`` evaluated in x's dtype (for bf16 that is: silu in
+    fp32 rounded to bf16, then a bf16 multiply)."""
+    d = x.shape[-1] // 2
+    return torch.nn.functional.silu(x[..., :d]) * x[..., d:]
+
+
+def fused_experts_block_fp8(a, w1, w2, w1_s, w2_s, topk_weight, topk_ids, block_shape=(128, 128)):
+    """Expert MLP of ``torch_w8a8_block_fp8_moe`` (``test_block_fp8.py:418-447``) with the
+    routing result passed in.  a ``[M, H]`` bf16; w1 ``[E, 2I, H]``, w2 ``[E, H, I]`` e4m3;
+    w1_s ``[E, 2I/128, H/128]``, w2_s ``[E, H/128, I/128]``; topk_* ``[M, topk]``.
+    Experts with id < 0 or >= E contribute zero (non-local experts under expert
+    parallelism, ``fused_moe_triton_kernels.py:421-437``)."""
+    Bt, D = a.shape
+    topk = topk_ids.shape[1]
+    bk = block_shape[1]
+    rep = a.view(Bt, -1, D).repeat(1, topk, 1).reshape(-1, D)
+    out = torch.zeros(Bt * topk, w2.shape[1], dtype=a.dtype)
+    ids = topk_ids.reshape(-1)
+    a_q, a_s = per_token_group_quant_fp8(rep, bk)
+    a_q = a_q.to(torch.float32)
+    for e in range(w1.shape[0]):
+        mask = ids == e
+        if mask.sum():
+            h = w8a8_block_fp8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, a.dtype)
+            act = silu_and_mul(h)
+            act_q, act_s = per_token_group_quant_fp8(act.contiguous(), bk)
+            out[mask] = w8a8_block_fp8_matmul(act_q, w2[e], act_s, w2_s[e], block_shape, a.dtype)
+    return (out.view(Bt, -1, w2.shape[1]) * topk_weight.view(Bt, -1, 1).to(out.dtype)).sum(dim=1)
+
+
+def moe_block_fp8_from_scores(a, w1, w2, w1_s, w2_s, score, topk, block_shape=(128, 128)):
+    """``torch_w8a8_block_fp8_moe`` including its routing: fp32 softmax then ``torch.topk``
+    with no renormalisation (``test_block_fp8.py:424-425``)."""
+    p = torch.softmax(score, dim=-1, dtype=torch.float32)
+    w, ids = torch.topk(p, topk)
+    return fused_experts_block_fp8(a, w1, w2, w1_s, w2_s, w, ids, block_shape)
+
+
+# --------------------------------------------------------------------------------------
+# MP / MS: integer routing tables and the row shuffles
+# --------------------------------------------------------------------------------------
+def prepare_moe_input(topk_ids: np.ndarray, num_experts: int, n: int, k: int):
+    """Routing tables of ``prepare_moe_input`` (``sgl-kernel/csrc/moe/prepare_moe_input.cu:13-167``).
+
+    Returns int32 arrays ``expert_offsets [E+1]``, ``problem_sizes1 [E,3] = (cnt, 2n, k)``,
+    ``problem_sizes2 [E,3] = (cnt, k, n)``, ``a_map [M*topk]`` (sorted row -> source token)
+    and ``c_map [M*topk]`` (token-major slot -> sorted row).  The reference hands out slots
+    inside one expert's segment in atomic order; here the order is the stable one
+    (ascending flat index), which is one of the orders the reference can produce.  Ids
+    outside ``[0, E)`` get no row: their ``c_map`` entry is -1.
+    """
+    ids = np.asarray(topk_ids, dtype=np.int64)
+    topk = ids.shape[1]
+    flat = ids.reshape(-1)
+    valid = (flat >= 0) & (flat < num_experts)
+    cnt = np.bincount(flat[valid], minlength=num_experts).astype(np.int32)
+    offs = np.zeros(num_experts + 1, dtype=np.int32)
+    offs[1:] = np.cumsum(cnt)
+    ps1 = np.stack([cnt, np.full_like(cnt, 2 * n), np.full_like(cnt, k)], axis=1).astype(np.int32)
+    ps2 = np.stack([cnt, np.full_like(cnt, k), np.full_like(cnt, n)], axis=1).astype(np.int32)
+    total = int(offs[-1])
+    order = np.argsort(np.where(valid, flat, num_experts), kind="stable")[:total]
+    a_map = np.full(flat.shape[0], 0, dtype=np.int32)
+    a_map[:total] = (order // topk).astype(np.int32)
+    c_map = np.full(flat.shape[0], -1, dtype=np.int32)
+    c_map[order] = np.arange(total, dtype=np.int32)
+    return offs, ps1, ps2, a_map, c_map
+
+
+def shuffle_rows(x: torch.Tensor, dst2src: np.ndarray, n_dst: int | None = None) -> torch.Tensor:
+    """``shuffle_rows`` (``prepare_moe_input.cu:169-256``): ``out[i] = x[dst2src[i]]``."""
+    idx = torch.as_tensor(np.asarray(dst2src[: n_dst if n_dst is not None else len(dst2src)]),
+                          dtype=torch.long)
+    if x.dtype == FP8:
+        return x.view(torch.uint8)[idx].view(FP8)
+    return x[idx]
+
+
+def apply_shuffle_mul_sum(c2: torch.Tensor, c_map: np.ndarray, factors: torch.Tensor | None,
+                          m: int) -> torch.Tensor:
+    """``apply_shuffle_mul_sum`` (``prepare_moe_input.cu:258-392``):
+    ``out[i] = cast(sum_j fp32(factors[i,j]) * fp32(c2[c_map[i*topk+j]]))`` with the sum taken
+    in fp32 in ascending j.  Slots with ``c_map < 0`` (non-local experts) are skipped."""
+    cm = torch.as_tensor(np.asarray(c_map), dtype=torch.long).view(m, -1)
+    topk = cm.shape[1]
+    acc = torch.zeros(m, c2.shape[1], dtype=torch.float32)
+    f = None if factors is None else factors.reshape(m, topk).to(torch.float32)
+    for j in range(topk):
+        ok = cm[:, j] >= 0
+        rows = c2[cm[:, j].clamp(min=0)].to(torch.float32)
+        term = rows if f is None else rows * f[:, j:j + 1]
+        acc = acc + torch.where(ok[:, None], term, torch.zeros_like(term))
+    return acc.to(c2.dtype)
