@@ -1,0 +1,177 @@
+/*
+ * sglb200 — C ABI of the B200 (sm_100a) block-FP8 W8A8 hot path.
+ *
+ * One shared library, plain pointers and sizes, no C++ or torch types.  Every entry point
+ *   - works on DEVICE pointers and enqueues on the CUDA stream passed as `stream`
+ *     (a cudaStream_t cast to void*; NULL = the legacy default stream),
+ *   - validates shapes / strides / alignment on the host BEFORE launching anything and
+ *     returns 0 (SGLB200_OK) or a negative SGLB200_ERR_* code; it never throws, never
+ *     synchronises the device, and never allocates device memory unless its comment says so,
+ *   - borrows its inputs (never freed or written) and writes only the caller-allocated
+ *     outputs and the caller-provided scratch buffers named in its signature.
+ * sglb200_status_string() turns a code into text; sglb200_last_error_detail() returns a
+ * thread-local message describing the last failed check (which argument, which value).
+ *
+ * Reference files cited below are paths inside the vincent-shop/sglang tree.
+ */
+#ifndef SGLB200_H_
+#define SGLB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SGLB200_OK 0
+#define SGLB200_ERR_SHAPE (-1)       /* a size or stride is inconsistent or unsupported        */
+#define SGLB200_ERR_ALIGN (-2)       /* a pointer or leading dimension is not aligned as required */
+#define SGLB200_ERR_ARCH (-3)        /* the current device is not compute capability 10.x      */
+#define SGLB200_ERR_LAUNCH (-4)      /* the CUDA runtime refused the launch or a set-up call   */
+#define SGLB200_ERR_DTYPE (-5)       /* unsupported element type code                           */
+#define SGLB200_ERR_NULL (-6)        /* a required pointer is NULL                              */
+#define SGLB200_ERR_WORKSPACE (-7)   /* scratch buffer too small                                */
+
+/* element type codes used by the `*_dtype` arguments */
+#define SGLB200_BF16 0
+#define SGLB200_F16 1
+#define SGLB200_F32 2
+
+const char* sglb200_status_string(int status);
+const char* sglb200_last_error_detail(void);
+/* Library version, "major.minor". */
+const char* sglb200_version(void);
+
+/*
+ * Q — per-token-group quantisation to e4m3.
+ * Replaces: sgl_per_token_group_quant_8bit  sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217
+ *           (schema sgl-kernel/csrc/common_extension.cc:173-176) for the e4m3 destination type.
+ *
+ * input  [num_rows, hidden] contiguous, dtype in_dtype (bf16 / f16 / f32), 16-byte aligned.
+ * out_q  [num_rows, hidden] e4m3 bytes, contiguous, 8-byte aligned.
+ * out_s  one scale per (row, group), group = group_size consecutive elements of a row,
+ *        group_size in {16, 32, 64, 128}, hidden % group_size == 0:
+ *          scale_ue8m0 == 0: float at out_s[row * s_stride_row + g * s_stride_group]
+ *                            (row-major: (G, 1); column-major: (1, M) or (1, align(M,4)))
+ *          scale_ue8m0 != 0: out_s is int32; byte g % 4 of the int32 at
+ *                            out_s[row * s_stride_row + (g / 4) * s_stride_group] is the biased
+ *                            exponent of the power-of-two scale; bytes of a word past the last
+ *                            group are written as zero.  (Strides count int32 words.)
+ * Arithmetic (bit-exact with native_per_token_group_quant_fp8, python/sglang/test/test_block_fp8.py:23-48):
+ *   amax = max(max|x|, eps); s = amax / fp8_max (IEEE); UE8M0: s = 2^ceil(log2 s);
+ *   q = RNE_e4m3(clamp(x / s, fp8_min, fp8_max)) with a correctly rounded fp32 quotient.
+ * `eps` is used as given, in fp32: a caller that wants the torch-native behaviour for bf16 input
+ * passes eps already rounded to bf16 (the Python wrapper does).
+ */
+int sglb200_per_token_group_quant_fp8(const void* input, int in_dtype, void* out_q, void* out_s,
+                                      int64_t num_rows, int64_t hidden, int group_size, float eps,
+                                      float fp8_min, float fp8_max, int scale_ue8m0,
+                                      int64_t s_stride_row, int64_t s_stride_group, void* stream);
+
+/*
+ * Fused SiLU-and-mul + per-token-group quantisation (one pass over the gate_up activations).
+ * Replaces: sgl_per_token_group_quant_8bit_v2 with fuse_silu_and_mul, unmasked layout
+ *           sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:336-347,394-514.
+ * input [num_rows, 2 * hidden] (gate = first half, up = second half, as SiluAndMul,
+ * python/sglang/srt/layers/activation.py:68-70); act = round_in_dtype(round_in_dtype(silu(gate)) * up);
+ * outputs as sglb200_per_token_group_quant_fp8 over act [num_rows, hidden].
+ * If out_act is not NULL the activation (in_dtype, [num_rows, hidden]) is also stored.
+ */
+int sglb200_silu_mul_group_quant_fp8(const void* input, int in_dtype, void* out_q, void* out_s, void* out_act,
+                                     int64_t num_rows, int64_t hidden, int group_size, float eps,
+                                     float fp8_min, float fp8_max, int scale_ue8m0,
+                                     int64_t s_stride_row, int64_t s_stride_group, void* stream);
+
+/*
+ * G — block-scaled FP8 GEMM:  out[m, n] = cast( sum_kb ( sum_{k in kb} a[m,k] * b[n,k] ) * sa[m,kb] * sb[n/128,kb] ).
+ * Replaces: fp8_blockwise_scaled_mm  sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:368-465
+ *           (schema common_extension.cc:168-171) and the Triton twin w8a8_block_fp8_matmul_triton
+ *           python/sglang/srt/layers/quantization/fp8_kernel.py:1068-1145.
+ *
+ * a   [M, K] e4m3, row stride lda bytes (lda % 16 == 0, pointer 16-byte aligned).
+ * b   [N, K] e4m3 K-contiguous (the weight as stored; the reference's column-major mat_b [K, N] is the
+ *     same memory), row stride ldb bytes (ldb % 16 == 0, pointer 16-byte aligned).
+ * sa  float, element (m, kb) at sa[m * sa_stride_m + kb * sa_stride_k]   (M-major or K-major).
+ * sb  float, element (nb, kb) at sb[nb * sb_stride_n + kb * sb_stride_k], nb = n / 128, kb = k / 128.
+ * out [M, N] out_dtype (bf16 / f16), row stride ldc ELEMENTS, (ldc * 2) % 16 == 0, pointer 16-byte aligned.
+ * K need not be a multiple of 128 (the tail block is zero-filled), but K % 16 == 0.
+ * fp32 accumulation; each 128-deep partial product is scaled and added in registers.
+ * Any M >= 0 is accepted with no padding copy (the reference pads M to a multiple of 4).
+ */
+int sglb200_fp8_blockwise_scaled_mm(const void* a, const void* b, const float* sa, const float* sb, void* out,
+                                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                    int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                                    int64_t sb_stride_k, int out_dtype, void* stream);
+
+/*
+ * MG — grouped (per-expert) block-scaled FP8 GEMM over rows sorted by expert.
+ * Replaces: fp8_blockwise_scaled_grouped_mm  sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810
+ *           and its pointer-table helper sgl-kernel/csrc/moe/cutlass_moe_helper.cu:17-142
+ *           (schema common_extension.cc:274-279).  No pointer arrays, layout tables or workspace are needed.
+ *
+ * a   [total_rows, K] e4m3 (row stride lda bytes), rows of expert e are expert_offsets[e] .. expert_offsets[e+1]-1.
+ * b   [E, N, K] e4m3, K-contiguous, expert stride ldb_e bytes, row stride ldb bytes.
+ * sa  float [total_rows, ceil(K/128)] with strides (sa_stride_m, sa_stride_k).
+ * sb  float [E, ceil(N/128), ceil(K/128)] with strides (sb_stride_e, sb_stride_n, sb_stride_k).
+ * out [total_rows, N] out_dtype, row stride ldc elements.
+ * expert_offsets  int32 on the device, non-decreasing; [E + 1] entries when problem_sizes is NULL.
+ * problem_sizes   optional int32 [E, 3] on the device (the reference's table): when given, expert e owns
+ *                 problem_sizes[3e] rows starting at expert_offsets[e] and only E offsets are read.
+ */
+int sglb200_fp8_blockwise_scaled_grouped_mm(const void* a, const void* b, const float* sa, const float* sb,
+                                            void* out, const int32_t* expert_offsets,
+                                            const int32_t* problem_sizes, int64_t total_rows,
+                                            int64_t num_experts, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                            int64_t ldb_e, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
+                                            int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k,
+                                            int out_dtype, void* stream);
+
+/*
+ * MP — routing tables for the sorted-by-expert layout.
+ * Replaces: prepare_moe_input  sgl-kernel/csrc/moe/prepare_moe_input.cu:13-167 (schema common_extension.cc:281-285).
+ *
+ * topk_ids [num_tokens, topk] int32.  Outputs (all int32, device):
+ *   expert_offsets [E + 1]; problem_sizes1 [E, 3] = (count, 2n, k); problem_sizes2 [E, 3] = (count, k, n)
+ *   (either may be NULL); a_map [num_tokens * topk]: sorted row -> source token;
+ *   c_map [num_tokens * topk]: token-major slot -> sorted row, -1 for ids outside [0, E).
+ * Rows of one expert keep ascending slot order (deterministic; the reference's order is atomic order).
+ * One launch, one thread block: num_tokens * topk <= 2^24, E <= 1024.
+ */
+int sglb200_prepare_moe_input(const int32_t* topk_ids, int32_t* expert_offsets, int32_t* problem_sizes1,
+                              int32_t* problem_sizes2, int32_t* a_map, int32_t* c_map, int64_t num_tokens,
+                              int64_t topk, int64_t num_experts, int64_t n, int64_t k, void* stream);
+
+/*
+ * MS — out[i, :] = in[dst2src[i], :] for i < num_dst_rows; rows are row_bytes long (multiple of 4).
+ * Replaces: shuffle_rows  sgl-kernel/csrc/moe/prepare_moe_input.cu:169-256 (schema common_extension.cc:287-288).
+ */
+int sglb200_shuffle_rows(const void* input, const int32_t* dst2src, void* output, int64_t num_dst_rows,
+                         int64_t row_bytes, void* stream);
+
+/*
+ * MS — out[i, :] = cast( sum_j factors[i*topk+j] * in[perm[i*topk+j], :] ), fp32 sum in ascending j;
+ * slots with perm < 0 are skipped; factors may be NULL (= 1).  dtype bf16 / f16 for in, out and factors.
+ * Replaces: apply_shuffle_mul_sum  sgl-kernel/csrc/moe/prepare_moe_input.cu:258-392 (schema common_extension.cc:289-290).
+ */
+int sglb200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* perm, const void* factors,
+                                  int64_t m, int64_t topk, int64_t hidden, int dtype, void* stream);
+
+/*
+ * SA — out[t, :] = round(silu(in[t, :d])) * in[t, d:], d = hidden; in [num_rows, 2*hidden].
+ * Replaces: silu_and_mul  sgl-kernel/csrc/elementwise/activation.cu:82-101 (schema common_extension.cc:82-83).
+ */
+int sglb200_silu_and_mul(const void* input, void* output, int64_t num_rows, int64_t hidden, int dtype,
+                         void* stream);
+
+/*
+ * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
+ * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps).  Reading clears it.  This call SYNCHRONISES the
+ * device (cudaMemcpyFromSymbol); it is for tests and debugging, not for the serving path.  Returns -1 if the
+ * read itself failed.  No counterpart in the reference (its kernels have no bounded waits).
+ */
+int sglb200_read_device_status(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SGLB200_H_ */

@@ -1,0 +1,73 @@
+"""ctypes binding of the C-ABI library ``libsglb200.so`` (declared in ``include/sglb200.h``).
+
+There is no CPU fallback: if the library is missing, :func:`lib` raises and tells the user to
+build it (``python -m sglang_b200.build``); if a call returns a negative status, :func:`check`
+raises ``RuntimeError`` with the library's own description, before anything ran on the GPU
+(the reference raises ``RuntimeError`` from ``TORCH_CHECK`` the same way,
+``sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:374-406``).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libsglb200.so")
+
+_P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
+
+# name -> argument types; every function returns int (status) unless listed in _RESTYPES
+SIGNATURES = {
+    "sglb200_per_token_group_quant_fp8": [_P, _I, _P, _P, _L, _L, _I, _F, _F, _F, _I, _L, _L, _P],
+    "sglb200_silu_mul_group_quant_fp8": [_P, _I, _P, _P, _P, _L, _L, _I, _F, _F, _F, _I, _L, _L, _P],
+    "sglb200_fp8_blockwise_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
+    "sglb200_fp8_blockwise_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
+                                                _L, _L, _L, _I, _P],
+    "sglb200_prepare_moe_input": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P],
+    "sglb200_shuffle_rows": [_P, _P, _P, _L, _L, _P],
+    "sglb200_apply_shuffle_mul_sum": [_P, _P, _P, _P, _L, _L, _L, _I, _P],
+    "sglb200_silu_and_mul": [_P, _P, _L, _L, _I, _P],
+    "sglb200_read_device_status": [],
+    "sglb200_status_string": [_I],
+    "sglb200_last_error_detail": [],
+    "sglb200_version": [],
+}
+_RESTYPES = {"sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library (loaded on first use).  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build the CUDA library with `python -m sglang_b200.build` "
+                "(needs nvcc with sm_100a support). sglang_b200 has no CPU or PyTorch fallback.")
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, argtypes in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError here = header and library out of step
+            fn.argtypes = argtypes
+            fn.restype = _RESTYPES.get(name, c_int)
+        _lib = handle
+    return _lib
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        L = lib()
+        raise RuntimeError(f"{what}: {L.sglb200_status_string(status).decode()} "
+                           f"({L.sglb200_last_error_detail().decode()})")
+
+
+DTYPE_CODES = {"torch.bfloat16": 0, "torch.float16": 1, "torch.float32": 2}
+
+
+def dtype_code(dtype) -> int:
+    try:
+        return DTYPE_CODES[str(dtype)]
+    except KeyError:
+        raise RuntimeError(f"unsupported dtype {dtype}: expected bfloat16, float16 or float32") from None

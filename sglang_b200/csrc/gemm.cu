@@ -1,0 +1,513 @@
+// Block-scaled FP8 GEMM for sm_100a, dense and grouped (per-expert) in one persistent kernel.
+//
+//   out[m, n] = cast( sum_kb ( sum_{k in kb} a[m,k] * b[n,k] ) * sa[m,kb] * sb[n/128,kb] )
+//
+// One CTA per SM, 192 threads, warp-specialised:
+//   warp 0     TMA producer: A tile [128 rows x 128 B] and B tile [128 rows x 128 B] per k-block into a
+//              6-stage ring of 128-byte-swizzled shared memory (32 KiB per stage).
+//   warp 1     MMA issuer: per k-block four tcgen05.mma (128 x 128 x 32, e4m3 -> f32) that OVERWRITE one of
+//              four 128-column TMEM accumulator stages, then tcgen05.commit to free the smem stage and to
+//              publish the TMEM stage.
+//   warps 2-5  promotion + epilogue: each thread owns one accumulator row; per k-block it pulls the 128
+//              partial sums of its row out of TMEM (tcgen05.ld, double-buffered in 32-column pieces),
+//              multiplies by sa[m,kb] * sb[nb,kb] and adds into 128 fp32 registers; after the last
+//              k-block it rounds to bf16/f16 and writes 256 contiguous bytes of the output row.
+// The four TMEM stages let the tensor core run up to four k-blocks ahead of the promotion warps, and the
+// promotion of tile i's tail overlaps the loads and MMAs of tile i+1.
+//
+// Every wait on an mbarrier is bounded (about two seconds); on time-out the CTA records a code in
+// g_device_status, stops issuing work, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace sglb {
+
+__device__ int g_device_status = 0;
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 128;
+constexpr int kStages = 6;
+constexpr int kAccStages = 4;
+constexpr int kThreads = 192;
+constexpr uint32_t kTileABytes = BM * BK;
+constexpr uint32_t kTileBBytes = BN * BK;
+constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes;
+constexpr uint32_t kTmemCols = kAccStages * BN;  // 512
+constexpr int kMaxExperts = 1024;
+constexpr int kGroupM = 16;  // m-tiles per raster group (dense)
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/ +
+                              (kMaxExperts + 1) * sizeof(int32_t);
+
+struct GemmParams {
+  const float* sa;
+  const float* sb;
+  void* out;
+  const int32_t* expert_offsets;  // null: dense
+  const int32_t* problem_sizes;   // grouped, optional [E,3]: rows of expert e = problem_sizes[3e]
+  int32_t total_rows, N, K, num_experts;
+  int32_t m_tiles, n_tiles, k_tiles;
+  int64_t ldc;
+  int64_t sa_stride_m, sa_stride_k;
+  int64_t sb_stride_e, sb_stride_n, sb_stride_k;
+  int32_t out_dtype;
+};
+
+struct Tile {
+  int32_t row0;     // first row of the tile in a / out
+  int32_t row_end;  // one past the last row this tile may write
+  int32_t n0;
+  int32_t expert;
+};
+
+struct SharedCtl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t acc_full[kAccStages];
+  uint64_t acc_empty[kAccStages];
+  uint32_t tmem_base;
+  volatile int32_t abort_flag;
+  int32_t total_tiles;
+};
+
+template <bool GROUPED>
+__device__ __forceinline__ Tile get_tile(const GemmParams& p, const int32_t* tile_start, int32_t t) {
+  Tile tl;
+  if constexpr (!GROUPED) {
+    const int32_t per_group = kGroupM * p.n_tiles;
+    const int32_t gid = t / per_group;
+    const int32_t first_m = gid * kGroupM;
+    const int32_t gm = min(p.m_tiles - first_m, kGroupM);
+    const int32_t local = t - gid * per_group;
+    const int32_t nt = local / gm;
+    const int32_t mt = first_m + (local - nt * gm);
+    tl.row0 = mt * BM;
+    tl.row_end = p.total_rows;
+    tl.n0 = nt * BN;
+    tl.expert = 0;
+  } else {
+    int32_t lo = 0, hi = p.num_experts;  // last e with tile_start[e] <= t
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (tile_start[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int32_t e = lo;
+    const int32_t r0 = __ldg(p.expert_offsets + e);
+    const int32_t r1 = p.problem_sizes ? r0 + __ldg(p.problem_sizes + 3 * e) : __ldg(p.expert_offsets + e + 1);
+    const int32_t me = (r1 - r0 + BM - 1) / BM;
+    const int32_t local = t - tile_start[e];
+    const int32_t nt = local / me;
+    const int32_t mt = local - nt * me;
+    tl.row0 = r0 + mt * BM;
+    tl.row_end = r1;
+    tl.n0 = nt * BN;
+    tl.expert = e;
+  }
+  return tl;
+}
+
+__device__ __forceinline__ void record_timeout(SharedCtl* ctl, int code) {
+  ctl->abort_flag = 1;
+  atomicCAS(&g_device_status, 0, code);
+}
+
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row(const float (&acc)[BN], OutT* out_row, int32_t n0, int32_t N) {
+#pragma unroll
+  for (int c = 0; c < BN / 8; ++c) {
+    if (n0 + c * 8 < N) {
+      uint4 u;
+      u.x = pack2<OutT>(acc[c * 8 + 0], acc[c * 8 + 1]);
+      u.y = pack2<OutT>(acc[c * 8 + 2], acc[c * 8 + 3]);
+      u.z = pack2<OutT>(acc[c * 8 + 4], acc[c * 8 + 5]);
+      u.w = pack2<OutT>(acc[c * 8 + 6], acc[c * 8 + 7]);
+      *reinterpret_cast<uint4*>(out_row + c * 8) = u;
+    }
+  }
+}
+
+__device__ __forceinline__ void fma32(float* acc, const uint32_t (&v)[32], float scale) {
+#pragma unroll
+  for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v[j]), scale, acc[j]);
+}
+
+template <bool GROUPED>
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem + (size_t)kStages * kStageBytes);
+  int32_t* tile_start = reinterpret_cast<int32_t*>(smem + (size_t)kStages * kStageBytes + 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---------------------------------------------------------------- set-up
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&ctl->full[i], 1);
+      ptx::mbar_init(&ctl->empty[i], 1);
+    }
+    for (int i = 0; i < kAccStages; ++i) {
+      ptx::mbar_init(&ctl->acc_full[i], 1);
+      ptx::mbar_init(&ctl->acc_empty[i], 4);  // one arrival per promotion warp
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  if constexpr (GROUPED) {
+    if (warp == 0) {  // exclusive prefix sum of tiles per expert
+      int32_t running = 0;
+      for (int32_t base = 0; base < p.num_experts; base += 32) {
+        const int32_t e = base + lane;
+        int32_t v = 0;
+        if (e < p.num_experts) {
+          const int32_t cnt = p.problem_sizes ? __ldg(p.problem_sizes + 3 * e)
+                                              : __ldg(p.expert_offsets + e + 1) - __ldg(p.expert_offsets + e);
+          v = ((cnt + BM - 1) / BM) * p.n_tiles;
+        }
+        int32_t incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += o;
+        }
+        if (e < p.num_experts) tile_start[e] = running + incl - v;
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) {
+        tile_start[p.num_experts] = running;
+        ctl->total_tiles = running;
+      }
+    }
+  } else {
+    if (threadIdx.x == 0) ctl->total_tiles = p.m_tiles * p.n_tiles;
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int32_t total_tiles = ctl->total_tiles;
+
+  // ---------------------------------------------------------------- roles
+  if (warp == 0) {
+    // ===== TMA producer
+    uint32_t stage = 0, phase = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles && !ctl->abort_flag; t += gridDim.x) {
+      const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+      for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
+        if (lane == 0) {
+          if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1)) {
+            record_timeout(ctl, 1);
+          } else {
+            uint8_t* sa_tile = stage_base + (size_t)stage * kStageBytes;
+            uint8_t* sb_tile = sa_tile + kTileABytes;
+            ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
+            ptx::tma_load_2d(sa_tile, &map_a, &ctl->full[stage], kb * BK, tl.row0);
+            ptx::tma_load_3d(sb_tile, &map_b, &ctl->full[stage], kb * BK, tl.n0, tl.expert);
+          }
+        }
+        __syncwarp();
+        if (ctl->abort_flag) break;
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer
+    constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles && !ctl->abort_flag; t += gridDim.x) {
+      for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
+        if (lane == 0) {
+          if (!ptx::mbar_wait(&ctl->acc_empty[acc], acc_phase ^ 1)) {
+            record_timeout(ctl, 2);
+          } else if (!ptx::mbar_wait(&ctl->full[stage], phase)) {
+            record_timeout(ctl, 3);
+          } else {
+            ptx::tc_fence_after();
+            const uint32_t a_addr = ptx::smem_u32(stage_base + (size_t)stage * kStageBytes);
+            const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_addr);
+            const uint64_t b_desc = ptx::make_kmajor_sw128_desc(a_addr + kTileABytes);
+            const uint32_t d_tmem = tmem_base + acc * BN;
+#pragma unroll
+            for (uint32_t k = 0; k < BK / 32; ++k) {
+              // 32 bytes further along K inside the swizzle atom: +2 in the 16-byte address field
+              ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k);
+            }
+            ptx::mma_commit(&ctl->empty[stage]);
+            ptx::mma_commit(&ctl->acc_full[acc]);
+          }
+        }
+        __syncwarp();
+        if (ctl->abort_flag) break;
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ===== promotion + epilogue (warps 2..5); TMEM lane quarter = warp % 4
+    const int q = warp & 3;
+    const int r_in_tile = q * 32 + lane;
+    uint32_t acc_stage = 0, acc_phase = 0;
+    float acc[BN];
+    for (int32_t t = blockIdx.x; t < total_tiles && !ctl->abort_flag; t += gridDim.x) {
+      const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+      const int32_t row = tl.row0 + r_in_tile;
+      const int32_t row_c = min(row, p.total_rows - 1);
+      const float* sa_row = p.sa + (int64_t)row_c * p.sa_stride_m;
+      const float* sb_blk = p.sb + (int64_t)tl.expert * p.sb_stride_e + (int64_t)(tl.n0 / BN) * p.sb_stride_n;
+#pragma unroll
+      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
+      float sa_cur = __ldg(sa_row), sb_cur = __ldg(sb_blk);
+      bool ok = true;
+      for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
+        float sa_nxt = 0.f, sb_nxt = 0.f;
+        if (kb + 1 < p.k_tiles) {
+          sa_nxt = __ldg(sa_row + (int64_t)(kb + 1) * p.sa_stride_k);
+          sb_nxt = __ldg(sb_blk + (int64_t)(kb + 1) * p.sb_stride_k);
+        }
+        const float scale = sa_cur * sb_cur;
+        if (!ptx::mbar_wait(&ctl->acc_full[acc_stage], acc_phase)) {
+          record_timeout(ctl, 4);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * BN;
+        uint32_t va[32], vb[32];
+        ptx::tmem_ld_32x32(taddr, va);
+        ptx::tmem_ld_wait(va);
+        ptx::tmem_ld_32x32(taddr + 32, vb);
+        fma32(acc, va, scale);
+        ptx::tmem_ld_wait(vb);
+        ptx::tmem_ld_32x32(taddr + 64, va);
+        fma32(acc + 32, vb, scale);
+        ptx::tmem_ld_wait(va);
+        ptx::tmem_ld_32x32(taddr + 96, vb);
+        fma32(acc + 64, va, scale);
+        ptx::tmem_ld_wait(vb);
+        // every TMEM read of this stage has landed: hand the stage back to the MMA warp
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&ctl->acc_empty[acc_stage]);
+        fma32(acc + 96, vb, scale);
+        sa_cur = sa_nxt;
+        sb_cur = sb_nxt;
+        if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+      }
+      if (!ok) break;
+      if (row < tl.row_end) {
+        if (p.out_dtype == SGLB200_BF16) {
+          store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + tl.n0, tl.n0, p.N);
+        } else {
+          store_row<__half>(acc, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + tl.n0, tl.n0, p.N);
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- tear-down
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      ptr = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// rank-2 or rank-3 byte tensor, innermost extent K, 128-byte-swizzled boxes of [rows x 128 B]
+int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+             uint32_t box_rows, CUtensorMapL2promotion promo) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  cuuint64_t gdim[3] = {dims[0], dims[1], rank == 3 ? dims[2] : 1};
+  cuuint64_t gstr[2] = {strides_bytes[0], rank == 3 ? strides_bytes[1] : 0};
+  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SGLB200_OK;
+}
+
+template <bool GROUPED>
+int set_smem_attr_once() {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kSmemBytes);
+    if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    done[dev] = true;
+  }
+  return SGLB200_OK;
+}
+
+int gemm_common(const void* a, const void* b, const float* sa, const float* sb, void* out,
+                const int32_t* expert_offsets, const int32_t* problem_sizes, int64_t total_rows, int64_t num_experts, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
+                int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream) {
+  const bool grouped = expert_offsets != nullptr;
+  SGLB_REQUIRE(total_rows >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size",
+               (long long)total_rows, (long long)N, (long long)K);
+  SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE,
+               "out_dtype=%d: only bf16 (0) and f16 (1)", out_dtype);
+  SGLB_REQUIRE(total_rows < ((int64_t)1 << 31) - 256 && N < ((int64_t)1 << 31) - 256 && K < ((int64_t)1 << 31) - 256,
+               SGLB200_ERR_SHAPE, "a dimension exceeds 2^31");
+  SGLB_REQUIRE(K > 0 || total_rows == 0 || N == 0, SGLB200_ERR_SHAPE, "K must be positive");
+  SGLB_REQUIRE(K % 16 == 0, SGLB200_ERR_SHAPE, "K=%lld must be a multiple of 16", (long long)K);
+  SGLB_REQUIRE(N % 8 == 0, SGLB200_ERR_SHAPE, "N=%lld must be a multiple of 8 (16-byte output rows)", (long long)N);
+  if (grouped)
+    SGLB_REQUIRE(num_experts >= 1 && num_experts <= kMaxExperts, SGLB200_ERR_SHAPE, "num_experts=%lld: 1..%d",
+                 (long long)num_experts, kMaxExperts);
+  if (total_rows == 0 || N == 0) return SGLB200_OK;
+  SGLB_REQUIRE(a && b && sa && sb && out, SGLB200_ERR_NULL, "a/b/sa/sb/out must not be NULL");
+  SGLB_REQUIRE(lda >= K && lda % 16 == 0, SGLB200_ERR_ALIGN, "lda=%lld must be >= K and a multiple of 16", (long long)lda);
+  SGLB_REQUIRE(ldb >= K && ldb % 16 == 0, SGLB200_ERR_ALIGN, "ldb=%lld must be >= K and a multiple of 16", (long long)ldb);
+  SGLB_REQUIRE(!grouped || (ldb_e % 16 == 0 && ldb_e >= ldb), SGLB200_ERR_ALIGN,
+               "ldb_e=%lld must be a multiple of 16 and >= ldb", (long long)ldb_e);
+  SGLB_REQUIRE(ldc >= N && (ldc * 2) % 16 == 0, SGLB200_ERR_ALIGN, "ldc=%lld must be >= N and a multiple of 8",
+               (long long)ldc);
+  SGLB_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(out, 16), SGLB200_ERR_ALIGN,
+               "a, b and out must be 16-byte aligned");
+  SGLB_REQUIRE(aligned(sa, 4) && aligned(sb, 4), SGLB200_ERR_ALIGN, "scale pointers must be 4-byte aligned");
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
+               di.cc_major, di.cc_minor);
+
+  alignas(64) CUtensorMap map_a, map_b;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)total_rows};
+    const uint64_t str[1] = {(uint64_t)lda};
+    if (int rc = make_map(&map_a, a, 2, dims, str, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+  }
+  {
+    const uint64_t E = grouped ? (uint64_t)num_experts : 1;
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, E};
+    const uint64_t str[2] = {(uint64_t)ldb, grouped ? (uint64_t)ldb_e : (uint64_t)ldb * (uint64_t)N};
+    if (int rc = make_map(&map_b, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+  }
+
+  GemmParams p;
+  p.sa = sa;
+  p.sb = sb;
+  p.out = out;
+  p.expert_offsets = expert_offsets;
+  p.problem_sizes = problem_sizes;
+  p.total_rows = (int32_t)total_rows;
+  p.N = (int32_t)N;
+  p.K = (int32_t)K;
+  p.num_experts = grouped ? (int32_t)num_experts : 1;
+  p.m_tiles = (int32_t)((total_rows + BM - 1) / BM);
+  p.n_tiles = (int32_t)((N + BN - 1) / BN);
+  p.k_tiles = (int32_t)((K + BK - 1) / BK);
+  p.ldc = ldc;
+  p.sa_stride_m = sa_stride_m;
+  p.sa_stride_k = sa_stride_k;
+  p.sb_stride_e = grouped ? sb_stride_e : 0;
+  p.sb_stride_n = sb_stride_n;
+  p.sb_stride_k = sb_stride_k;
+  p.out_dtype = out_dtype;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (grouped) {
+    if (int rc = set_smem_attr_once<true>()) return rc;
+    // an upper bound on the tile count without reading the device: every expert can add one ragged m-tile
+    const int64_t max_tiles = ((total_rows + BM - 1) / BM + num_experts) * p.n_tiles;
+    const int grid = (int)(max_tiles < di.sm_count ? max_tiles : di.sm_count);
+    fp8_block_gemm_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+  } else {
+    if (int rc = set_smem_attr_once<false>()) return rc;
+    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+    const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
+    fp8_block_gemm_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+  }
+  SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
+  return SGLB200_OK;
+}
+
+}  // namespace
+}  // namespace sglb
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm(const void* a, const void* b, const float* sa, const float* sb,
+                                               void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                               int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
+                                               int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream) {
+  return sglb::gemm_common(a, b, sa, sb, out, nullptr, nullptr, M, 1, N, K, lda, ldb, 0, ldc, sa_stride_m, sa_stride_k, 0,
+                           sb_stride_n, sb_stride_k, out_dtype, stream);
+}
+
+extern "C" int sglb200_fp8_blockwise_scaled_grouped_mm(const void* a, const void* b, const float* sa, const float* sb,
+                                                       void* out, const int32_t* expert_offsets,
+                                                       const int32_t* problem_sizes, int64_t total_rows,
+                                                       int64_t num_experts, int64_t N, int64_t K, int64_t lda,
+                                                       int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sa_stride_m,
+                                                       int64_t sa_stride_k, int64_t sb_stride_e, int64_t sb_stride_n,
+                                                       int64_t sb_stride_k, int out_dtype, void* stream) {
+  SGLB_REQUIRE(expert_offsets != nullptr, SGLB200_ERR_NULL, "expert_offsets must not be NULL");
+  return sglb::gemm_common(a, b, sa, sb, out, expert_offsets, problem_sizes, total_rows, num_experts, N, K, lda, ldb, ldb_e, ldc,
+                           sa_stride_m, sa_stride_k, sb_stride_e, sb_stride_n, sb_stride_k, out_dtype, stream);
+}
+
+// Reads (and clears) the device-side status word: 0, or the code of the first bounded wait that
+// timed out (1 producer, 2/3 MMA issuer, 4 promotion warps).  Synchronises the device: for tests
+// and debugging, not for the serving path.
+extern "C" int sglb200_read_device_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, sglb::g_device_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(sglb::g_device_status, &z, sizeof(int));
+  }
+  return v;
+}

@@ -1,0 +1,46 @@
+"""Block-FP8 linear helpers (``python/sglang/srt/layers/quantization/fp8_utils.py``)."""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+
+
+def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
+                          weight_scale: torch.Tensor, input_scale: Optional[torch.Tensor] = None,
+                          bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Quantise the activations per 1x128 group, multiply by the block-scaled weight, add bias.
+
+    Same signature and result layout as the reference's ``*_w8a8_block_fp8_linear`` family
+    (``fp8_utils.py:184-301``), which ``dispatch_w8a8_block_fp8_linear`` (``:139-149``) picks
+    from; here there is one implementation.  ``weight [N, K]`` e4m3, ``weight_scale
+    [ceil(N/128), ceil(K/128)]`` fp32.  Activation scales are written M-major so the GEMM's
+    per-row scale loads coalesce."""
+    assert input_scale is None
+    input_2d = input.view(-1, input.shape[-1])
+    if not input_2d.is_contiguous():
+        input_2d = input_2d.contiguous()
+    output_shape = [*input.shape[:-1], weight.shape[0]]
+    q_input, x_scale = sglang_per_token_group_quant_fp8(input_2d, block_size[1], column_major_scales=True,
+                                                        scale_tma_aligned=True)
+    output = w8a8_block_fp8_matmul(q_input, weight, x_scale, weight_scale, block_size, output_dtype=input_2d.dtype)
+    if bias is not None:
+        output += bias
+    return output.to(dtype=input_2d.dtype).view(*output_shape)
+
+
+def dispatch_w8a8_block_fp8_linear():
+    """``dispatch_w8a8_block_fp8_linear`` (``fp8_utils.py:139-149``): one back-end."""
+    return w8a8_block_fp8_linear
+
+
+def block_quant_dequant(x_q_block: torch.Tensor, x_s: torch.Tensor, block_size: List[int],
+                        dtype: torch.dtype) -> torch.Tensor:
+    """Expand block scales and dequantise (``fp8_utils.py:393-413``); offline helper."""
+    block_n, block_k = block_size
+    *_, n, k = x_q_block.shape
+    rep = x_s.repeat_interleave(block_n, dim=-2).repeat_interleave(block_k, dim=-1)[..., :n, :k]
+    return (x_q_block.to(torch.float32) * rep).to(dtype)

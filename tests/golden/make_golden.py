@@ -97,7 +97,10 @@ def main(ref_root):
         x = quant_inputs(gen, M, K, dtype)
         if dtype == torch.float16:
             x = x.float().clamp(-6e4, 6e4).to(dtype)
-            x[0, :128] = 1e-3  # fp16(1e-10) == 0: the reference's all-zero fp16 group is NaN; keep it out
+            # fp16(1e-10) == 0, so the reference turns an all-zero fp16 group into 0/0 = NaN codes;
+            # keep such groups out of the fixture (the CUDA kernel keeps eps in fp32 there)
+            zero = x.view(M, K // g, g).abs().amax(-1) == 0
+            x.view(M, K // g, g)[..., 0][zero] = 1e-3
         q, s = q_ref(x, g)
         out[f"{name}_x"] = raw(x)
         out[f"{name}_q"] = raw(q)
