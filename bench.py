@@ -1,0 +1,365 @@
+#!/usr/bin/env python
+"""Benchmark of the block-FP8 W8A8 linear path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M]
+
+Workload ("dsv3_linear_sweep"): one step = one forward of the block-FP8 linear (per-token-group
+quant of the bf16 activations + block-scaled FP8 GEMM, bf16 out) for each of the five
+DeepSeek-V3 projection shapes (N, K) at M tokens.  With N GPUs the same layers are
+tensor-parallel, the way the model shards them: column-parallel for q_b_proj (24576, 1536) and
+gate_up (36864, 7168); row-parallel with an NCCL all-reduce for o_proj (7168, 16384) and
+down_proj (7168, 18432); kv_a_proj (576, 7168) replicated.  Total work is fixed ("strong").
+Synthetic data: activations ~N(0,1) with 1% of entries x50, weights ~N(0, 0.02) block-quantised.
+
+Prints ONE JSON line.  `value` = TFLOP/s of the whole step (2*M*N*K summed over the shapes, inputs
+resident in HBM); `e2e` = the same through Fp8LinearMethod.apply from pinned host buffers with the
+result copied back; `roofline` = the GEMM kernel alone (CUDA events around each launch) against
+2 x the measured dense bf16 rate; `quant` = the per-token-group quant kernel on M=16384 x 7168
+against measured HBM bandwidth; `cpu_baseline` = the reference's CPU kernel (or the oracle port)
+on a bounded sample.  `--impl reference` times only that CPU path.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [  # (name, N, K, tensor-parallel mode)
+    ("q_b_proj", 24576, 1536, "column"),
+    ("kv_a_proj", 576, 7168, "replicated"),
+    ("o_proj", 7168, 16384, "row"),
+    ("gate_up_proj", 36864, 7168, "column"),
+    ("down_proj", 7168, 18432, "row"),
+]
+METRIC = "block_fp8_linear_tflops"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clock sampling
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_id: str):
+        self.gpu_id, self.rows, self.proc, self.thread = gpu_id, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=lambda: [self.rows.append(l) for l in self.proc.stdout], daemon=True)
+        self.thread.start()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        clk, mx, reasons = [], None, set()
+        for line in self.rows:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6 or not f[0].isdigit():
+                continue
+            clk.append(int(f[0]))
+            mx = int(f[1])
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clk) if clk else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clk)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_arm(steps: int, warmup: int, m_sample: int):
+    """The reference's CPU implementation of the path on this host: sgl-kernel's AMX
+    fp8_scaled_mm_cpu (W8A16) built from the reference sources when it loads here, else the
+    torch-native oracle port.  One pass = the five shapes at `m_sample` rows."""
+    import torch
+    import oracle
+    from oracle.build_ref import load_ref
+    ops = load_ref()
+    kind = "reference" if ops is not None else "port"
+    if ops is None:
+        m_sample = min(m_sample, 64)
+    g = torch.Generator().manual_seed(0)
+    layers = []
+    for name, N, K, _ in SHAPES:
+        if ops is None and N * K > 24576 * 1536:
+            continue  # the torch-native port is ~100x slower: keep the two small shapes
+        w = (torch.randn(N, K, generator=g) * 0.02)
+        wq, ws = oracle.block_quant_weight(w)
+        x = torch.randn(m_sample, K, generator=g).bfloat16()
+        layers.append((x, ops.convert_weight_packed(wq) if ops is not None else wq, ws, N, K))
+    flops = sum(2.0 * m_sample * N * K for _, _, _, N, K in layers)
+
+    def one_pass():
+        for x, wq, ws, N, K in layers:
+            if ops is not None:
+                ops.fp8_scaled_mm_cpu(x, wq, ws, [128, 128], None, torch.bfloat16, True)
+            else:
+                aq, a_s = oracle.per_token_group_quant_fp8(x, 128)
+                oracle.w8a8_block_fp8_matmul(aq, wq, a_s, ws)
+
+    for _ in range(warmup):
+        one_pass()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_pass()
+    dt = (time.perf_counter() - t0) / steps
+    names = "+".join(s[0] for s in SHAPES if any(l[3] == s[1] and l[4] == s[2] for l in layers))
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{names} at M={m_sample} rows, {steps} passes after {warmup} warm-up; "
+                      + ("sgl-kernel fp8_scaled_mm_cpu (AMX bf16, W8A16)" if ops is not None
+                         else "torch-native oracle (W8A8)"),
+            "ms_per_pass": dt * 1e3}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=8192, help="tokens per step")
+    ap.add_argument("--cpu-m", type=int, default=1024, help="rows of the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant"],
+                    help="profiling aid: run only the linear sweep ('gemm') or only the quant bandwidth case")
+    ap.add_argument("--shape", default=None, help="profiling aid: restrict the sweep to one layer name")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "dsv3_linear_sweep", "M": args.m, "shapes_NK": [[s[1], s[2]] for s in SHAPES],
+              "parallelism": f"tp{world}", "block": [128, 128], "group": 128,
+              "l2": "working set per step (weights 555 MB + activations) exceeds the 126 MB L2; no explicit flush"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cb = cpu_arm(args.steps, args.warmup, args.cpu_m)
+        line = {"metric": METRIC, "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"], "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config,
+                "impl": "reference", "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    from sglang_b200.layers.quantization import (Fp8Config, Fp8LinearMethod, sglang_per_token_group_quant_fp8,
+                                                 w8a8_block_fp8_matmul)
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the product path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = load_peaks()
+    M = args.m
+
+    # ---- synthetic layers, sharded for this rank
+    method = Fp8LinearMethod(Fp8Config(), tp_size=world)
+    layers = []
+    gen = torch.Generator(device=dev).manual_seed(0)
+
+    def block_quant(w):
+        n, k = w.shape
+        n_p, k_p = -(-n // 128) * 128, -(-k // 128) * 128
+        wp = torch.zeros(n_p, k_p, device=dev)
+        wp[:n, :k] = w
+        v = wp.view(n_p // 128, 128, k_p // 128, 128)
+        s = v.abs().amax(dim=(1, 3), keepdim=True) / 448.0
+        s = torch.where(s == 0, torch.ones_like(s), s)
+        q = (v / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(n_p, k_p)[:n, :k].contiguous()
+        return q, s.view(n_p // 128, k_p // 128).contiguous()
+
+    total_flops = 0.0
+    shapes = [s for s in SHAPES if args.shape in (None, s[0])]
+    if args.shape is not None:
+        config["shapes_NK"] = [[s[1], s[2]] for s in shapes]
+    for name, N, K, mode in shapes:
+        total_flops += 2.0 * M * N * K
+        n_loc, k_loc = N, K
+        if world > 1 and mode == "column":
+            n_loc = N // world
+        if world > 1 and mode == "row":
+            k_loc = K // world
+        w = torch.randn(n_loc, k_loc, device=dev, generator=gen) * 0.02
+        wq, ws = block_quant(w)
+        del w
+        layer = torch.nn.Module()
+        method.create_weights(layer, k_loc, [n_loc], K, N, torch.bfloat16, device=dev)
+        layer.weight.data = wq
+        layer.weight_scale_inv.data = ws
+        x = torch.randn(M, k_loc, device=dev, generator=gen)
+        x = torch.where(torch.rand(M, k_loc, device=dev, generator=gen) < 0.01, x * 50.0, x).bfloat16()
+        layers.append({"name": name, "N": N, "K": K, "mode": mode, "n_loc": n_loc, "k_loc": k_loc, "layer": layer,
+                       "x": x, "gemm_ms": []})
+
+    def step(record=False):
+        for L in layers:
+            q, s = sglang_per_token_group_quant_fp8(L["x"], 128, column_major_scales=True, scale_tma_aligned=True)
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            y = w8a8_block_fp8_matmul(q, L["layer"].weight, s, L["layer"].weight_scale_inv, [128, 128], torch.bfloat16)
+            if record:
+                e1.record()
+                L["ev"].append((e0, e1))
+            if world > 1 and L["mode"] == "row":
+                dist.all_reduce(y)
+        return y
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup if args.only != "quant" else 0):
+        step()
+    for L in layers:
+        L["ev"] = []
+    if args.only == "quant":
+        args.steps = 1
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
+    fence()
+    sampler.start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(args.steps):
+        step(record=True)
+    t1.record()
+    fence()
+    clocks = sampler.stop()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms) / args.steps
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # GEMM kernel alone: CUDA events around every launch in the timed region
+    gemm_ms, gemm_flops, per_shape = 0.0, 0.0, {}
+    for L in layers:
+        t = [a.elapsed_time(b) for a, b in L["ev"]]
+        f = 2.0 * M * L["n_loc"] * L["k_loc"]
+        gemm_ms += sum(t)
+        gemm_flops += f * len(t)
+        per_shape[L["name"]] = {"N": L["n_loc"], "K": L["k_loc"], "gemm_ms": statistics.median(t),
+                                "gemm_tflops": f / (statistics.median(t) * 1e-3) / 1e12}
+    fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
+                "frac": achieved / fp8_peak, "traffic": None, "kernel": "fp8_block_gemm_kernel",
+                "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
+                "frac_of_nominal_fp8": achieved / 4500.0, "launches": args.steps * len(layers),
+                "avg_launch_ms": gemm_ms / (args.steps * len(layers))}
+
+    # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed between launches
+    quant = None
+    if rank == 0 and args.only != "gemm":
+        xq = torch.randn(16384, 7168, device=dev, generator=gen)
+        xq = (xq * 10 ** (torch.rand(16384, 1, device=dev, generator=gen) * 4 - 2)).bfloat16()
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        times = []
+        for i in range(8):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            sglang_per_token_group_quant_fp8(xq, 128, column_major_scales=True, scale_tma_aligned=True)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(e0.elapsed_time(e1))
+        qbytes = 16384 * 7168 * 3 + 16384 * 56 * 4
+        qms = statistics.median(times)
+        quant = {"workload": "per_token_group_quant_fp8 M=16384 K=7168 bf16 -> e4m3 + f32 column-major scales",
+                 "bytes": qbytes, "ms": qms, "gbs": qbytes / (qms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                 "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                 "l2": "256 MB buffer zeroed between launches"}
+        del xq, flush
+
+    if args.only != "all":
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "only": args.only, "value": value, "unit": "TFLOP/s", "n_gpus": world,
+                              "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "config": config,
+                              "clocks": clocks, "roofline": roofline, "quant": quant, "per_shape": per_shape}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- end to end through the public API from pinned host memory
+    host_x = [L["x"].cpu().pin_memory() for L in layers]
+    host_y = [torch.empty(M, L["n_loc"], dtype=torch.bfloat16).pin_memory() for L in layers]
+    h2d = sum(t.numel() * 2 for t in host_x)
+    d2h = sum(t.numel() * 2 for t in host_y)
+
+    def e2e_step():
+        for L, hx, hy in zip(layers, host_x, host_y):
+            xd = hx.to(dev, non_blocking=True)
+            y = method.apply(L["layer"], xd)
+            if world > 1 and L["mode"] == "row":
+                dist.all_reduce(y)
+            hy.copy_(y, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 5))
+    for _ in range(2):
+        e2e_step()
+    fence()
+    t0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    t1.record()
+    fence()
+    ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    e2e_ms = float(ms) / e2e_steps
+    e2e = {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
+           "api": "Fp8LinearMethod.apply on pinned-host activations, result copied back to pinned host"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu_baseline = cpu_arm(3, 1, args.cpu_m)
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks,
+                "e2e": e2e, "gpu_launches": args.steps * len(layers) * 2, "roofline": roofline,
+                "cpu_baseline": cpu_baseline, "quant": quant, "per_shape": per_shape, "impl": "ours"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

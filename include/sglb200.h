@@ -151,10 +151,14 @@ int sglb200_shuffle_rows(const void* input, const int32_t* dst2src, void* output
 /*
  * MS — out[i, :] = cast( sum_j factors[i*topk+j] * in[perm[i*topk+j], :] ), fp32 sum in ascending j;
  * slots with perm < 0 are skipped; factors may be NULL (= 1).  dtype bf16 / f16 for in, out and factors.
+ * round_products == 0: products stay in fp32 (the arithmetic of the reference's CUDA kernel);
+ * round_products != 0: each product is rounded to dtype before it is added, which is what the torch-native
+ * expert MLP computes ((out * w.to(dtype)).sum(1), python/sglang/test/test_block_fp8.py:445-447).
  * Replaces: apply_shuffle_mul_sum  sgl-kernel/csrc/moe/prepare_moe_input.cu:258-392 (schema common_extension.cc:289-290).
  */
 int sglb200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* perm, const void* factors,
-                                  int64_t m, int64_t topk, int64_t hidden, int dtype, void* stream);
+                                  int64_t m, int64_t topk, int64_t hidden, int dtype, int round_products,
+                                  void* stream);
 
 /*
  * SA — out[t, :] = round(silu(in[t, :d])) * in[t, d:], d = hidden; in [num_rows, 2*hidden].

@@ -134,8 +134,8 @@ def w8a8_block_fp8_matmul(A, B, As, Bs, block_size=(128, 128), output_dtype=torc
     N = B.shape[0]
     lead = A.shape[:-1]
     A = A.reshape(-1, K)
-    As = As.reshape(A.shape[0], -1).to(torch.float32)
     nt, kt = -(-N // bn), -(-K // bk)
+    As = As.reshape(A.shape[0], kt).to(torch.float32)
     assert Bs.shape == (nt, kt) and As.shape[1] == kt
     C = torch.zeros(A.shape[0], N, dtype=torch.float32)
     for i in range(kt):

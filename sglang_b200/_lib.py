@@ -27,7 +27,7 @@ SIGNATURES = {
                                                 _L, _L, _L, _I, _P],
     "sglb200_prepare_moe_input": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P],
     "sglb200_shuffle_rows": [_P, _P, _P, _L, _L, _P],
-    "sglb200_apply_shuffle_mul_sum": [_P, _P, _P, _P, _L, _L, _L, _I, _P],
+    "sglb200_apply_shuffle_mul_sum": [_P, _P, _P, _P, _L, _L, _L, _I, _I, _P],
     "sglb200_silu_and_mul": [_P, _P, _L, _L, _I, _P],
     "sglb200_read_device_status": [],
     "sglb200_status_string": [_I],

@@ -124,7 +124,9 @@ struct Cvt<__half> {
   static __device__ __forceinline__ __half t(float x) { return __float2half_rn(x); }
 };
 
-template <typename T>
+// ROUND: each product is rounded to T before it is added (the torch-native expert-MLP reference sums
+// bf16 products); otherwise products stay in fp32 (the reference's CUDA combine kernel).
+template <typename T, bool ROUND>
 __global__ void __launch_bounds__(256)
 combine_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ perm,
                const T* __restrict__ factors, int32_t topk, int32_t hidden) {
@@ -141,7 +143,13 @@ combine_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __r
       const uint4 u = __ldg(reinterpret_cast<const uint4*>(in + (int64_t)src * hidden) + c);
       const T* h = reinterpret_cast<const T*>(&u);
 #pragma unroll
-      for (int x = 0; x < 8; ++x) acc[x] = fmaf(w, Cvt<T>::f(h[x]), acc[x]);
+      for (int x = 0; x < 8; ++x) {
+        if constexpr (ROUND) {
+          acc[x] += Cvt<T>::f(Cvt<T>::t(w * Cvt<T>::f(h[x])));
+        } else {
+          acc[x] = fmaf(w, Cvt<T>::f(h[x]), acc[x]);
+        }
+      }
     }
     uint4 o;
     T* oh = reinterpret_cast<T*>(&o);
@@ -155,7 +163,11 @@ combine_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __r
       const int32_t src = perm[i * topk + j];
       if (src < 0) continue;
       const float w = factors ? Cvt<T>::f(factors[i * topk + j]) : 1.f;
-      acc = fmaf(w, Cvt<T>::f(in[(int64_t)src * hidden + d]), acc);
+      if constexpr (ROUND) {
+        acc += Cvt<T>::f(Cvt<T>::t(w * Cvt<T>::f(in[(int64_t)src * hidden + d])));
+      } else {
+        acc = fmaf(w, Cvt<T>::f(in[(int64_t)src * hidden + d]), acc);
+      }
     }
     out[i * hidden + d] = Cvt<T>::t(acc);
   }
@@ -256,7 +268,8 @@ extern "C" int sglb200_shuffle_rows(const void* input, const int32_t* dst2src, v
 }
 
 extern "C" int sglb200_apply_shuffle_mul_sum(const void* input, void* output, const int32_t* perm, const void* factors,
-                                             int64_t m, int64_t topk, int64_t hidden, int dtype, void* stream) {
+                                             int64_t m, int64_t topk, int64_t hidden, int dtype, int round_products,
+                                             void* stream) {
   SGLB_REQUIRE(m >= 0 && topk >= 1 && hidden >= 0, SGLB200_ERR_SHAPE, "m=%lld topk=%lld hidden=%lld", (long long)m,
                (long long)topk, (long long)hidden);
   SGLB_REQUIRE(dtype == SGLB200_BF16 || dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "dtype=%d", dtype);
@@ -270,16 +283,15 @@ extern "C" int sglb200_apply_shuffle_mul_sum(const void* input, void* output, co
   if (int rc = check_arch()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int threads = (int)(hidden / 8 < 32 ? 32 : (hidden / 8 > 256 ? 256 : (hidden / 8 + 31) / 32 * 32));
+#define SGLB_COMBINE(T, R)                                                                                   \
+  combine_kernel<T, R><<<(int)m, threads, 0, st>>>(static_cast<const T*>(input), static_cast<T*>(output), perm, \
+                                                   static_cast<const T*>(factors), (int32_t)topk, (int32_t)hidden)
   if (dtype == SGLB200_BF16) {
-    combine_kernel<__nv_bfloat16><<<(int)m, threads, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(output), perm,
-        static_cast<const __nv_bfloat16*>(factors), (int32_t)topk, (int32_t)hidden);
+    if (round_products) SGLB_COMBINE(__nv_bfloat16, true); else SGLB_COMBINE(__nv_bfloat16, false);
   } else {
-    combine_kernel<__half><<<(int)m, threads, 0, st>>>(static_cast<const __half*>(input),
-                                                       static_cast<__half*>(output), perm,
-                                                       static_cast<const __half*>(factors), (int32_t)topk,
-                                                       (int32_t)hidden);
+    if (round_products) SGLB_COMBINE(__half, true); else SGLB_COMBINE(__half, false);
   }
+#undef SGLB_COMBINE
   SGLB_CHECK_LAUNCH("combine_kernel");
   return SGLB200_OK;
 }

@@ -58,9 +58,11 @@ def shuffle_rows(input_tensor, dst2src_map, output_tensor_shape):
     return out
 
 
-def apply_shuffle_mul_sum(input, output, permutation, factors):
+def apply_shuffle_mul_sum(input, output, permutation, factors, round_products: bool = False):
     """``output[i] = sum_j factors[i, j] * input[permutation[i * topk + j]]`` in fp32
-    (``prepare_moe_input.cu:258-392``)."""
+    (``prepare_moe_input.cu:258-392``).  ``round_products=True`` rounds every product to the
+    tensor dtype before adding, the arithmetic of the torch-native expert MLP
+    (``python/sglang/test/test_block_fp8.py:445-447``)."""
     _req(input.dim() == 2, "input_tensor must be 2D [m * topk, row_stride]")
     _req(output.dim() == 2, "output_tensor must be 2D [m, row_stride]")
     _req(permutation.dim() == 1 and permutation.dtype == torch.int32, "permutation must be 1D [m * topk]")
@@ -78,7 +80,8 @@ def apply_shuffle_mul_sum(input, output, permutation, factors):
     with torch.cuda.device(input.device):
         check(lib().sglb200_apply_shuffle_mul_sum(input.data_ptr(), output.data_ptr(), permutation.data_ptr(), fptr,
                                                   m, max(topk, 1), output.size(1), dtype_code(output.dtype),
-                                                  _stream(input)), "apply_shuffle_mul_sum")
+                                                  int(bool(round_products)), _stream(input)),
+              "apply_shuffle_mul_sum")
 
 
 def fp8_blockwise_scaled_grouped_mm(output, a_ptrs, b_ptrs, out_ptrs, a_scales_ptrs, b_scales_ptrs, a, b,
