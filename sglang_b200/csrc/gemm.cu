@@ -2,16 +2,19 @@
 //
 //   out[m, n] = cast( sum_kb ( sum_{k in kb} a[m,k] * b[n,k] ) * sa[m,kb] * sb[n/128,kb] )
 //
-// One CTA per SM, 192 threads, warp-specialised:
+// One CTA per SM, 320 threads, warp-specialised:
 //   warp 0     TMA producer: A tile [128 rows x 128 B] and B tile [128 rows x 128 B] per k-block into a
 //              6-stage ring of 128-byte-swizzled shared memory (32 KiB per stage).
 //   warp 1     MMA issuer: per k-block four tcgen05.mma (128 x 128 x 32, e4m3 -> f32) that OVERWRITE one of
 //              four 128-column TMEM accumulator stages, then tcgen05.commit to free the smem stage and to
 //              publish the TMEM stage.
-//   warps 2-5  promotion + epilogue: each thread owns one accumulator row; per k-block it pulls the 128
-//              partial sums of its row out of TMEM (tcgen05.ld, double-buffered in 32-column pieces),
-//              multiplies by sa[m,kb] * sb[nb,kb] and adds into 128 fp32 registers; after the last
-//              k-block it rounds to bf16/f16 and writes 256 contiguous bytes of the output row.
+//   warps 2-9  promotion + epilogue: two warps per TMEM lane quarter, each owning 64 of the tile's 128
+//              columns.  A thread owns one accumulator row: per k-block it pulls its 64 partial sums out
+//              of TMEM (two tcgen05.ld of 32 columns, one wait), multiplies by sa[m,kb] * sb[nb,kb] and
+//              adds into 64 fp32 registers with packed fp32x2 FMAs; after the last k-block it rounds to
+//              bf16/f16 and writes 128 contiguous bytes of the output row.  Scales are fetched four
+//              k-blocks ahead so their latency never sits on the promotion path.  Two warps per quarter
+//              hide each other's TMEM-load latency.
 // The four TMEM stages let the tensor core run up to four k-blocks ahead of the promotion warps, and the
 // promotion of tile i's tail overlaps the loads and MMAs of tile i+1.
 //
@@ -33,7 +36,10 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 128;
 constexpr int kStages = 6;
 constexpr int kAccStages = 4;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiCols = BN / (kEpiWarps / 4);  // columns per promotion warp (64)
+constexpr int kScaleAhead = 4;                 // k-blocks of scale prefetch
 constexpr uint32_t kTileABytes = BM * BK;
 constexpr uint32_t kTileBBytes = BN * BK;
 constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes;
@@ -128,24 +134,27 @@ __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// acc holds kEpiCols consecutive columns starting at column n_first of the output row
 template <typename OutT>
-__device__ __forceinline__ void store_row(const float (&acc)[BN], OutT* out_row, int32_t n0, int32_t N) {
+__device__ __forceinline__ void store_row(const float2 (&acc)[kEpiCols / 2], OutT* out_row, int32_t n_first, int32_t N) {
 #pragma unroll
-  for (int c = 0; c < BN / 8; ++c) {
-    if (n0 + c * 8 < N) {
+  for (int c = 0; c < kEpiCols / 8; ++c) {
+    if (n_first + c * 8 < N) {
       uint4 u;
-      u.x = pack2<OutT>(acc[c * 8 + 0], acc[c * 8 + 1]);
-      u.y = pack2<OutT>(acc[c * 8 + 2], acc[c * 8 + 3]);
-      u.z = pack2<OutT>(acc[c * 8 + 4], acc[c * 8 + 5]);
-      u.w = pack2<OutT>(acc[c * 8 + 6], acc[c * 8 + 7]);
+      u.x = pack2<OutT>(acc[c * 4 + 0].x, acc[c * 4 + 0].y);
+      u.y = pack2<OutT>(acc[c * 4 + 1].x, acc[c * 4 + 1].y);
+      u.z = pack2<OutT>(acc[c * 4 + 2].x, acc[c * 4 + 2].y);
+      u.w = pack2<OutT>(acc[c * 4 + 3].x, acc[c * 4 + 3].y);
       *reinterpret_cast<uint4*>(out_row + c * 8) = u;
     }
   }
 }
 
-__device__ __forceinline__ void fma32(float* acc, const uint32_t (&v)[32], float scale) {
+// acc[j] += v[2j], v[2j+1] * scale, two columns per instruction
+__device__ __forceinline__ void fma32(float2* acc, const uint32_t (&v)[32], float2 scale2) {
 #pragma unroll
-  for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(v[j]), scale, acc[j]);
+  for (int j = 0; j < 16; ++j)
+    acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), scale2, acc[j]);
 }
 
 template <bool GROUPED>
@@ -169,7 +178,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
     for (int i = 0; i < kAccStages; ++i) {
       ptx::mbar_init(&ctl->acc_full[i], 1);
-      ptx::mbar_init(&ctl->acc_empty[i], 4);  // one arrival per promotion warp
+      ptx::mbar_init(&ctl->acc_empty[i], kEpiWarps);  // one arrival per promotion warp
     }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -216,117 +225,138 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const int32_t total_tiles = ctl->total_tiles;
 
   // ---------------------------------------------------------------- roles
+  // The per-k-block loops of the producer and the MMA issuer are a serial chain for one warp, so they
+  // are kept to a handful of instructions: barrier and tile addresses live in registers as 32-bit
+  // shared-window addresses, every lane waits (no divergence to repair) and lane 0 alone issues.
+  const uint32_t full0 = ptx::smem_u32(&ctl->full[0]);
+  const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t acc_full0 = ptx::smem_u32(&ctl->acc_full[0]);
+  const uint32_t acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
+  const uint32_t stage0 = ptx::smem_u32(stage_base);
+
   if (warp == 0) {
     // ===== TMA producer
     uint32_t stage = 0, phase = 0;
-    for (int32_t t = blockIdx.x; t < total_tiles && !ctl->abort_flag; t += gridDim.x) {
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+      bool ok = true;
       for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
-        if (lane == 0) {
-          if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1)) {
-            record_timeout(ctl, 1);
-          } else {
-            uint8_t* sa_tile = stage_base + (size_t)stage * kStageBytes;
-            uint8_t* sb_tile = sa_tile + kTileABytes;
-            ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
-            ptx::tma_load_2d(sa_tile, &map_a, &ctl->full[stage], kb * BK, tl.row0);
-            ptx::tma_load_3d(sb_tile, &map_b, &ctl->full[stage], kb * BK, tl.n0, tl.expert);
-          }
+        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
+          record_timeout(ctl, 1);
+          ok = false;
+          break;
         }
-        __syncwarp();
-        if (ctl->abort_flag) break;
+        if (lane == 0) {
+          const uint32_t dst = stage0 + stage * kStageBytes;
+          ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
+          ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.row0);
+          ptx::tma_load_3d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, tl.n0, tl.expert);
+        }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
+      if (!ok || ctl->abort_flag) break;
     }
   } else if (warp == 1) {
     // ===== MMA issuer
     constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
+    const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-    for (int32_t t = blockIdx.x; t < total_tiles && !ctl->abort_flag; t += gridDim.x) {
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      bool ok = true;
       for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
-        if (lane == 0) {
-          if (!ptx::mbar_wait(&ctl->acc_empty[acc], acc_phase ^ 1)) {
-            record_timeout(ctl, 2);
-          } else if (!ptx::mbar_wait(&ctl->full[stage], phase)) {
-            record_timeout(ctl, 3);
-          } else {
-            ptx::tc_fence_after();
-            const uint32_t a_addr = ptx::smem_u32(stage_base + (size_t)stage * kStageBytes);
-            const uint64_t a_desc = ptx::make_kmajor_sw128_desc(a_addr);
-            const uint64_t b_desc = ptx::make_kmajor_sw128_desc(a_addr + kTileABytes);
-            const uint32_t d_tmem = tmem_base + acc * BN;
-#pragma unroll
-            for (uint32_t k = 0; k < BK / 32; ++k) {
-              // 32 bytes further along K inside the swizzle atom: +2 in the 16-byte address field
-              ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, k);
-            }
-            ptx::mma_commit(&ctl->empty[stage]);
-            ptx::mma_commit(&ctl->acc_full[acc]);
-          }
+        if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) {
+          record_timeout(ctl, 2);
+          ok = false;
+          break;
         }
-        __syncwarp();
-        if (ctl->abort_flag) break;
+        if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
+          record_timeout(ctl, 3);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          // descriptors differ from stage 0's only in the 16-byte address field
+          const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
+          const uint64_t b_desc = a_desc + (kTileABytes >> 4);
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          ptx::mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, 0);
+#pragma unroll
+          for (uint32_t k = 1; k < BK / 32; ++k) {
+            // 32 bytes further along K inside the swizzle atom: +2 in the address field
+            ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1);
+          }
+          ptx::mma_commit_a(empty0 + stage * 8);
+          ptx::mma_commit_a(acc_full0 + acc * 8);
+        }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
       }
+      if (!ok || ctl->abort_flag) break;
     }
   } else {
-    // ===== promotion + epilogue (warps 2..5); TMEM lane quarter = warp % 4
+    // ===== promotion + epilogue (warps 2..9); TMEM lane quarter = warp % 4, column half = (warp - 2) / 4
     const int q = warp & 3;
+    const int col0 = ((warp - 2) >> 2) * kEpiCols;
     const int r_in_tile = q * 32 + lane;
     uint32_t acc_stage = 0, acc_phase = 0;
-    float acc[BN];
-    for (int32_t t = blockIdx.x; t < total_tiles && !ctl->abort_flag; t += gridDim.x) {
+    float2 acc[kEpiCols / 2];
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       const int32_t row = tl.row0 + r_in_tile;
       const int32_t row_c = min(row, p.total_rows - 1);
       const float* sa_row = p.sa + (int64_t)row_c * p.sa_stride_m;
       const float* sb_blk = p.sb + (int64_t)tl.expert * p.sb_stride_e + (int64_t)(tl.n0 / BN) * p.sb_stride_n;
 #pragma unroll
-      for (int j = 0; j < BN; ++j) acc[j] = 0.f;
-      float sa_cur = __ldg(sa_row), sb_cur = __ldg(sb_blk);
-      bool ok = true;
-      for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
-        float sa_nxt = 0.f, sb_nxt = 0.f;
-        if (kb + 1 < p.k_tiles) {
-          sa_nxt = __ldg(sa_row + (int64_t)(kb + 1) * p.sa_stride_k);
-          sb_nxt = __ldg(sb_blk + (int64_t)(kb + 1) * p.sb_stride_k);
-        }
-        const float scale = sa_cur * sb_cur;
-        if (!ptx::mbar_wait(&ctl->acc_full[acc_stage], acc_phase)) {
-          record_timeout(ctl, 4);
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * BN;
-        uint32_t va[32], vb[32];
-        ptx::tmem_ld_32x32(taddr, va);
-        ptx::tmem_ld_wait(va);
-        ptx::tmem_ld_32x32(taddr + 32, vb);
-        fma32(acc, va, scale);
-        ptx::tmem_ld_wait(vb);
-        ptx::tmem_ld_32x32(taddr + 64, va);
-        fma32(acc + 32, vb, scale);
-        ptx::tmem_ld_wait(va);
-        ptx::tmem_ld_32x32(taddr + 96, vb);
-        fma32(acc + 64, va, scale);
-        ptx::tmem_ld_wait(vb);
-        // every TMEM read of this stage has landed: hand the stage back to the MMA warp
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&ctl->acc_empty[acc_stage]);
-        fma32(acc + 96, vb, scale);
-        sa_cur = sa_nxt;
-        sb_cur = sb_nxt;
-        if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+      for (int j = 0; j < kEpiCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+      float sa_ring[kScaleAhead], sb_ring[kScaleAhead];
+#pragma unroll
+      for (int u = 0; u < kScaleAhead; ++u) {
+        const int32_t kc = min(u, p.k_tiles - 1);
+        sa_ring[u] = __ldg(sa_row + (int64_t)kc * p.sa_stride_k);
+        sb_ring[u] = __ldg(sb_blk + (int64_t)kc * p.sb_stride_k);
       }
-      if (!ok) break;
+      bool ok = true;
+      for (int32_t kb0 = 0; kb0 < p.k_tiles && ok; kb0 += kScaleAhead) {
+#pragma unroll
+        for (int u = 0; u < kScaleAhead; ++u) {
+          const int32_t kb = kb0 + u;
+          if (kb >= p.k_tiles) break;
+          const float scale = sa_ring[u] * sb_ring[u];
+          {  // fetch the scales of k-block kb + kScaleAhead into the slot just consumed
+            const int32_t kn = min(kb + kScaleAhead, p.k_tiles - 1);
+            sa_ring[u] = __ldg(sa_row + (int64_t)kn * p.sa_stride_k);
+            sb_ring[u] = __ldg(sb_blk + (int64_t)kn * p.sb_stride_k);
+          }
+          if (!ptx::mbar_wait_a(acc_full0 + acc_stage * 8, acc_phase)) {
+            record_timeout(ctl, 4);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * BN + col0;
+          uint32_t va[32], vb[32];
+          ptx::tmem_ld_32x32(taddr, va);
+          ptx::tmem_ld_32x32(taddr + 32, vb);
+          ptx::tmem_ld_wait(va);
+          ptx::tmem_ld_wait(vb);
+          // every TMEM read of this stage has landed: hand the stage back to the MMA warp
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_a(acc_empty0 + acc_stage * 8);
+          const float2 scale2 = make_float2(scale, scale);
+          fma32(acc, va, scale2);
+          fma32(acc + 16, vb, scale2);
+          if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+        }
+      }
+      if (!ok || ctl->abort_flag) break;
       if (row < tl.row_end) {
+        const int32_t n_first = tl.n0 + col0;
         if (p.out_dtype == SGLB200_BF16) {
-          store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + tl.n0, tl.n0, p.N);
+          store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
         } else {
-          store_row<__half>(acc, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + tl.n0, tl.n0, p.N);
+          store_row<__half>(acc, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
         }
       }
     }

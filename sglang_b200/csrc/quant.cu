@@ -1,9 +1,15 @@
 // Per-token-group quantisation to e4m3 (and the fused SiLU-and-mul variant).
 //
-// HBM-bound, one pass: every thread loads 8 consecutive elements (16 bytes of bf16/f16) of
-// UNROLL different groups up front, so a 256-thread block has UNROLL * 4 KiB in flight; the
-// group maximum is a butterfly of __shfl_xor over the group's lanes; codes leave as one
-// 8-byte store per thread.  The input is read once.  Algorithmic bytes per group of 128 bf16:
+// HBM-bound, one pass, written to keep the instruction count per element low enough that the
+// issue slots do not become the limit (about 8 instructions per element for bf16 input):
+//   * a thread owns 16 consecutive-in-pairs elements of a group (two 16-byte loads), so a group of
+//     128 is 8 lanes and the scale arithmetic is shared by 16 elements;
+//   * the group maximum is taken on packed 16-bit pairs and finished with a 3-step butterfly;
+//   * the scale amax/448 and the per-element quotients use FMA-based correctly rounded divisions
+//     (quant_math.cuh), evaluated two lanes at a time with the packed fp32x2 FMA of sm_100;
+//   * codes are converted two at a time (cvt.rn.satfinite.e4m3x2.f32) and the sign bit is taken
+//     from the input so that -0 stays -0.
+// Every thread has UNROLL groups (4 x 16 B) in flight.  Algorithmic bytes per group of 128 bf16:
 // 256 read + 128 written + 4 (float scale) or 1 (UE8M0 byte).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -16,70 +22,7 @@ namespace sglb {
 namespace {
 
 constexpr int kThreads = 256;
-
-template <typename T>
-struct Vec8;
-
-template <>
-struct Vec8<__nv_bfloat16> {
-  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
-    uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = __bfloat1622float2(h[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
-  }
-  static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
-    uint4 u;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = u;
-  }
-};
-
-template <>
-struct Vec8<__half> {
-  static __device__ __forceinline__ void load(const __half* p, float (&v)[8]) {
-    uint4 u = __ldcs(reinterpret_cast<const uint4*>(p));
-    const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = __half22float2(h[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
-  }
-  static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
-  static __device__ __forceinline__ void store(__half* p, const float (&v)[8]) {
-    uint4 u;
-    __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = u;
-  }
-};
-
-template <>
-struct Vec8<float> {
-  static __device__ __forceinline__ void load(const float* p, float (&v)[8]) {
-    float4 a = __ldcs(reinterpret_cast<const float4*>(p));
-    float4 b = __ldcs(reinterpret_cast<const float4*>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-  }
-  static __device__ __forceinline__ float round(float x) { return x; }
-  static __device__ __forceinline__ void store(float* p, const float (&v)[8]) {
-    reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
-    reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
-  }
-};
-
-__device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
+constexpr int kUnroll = 2;
 
 struct QuantParams {
   const void* in;
@@ -88,84 +31,191 @@ struct QuantParams {
   void* out_act;  // fused variant only, may be null
   uint32_t num_groups;  // rows * groups_per_row
   uint32_t groups_per_row;
-  uint32_t hidden;  // elements per output row
+  uint32_t div_mul, div_shift;  // t / groups_per_row == (uint64(t) * div_mul) >> div_shift for t < 2^31
+  uint32_t hidden;              // elements per output row
   float eps, fp8_min, fp8_max;
   int64_t s_stride_row, s_stride_group;
 };
 
-// TPG = lanes per group (group_size / 8); UNROLL = groups per thread.
-template <typename T, int TPG, int UNROLL, bool UE8M0, bool FUSE_SILU>
-__global__ void __launch_bounds__(kThreads) group_quant_kernel(const QuantParams p) {
-  constexpr int kGroupsPerIter = kThreads / TPG;
-  const uint32_t tg = threadIdx.x / TPG;
-  const uint32_t lane = threadIdx.x % TPG;
-  const uint32_t base = blockIdx.x * (uint32_t)(kGroupsPerIter * UNROLL) + tg;
+// ---- element traits: E = elements per 16-byte vector -----------------------------------------
+template <typename T>
+struct Elem;
 
-  float v[UNROLL][8];
-  uint32_t row[UNROLL], grp[UNROLL];
-  bool live[UNROLL];
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int E = 8;
+  // |.| maximum over the 8 packed values of a vector, as fp32
+  static __device__ __forceinline__ float vec_absmax(const uint4& u) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+    __nv_bfloat162 m = __hmax2(__habs2(h[0]), __habs2(h[1]));
+    m = __hmax2(m, __hmax2(__habs2(h[2]), __habs2(h[3])));
+    const float2 f = __bfloat1622float2(m);
+    return fmaxf(f.x, f.y);
+  }
+  static __device__ __forceinline__ float2 pair(uint32_t w) {  // two bf16 -> two fp32 (exact)
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  }
+  static __device__ __forceinline__ uint32_t sign_bytes(uint32_t w0, uint32_t w1) {  // bytes 1,3 of each word
+    return __byte_perm(w0, w1, 0x7531);
+  }
+  static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+};
+
+template <>
+struct Elem<__half> {
+  static constexpr int E = 8;
+  static __device__ __forceinline__ float vec_absmax(const uint4& u) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+    __half2 m = __hmax2(__habs2(h[0]), __habs2(h[1]));
+    m = __hmax2(m, __hmax2(__habs2(h[2]), __habs2(h[3])));
+    const float2 f = __half22float2(m);
+    return fmaxf(f.x, f.y);
+  }
+  static __device__ __forceinline__ float2 pair(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  }
+  static __device__ __forceinline__ uint32_t sign_bytes(uint32_t w0, uint32_t w1) {
+    return __byte_perm(w0, w1, 0x7531);
+  }
+  static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+};
+
+template <>
+struct Elem<float> {
+  static constexpr int E = 4;
+  static __device__ __forceinline__ float vec_absmax(const uint4& u) {
+    return fmaxf(fmaxf(fabsf(__uint_as_float(u.x)), fabsf(__uint_as_float(u.y))),
+                 fmaxf(fabsf(__uint_as_float(u.z)), fabsf(__uint_as_float(u.w))));
+  }
+  static __device__ __forceinline__ float round(float x) { return x; }
+};
+
+__device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
+
+// Two quotients x / s with the shared reciprocal r = RN(1/s): packed Markstein step.
+__device__ __forceinline__ float2 quotient2(float2 x, float2 rr, float2 neg_ss) {
+  const float2 q0 = __fmul2_rn(x, rr);
+  const float2 rem = __ffma2_rn(q0, neg_ss, x);
+  return __ffma2_rn(rem, rr, q0);
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+
+// 16-bit input types.  LPG = lanes per group = group_size / 16; each lane owns vectors `lane` and
+// `lane + LPG` of its group (group_size 16: one lane, both vectors).
+template <typename T, int LPG, bool UE8M0, bool FUSE_SILU, bool CLAMP>
+__global__ void __launch_bounds__(kThreads) group_quant16_kernel(const QuantParams p) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  constexpr int kGroupsPerIter = kThreads / LPG;
+  constexpr int kGroupSize = LPG * 16;
+  constexpr int kSecond = (LPG == 1 && kGroupSize == 16) ? 1 : LPG;  // vector index of the second load
+  const uint32_t tg = threadIdx.x / LPG;
+  const uint32_t lane = threadIdx.x % LPG;
+  const uint32_t base = blockIdx.x * (uint32_t)(kGroupsPerIter * kUnroll) + tg;
+  const float inv_max = __frcp_rn(p.fp8_max);
+  const bool fast_scale = p.fp8_max == 448.0f;
+
+  uint4 raw[kUnroll][2];
+  uint32_t row[kUnroll], grp[kUnroll];
+  bool live[kUnroll];
 
 #pragma unroll
-  for (int i = 0; i < UNROLL; ++i) {
+  for (int i = 0; i < kUnroll; ++i) {
     const uint32_t t = base + (uint32_t)i * kGroupsPerIter;
     live[i] = t < p.num_groups;
-    row[i] = live[i] ? t / p.groups_per_row : 0u;
-    grp[i] = live[i] ? t - row[i] * p.groups_per_row : 0u;
+    const uint32_t tt = live[i] ? t : 0u;
+    row[i] = (uint32_t)(((uint64_t)tt * p.div_mul) >> p.div_shift);
+    grp[i] = tt - row[i] * p.groups_per_row;
+    raw[i][0] = raw[i][1] = make_uint4(0, 0, 0, 0);
     if (live[i]) {
-      const size_t col = (size_t)grp[i] * (TPG * 8) + lane * 8;
       if constexpr (FUSE_SILU) {
-        const T* g = static_cast<const T*>(p.in) + (size_t)row[i] * p.hidden * 2 + col;
-        float u[8];
-        Vec8<T>::load(g, v[i]);
-        Vec8<T>::load(g + p.hidden, u);
+        const T* g = static_cast<const T*>(p.in) + (size_t)row[i] * p.hidden * 2 + (size_t)grp[i] * kGroupSize;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = Vec8<T>::round(Vec8<T>::round(silu_f32(v[i][j])) * u[j]);
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t vec = lane + h * kSecond;
+          const uint4 gv = __ldcs(reinterpret_cast<const uint4*>(g) + vec);
+          const uint4 uv = __ldcs(reinterpret_cast<const uint4*>(g + p.hidden) + vec);
+          const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gv);
+          const uint32_t* uw = reinterpret_cast<const uint32_t*>(&uv);
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&raw[i][h]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 gf = Elem<T>::pair(gw[j]), uf = Elem<T>::pair(uw[j]);
+            ow[j] = Elem<T>::pack(Elem<T>::round(silu_f32(gf.x)) * uf.x, Elem<T>::round(silu_f32(gf.y)) * uf.y);
+          }
+        }
       } else {
-        Vec8<T>::load(static_cast<const T*>(p.in) + (size_t)row[i] * p.hidden + col, v[i]);
+        const uint4* g = reinterpret_cast<const uint4*>(static_cast<const T*>(p.in) + (size_t)tt * kGroupSize);
+        raw[i][0] = __ldcs(g + lane);
+        raw[i][1] = __ldcs(g + lane + kSecond);
       }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
     }
   }
 
 #pragma unroll
-  for (int i = 0; i < UNROLL; ++i) {
-    float amax = p.eps;
+  for (int i = 0; i < kUnroll; ++i) {
+    float amax = fmaxf(p.eps, fmaxf(Elem<T>::vec_absmax(raw[i][0]), Elem<T>::vec_absmax(raw[i][1])));
 #pragma unroll
-    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
-#pragma unroll
-    for (int m = TPG / 2; m >= 1; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+    for (int m = LPG / 2; m >= 1; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
 
-    const float s = group_scale(amax, p.fp8_max, UE8M0);
-    const GroupDivisor d = make_divisor(s, sizeof(T) == 2);
-
+    const float s = fast_scale ? group_scale_fast(amax, p.fp8_max, inv_max, UE8M0) : group_scale(amax, p.fp8_max, UE8M0);
     if (!live[i]) continue;  // after the shuffles: every lane of the warp takes part in them
+    const bool fast = (s >= 7.888609e-31f) && (s <= 1.2676506e30f);
+    const float r = __frcp_rn(s);
+    const float2 rr = make_float2(r, r), nss = make_float2(-s, -s);
 
-    uint32_t packed[2];
+    const size_t off = (size_t)row[i] * p.hidden + (size_t)grp[i] * kGroupSize;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      float q[4];
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&raw[i][h]);
+      uint32_t packed[2];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) q[j] = fminf(fmaxf(quotient(v[i][4 * h + j], d), p.fp8_min), p.fp8_max);
-      const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(q[0], q[1]), __NV_SATFINITE, __NV_E4M3);
-      const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(q[2], q[3]), __NV_SATFINITE, __NV_E4M3);
-      packed[h] = lo | (hi << 16);
-    }
-    const size_t off = (size_t)row[i] * p.hidden + (size_t)grp[i] * (TPG * 8) + lane * 8;
-    __stcs(reinterpret_cast<uint2*>(p.out_q + off), make_uint2(packed[0], packed[1]));
-    if constexpr (FUSE_SILU) {
-      if (p.out_act != nullptr) Vec8<T>::store(static_cast<T*>(p.out_act) + off, v[i]);
+      for (int j = 0; j < 2; ++j) {
+        float2 qa, qb;
+        const float2 xa = Elem<T>::pair(w[2 * j]), xb = Elem<T>::pair(w[2 * j + 1]);
+        if (fast) {
+          qa = quotient2(xa, rr, nss);
+          qb = quotient2(xb, rr, nss);
+        } else {
+          qa = make_float2(__fdiv_rn(xa.x, s), __fdiv_rn(xa.y, s));
+          qb = make_float2(__fdiv_rn(xb.x, s), __fdiv_rn(xb.y, s));
+        }
+        if constexpr (CLAMP) {
+          qa.x = fminf(fmaxf(qa.x, p.fp8_min), p.fp8_max);
+          qa.y = fminf(fmaxf(qa.y, p.fp8_min), p.fp8_max);
+          qb.x = fminf(fmaxf(qb.x, p.fp8_min), p.fp8_max);
+          qb.y = fminf(fmaxf(qb.y, p.fp8_min), p.fp8_max);
+        }
+        const uint32_t codes = cvt_e4m3x2(qa.x, qa.y) | (cvt_e4m3x2(qb.x, qb.y) << 16);
+        // the quotient carries x's sign (s > 0): take bit 7 of every code from the input, so -0 / s = -0
+        const uint32_t signs = Elem<T>::sign_bytes(w[2 * j], w[2 * j + 1]);
+        packed[j] = (codes & 0x7f7f7f7fu) | (signs & 0x80808080u);
+      }
+      const uint32_t vec = lane + h * kSecond;
+      __stcs(reinterpret_cast<uint2*>(p.out_q + off) + vec, make_uint2(packed[0], packed[1]));
+      if constexpr (FUSE_SILU) {
+        if (p.out_act != nullptr) reinterpret_cast<uint4*>(static_cast<T*>(p.out_act) + off)[vec] = raw[i][h];
+      }
     }
 
     if (lane == 0) {
       if constexpr (UE8M0) {
-        uint8_t* w = reinterpret_cast<uint8_t*>(p.out_s) +
-                     4 * ((int64_t)row[i] * p.s_stride_row + (int64_t)(grp[i] >> 2) * p.s_stride_group);
+        uint8_t* wp = reinterpret_cast<uint8_t*>(p.out_s) +
+                      4 * ((int64_t)row[i] * p.s_stride_row + (int64_t)(grp[i] >> 2) * p.s_stride_group);
         const uint32_t b = grp[i] & 3u;
-        w[b] = (uint8_t)(float_to_bits(s) >> 23);
+        wp[b] = (uint8_t)(__float_as_uint(s) >> 23);
         if (grp[i] + 1 == p.groups_per_row) {
-          for (uint32_t z = b + 1; z < 4; ++z) w[z] = 0;  // bytes of the word past the last group
+          for (uint32_t z = b + 1; z < 4; ++z) wp[z] = 0;  // bytes of the word past the last group
         }
       } else {
         static_cast<float*>(p.out_s)[(int64_t)row[i] * p.s_stride_row + (int64_t)grp[i] * p.s_stride_group] = s;
@@ -174,29 +224,114 @@ __global__ void __launch_bounds__(kThreads) group_quant_kernel(const QuantParams
   }
 }
 
-template <typename T, int TPG, bool FUSE>
-int launch_tpg(const QuantParams& p, bool ue8m0, cudaStream_t stream) {
-  constexpr int UNROLL = 4;
-  constexpr int kGroupsPerBlock = (kThreads / TPG) * UNROLL;
+// fp32 input (rare): 8 elements per lane, plain IEEE divisions.
+template <int LPG, bool UE8M0, bool FUSE_SILU>
+__global__ void __launch_bounds__(kThreads) group_quant32_kernel(const QuantParams p) {
+  constexpr int kGroupsPerIter = kThreads / LPG;
+  constexpr int kGroupSize = LPG * 8;
+  const uint32_t tg = threadIdx.x / LPG;
+  const uint32_t lane = threadIdx.x % LPG;
+  const uint32_t t = blockIdx.x * (uint32_t)kGroupsPerIter + tg;
+  const bool live = t < p.num_groups;
+  const uint32_t tt = live ? t : 0u;
+  const uint32_t row = (uint32_t)(((uint64_t)tt * p.div_mul) >> p.div_shift);
+  const uint32_t grp = tt - row * p.groups_per_row;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  if (live) {
+    if constexpr (FUSE_SILU) {
+      const float* g = static_cast<const float*>(p.in) + (size_t)row * p.hidden * 2 + (size_t)grp * kGroupSize + lane * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = silu_f32(__ldcs(g + j)) * __ldcs(g + p.hidden + j);
+    } else {
+      const float4* g = reinterpret_cast<const float4*>(static_cast<const float*>(p.in) + (size_t)tt * kGroupSize) + lane * 2;
+      const float4 a = __ldcs(g), b = __ldcs(g + 1);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+  }
+  float amax = p.eps;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+  for (int m = LPG / 2; m >= 1; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+  const float s = group_scale(amax, p.fp8_max, UE8M0);
+  if (!live) return;
+  uint32_t packed[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    float q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) q[j] = fminf(fmaxf(__fdiv_rn(v[4 * h + j], s), p.fp8_min), p.fp8_max);
+    packed[h] = cvt_e4m3x2(q[0], q[1]) | (cvt_e4m3x2(q[2], q[3]) << 16);
+  }
+  const size_t off = (size_t)row * p.hidden + (size_t)grp * kGroupSize + lane * 8;
+  __stcs(reinterpret_cast<uint2*>(p.out_q + off), make_uint2(packed[0], packed[1]));
+  if constexpr (FUSE_SILU) {
+    if (p.out_act != nullptr) {
+      float* o = static_cast<float*>(p.out_act) + off;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[j];
+    }
+  }
+  if (lane == 0) {
+    if constexpr (UE8M0) {
+      uint8_t* wp = reinterpret_cast<uint8_t*>(p.out_s) +
+                    4 * ((int64_t)row * p.s_stride_row + (int64_t)(grp >> 2) * p.s_stride_group);
+      const uint32_t b = grp & 3u;
+      wp[b] = (uint8_t)(__float_as_uint(s) >> 23);
+      if (grp + 1 == p.groups_per_row) {
+        for (uint32_t z = b + 1; z < 4; ++z) wp[z] = 0;
+      }
+    } else {
+      static_cast<float*>(p.out_s)[(int64_t)row * p.s_stride_row + (int64_t)grp * p.s_stride_group] = s;
+    }
+  }
+}
+
+template <typename T, int LPG, bool FUSE>
+int launch16(const QuantParams& p, bool ue8m0, bool clamp, cudaStream_t stream) {
+  constexpr int kGroupsPerBlock = (kThreads / LPG) * kUnroll;
   const uint32_t blocks = (p.num_groups + kGroupsPerBlock - 1) / kGroupsPerBlock;
   if (ue8m0) {
-    group_quant_kernel<T, TPG, UNROLL, true, FUSE><<<blocks, kThreads, 0, stream>>>(p);
+    if (clamp) group_quant16_kernel<T, LPG, true, FUSE, true><<<blocks, kThreads, 0, stream>>>(p);
+    else group_quant16_kernel<T, LPG, true, FUSE, false><<<blocks, kThreads, 0, stream>>>(p);
   } else {
-    group_quant_kernel<T, TPG, UNROLL, false, FUSE><<<blocks, kThreads, 0, stream>>>(p);
+    if (clamp) group_quant16_kernel<T, LPG, false, FUSE, true><<<blocks, kThreads, 0, stream>>>(p);
+    else group_quant16_kernel<T, LPG, false, FUSE, false><<<blocks, kThreads, 0, stream>>>(p);
   }
-  SGLB_CHECK_LAUNCH("group_quant_kernel");
+  SGLB_CHECK_LAUNCH("group_quant16_kernel");
   return SGLB200_OK;
 }
 
 template <typename T, bool FUSE>
-int launch_t(const QuantParams& p, int group_size, bool ue8m0, cudaStream_t stream) {
+int launch_t16(const QuantParams& p, int group_size, bool ue8m0, bool clamp, cudaStream_t stream) {
   switch (group_size) {
-    case 128: return launch_tpg<T, 16, FUSE>(p, ue8m0, stream);
-    case 64: return launch_tpg<T, 8, FUSE>(p, ue8m0, stream);
-    case 32: return launch_tpg<T, 4, FUSE>(p, ue8m0, stream);
-    case 16: return launch_tpg<T, 2, FUSE>(p, ue8m0, stream);
+    case 128: return launch16<T, 8, FUSE>(p, ue8m0, clamp, stream);
+    case 64: return launch16<T, 4, FUSE>(p, ue8m0, clamp, stream);
+    case 32: return launch16<T, 2, FUSE>(p, ue8m0, clamp, stream);
+    default: return launch16<T, 1, FUSE>(p, ue8m0, clamp, stream);
   }
-  return fail(SGLB200_ERR_SHAPE, "group_size=%d: must be 16, 32, 64 or 128", group_size);
+}
+
+template <int LPG, bool FUSE>
+int launch32(const QuantParams& p, bool ue8m0, cudaStream_t stream) {
+  constexpr int kGroupsPerBlock = kThreads / LPG;
+  const uint32_t blocks = (p.num_groups + kGroupsPerBlock - 1) / kGroupsPerBlock;
+  if (ue8m0) group_quant32_kernel<LPG, true, FUSE><<<blocks, kThreads, 0, stream>>>(p);
+  else group_quant32_kernel<LPG, false, FUSE><<<blocks, kThreads, 0, stream>>>(p);
+  SGLB_CHECK_LAUNCH("group_quant32_kernel");
+  return SGLB200_OK;
+}
+
+template <bool FUSE>
+int launch_t32(const QuantParams& p, int group_size, bool ue8m0, cudaStream_t stream) {
+  switch (group_size) {
+    case 128: return launch32<16, FUSE>(p, ue8m0, stream);
+    case 64: return launch32<8, FUSE>(p, ue8m0, stream);
+    case 32: return launch32<4, FUSE>(p, ue8m0, stream);
+    default: return launch32<2, FUSE>(p, ue8m0, stream);
+  }
 }
 
 template <bool FUSE>
@@ -234,6 +369,13 @@ int quant_entry(const void* input, int in_dtype, void* out_q, void* out_s, void*
   p.out_act = out_act;
   p.num_groups = (uint32_t)(num_rows * G);
   p.groups_per_row = (uint32_t)G;
+  {  // round-up magic number: with s = ceil(log2 G), m = ceil(2^(31+s) / G) < 2^32 and
+     // floor(t / G) == (t * m) >> (31 + s) for every t < 2^31
+    uint32_t sh = 0;
+    while (((uint64_t)1 << sh) < (uint64_t)G) ++sh;
+    p.div_shift = 31 + sh;
+    p.div_mul = (uint32_t)((((uint64_t)1 << (31 + sh)) + (uint64_t)G - 1) / (uint64_t)G);
+  }
   p.hidden = (uint32_t)hidden;
   p.eps = eps;
   p.fp8_min = fp8_min;
@@ -241,10 +383,12 @@ int quant_entry(const void* input, int in_dtype, void* out_q, void* out_s, void*
   p.s_stride_row = s_stride_row;
   p.s_stride_group = s_stride_group;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // with the e4m3 limits the saturating conversion already clamps; other limits need the explicit clamp
+  const bool clamp = !(fp8_max == 448.0f && fp8_min == -448.0f);
   switch (in_dtype) {
-    case SGLB200_BF16: return launch_t<__nv_bfloat16, FUSE>(p, group_size, scale_ue8m0 != 0, st);
-    case SGLB200_F16: return launch_t<__half, FUSE>(p, group_size, scale_ue8m0 != 0, st);
-    default: return launch_t<float, FUSE>(p, group_size, scale_ue8m0 != 0, st);
+    case SGLB200_BF16: return launch_t16<__nv_bfloat16, FUSE>(p, group_size, scale_ue8m0 != 0, clamp, st);
+    case SGLB200_F16: return launch_t16<__half, FUSE>(p, group_size, scale_ue8m0 != 0, clamp, st);
+    default: return launch_t32<FUSE>(p, group_size, scale_ue8m0 != 0, st);
   }
 }
 

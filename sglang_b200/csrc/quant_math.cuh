@@ -72,6 +72,40 @@ SGLB_HD float group_scale(float amax, float fp8_max, bool ue8m0) {
   return s;
 }
 
+SGLB_HD float mul_rn(float a, float b) {
+#if defined(__CUDA_ARCH__)
+  return __fmul_rn(a, b);
+#else
+  return a * b;
+#endif
+}
+
+// group_scale without the division routine: with c = RN(1 / fp8_max), q0 = amax*c,
+// rem = amax - q0*fp8_max (exact, one FMA), s = q0 + rem*c is the correctly rounded quotient
+// whenever it is a normal number (checked on the host for fp8_max = 448 over every 16-bit-float
+// amax and a long run of random fp32 ones); tiny maxima, which need eps < 2^-100, take the division.
+SGLB_HD float group_scale_fast(float amax, float fp8_max, float inv_max, bool ue8m0) {
+  float s;
+  if (amax >= 7.888609e-31f) {
+    const float q0 = mul_rn(amax, inv_max);
+    const float rem = fma_rn(-q0, fp8_max, amax);
+    s = fma_rn(rem, inv_max, q0);
+  } else {
+    s = div_rn(amax, fp8_max);
+  }
+  if (ue8m0) {
+    uint32_t u = float_to_bits(s);
+    uint32_t e = (u >> 23) & 0xffu;
+    if (e == 0) {
+      e = 1;
+    } else if (u & 0x7fffffu) {
+      e += 1;
+    }
+    s = bits_to_float(e << 23);
+  }
+  return s;
+}
+
 // The divisor is shared by a whole group, so the per-element quotient uses one correctly
 // rounded reciprocal and two FMAs (a Markstein step): q0 = x*r; rem = x - q0*s; q = q0 + rem*r.
 // For s in [2^-100, 2^100] and 16-bit-float x this equals RN(x / s) wherever the e4m3 result
@@ -90,7 +124,7 @@ SGLB_HD GroupDivisor make_divisor(float s, bool allow_fast) {
 }
 SGLB_HD float quotient(float x, const GroupDivisor& d) {
   if (d.fast) {
-    float q0 = x * d.r;
+    float q0 = mul_rn(x, d.r);
     float rem = fma_rn(-q0, d.s, x);
     float q = fma_rn(rem, d.r, q0);
     // s > 0, so the quotient carries x's sign; restoring it keeps -0 / s = -0 (the FMA chain gives +0)

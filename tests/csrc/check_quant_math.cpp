@@ -61,6 +61,26 @@ int main(int argc, char** argv) {
       }
     }
   }
+  // the FMA-based scale against the IEEE division: every 16-bit amax, then random fp32 amax
+  long long bad_scale = 0;
+  const float inv448 = 1.0f / 448.0f;
+  for (unsigned ia = 1; ia < top; ++ia) {
+    float amax = from16((uint16_t)ia, bf16);
+    for (int mode = 0; mode < 2; ++mode)
+      bad_scale += sglb::float_to_bits(sglb::group_scale_fast(amax, 448.0f, inv448, mode == 1)) !=
+                   sglb::float_to_bits(sglb::group_scale(amax, 448.0f, mode == 1));
+  }
+  unsigned long long rng = 0x9E3779B97F4A7C15ull;
+  for (long long i = 0; i < 200000000ll / stride; ++i) {
+    rng = rng * 6364136223846793005ull + 1442695040888963407ull;
+    uint32_t u = (uint32_t)(rng >> 33) & 0x7fffffffu;
+    float amax = sglb::bits_to_float(u);
+    if (!(amax >= 1e-37f && amax < 3e38f)) continue;
+    bad_scale += sglb::float_to_bits(sglb::group_scale_fast(amax, 448.0f, inv448, false)) !=
+                 sglb::float_to_bits(sglb::group_scale(amax, 448.0f, false));
+  }
+  bad_code += bad_scale;
+  printf("scale_mismatch=%lld ", bad_scale);
   printf("format=%s stride=%d pairs=%lld fast_divisors=%lld fp32_mismatch=%lld code_mismatch=%lld\n",
          bf16 ? "bf16" : "f16", stride, n, n_fast, bad_f32, bad_code);
   return bad_code == 0 ? 0 : 1;
