@@ -2,13 +2,13 @@
 //
 //   out[m, n] = cast( sum_kb ( sum_{k in kb} a[m,k] * b[n,k] ) * sa[m,kb] * sb[n/128,kb] )
 //
-// One CTA per SM, 320 threads, warp-specialised:
-//   warp 0     TMA producer: A tile [128 rows x 128 B] and B tile [128 rows x 128 B] per k-block into a
+// One CTA per SM, 384 threads, warp-specialised:
+//   warps 0-1  TMA producers (k-blocks alternate between them): A tile [128 rows x 128 B] and B tile [128 rows x 128 B] per k-block into a
 //              6-stage ring of 128-byte-swizzled shared memory (32 KiB per stage).
-//   warp 1     MMA issuer: per k-block four tcgen05.mma (128 x 128 x 32, e4m3 -> f32) that OVERWRITE one of
+//   warps 2-3  MMA issuers (k-blocks alternate): per k-block four tcgen05.mma (128 x 128 x 32, e4m3 -> f32) that OVERWRITE one of
 //              four 128-column TMEM accumulator stages, then tcgen05.commit to free the smem stage and to
 //              publish the TMEM stage.
-//   warps 2-9  promotion + epilogue: two warps per TMEM lane quarter, each owning 64 of the tile's 128
+//   warps 4-11 promotion + epilogue: two warps per TMEM lane quarter, each owning 64 of the tile's 128
 //              columns.  A thread owns one accumulator row: per k-block it pulls its 64 partial sums out
 //              of TMEM (two tcgen05.ld of 32 columns, one wait), multiplies by sa[m,kb] * sb[nb,kb] and
 //              adds into 64 fp32 registers with packed fp32x2 FMAs; after the last k-block it rounds to
@@ -36,7 +36,8 @@ namespace {
 constexpr int BM = 128, BN = 128, BK = 128;
 constexpr int kStages = 6;
 constexpr int kAccStages = 4;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+constexpr int kIssuers = 2;  // producer warps and MMA warps: each pair splits the k-blocks even/odd
 constexpr int kEpiWarps = 8;
 constexpr int kEpiCols = BN / (kEpiWarps / 4);  // columns per promotion warp (64)
 constexpr int kScaleAhead = 4;                 // k-blocks of scale prefetch
@@ -186,7 +187,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     ptx::prefetch_tensormap(&map_a);
     ptx::prefetch_tensormap(&map_b);
   }
-  if (warp == 1) {
+  if (warp == kIssuers) {
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
@@ -234,60 +235,67 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const uint32_t acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
   const uint32_t stage0 = ptx::smem_u32(stage_base);
 
-  if (warp == 0) {
-    // ===== TMA producer
-    uint32_t stage = 0, phase = 0;
+  if (warp < kIssuers) {
+    // ===== TMA producers.  Issuing a TMA or an MMA and touching an mbarrier each cost the issuing
+    // thread on the order of a hundred cycles, and the tensor pipe does not queue far ahead, so one
+    // warp per role cannot feed it: two warps per role take the k-blocks of the CTA alternately.
+    uint32_t stage = 0, phase = 0, g = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       bool ok = true;
-      for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
-        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
-          record_timeout(ctl, 1);
-          ok = false;
-          break;
-        }
-        if (lane == 0) {
-          const uint32_t dst = stage0 + stage * kStageBytes;
-          ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
-          ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.row0);
-          ptx::tma_load_3d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, tl.n0, tl.expert);
+      for (int32_t kb = 0; kb < p.k_tiles; ++kb, ++g) {
+        if ((g & (kIssuers - 1)) == (uint32_t)warp) {
+          if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
+            record_timeout(ctl, 1);
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            const uint32_t dst = stage0 + stage * kStageBytes;
+            ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
+            ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.row0);
+            ptx::tma_load_3d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, tl.n0, tl.expert);
+          }
         }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
       if (!ok || ctl->abort_flag) break;
     }
-  } else if (warp == 1) {
-    // ===== MMA issuer
+  } else if (warp < 2 * kIssuers) {
+    // ===== MMA issuers (k-blocks alternate between the two warps; each k-block has its own TMEM stage)
+    const uint32_t me = warp - kIssuers;
     constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
     const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
-    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, g = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       bool ok = true;
-      for (int32_t kb = 0; kb < p.k_tiles; ++kb) {
-        if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) {
-          record_timeout(ctl, 2);
-          ok = false;
-          break;
-        }
-        if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
-          record_timeout(ctl, 3);
-          ok = false;
-          break;
-        }
-        ptx::tc_fence_after();
-        if (lane == 0) {
-          // descriptors differ from stage 0's only in the 16-byte address field
-          const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
-          const uint64_t b_desc = a_desc + (kTileABytes >> 4);
-          const uint32_t d_tmem = tmem_base + acc * BN;
-          ptx::mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, 0);
-#pragma unroll
-          for (uint32_t k = 1; k < BK / 32; ++k) {
-            // 32 bytes further along K inside the swizzle atom: +2 in the address field
-            ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1);
+      for (int32_t kb = 0; kb < p.k_tiles; ++kb, ++g) {
+        if ((g & (kIssuers - 1)) == me) {
+          if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) {
+            record_timeout(ctl, 2);
+            ok = false;
+            break;
           }
-          ptx::mma_commit_a(empty0 + stage * 8);
-          ptx::mma_commit_a(acc_full0 + acc * 8);
+          if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
+            record_timeout(ctl, 3);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            // descriptors differ from stage 0's only in the 16-byte address field
+            const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
+            const uint64_t b_desc = a_desc + (kTileABytes >> 4);
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            ptx::mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, 0);
+#pragma unroll
+            for (uint32_t k = 1; k < BK / 32; ++k) {
+              // 32 bytes further along K inside the swizzle atom: +2 in the address field
+              ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1);
+            }
+            ptx::mma_commit_a(empty0 + stage * 8);
+            ptx::mma_commit_a(acc_full0 + acc * 8);
+          }
         }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
         if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
@@ -295,9 +303,9 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       if (!ok || ctl->abort_flag) break;
     }
   } else {
-    // ===== promotion + epilogue (warps 2..9); TMEM lane quarter = warp % 4, column half = (warp - 2) / 4
+    // ===== promotion + epilogue (warps 4..11); TMEM lane quarter = warp % 4, column half = (warp - 4) / 4
     const int q = warp & 3;
-    const int col0 = ((warp - 2) >> 2) * kEpiCols;
+    const int col0 = ((warp - 2 * kIssuers) >> 2) * kEpiCols;
     const int r_in_tile = q * 32 + lane;
     uint32_t acc_stage = 0, acc_phase = 0;
     float2 acc[kEpiCols / 2];
@@ -365,7 +373,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   // ---------------------------------------------------------------- tear-down
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == kIssuers) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
   }

@@ -1,0 +1,10 @@
+"""Tensor-parallel block-FP8 linear layers (the part of ``python/sglang/srt/layers/linear.py`` and
+``srt/distributed`` this path touches): column/row sharding of block-quantised weights and the
+all-reduce after row-parallel layers, over ``torch.distributed`` (NCCL on GPUs)."""
+
+from .parallel_linear import (  # noqa: F401
+    ColumnParallelBlockFp8Linear,
+    RowParallelBlockFp8Linear,
+    shard_block_fp8_weight,
+    tensor_model_parallel_all_reduce,
+)

@@ -1,0 +1,97 @@
+"""Column- and row-parallel block-FP8 linear layers.
+
+Mirrors ``ColumnParallelLinear`` / ``RowParallelLinear`` (``python/sglang/srt/layers/linear.py:263-430,
+1194-1386``) for block-quantised weights: one process per GPU, the weight shard of this rank,
+``quant_method.apply`` for the local GEMM, and ``tensor_model_parallel_all_reduce``
+(``python/sglang/srt/distributed/communication_op.py:11-13``) on the row-parallel output.
+Splits must fall on 128-element block boundaries (``quantization/fp8.py:251-269``), so activation
+groups and weight blocks never straddle ranks and the local quantisation is exactly the slice of
+the global one.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+BLOCK = 128
+
+
+def tensor_model_parallel_all_reduce(x: torch.Tensor, group=None) -> torch.Tensor:
+    """Sum over the tensor-parallel group, in place (no-op for a single rank)."""
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(x, group=group)
+    return x
+
+
+def shard_block_fp8_weight(weight: torch.Tensor, scale: torch.Tensor, rank: int, world: int,
+                           dim: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Slice ``weight [N, K]`` (e4m3) and ``scale [ceil(N/128), ceil(K/128)]`` for one rank along
+    ``dim`` (0 = output/column-parallel, 1 = input/row-parallel).  The per-rank extent must be a
+    multiple of the 128 block, as ``Fp8LinearMethod.create_weights`` requires."""
+    size = weight.shape[dim]
+    if size % world != 0 or (size // world) % BLOCK != 0:
+        raise ValueError(f"dimension {dim} of size {size} cannot be split over {world} ranks on "
+                         f"{BLOCK}-element block boundaries")
+    per = size // world
+    w = weight.narrow(dim, rank * per, per).contiguous()
+    s = scale.narrow(dim, rank * per // BLOCK, per // BLOCK).contiguous()
+    return w, s
+
+
+class _ParallelBase(torch.nn.Module):
+    def __init__(self, weight, scale, bias, apply_fn, group):
+        super().__init__()
+        self.weight = torch.nn.Parameter(weight, requires_grad=False)
+        self.weight_scale_inv = torch.nn.Parameter(scale, requires_grad=False)
+        self.bias = None if bias is None else torch.nn.Parameter(bias, requires_grad=False)
+        self.group = group
+        if apply_fn is None:
+            from ..layers.quantization import Fp8Config, Fp8LinearMethod
+            apply_fn = Fp8LinearMethod(Fp8Config()).apply
+        self._apply = apply_fn
+
+
+class ColumnParallelBlockFp8Linear(_ParallelBase):
+    """``Y_r = X W_r^T``: each rank owns ``N / tp`` output features; no exchange unless
+    ``gather_output`` (then an all-gather along the last dimension, ``linear.py:430``)."""
+
+    def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
+                 gather_output: bool = False, apply_fn: Optional[Callable] = None, group=None):
+        w, s = shard_block_fp8_weight(weight, scale, rank, world, 0)
+        b = None if bias is None else bias.chunk(world)[rank].contiguous()
+        super().__init__(w, s, b, apply_fn, group)
+        self.gather_output, self.world = gather_output, world
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self._apply(self, x, self.bias)
+        if self.gather_output and self.world > 1:
+            parts = [torch.empty_like(y) for _ in range(self.world)]
+            dist.all_gather(parts, y.contiguous(), group=self.group)
+            y = torch.cat(parts, dim=-1)
+        return y
+
+
+class RowParallelBlockFp8Linear(_ParallelBase):
+    """``Y = sum_r X_r W_r^T``: each rank owns ``K / tp`` input features of the weight and the
+    matching slice of the activations; the partial outputs are summed with one all-reduce
+    (``linear.py:1361-1386``).  The bias is added once, on rank 0, before the reduction."""
+
+    def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
+                 input_is_parallel: bool = True, reduce_results: bool = True,
+                 apply_fn: Optional[Callable] = None, group=None):
+        w, s = shard_block_fp8_weight(weight, scale, rank, world, 1)
+        super().__init__(w, s, bias if rank == 0 else None, apply_fn, group)
+        self.rank, self.world = rank, world
+        self.input_is_parallel, self.reduce_results = input_is_parallel, reduce_results
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not self.input_is_parallel:
+            per = x.shape[-1] // self.world
+            x = x.narrow(-1, self.rank * per, per).contiguous()
+        y = self._apply(self, x, self.bias)
+        if self.reduce_results:
+            y = tensor_model_parallel_all_reduce(y, self.group)
+        return y

@@ -1,0 +1,123 @@
+"""CPU-side checks: the C-ABI library loads without a GPU and exports every symbol the header
+declares; host-side validation raises before anything could launch; the quantiser's FMA division
+is checked against the IEEE division on a sample of the exhaustive host test."""
+
+import os
+import re
+import subprocess
+import sys
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "sglb200.h")
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from sglang_b200 import build
+    path = build.build()
+    assert os.path.exists(path)
+    return path
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sglb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(built_lib):
+    from sglang_b200._lib import SIGNATURES, lib
+    handle = lib()
+    declared = _declared_symbols()
+    assert len(declared) >= 12
+    for name in declared:
+        assert hasattr(handle, name), f"{name} is declared in include/sglb200.h but not exported"
+    assert sorted(SIGNATURES) == declared, "ctypes signatures and header are out of step"
+    assert handle.sglb200_version().decode() == "0.1"
+    assert handle.sglb200_status_string(0).decode() == "ok"
+    assert "alignment" in handle.sglb200_status_string(-2).decode()
+
+
+def test_header_cites_the_reference_for_each_kernel_entry():
+    text = open(HEADER).read()
+    for name in ["per_token_group_quant_8bit.cu", "fp8_blockwise_gemm_kernel.cu", "fp8_blockwise_moe_kernel.cu",
+                 "prepare_moe_input.cu", "activation.cu", "common_extension.cc"]:
+        assert name in text
+
+
+def test_host_validation_without_gpu(built_lib):
+    """Shape / dtype / null checks come first, so they are reachable on a machine with no GPU."""
+    from sglang_b200._lib import check, lib
+    L = lib()
+    assert L.sglb200_per_token_group_quant_fp8(None, 0, None, None, 4, 200, 128, 1e-10, -448.0, 448.0, 0, 2, 1, None) == -1
+    assert "multiple of group_size" in L.sglb200_last_error_detail().decode()
+    assert L.sglb200_per_token_group_quant_fp8(None, 0, None, None, 4, 256, 8, 1e-10, -448.0, 448.0, 0, 2, 1, None) == -1
+    assert L.sglb200_per_token_group_quant_fp8(None, 7, None, None, 4, 256, 128, 1e-10, -448.0, 448.0, 0, 2, 1, None) == -5
+    assert L.sglb200_per_token_group_quant_fp8(None, 0, None, None, 4, 256, 128, 1e-10, -448.0, 448.0, 0, 2, 1, None) == -6
+    assert L.sglb200_per_token_group_quant_fp8(None, 0, None, None, 0, 256, 128, 1e-10, -448.0, 448.0, 0, 2, 1, None) == 0
+    assert L.sglb200_fp8_blockwise_scaled_mm(None, None, None, None, None, 4, 128, 100, 100, 100, 128, 1, 4, 1, 1, 0, None) == -1
+    assert L.sglb200_fp8_blockwise_scaled_mm(None, None, None, None, None, 4, 128, 128, 128, 128, 128, 1, 4, 1, 1, 2, None) == -5
+    assert L.sglb200_fp8_blockwise_scaled_mm(None, None, None, None, None, 0, 128, 128, 128, 128, 128, 1, 4, 1, 1, 0, None) == 0
+    assert L.sglb200_shuffle_rows(None, None, None, 4, 6, None) == -1
+    assert L.sglb200_prepare_moe_input(None, None, None, None, None, None, 4, 2, 5000, 1, 1, None) == -1
+    with pytest.raises(RuntimeError, match="bad shape"):
+        check(-1, "op")
+
+
+def test_ops_refuse_cpu_tensors(built_lib):
+    from sglang_b200.sgl_kernel import fp8_blockwise_scaled_mm, silu_and_mul
+    a = torch.zeros(4, 128, dtype=torch.float8_e4m3fn)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        fp8_blockwise_scaled_mm(a, a.t(), torch.ones(4, 1), torch.ones(1, 1), torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        silu_and_mul(torch.zeros(4, 16, dtype=torch.bfloat16))
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    import sglang_b200._lib as L
+    monkeypatch.setattr(L, "_lib", None)
+    monkeypatch.setattr(L, "LIB_PATH", "/nonexistent/libsglb200.so")
+    with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
+        L.lib()
+
+
+@pytest.mark.parametrize("fmt", ["bf16", "f16"])
+def test_fma_division_matches_ieee_on_a_sample(tmp_path, fmt):
+    """tests/csrc/check_quant_math.cpp with stride 97 (the full run, stride 1, takes ~15 s per format)."""
+    exe = str(tmp_path / "check_quant_math")
+    subprocess.check_call(["g++", "-O2", "-fopenmp", "-x", "c++", "-o", exe,
+                           os.path.join(ROOT, "tests", "csrc", "check_quant_math.cpp"),
+                           "-L/usr/lib/gcc/x86_64-linux-gnu/13", "-lgomp"])
+    out = subprocess.run([exe, fmt, "97"], capture_output=True, text=True)
+    assert out.returncode == 0, out.stdout
+    assert "code_mismatch=0" in out.stdout and "scale_mismatch=0" in out.stdout
+
+
+def test_linear_method_create_weights_checks():
+    from sglang_b200.layers.quantization import Fp8Config, Fp8LinearMethod
+    cfg = Fp8Config.from_config({"quant_method": "fp8", "activation_scheme": "dynamic", "weight_block_size": [128, 128]})
+    layer = torch.nn.Module()
+    Fp8LinearMethod(cfg, tp_size=1).create_weights(layer, 7168, [576], 7168, 576, torch.bfloat16)
+    assert layer.weight.shape == (576, 7168) and layer.weight.dtype == torch.float8_e4m3fn
+    assert layer.weight_scale_inv.shape == (5, 56) and layer.input_scale is None
+    with pytest.raises(ValueError, match="block_k"):
+        Fp8LinearMethod(cfg, tp_size=8).create_weights(torch.nn.Module(), 200, [512], 1600, 512, torch.bfloat16)
+    with pytest.raises(ValueError, match="block_n"):
+        Fp8LinearMethod(cfg, tp_size=1).create_weights(torch.nn.Module(), 1024, [192, 192], 1024, 384, torch.bfloat16)
+    with pytest.raises(ValueError):
+        Fp8Config(weight_block_size=[64, 64])
+    with pytest.raises(ValueError):
+        Fp8Config(activation_scheme="static")
+
+
+def test_scale_allocator_layouts():
+    from sglang_b200.layers.quantization import create_per_token_group_quant_fp8_output_scale as alloc
+    assert alloc((6, 640), "cpu", 128, False, False, False).stride() == (5, 1)
+    assert alloc((6, 640), "cpu", 128, True, False, False).stride() == (1, 6)
+    t = alloc((6, 640), "cpu", 128, True, True, False)
+    assert t.shape == (6, 5) and t.stride() == (1, 8)
+    u = alloc((6, 640), "cpu", 128, True, True, True)
+    assert u.dtype == torch.int32 and u.shape == (6, 2) and u.stride() == (1, 8)

@@ -1,0 +1,92 @@
+"""Tensor-parallel host logic on two CPU ranks (gloo): weight/scale sharding on block boundaries,
+local quantisation equal to the slice of the global one, and the row-parallel all-reduce.  The
+local GEMM is the CPU oracle here (test stand-in); on GPUs the layers call Fp8LinearMethod.apply."""
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _oracle_apply(layer, x, bias=None):
+    import oracle
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    q, s = oracle.per_token_group_quant_fp8(x2, 128)
+    y = oracle.w8a8_block_fp8_matmul(q, layer.weight.data, s, layer.weight_scale_inv.data)
+    if bias is not None:
+        y = y + bias
+    return y.reshape(*x.shape[:-1], layer.weight.shape[0])
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from sglang_b200.distributed import (ColumnParallelBlockFp8Linear, RowParallelBlockFp8Linear,
+                                             shard_block_fp8_weight)
+        g = torch.Generator().manual_seed(0)
+        M, H, I = 24, 512, 768
+        x = torch.randn(M, H, generator=g).bfloat16()
+        w_up, s_up = oracle.block_quant_weight(torch.randn(I, H, generator=g) * 0.05)
+        w_dn, s_dn = oracle.block_quant_weight(torch.randn(H, I, generator=g) * 0.05)
+        bias = torch.randn(H, generator=g).bfloat16()
+
+        up = ColumnParallelBlockFp8Linear(w_up, s_up, rank, world, apply_fn=_oracle_apply)
+        down = RowParallelBlockFp8Linear(w_dn, s_dn, rank, world, bias=bias, apply_fn=_oracle_apply)
+        assert up.weight.shape == (I // world, H) and up.weight_scale_inv.shape == (I // 128 // world, H // 128)
+        assert down.weight.shape == (H, I // world) and down.weight_scale_inv.shape == (H // 128, I // 128 // world)
+
+        h_local = up(x)                      # [M, I / world]
+        y = down(h_local)                    # all-reduced [M, H]
+
+        # single-rank reference of the same two layers
+        class L:  # noqa: D401
+            pass
+        ref_up, ref_dn = L(), L()
+        ref_up.weight, ref_up.weight_scale_inv = torch.nn.Parameter(w_up, False), torch.nn.Parameter(s_up, False)
+        ref_dn.weight, ref_dn.weight_scale_inv = torch.nn.Parameter(w_dn, False), torch.nn.Parameter(s_dn, False)
+        h_ref = _oracle_apply(ref_up, x)
+        per = I // world
+        assert torch.equal(h_local, h_ref[:, rank * per:(rank + 1) * per]), "column shard differs from the slice"
+        # local activation quantisation == slice of the global one (groups do not straddle ranks)
+        q_g, s_g = oracle.per_token_group_quant_fp8(h_ref.contiguous(), 128)
+        q_l, s_l = oracle.per_token_group_quant_fp8(h_local.contiguous(), 128)
+        assert torch.equal(q_l.view(torch.uint8), q_g[:, rank * per:(rank + 1) * per].view(torch.uint8))
+        assert torch.equal(s_l, s_g[:, rank * per // 128:(rank + 1) * per // 128])
+        y_ref = _oracle_apply(ref_dn, h_ref, bias)
+        rel = float((y.float() - y_ref.float()).norm() / y_ref.float().norm())
+        assert rel < 1e-2, rel   # partial sums are rounded to bf16 per rank before the reduction
+
+        gathered = ColumnParallelBlockFp8Linear(w_up, s_up, rank, world, gather_output=True, apply_fn=_oracle_apply)(x)
+        assert torch.equal(gathered, h_ref)
+        try:
+            shard_block_fp8_weight(w_up[:640], s_up[:5], rank, world, 0)   # 320 rows per rank: not a block multiple
+            raise AssertionError("bad split accepted")
+        except ValueError:
+            pass
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, f"{type(e).__name__}: {e}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_two_ranks_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
