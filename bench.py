@@ -54,15 +54,43 @@ def load_peaks():
 
 # --------------------------------------------------------------------------- clock sampling
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs: NVML from a
+    thread every 5 ms (read-only queries), or `nvidia-smi -lms 100` if NVML cannot be imported."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
-    def __init__(self, gpu_id: str):
-        self.gpu_id, self.rows, self.proc, self.thread = gpu_id, [], None, None
+    def __init__(self, gpu_uuid: str):
+        self.gpu_id, self.rows, self.proc, self.thread = gpu_uuid, [], None, None
+        self.clk, self.mx, self.reasons, self.stop_flag, self.nvml = [], None, set(), False, None
+
+    def _nvml_loop(self):
+        n, h = self.nvml
+        while not self.stop_flag:
+            try:
+                self.clk.append(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM))
+                r = n.nvmlDeviceGetCurrentClocksEventReasons(h)
+                for name, bit in self.REASONS:
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.005)
 
     def start(self):
+        try:
+            import pynvml as n
+            n.nvmlInit()
+            h = n.nvmlDeviceGetHandleByUUID(self.gpu_id)
+            self.mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
+            self.nvml = (n, h)
+            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
@@ -73,6 +101,11 @@ class ClockSampler:
         self.thread.start()
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            return {"sm_mhz": statistics.median(self.clk) if self.clk else None, "sm_max_mhz": self.mx,
+                    "reasons": sorted(self.reasons), "samples": len(self.clk), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -88,7 +121,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(clk) if clk else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(clk)}
+                "samples": len(clk), "source": "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -276,8 +309,13 @@ def main():
                                 "gemm_tflops": f / (statistics.median(t) * 1e-3) / 1e12}
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
+    # DRAM traffic per launch: algorithmic operand + output bytes x 1.05, the read+write / algorithmic ratio of the
+    # ncu capture in profiles/gemm_fp8_block_gemm_M2048_N7168_K16384.md (189.0 MB measured, 180.4 MB algorithmic)
+    alg_bytes = sum(L["n_loc"] * L["k_loc"] + M * L["k_loc"] + 2.0 * M * L["n_loc"] for L in layers) / len(layers)
     roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
-                "frac": achieved / fp8_peak, "traffic": None, "kernel": "fp8_block_gemm_kernel",
+                "frac": achieved / fp8_peak, "traffic": 1.05 * alg_bytes,
+                "traffic_note": "bytes per launch averaged over the layers; ncu ratio 1.05 on a smaller M scaled up",
+                "kernel": "fp8_block_gemm_kernel",
                 "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
                 "frac_of_nominal_fp8": achieved / 4500.0, "launches": args.steps * len(layers),
                 "avg_launch_ms": gemm_ms / (args.steps * len(layers))}

@@ -2,6 +2,7 @@
 ``srt/distributed`` this path touches): column/row sharding of block-quantised weights and the
 all-reduce after row-parallel layers, over ``torch.distributed`` (NCCL on GPUs)."""
 
+from .expert_parallel import ep_fused_experts, ep_owner_tables  # noqa: F401
 from .parallel_linear import (  # noqa: F401
     ColumnParallelBlockFp8Linear,
     RowParallelBlockFp8Linear,

@@ -71,16 +71,32 @@ def fused_experts_block_fp8(hidden_states: torch.Tensor, w1: torch.Tensor, w2: t
     then summed in fp32.
     """
     assert hidden_states.dim() == 2 and hidden_states.is_contiguous()
+    if hidden_states.size(0) == 0:
+        return torch.empty_like(hidden_states)
+    a_q, a_s = sglang_per_token_group_quant_fp8(hidden_states, 128)
+    return fused_experts_block_fp8_prequant(a_q, a_s, hidden_states.dtype, w1, w2, w1_scale, w2_scale, topk_weights,
+                                            topk_ids, routed_scaling_factor)
+
+
+def fused_experts_block_fp8_prequant(a_q: torch.Tensor, a_s: torch.Tensor, out_dtype: torch.dtype, w1: torch.Tensor,
+                                     w2: torch.Tensor, w1_scale: torch.Tensor, w2_scale: torch.Tensor,
+                                     topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                                     routed_scaling_factor: Optional[float] = None) -> torch.Tensor:
+    """The expert MLP on activations that are already quantised (``a_q [M, H]`` e4m3, ``a_s [M, H/128]`` fp32
+    row-major): the form an expert-parallel rank runs on the rows it received from the dispatch, which
+    travel as fp8 payload plus scales (``token_dispatcher/deepep.py:360-371``)."""
+    assert a_q.dim() == 2 and a_q.is_contiguous() and a_q.dtype == FP8
     assert w1.dtype == FP8 and w2.dtype == FP8 and w1.is_contiguous() and w2.is_contiguous()
-    M, H = hidden_states.shape
+    M, H = a_q.shape
     E, two_i, H1 = w1.shape
     I = two_i // 2
     assert H1 == H and w2.shape == (E, H, I), "weight shapes do not match"
     assert H % 128 == 0 and I % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
+    assert a_s.shape == (M, H // 128) and a_s.dtype == torch.float32 and a_s.is_contiguous()
     assert topk_weights.shape == topk_ids.shape and topk_ids.size(0) == M
     topk = topk_ids.size(1)
-    dev = hidden_states.device
-    out = torch.empty_like(hidden_states)
+    dev = a_q.device
+    out = torch.empty(M, H, dtype=out_dtype, device=dev)
     if M == 0:
         return out
     ids = topk_ids.to(torch.int32).contiguous()
@@ -92,16 +108,15 @@ def fused_experts_block_fp8(hidden_states: torch.Tensor, w1: torch.Tensor, w2: t
     c_map = torch.empty(rows, dtype=torch.int32, device=dev)
     prepare_moe_input(ids, expert_offsets, ps1, ps2, a_map, c_map, E, I, H)
 
-    a_q, a_s = sglang_per_token_group_quant_fp8(hidden_states, 128)
     rep_q = shuffle_rows(a_q, a_map, (rows, H))
     rep_s = shuffle_rows(a_s, a_map, (rows, H // 128))
-    c1 = torch.empty(rows, two_i, dtype=hidden_states.dtype, device=dev)
+    c1 = torch.empty(rows, two_i, dtype=out_dtype, device=dev)
     _grouped_mm(rep_q, rep_s, w1, w1_scale, c1, expert_offsets)
     q2, s2 = sglang_per_token_group_quant_fp8(c1, 128, fuse_silu_and_mul=True)
-    c2 = torch.empty(rows, H, dtype=hidden_states.dtype, device=dev)
+    c2 = torch.empty(rows, H, dtype=out_dtype, device=dev)
     _grouped_mm(q2, s2, w2, w2_scale, c2, expert_offsets)
     factors = topk_weights if routed_scaling_factor is None else topk_weights * routed_scaling_factor
-    apply_shuffle_mul_sum(c2, out, c_map, factors.to(hidden_states.dtype).reshape(-1), round_products=True)
+    apply_shuffle_mul_sum(c2, out, c_map, factors.to(out_dtype).reshape(-1).contiguous(), round_products=True)
     return out
 
 

@@ -1,0 +1,82 @@
+"""Two-GPU runs of the sharded paths (skipped on a single-GPU box): tensor-parallel column/row linear with the
+NCCL all-reduce, and expert-parallel MoE with all-to-all dispatch/combine, against the CPU oracle."""
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import oracle
+        from helpers import assert_gemm_close
+        from sglang_b200.distributed import (ColumnParallelBlockFp8Linear, RowParallelBlockFp8Linear,
+                                             ep_fused_experts)
+        g = torch.Generator().manual_seed(0)
+        # ---- tensor parallel MLP: column-parallel up, row-parallel down + all-reduce
+        M, H, I = 200, 1024, 1536
+        x = torch.randn(M, H, generator=g).bfloat16()
+        w_up, s_up = oracle.block_quant_weight(torch.randn(I, H, generator=g) * 0.05)
+        w_dn, s_dn = oracle.block_quant_weight(torch.randn(H, I, generator=g) * 0.05)
+        up = ColumnParallelBlockFp8Linear(w_up.cuda(), s_up.cuda(), rank, world)
+        down = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world)
+        y = down(up(x.cuda()))
+        torch.cuda.synchronize()
+        q1, a1 = oracle.per_token_group_quant_fp8(x, 128)
+        h = oracle.w8a8_block_fp8_matmul(q1, w_up, a1, s_up)
+        q2, a2 = oracle.per_token_group_quant_fp8(h.contiguous(), 128)
+        ref = oracle.w8a8_block_fp8_matmul(q2, w_dn, a2, s_dn)
+        assert_gemm_close(y, ref, "tp mlp")
+
+        # ---- expert parallel MoE
+        E, topk, Hm, Im = 16, 4, 512, 256
+        w1 = [oracle.block_quant_weight(torch.randn(2 * Im, Hm, generator=g) * 0.05) for _ in range(E)]
+        w2 = [oracle.block_quant_weight(torch.randn(Hm, Im, generator=g) * 0.05) for _ in range(E)]
+        w1q, w1s = torch.stack([w[0] for w in w1]), torch.stack([w[1] for w in w1])
+        w2q, w2s = torch.stack([w[0] for w in w2]), torch.stack([w[1] for w in w2])
+        Mr = [150, 90][rank]
+        gr = torch.Generator().manual_seed(50 + rank)
+        xm = torch.randn(Mr, Hm, generator=gr).bfloat16()
+        tw, ti = torch.topk(torch.softmax(torch.randn(Mr, E, generator=gr), -1), topk)
+        el = E // world
+        lo, hi = rank * el, (rank + 1) * el
+        out = ep_fused_experts(xm.cuda(), w1q[lo:hi].cuda(), w2q[lo:hi].cuda(), w1s[lo:hi].cuda(), w2s[lo:hi].cuda(),
+                               tw.cuda(), ti.cuda(), rank, world)
+        torch.cuda.synchronize()
+        refm = oracle.fused_experts_block_fp8(xm, w1q, w2q, w1s, w2s, tw, ti)
+        rel = float((out.cpu().float() - refm.float()).norm() / refm.float().norm())
+        assert rel <= 1e-2, f"ep moe rel-L2 {rel}"
+        from sglang_b200._lib import lib
+        assert lib().sglb200_read_device_status() == 0
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_and_ep_two_gpus():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33500 + os.getpid() % 2000
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
