@@ -104,6 +104,24 @@ int sglb200_fp8_blockwise_scaled_mm(const void* a, const void* b, const float* s
                                     int64_t sb_stride_k, int out_dtype, void* stream);
 
 /*
+ * G with split-K for small M.  When the output tiles alone cannot occupy the SMs (M <= 128 at most shapes) the kernel is
+ * bound by streaming the weights; cutting K into ranges that run on different SMs restores the bandwidth.  The ranges
+ * write fp32 partial sums to `workspace` ([splits, M, N] floats) and a second small kernel adds them in ascending
+ * split order and casts.  sglb200_fp8_blockwise_scaled_mm_workspace_bytes() returns the size this needs for a shape on
+ * the current device (0 = split-K would not be used); with workspace == NULL or a workspace that is too small the call
+ * is exactly sglb200_fp8_blockwise_scaled_mm.  The workspace is scratch: contents on entry are ignored, calls on the
+ * same stream may share it.  Replaces the per-call cudaMalloc'ed CUTLASS workspace of the reference
+ * (sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:162-163) and its stream-K path
+ * (sgl-kernel/csrc/cutlass_extensions/gemm/fp8_blockwise_gemm_sm90_dispatch.cuh:179-197).
+ */
+int64_t sglb200_fp8_blockwise_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int sglb200_fp8_blockwise_scaled_mm_ws(const void* a, const void* b, const float* sa, const float* sb, void* out,
+                                       int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                       int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                                       int64_t sb_stride_k, int out_dtype, void* workspace, int64_t workspace_bytes,
+                                       void* stream);
+
+/*
  * MG — grouped (per-expert) block-scaled FP8 GEMM over rows sorted by expert.
  * Replaces: fp8_blockwise_scaled_grouped_mm  sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810
  *           and its pointer-table helper sgl-kernel/csrc/moe/cutlass_moe_helper.cu:17-142

@@ -23,6 +23,8 @@ SIGNATURES = {
     "sglb200_per_token_group_quant_fp8": [_P, _I, _P, _P, _L, _L, _I, _F, _F, _F, _I, _L, _L, _P],
     "sglb200_silu_mul_group_quant_fp8": [_P, _I, _P, _P, _P, _L, _L, _I, _F, _F, _F, _I, _L, _L, _P],
     "sglb200_fp8_blockwise_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
+    "sglb200_fp8_blockwise_scaled_mm_ws": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _L, _P],
+    "sglb200_fp8_blockwise_scaled_mm_workspace_bytes": [_L, _L, _L],
     "sglb200_fp8_blockwise_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
                                                 _L, _L, _L, _I, _P],
     "sglb200_prepare_moe_input": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P],
@@ -34,7 +36,7 @@ SIGNATURES = {
     "sglb200_last_error_detail": [],
     "sglb200_version": [],
 }
-_RESTYPES = {"sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
+_RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
 
 _lib = None
 
@@ -61,6 +63,23 @@ def check(status: int, what: str) -> None:
         L = lib()
         raise RuntimeError(f"{what}: {L.sglb200_status_string(status).decode()} "
                            f"({L.sglb200_last_error_detail().decode()})")
+
+
+def blockwise_mm(a_ptr, b_ptr, sa_ptr, sb_ptr, out_ptr, M, N, K, lda, ldb, ldc, sa_m, sa_k, sb_n, sb_k, out_code, device,
+                 stream) -> None:
+    """One dense block-scaled GEMM launch; picks the split-K entry with a torch-allocated scratch buffer when the
+    library asks for one (small M), else the plain entry."""
+    import torch
+    L = lib()
+    ws_bytes = L.sglb200_fp8_blockwise_scaled_mm_workspace_bytes(M, N, K)
+    if ws_bytes > 0:
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=device)
+        check(L.sglb200_fp8_blockwise_scaled_mm_ws(a_ptr, b_ptr, sa_ptr, sb_ptr, out_ptr, M, N, K, lda, ldb, ldc, sa_m,
+                                                   sa_k, sb_n, sb_k, out_code, ws.data_ptr(), ws_bytes, stream),
+              "fp8_blockwise_scaled_mm (split-K)")
+    else:
+        check(L.sglb200_fp8_blockwise_scaled_mm(a_ptr, b_ptr, sa_ptr, sb_ptr, out_ptr, M, N, K, lda, ldb, ldc, sa_m,
+                                                sa_k, sb_n, sb_k, out_code, stream), "fp8_blockwise_scaled_mm")
 
 
 DTYPE_CODES = {"torch.bfloat16": 0, "torch.float16": 1, "torch.float32": 2}

@@ -62,6 +62,10 @@ struct GemmParams {
   int64_t sa_stride_m, sa_stride_k;
   int64_t sb_stride_e, sb_stride_n, sb_stride_k;
   int32_t out_dtype;
+  // split-K (dense only): k_splits > 1 cuts the k-blocks into ranges of kb_per_split; every (tile, split) writes
+  // its fp32 partial sums to partial[split][row][col] (row stride N) and a second kernel adds the splits up
+  float* partial;
+  int32_t k_splits, kb_per_split;
 };
 
 struct Tile {
@@ -69,6 +73,8 @@ struct Tile {
   int32_t row_end;  // one past the last row this tile may write
   int32_t n0;
   int32_t expert;
+  int32_t kb0, kb1;  // k-block range of this work item
+  int32_t split;
 };
 
 struct SharedCtl {
@@ -84,7 +90,17 @@ struct SharedCtl {
 template <bool GROUPED>
 __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int32_t* tile_start, int32_t t) {
   Tile tl;
+  tl.kb0 = 0;
+  tl.kb1 = p.k_tiles;
+  tl.split = 0;
   if constexpr (!GROUPED) {
+    if (p.k_splits > 1) {
+      const int32_t mn = p.m_tiles * p.n_tiles;
+      tl.split = t / mn;
+      t -= tl.split * mn;
+      tl.kb0 = tl.split * p.kb_per_split;
+      tl.kb1 = min(tl.kb0 + p.kb_per_split, p.k_tiles);
+    }
     const int32_t per_group = kGroupM * p.n_tiles;
     const int32_t gid = t / per_group;
     const int32_t first_m = gid * kGroupM;
@@ -217,7 +233,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
     }
   } else {
-    if (threadIdx.x == 0) ctl->total_tiles = p.m_tiles * p.n_tiles;
+    if (threadIdx.x == 0) ctl->total_tiles = p.m_tiles * p.n_tiles * p.k_splits;
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -243,7 +259,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       bool ok = true;
-      for (int32_t kb = 0; kb < p.k_tiles; ++kb, ++g) {
+      for (int32_t kb = tl.kb0; kb < tl.kb1; ++kb, ++g) {
         if ((g & (kIssuers - 1)) == (uint32_t)warp) {
           if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
             record_timeout(ctl, 1);
@@ -269,7 +285,12 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, g = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       bool ok = true;
-      for (int32_t kb = 0; kb < p.k_tiles; ++kb, ++g) {
+      int32_t kb_count = p.k_tiles;
+      if (p.k_splits > 1) {
+        const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+        kb_count = tl.kb1 - tl.kb0;
+      }
+      for (int32_t kb = 0; kb < kb_count; ++kb, ++g) {
         if ((g & (kIssuers - 1)) == me) {
           if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) {
             record_timeout(ctl, 2);
@@ -320,19 +341,19 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       float sa_ring[kScaleAhead], sb_ring[kScaleAhead];
 #pragma unroll
       for (int u = 0; u < kScaleAhead; ++u) {
-        const int32_t kc = min(u, p.k_tiles - 1);
+        const int32_t kc = min(tl.kb0 + u, tl.kb1 - 1);
         sa_ring[u] = __ldg(sa_row + (int64_t)kc * p.sa_stride_k);
         sb_ring[u] = __ldg(sb_blk + (int64_t)kc * p.sb_stride_k);
       }
       bool ok = true;
-      for (int32_t kb0 = 0; kb0 < p.k_tiles && ok; kb0 += kScaleAhead) {
+      for (int32_t kb0 = tl.kb0; kb0 < tl.kb1 && ok; kb0 += kScaleAhead) {
 #pragma unroll
         for (int u = 0; u < kScaleAhead; ++u) {
           const int32_t kb = kb0 + u;
-          if (kb >= p.k_tiles) break;
+          if (kb >= tl.kb1) break;
           const float scale = sa_ring[u] * sb_ring[u];
           {  // fetch the scales of k-block kb + kScaleAhead into the slot just consumed
-            const int32_t kn = min(kb + kScaleAhead, p.k_tiles - 1);
+            const int32_t kn = min(kb + kScaleAhead, tl.kb1 - 1);
             sa_ring[u] = __ldg(sa_row + (int64_t)kn * p.sa_stride_k);
             sb_ring[u] = __ldg(sb_blk + (int64_t)kn * p.sb_stride_k);
           }
@@ -361,7 +382,15 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       if (!ok || ctl->abort_flag) break;
       if (row < tl.row_end) {
         const int32_t n_first = tl.n0 + col0;
-        if (p.out_dtype == SGLB200_BF16) {
+        if (p.partial != nullptr) {
+          float* dst = p.partial + ((int64_t)tl.split * p.total_rows + row) * p.N + n_first;
+#pragma unroll
+          for (int c = 0; c < kEpiCols / 4; ++c) {
+            if (n_first + c * 4 < p.N)
+              *reinterpret_cast<float4*>(dst + c * 4) =
+                  make_float4(acc[2 * c].x, acc[2 * c].y, acc[2 * c + 1].x, acc[2 * c + 1].y);
+          }
+        } else if (p.out_dtype == SGLB200_BF16) {
           store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
         } else {
           store_row<__half>(acc, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
@@ -376,6 +405,34 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   if (warp == kIssuers) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// out[m, n] = cast(sum_s partial[s][m][n]); 8 columns per thread, splits added in ascending order
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int32_t M, int32_t N, int64_t ldc,
+                     int32_t splits) {
+  const int32_t vec_per_row = N / 8;
+  const int64_t total = (int64_t)M * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int32_t m = (int32_t)(i / vec_per_row);
+    const int32_t c = (int32_t)(i - (int64_t)m * vec_per_row) * 8;
+    float a[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] = 0.f;
+    for (int32_t sp = 0; sp < splits; ++sp) {
+      const float4* src = reinterpret_cast<const float4*>(partial + ((int64_t)sp * M + m) * N + c);
+      const float4 x = __ldcs(src), y = __ldcs(src + 1);
+      a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
+      a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+    }
+    uint4 u;
+    u.x = pack2<OutT>(a[0], a[1]);
+    u.y = pack2<OutT>(a[2], a[3]);
+    u.z = pack2<OutT>(a[4], a[5]);
+    u.w = pack2<OutT>(a[6], a[7]);
+    *reinterpret_cast<uint4*>(out + (int64_t)m * ldc + c) = u;
   }
 }
 
@@ -413,6 +470,19 @@ int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
   return SGLB200_OK;
 }
 
+// Number of k-splits for a dense problem: only when the output tiles alone cannot occupy the SMs (small M, where the
+// kernel streams the weights once and is HBM-bound), enough splits for about two work items per SM, each at least
+// four k-blocks deep.  Returns 1 when split-K does not apply.
+int splitk_choice(int64_t M, int64_t N, int64_t K, int sm_count) {
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const int64_t k_tiles = (K + BK - 1) / BK;
+  if (tiles * 2 > sm_count || k_tiles < 8) return 1;
+  int64_t splits = (2 * (int64_t)sm_count + tiles - 1) / tiles;
+  if (splits > k_tiles / 4) splits = k_tiles / 4;
+  if (splits > 32) splits = 32;
+  return splits < 2 ? 1 : (int)splits;
+}
+
 template <bool GROUPED>
 int set_smem_attr_once() {
   static bool done[64] = {false};
@@ -430,7 +500,8 @@ int set_smem_attr_once() {
 int gemm_common(const void* a, const void* b, const float* sa, const float* sb, void* out,
                 const int32_t* expert_offsets, const int32_t* problem_sizes, int64_t total_rows, int64_t num_experts, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
-                int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream) {
+                int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream,
+                float* workspace = nullptr, int64_t workspace_floats = 0) {
   const bool grouped = expert_offsets != nullptr;
   SGLB_REQUIRE(total_rows >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size",
                (long long)total_rows, (long long)N, (long long)K);
@@ -493,6 +564,17 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   p.sb_stride_n = sb_stride_n;
   p.sb_stride_k = sb_stride_k;
   p.out_dtype = out_dtype;
+  p.partial = nullptr;
+  p.k_splits = 1;
+  p.kb_per_split = p.k_tiles;
+  if (!grouped && workspace != nullptr) {
+    const int splits = splitk_choice(total_rows, N, K, di.sm_count);
+    if (splits > 1 && (int64_t)splits * total_rows * N <= workspace_floats) {
+      p.partial = workspace;
+      p.kb_per_split = (p.k_tiles + splits - 1) / splits;
+      p.k_splits = (p.k_tiles + p.kb_per_split - 1) / p.kb_per_split;
+    }
+  }
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (grouped) {
@@ -503,9 +585,22 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     fp8_block_gemm_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
   } else {
     if (int rc = set_smem_attr_once<false>()) return rc;
-    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
     fp8_block_gemm_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+    if (p.partial != nullptr) {
+      SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
+      const int64_t vecs = total_rows * (N / 8);
+      int rgrid = (int)((vecs + 255) / 256);
+      if (rgrid > di.sm_count * 8) rgrid = di.sm_count * 8;
+      if (out_dtype == SGLB200_BF16) {
+        splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(p.partial, static_cast<__nv_bfloat16*>(out),
+                                                                  (int32_t)total_rows, (int32_t)N, ldc, p.k_splits);
+      } else {
+        splitk_reduce_kernel<__half><<<rgrid, 256, 0, st>>>(p.partial, static_cast<__half*>(out), (int32_t)total_rows,
+                                                           (int32_t)N, ldc, p.k_splits);
+      }
+    }
   }
   SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
   return SGLB200_OK;
@@ -532,6 +627,28 @@ extern "C" int sglb200_fp8_blockwise_scaled_grouped_mm(const void* a, const void
   SGLB_REQUIRE(expert_offsets != nullptr, SGLB200_ERR_NULL, "expert_offsets must not be NULL");
   return sglb::gemm_common(a, b, sa, sb, out, expert_offsets, problem_sizes, total_rows, num_experts, N, K, lda, ldb, ldb_e, ldc,
                            sa_stride_m, sa_stride_k, sb_stride_e, sb_stride_n, sb_stride_k, out_dtype, stream);
+}
+
+extern "C" int64_t sglb200_fp8_blockwise_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  sglb::DeviceInfo di;
+  int sms = 148;
+  if (sglb::device_info(&di) == SGLB200_OK) sms = di.sm_count;
+  const int splits = sglb::splitk_choice(M, N, K, sms);
+  return splits > 1 ? (int64_t)splits * M * N * (int64_t)sizeof(float) : 0;
+}
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm_ws(const void* a, const void* b, const float* sa, const float* sb,
+                                                  void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                                  int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
+                                                  int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
+                                                  void* workspace, int64_t workspace_bytes, void* stream) {
+  SGLB_REQUIRE(workspace_bytes >= 0, SGLB200_ERR_WORKSPACE, "workspace_bytes=%lld", (long long)workspace_bytes);
+  SGLB_REQUIRE(workspace == nullptr || sglb::aligned(workspace, 16), SGLB200_ERR_ALIGN,
+               "workspace must be 16-byte aligned");
+  return sglb::gemm_common(a, b, sa, sb, out, nullptr, nullptr, M, 1, N, K, lda, ldb, 0, ldc, sa_stride_m, sa_stride_k,
+                           0, sb_stride_n, sb_stride_k, out_dtype, stream, static_cast<float*>(workspace),
+                           workspace ? workspace_bytes / (int64_t)sizeof(float) : 0);
 }
 
 // Reads (and clears) the device-side status word: 0, or the code of the first bounded wait that

@@ -9,7 +9,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from ...sgl_kernel import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_8bit
-from ..._lib import check, dtype_code, lib
+from ..._lib import blockwise_mm, dtype_code
 
 fp8_dtype = torch.float8_e4m3fn
 fp8_max = torch.finfo(fp8_dtype).max
@@ -94,8 +94,7 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
     if M == 0:
         return C
     with torch.cuda.device(A.device):
-        check(lib().sglb200_fp8_blockwise_scaled_mm(
-            A2.data_ptr(), B.data_ptr(), As2.data_ptr(), Bs.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
-            As2.stride(0), As2.stride(1), Bs.stride(0), Bs.stride(1), dtype_code(output_dtype),
-            torch.cuda.current_stream(A.device).cuda_stream), "w8a8_block_fp8_matmul")
+        blockwise_mm(A2.data_ptr(), B.data_ptr(), As2.data_ptr(), Bs.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
+                     As2.stride(0), As2.stride(1), Bs.stride(0), Bs.stride(1), dtype_code(output_dtype), A.device,
+                     torch.cuda.current_stream(A.device).cuda_stream)
     return C

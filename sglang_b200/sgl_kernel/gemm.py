@@ -6,7 +6,7 @@ from typing import Optional
 
 import torch
 
-from .._lib import check, dtype_code, lib
+from .._lib import blockwise_mm, check, dtype_code, lib
 
 FP8 = torch.float8_e4m3fn
 
@@ -57,11 +57,9 @@ def fp8_blockwise_scaled_mm(mat_a, mat_b, scales_a, scales_b, out_dtype):
     lda = mat_a.stride(0) if M > 1 else max(mat_a.stride(0), K)
     ldb = mat_b.stride(1) if N > 1 else max(mat_b.stride(1), K)
     with torch.cuda.device(mat_a.device):
-        check(lib().sglb200_fp8_blockwise_scaled_mm(
-            mat_a.data_ptr(), mat_b.data_ptr(), scales_a.data_ptr(), scales_b.data_ptr(), out.data_ptr(),
-            M, N, K, lda, ldb, out.stride(0),
-            scales_a.stride(0), scales_a.stride(1), scales_b.stride(1), scales_b.stride(0),
-            dtype_code(out_dtype), _stream(mat_a)), "fp8_blockwise_scaled_mm")
+        blockwise_mm(mat_a.data_ptr(), mat_b.data_ptr(), scales_a.data_ptr(), scales_b.data_ptr(), out.data_ptr(),
+                     M, N, K, lda, ldb, out.stride(0), scales_a.stride(0), scales_a.stride(1), scales_b.stride(1),
+                     scales_b.stride(0), dtype_code(out_dtype), mat_a.device, _stream(mat_a))
     return out
 
 

@@ -123,3 +123,18 @@ def test_linear_method_apply():
     ref = (oracle.w8a8_block_fp8_matmul(aq, wq, a_s, ws) + bias).view(3, 15, N)
     assert y.shape == (3, 15, N) and y.dtype == torch.bfloat16
     assert_gemm_close(y, ref, "linear apply")
+
+
+@pytest.mark.parametrize("M", [1, 16, 64, 128])
+@pytest.mark.parametrize("N,K", [(576, 7168), (7168, 2048), (1536, 4096)])
+def test_small_m_split_k(M, N, K):
+    """Small M: the split-K path (fp32 partial sums in a scratch buffer + reduce) against the oracle."""
+    from sglang_b200._lib import lib
+    a = make_activations(M, K, seed=M * 3 + N)
+    aq, a_s = oracle.per_token_group_quant_fp8(a, 128)
+    wq, ws = make_weight(N, K, seed=N + K)
+    ref = oracle.w8a8_block_fp8_matmul(aq, wq, a_s, ws)
+    assert lib().sglb200_fp8_blockwise_scaled_mm_workspace_bytes(M, N, K) > 0, "expected split-K for this shape"
+    out = _run(aq, a_s, wq, ws, m_major=True)
+    assert_gemm_close(out, ref, f"split-K M={M} N={N} K={K}")
+    assert lib().sglb200_fp8_blockwise_scaled_mm_workspace_bytes(4096, N, K) == 0
