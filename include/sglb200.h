@@ -122,6 +122,29 @@ int sglb200_fp8_blockwise_scaled_mm_ws(const void* a, const void* b, const float
                                        void* stream);
 
 /*
+ * G with split-K for callers that cannot allocate.  No counterpart in the reference.
+ *
+ * Same arguments and result as sglb200_fp8_blockwise_scaled_mm, same split-K decision as the _ws entry, but the
+ * scratch is a fixed 16 MiB device array inside the library image (sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes()),
+ * so this call never touches cudaMalloc, cudaFree or any allocating routine.  It exists for hosts that must not
+ * allocate where they run the GEMM: an engine that gave all device memory to its own pool, a region in which
+ * allocation is forbidden, a C caller without an allocator.
+ *   - Shapes whose split-K scratch (sglb200_fp8_blockwise_scaled_mm_workspace_bytes) exceeds the built-in buffer are
+ *     REJECTED with SGLB200_ERR_WORKSPACE (nothing is launched); shapes that do not use split-K run as usual.
+ *   - The first call on each device looks the array's device address up (cudaGetSymbolAddress, that device current);
+ *     make that first call outside any stream capture.
+ *   - Every call on a device shares the one array, which keeps whatever the previous call left in it.  The kernels
+ *     overwrite every element they later read, so nothing needs clearing, but two calls that overlap on the GPU
+ *     (different streams, no dependency between them) race on it: serialise them.
+ *   - Every GPU that loads the library holds the 16 MiB until the process exits.
+ */
+int64_t sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes(void);
+int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void* b, const float* sa, const float* sb, void* out,
+                                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                            int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                                            int64_t sb_stride_k, int out_dtype, void* stream);
+
+/*
  * MG — grouped (per-expert) block-scaled FP8 GEMM over rows sorted by expert.
  * Replaces: fp8_blockwise_scaled_grouped_mm  sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810
  *           and its pointer-table helper sgl-kernel/csrc/moe/cutlass_moe_helper.cu:17-142

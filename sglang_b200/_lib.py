@@ -25,6 +25,8 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
     "sglb200_fp8_blockwise_scaled_mm_ws": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _L, _P],
     "sglb200_fp8_blockwise_scaled_mm_workspace_bytes": [_L, _L, _L],
+    "sglb200_fp8_blockwise_scaled_mm_noalloc": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
+    "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": [],
     "sglb200_fp8_blockwise_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
                                                 _L, _L, _L, _I, _P],
     "sglb200_prepare_moe_input": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P],
@@ -36,7 +38,8 @@ SIGNATURES = {
     "sglb200_last_error_detail": [],
     "sglb200_version": [],
 }
-_RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
+_RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64,
+             "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
 
 _lib = None
 

@@ -651,6 +651,69 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_ws(const void* a, const void* b, 
                            workspace ? workspace_bytes / (int64_t)sizeof(float) : 0);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Split-K GEMM for callers that cannot allocate device memory.
+//
+// Some hosts of this library may not call cudaMalloc or any allocating routine at the point where they run a
+// GEMM: an engine that has handed all device memory to its own pool and forbids side allocations, code running
+// inside a region where allocation is disallowed, or a plain C caller with no allocator at hand.  For them the
+// split-K scratch lives in the library image itself: a file-scope device array of fixed size that every GPU
+// loading the library holds until the process exits.
+// ---------------------------------------------------------------------------------------------------------
+namespace sglb {
+namespace {
+constexpr int64_t kStaticWsFloats = 4ll * 1024 * 1024;  // 16 MiB: splits * M * N fp32 partial sums
+static __device__ __align__(256) float g_static_splitk_ws[kStaticWsFloats];
+
+// In host code the array's name is only a handle; the device address has to be asked for, once per device,
+// with that device current.
+int static_ws_address(float** out) {
+  static float* addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(SGLB200_ERR_LAUNCH, "cudaGetDevice failed");
+  }
+  if (addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_splitk_ws);
+    if (e != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return fail(SGLB200_ERR_LAUNCH, "cudaGetSymbolAddress(static split-K scratch): %s", cudaGetErrorString(e));
+    }
+    addr[dev] = static_cast<float*>(ptr);
+  }
+  *out = addr[dev];
+  return SGLB200_OK;
+}
+}  // namespace
+}  // namespace sglb
+
+extern "C" int64_t sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes(void) {
+  return sglb::kStaticWsFloats * (int64_t)sizeof(float);
+}
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void* b, const float* sa, const float* sb,
+                                                       void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                                       int64_t ldb, int64_t ldc, int64_t sa_stride_m,
+                                                       int64_t sa_stride_k, int64_t sb_stride_n, int64_t sb_stride_k,
+                                                       int out_dtype, void* stream) {
+  const int64_t need = sglb200_fp8_blockwise_scaled_mm_workspace_bytes(M, N, K);
+  if (need > sglb::kStaticWsFloats * (int64_t)sizeof(float)) {
+    return sglb::fail(SGLB200_ERR_WORKSPACE,
+                      "M=%lld N=%lld K=%lld needs %lld bytes of split-K scratch; the built-in buffer holds %lld "
+                      "(use sglb200_fp8_blockwise_scaled_mm_ws with your own buffer, or sglb200_fp8_blockwise_scaled_mm)",
+                      (long long)M, (long long)N, (long long)K, (long long)need,
+                      (long long)(sglb::kStaticWsFloats * (int64_t)sizeof(float)));
+  }
+  float* ws = nullptr;
+  if (need > 0) {
+    if (int rc = sglb::static_ws_address(&ws)) return rc;
+  }
+  return sglb::gemm_common(a, b, sa, sb, out, nullptr, nullptr, M, 1, N, K, lda, ldb, 0, ldc, sa_stride_m, sa_stride_k,
+                           0, sb_stride_n, sb_stride_k, out_dtype, stream, ws, ws ? sglb::kStaticWsFloats : 0);
+}
+
 // Reads (and clears) the device-side status word: 0, or the code of the first bounded wait that
 // timed out (1 producer, 2/3 MMA issuer, 4 promotion warps).  Synchronises the device: for tests
 // and debugging, not for the serving path.
