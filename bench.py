@@ -169,6 +169,42 @@ def cpu_arm(steps: int, warmup: int, m_sample: int):
             "ms_per_pass": dt * 1e3}
 
 
+def moe_section(torch, dev, gen, M=4096, E=256, topk=8, H=7168, I=2048):
+    """Block-FP8 fused MoE, DeepSeek-V3 layer shape: 256 experts, top-8 of softmax(random logits), hidden 7168,
+    moe_intermediate 2048, M tokens; random e4m3 expert weights (11.3 GB) with random block scales."""
+    from sglang_b200.layers.moe import fused_experts_block_fp8
+
+    def rand_fp8(*shape):
+        t = torch.empty(shape, device=dev, dtype=torch.float8_e4m3fn)
+        flat = t.view(-1)
+        for i in range(0, flat.numel(), 1 << 28):
+            n = min(1 << 28, flat.numel() - i)
+            flat[i:i + n] = (torch.randn(n, device=dev, generator=gen) * 20).to(torch.float8_e4m3fn)
+        return t
+
+    w1, w2 = rand_fp8(E, 2 * I, H), rand_fp8(E, H, I)
+    w1s = torch.rand(E, 2 * I // 128, H // 128, device=dev, generator=gen) * 1e-3
+    w2s = torch.rand(E, H // 128, I // 128, device=dev, generator=gen) * 1e-3
+    a = torch.randn(M, H, device=dev, generator=gen).bfloat16()
+    tw, ti = torch.topk(torch.softmax(torch.randn(M, E, device=dev, generator=gen), -1), topk)
+    ti = ti.to(torch.int32)
+    for _ in range(3):
+        fused_experts_block_fp8(a, w1, w2, w1s, w2s, tw, ti)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 5
+    e0.record()
+    for _ in range(n):
+        fused_experts_block_fp8(a, w1, w2, w1s, w2s, tw, ti)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    flops = M * topk * (2.0 * H * 2 * I + 2.0 * I * H)
+    return {"workload": f"fused_experts block-FP8 E={E} top{topk} H={H} I={I} M={M}", "ms": ms,
+            "tflops": flops / (ms * 1e-3) / 1e12, "weight_bytes": w1.numel() + w2.numel(),
+            "kernels_per_call": 9}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -178,6 +214,7 @@ def main():
     ap.add_argument("--m", type=int, default=8192, help="tokens per step")
     ap.add_argument("--cpu-m", type=int, default=1024, help="rows of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE section (11.3 GB of expert weights)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "quant"],
                     help="profiling aid: run only the linear sweep ('gemm') or only the quant bandwidth case")
     ap.add_argument("--shape", default=None, help="profiling aid: restrict the sweep to one layer name")
@@ -353,6 +390,15 @@ def main():
             dist.destroy_process_group()
         return
 
+    # ---- fused MoE at the DeepSeek-V3 layer shape (BASELINE config 5), reported beside the headline
+    moe = None
+    if rank == 0 and world == 1 and not args.no_moe:
+        try:
+            moe = moe_section(torch, dev, gen)
+        except Exception as e:  # noqa: BLE001 - the headline must not depend on this section
+            moe = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
+
     # ---- end to end through the public API from pinned host memory
     host_x = [L["x"].cpu().pin_memory() for L in layers]
     host_y = [torch.empty(M, L["n_loc"], dtype=torch.bfloat16).pin_memory() for L in layers]
@@ -393,7 +439,7 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks,
                 "e2e": e2e, "gpu_launches": args.steps * len(layers) * 2, "roofline": roofline,
-                "cpu_baseline": cpu_baseline, "quant": quant, "per_shape": per_shape, "impl": "ours"}
+                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "impl": "ours"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
