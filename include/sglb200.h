@@ -145,6 +145,25 @@ int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void* b, const 
                                             int64_t sb_stride_k, int out_dtype, void* stream);
 
 /*
+ * G with power-of-two (UE8M0) scales, scaled by the tensor core itself (tcgen05.mma kind::mxf8f6f4.block_scale):
+ *   out[m, n] = cast( sum_k a[m,k] * 2^ea[m, k/128] * b[n,k] * 2^eb[n/128, k/128] ),  fp32 accumulation over all of K.
+ * Replaces: the reference's Blackwell route through DeepGEMM with UE8M0 scales, w8a8_block_fp8_matmul_deepgemm /
+ *           deep_gemm.fp8_gemm_nt (python/sglang/srt/layers/quantization/fp8_kernel.py:1047-1065,
+ *           deep_gemm_wrapper/entrypoint.py:68-112, configurer.py:24-25; weights requantised by
+ *           fp8_utils.py:416-512).
+ * a [M, K], b [N, K] e4m3 as for sglb200_fp8_blockwise_scaled_mm.
+ * sfa  packed exponents of the activation scales exactly as the quantiser writes them with scale_ue8m0 != 0:
+ *      int32 word (m, kg) at sfa[kg * sfa_ld + m], byte j = biased exponent of k-block 4*kg + j.
+ * sfb  packed exponents of the weight scales: int32 word (nb, kg) at sfb[nb * sfb_stride_n + kg * sfb_stride_k],
+ *      nb = n / 128, same byte order.
+ * Exact for power-of-two scales (the same products and an fp32 sum); scales that are not powers of two cannot be
+ * expressed and must use sglb200_fp8_blockwise_scaled_mm.
+ */
+int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb, void* out,
+                                int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sfa_ld,
+                                int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream);
+
+/*
  * MG — grouped (per-expert) block-scaled FP8 GEMM over rows sorted by expert.
  * Replaces: fp8_blockwise_scaled_grouped_mm  sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810
  *           and its pointer-table helper sgl-kernel/csrc/moe/cutlass_moe_helper.cu:17-142

@@ -97,7 +97,7 @@ def pack_scales(s: torch.Tensor, layout: str) -> torch.Tensor:
 # --------------------------------------------------------------------------------------
 # W: 128x128 block quantisation of weights (offline)
 # --------------------------------------------------------------------------------------
-def block_quant_weight(w: torch.Tensor, block=(128, 128)):
+def block_quant_weight(w: torch.Tensor, block=(128, 128), scale_ue8m0: bool = False):
     """Block-quantise ``w [N, K]`` to e4m3 with fp32 scales ``[ceil(N/bn), ceil(K/bk)]``.
 
     scale = block amax / 448 (1.0 for an all-zero block), code = RNE_e4m3(w / scale), as
@@ -112,6 +112,8 @@ def block_quant_weight(w: torch.Tensor, block=(128, 128)):
     v = wp.view(Np // bn, bn, Kp // bk, bk)
     s = v.abs().amax(dim=(1, 3), keepdim=True) / FP8_MAX
     s = torch.where(s == 0, torch.ones_like(s), s)
+    if scale_ue8m0:  # power-of-two block scales, as the reference requantises weights for Blackwell (fp8_utils.py:494-512)
+        s = ceil_to_ue8m0(s)
     q = (v / s).clamp(-FP8_MAX, FP8_MAX).to(FP8).view(Np, Kp)[:N, :K].contiguous()
     return q, s.view(Np // bn, Kp // bk).contiguous()
 

@@ -277,6 +277,15 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
       if (!ok || ctl->abort_flag) break;
     }
+    // Tail: tcgen05.commit arrives on the `empty` barriers asynchronously and nobody waits for the last ones, so the
+    // CTA could exit (and the next kernel's CTA re-initialise barriers at the same shared-memory addresses) while
+    // such an arrival is still in flight.  Acquire every stage once more before leaving.
+    if (warp == 0 && !ctl->abort_flag) {
+      for (int i = 0; i < kStages; ++i) {
+        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { record_timeout(ctl, 5); break; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
   } else if (warp < 2 * kIssuers) {
     // ===== MMA issuers (k-blocks alternate between the two warps; each k-block has its own TMEM stage)
     const uint32_t me = warp - kIssuers;
@@ -717,7 +726,12 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void
 // Reads (and clears) the device-side status word: 0, or the code of the first bounded wait that
 // timed out (1 producer, 2/3 MMA issuer, 4 promotion warps).  Synchronises the device: for tests
 // and debugging, not for the serving path.
+namespace sglb {
+int ue8m0_take_device_status();  // gemm_ue8m0.cu
+}
 extern "C" int sglb200_read_device_status(void) {
+  const int u = sglb::ue8m0_take_device_status();
+  if (u != 0) return u;
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, sglb::g_device_status, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();

@@ -1,0 +1,482 @@
+// Block-scaled FP8 GEMM with POWER-OF-TWO (UE8M0) scales, using the tensor core's own block scaling.
+//
+//   out[m, n] = cast( sum_k a[m,k] * 2^ea[m, k/128] * b[n,k] * 2^eb[n/128, k/128] )
+//
+// With power-of-two scales the scaling can be applied by tcgen05.mma kind::mxf8f6f4.block_scale itself (one UE8M0
+// factor per row per 32 elements of K, exact), so the whole K loop accumulates in TMEM like an ordinary GEMM and
+// there is no per-k-block promotion through registers, which is what bounds the fp32-scale kernel in gemm.cu.
+// This is the arrangement the reference uses on Blackwell through DeepGEMM (UE8M0 activation scales from the
+// quantiser, weights requantised to UE8M0: python/sglang/srt/layers/quantization/fp8_utils.py:416-512,
+// deep_gemm_wrapper/configurer.py:24-25).
+//
+// One CTA per SM, 416 threads:
+//   warps 0-1   TMA producers (k-blocks alternate): A tile 128 x 128 B and B tile 192 x 128 B into a 5-stage ring.
+//   warps 2-3   MMA issuers (k-blocks of a tile alternate; issuing an MMA blocks the thread for its duration, so two
+//               issuers keep the pipe fed while the other one handles its barriers).  Each issuer accumulates its
+//               k-blocks in its OWN 192-column TMEM accumulator, so no ordering between the two is needed; the
+//               epilogue adds the two.  Before the first k-block of every group of four, an issuer copies that
+//               group's scale words from shared memory into its own TMEM scale columns (tcgen05.cp).
+//   warp 4      scale loader: per tile and per group of four k-blocks, 128 packed scale words of A (one int32 holds the
+//               four exponent bytes of a row, the layout the quantiser writes) and 192 of B, written to shared memory
+//               in the 32 x 16 B arrangement tcgen05.cp.32x128b.warpx4 expects (lane l: rows l, l+32, l+64, l+96).
+//               The k-block inside the group picks the byte through the instruction descriptor's scale ids.
+//   warps 5-12  epilogue: after the last k-block, D0 + D1 -> bf16/f16 rows.
+// Every mbarrier wait is bounded; on time-out the CTA records a code in g_device_status and winds down.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace sglb {
+
+// status word of this kernel's bounded waits (device variables are private to a translation unit; the public
+// reader in gemm.cu collects this one through ue8m0_take_device_status)
+__device__ int g_ue8m0_status = 0;
+// Optional mirror of the status word in host-mapped memory (survives a lost context); set by the debug hook below.
+__device__ volatile int* g_ue8m0_mirror = nullptr;
+int ue8m0_take_device_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_ue8m0_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (v != 0) {
+    int z = 0;
+    cudaMemcpyToSymbol(g_ue8m0_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+namespace {
+
+constexpr int BM = 128, BN = 192, BK = 128;
+constexpr int kStages = 5;
+constexpr int kSfBufs = 4;
+constexpr int kThreads = 13 * 32;
+constexpr int kEpiWarp0 = 5, kEpiWarps = 8;
+constexpr int kEpiCols = BN / 2;  // 96 columns per epilogue warp
+constexpr uint32_t kTileABytes = BM * BK, kTileBBytes = BN * BK, kStageBytes = kTileABytes + kTileBBytes;
+constexpr uint32_t kSfABytes = 512, kSfBBytes = 1024, kSfBufBytes = kSfABytes + kSfBBytes;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kSfTmemBase = 2 * BN;  // 384: scale columns start after the two accumulators
+constexpr uint32_t kSfTmemPerSet = 12;    // 4 columns for A's scales + 8 for B's (192 rows -> two copies of 128)
+constexpr int kGroupM = 16;
+constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + (size_t)kSfBufs * kSfBufBytes + 256;
+
+struct Params {
+  const int32_t* sfa;  // packed exponents of A: word (m, kg) at sfa[kg * sfa_ld + m]
+  const int32_t* sfb;  // packed exponents of B: word (nb, kg) at sfb[nb * sfb_stride_n + kg * sfb_stride_k]
+  void* out;
+  int32_t M, N, K;
+  int32_t m_tiles, n_tiles, k_tiles, k_groups;
+  int64_t ldc, sfa_ld, sfb_stride_n, sfb_stride_k;
+  int32_t out_dtype;
+};
+
+struct Ctl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t sf_full[kSfBufs];
+  uint64_t sf_empty[kSfBufs];
+  uint64_t acc_full;
+  uint64_t acc_empty;
+  uint32_t tmem_base;
+  volatile int32_t abort_flag;
+};
+
+__device__ __forceinline__ void tile_coords(const Params& p, int32_t t, int32_t& m0, int32_t& n0) {
+  const int32_t per_group = kGroupM * p.n_tiles;
+  const int32_t gid = t / per_group;
+  const int32_t first_m = gid * kGroupM;
+  const int32_t gm = min(p.m_tiles - first_m, kGroupM);
+  const int32_t local = t - gid * per_group;
+  const int32_t nt = local / gm;
+  m0 = (first_m + (local - nt * gm)) * BM;
+  n0 = nt * BN;
+}
+
+__device__ __forceinline__ void timeout(Ctl* ctl, int code) {
+  ctl->abort_flag = 1;
+  atomicCAS(&g_ue8m0_status, 0, code);
+  if (g_ue8m0_mirror != nullptr) {
+    g_ue8m0_mirror[0] = code;
+    g_ue8m0_mirror[1] = (int)blockIdx.x;
+    __threadfence_system();
+  }
+}
+
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack_pair(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store32(const uint32_t (&a)[32], const uint32_t (&b)[32], bool use_b, OutT* dst,
+                                        int32_t n_first, int32_t N) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    if (n_first + c * 8 < N) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = __uint_as_float(a[c * 8 + j]) + (use_b ? __uint_as_float(b[c * 8 + j]) : 0.f);
+      uint4 u;
+      u.x = pack_pair<OutT>(v[0], v[1]);
+      u.y = pack_pair<OutT>(v[2], v[3]);
+      u.z = pack_pair<OutT>(v[4], v[5]);
+      u.w = pack_pair<OutT>(v[6], v[7]);
+      *reinterpret_cast<uint4*>(dst + c * 8) = u;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                      const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
+  Ctl* ctl = reinterpret_cast<Ctl*>(sf_smem + (size_t)kSfBufs * kSfBufBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&ctl->full[i], 1);
+      ptx::mbar_init(&ctl->empty[i], 1);
+    }
+    for (int i = 0; i < kSfBufs; ++i) {
+      ptx::mbar_init(&ctl->sf_full[i], 1);
+      ptx::mbar_init(&ctl->sf_empty[i], 2);  // both issuers copy the block into their own TMEM columns
+    }
+    ptx::mbar_init(&ctl->acc_full, 2);  // one commit per issuer
+    ptx::mbar_init(&ctl->acc_empty, kEpiWarps);
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int32_t total_tiles = p.m_tiles * p.n_tiles;
+
+  const uint32_t full0 = ptx::smem_u32(&ctl->full[0]);
+  const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t sf_full0 = ptx::smem_u32(&ctl->sf_full[0]);
+  const uint32_t sf_empty0 = ptx::smem_u32(&ctl->sf_empty[0]);
+  const uint32_t acc_full = ptx::smem_u32(&ctl->acc_full);
+  const uint32_t acc_empty = ptx::smem_u32(&ctl->acc_empty);
+  const uint32_t stage0 = ptx::smem_u32(smem);
+  const uint32_t sf0 = ptx::smem_u32(sf_smem);
+
+  if (warp < 2) {
+    // ===== TMA producers
+    uint32_t stage = 0, phase = 0, g = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      int32_t m0, n0;
+      tile_coords(p, t, m0, n0);
+      bool ok = true;
+      for (int32_t kb = 0; kb < p.k_tiles; ++kb, ++g) {
+        if ((g & 1) == (uint32_t)warp) {
+          if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
+            timeout(ctl, 11);
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            const uint32_t dst = stage0 + stage * kStageBytes;
+            ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
+            ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, m0);
+            ptx::tma_load_2d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, n0);
+          }
+        }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+      if (!ok || ctl->abort_flag) break;
+    }
+    // Tail: tcgen05.commit arrives on the `empty` barriers asynchronously.  Nobody waits for the last ones, so
+    // without this the CTA could exit (and the next kernel's CTA re-initialise barriers at the same shared-memory
+    // addresses) while such an arrival is still in flight.  Acquire every stage once more before leaving.
+    if (warp == 0 && !ctl->abort_flag) {
+      for (int i = 0; i < kStages; ++i) {
+        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { timeout(ctl, 17); break; }
+        if (++stage == kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp < 4) {
+    // ===== MMA issuers: issuer w takes the k-blocks kb with kb % 2 == w of every tile into accumulator w
+    const uint32_t w = warp - 2;
+    const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
+    const uint32_t d_tmem = tmem_base + w * BN;
+    uint32_t stage = 0, phase = 0, q = 0, tile_i = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_i) {
+      bool ok = ptx::mbar_wait_a(acc_empty, (tile_i & 1) ^ 1);
+      if (!ok) timeout(ctl, 12);
+      for (int32_t kg = 0; kg < p.k_groups && ok; ++kg, ++q) {
+        const uint32_t buf = q % kSfBufs;
+        if (!ptx::mbar_wait_a(sf_full0 + buf * 8, (q / kSfBufs) & 1)) {
+          timeout(ctl, 13);
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t sf_col = tmem_base + kSfTmemBase + (w * 2 + (q & 1)) * kSfTmemPerSet;
+        if (lane == 0) {
+          const uint32_t src = sf0 + buf * kSfBufBytes;
+          ptx::tmem_cp_32x128b_warpx4(sf_col, ptx::make_sf_desc(src));
+          ptx::tmem_cp_32x128b_warpx4(sf_col + 4, ptx::make_sf_desc(src + kSfABytes));
+          ptx::tmem_cp_32x128b_warpx4(sf_col + 8, ptx::make_sf_desc(src + kSfABytes + 512));
+          ptx::mma_commit_a(sf_empty0 + buf * 8);
+        }
+        const int32_t kb_end = min(kg * 4 + 4, p.k_tiles);
+        for (int32_t kb = kg * 4; kb < kb_end; ++kb) {
+          if ((uint32_t)(kb & 1) == w) {
+            if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
+              timeout(ctl, 14);
+              ok = false;
+              break;
+            }
+            ptx::tc_fence_after();
+            if (lane == 0) {
+              const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
+              const uint64_t b_desc = a_desc + (kTileABytes >> 4);
+              const uint32_t idesc = ptx::make_idesc_mxf8(BM, BN, (uint32_t)(kb & 3));
+              ptx::mma_mxf8_block_scaled(d_tmem, a_desc, b_desc, idesc, sf_col, sf_col + 4, kb >= 2 ? 1u : 0u);
+#pragma unroll
+              for (uint32_t k = 1; k < BK / 32; ++k)
+                ptx::mma_mxf8_block_scaled(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sf_col, sf_col + 4, 1u);
+              ptx::mma_commit_a(empty0 + stage * 8);
+            }
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok || ctl->abort_flag) break;
+      // this issuer's share of the tile is in flight: publish it when it is done (an issuer without any k-block,
+      // which happens only when the tile has a single k-block, still has to arrive)
+      if (lane == 0) {
+        if (p.k_tiles > (int32_t)w) ptx::mma_commit_a(acc_full); else ptx::mbar_arrive_a(acc_full);
+      }
+    }
+  } else if (warp == 4) {
+    // ===== scale loader
+    const int32_t nb_last = (p.N + 127) / 128 - 1;
+    uint32_t q = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      int32_t m0, n0;
+      tile_coords(p, t, m0, n0);
+      bool ok = true;
+      for (int32_t kg = 0; kg < p.k_groups; ++kg, ++q) {
+        const uint32_t buf = q % kSfBufs;
+        if (!ptx::mbar_wait_a(sf_empty0 + buf * 8, ((q / kSfBufs) & 1) ^ 1)) {
+          timeout(ctl, 15);
+          ok = false;
+          break;
+        }
+        uint8_t* dst = sf_smem + (size_t)buf * kSfBufBytes;
+        const int32_t* a_col = p.sfa + (int64_t)kg * p.sfa_ld;
+        uint4 va;
+        va.x = (uint32_t)__ldg(a_col + min(m0 + lane, p.M - 1));
+        va.y = (uint32_t)__ldg(a_col + min(m0 + 32 + lane, p.M - 1));
+        va.z = (uint32_t)__ldg(a_col + min(m0 + 64 + lane, p.M - 1));
+        va.w = (uint32_t)__ldg(a_col + min(m0 + 96 + lane, p.M - 1));
+        reinterpret_cast<uint4*>(dst)[lane] = va;
+        const int32_t* b_col = p.sfb + (int64_t)kg * p.sfb_stride_k;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint4 vb;
+          vb.x = (uint32_t)__ldg(b_col + (int64_t)min((n0 + j * 128 + lane) / 128, nb_last) * p.sfb_stride_n);
+          vb.y = (uint32_t)__ldg(b_col + (int64_t)min((n0 + j * 128 + 32 + lane) / 128, nb_last) * p.sfb_stride_n);
+          vb.z = (uint32_t)__ldg(b_col + (int64_t)min((n0 + j * 128 + 64 + lane) / 128, nb_last) * p.sfb_stride_n);
+          vb.w = (uint32_t)__ldg(b_col + (int64_t)min((n0 + j * 128 + 96 + lane) / 128, nb_last) * p.sfb_stride_n);
+          reinterpret_cast<uint4*>(dst + kSfABytes + j * 512)[lane] = vb;
+        }
+        ptx::fence_proxy_async();  // the tensor core reads this block through the async proxy
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_a(sf_full0 + buf * 8);
+      }
+      if (!ok || ctl->abort_flag) break;
+    }
+    // Tail, as for the producers: wait until both issuers' commits on every scale buffer have arrived.
+    if (!ctl->abort_flag) {
+      for (int i = 0; i < kSfBufs; ++i, ++q) {
+        if (!ptx::mbar_wait_a(sf_empty0 + (q % kSfBufs) * 8, ((q / kSfBufs) & 1) ^ 1)) { timeout(ctl, 18); break; }
+      }
+    }
+  } else {
+    // ===== epilogue (warps 5..12): TMEM lane quarter = warp % 4, column half = (warp - 5) / 4
+    const int qd = warp & 3;
+    const int col0 = ((warp - kEpiWarp0) >> 2) * kEpiCols;
+    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16) + col0;
+    const bool two = p.k_tiles > 1;
+    uint32_t tile_i = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_i) {
+      int32_t m0, n0;
+      tile_coords(p, t, m0, n0);
+      if (!ptx::mbar_wait_a(acc_full, tile_i & 1)) {
+        timeout(ctl, 16);
+        break;
+      }
+      ptx::tc_fence_after();
+      const int32_t row = m0 + qd * 32 + lane;
+#pragma unroll
+      for (int c = 0; c < kEpiCols / 32; ++c) {
+        uint32_t va[32], vb[32];
+        ptx::tmem_ld_32x32(tlane + c * 32, va);
+        ptx::tmem_ld_32x32(tlane + BN + c * 32, vb);
+        ptx::tmem_ld_wait(va);
+        ptx::tmem_ld_wait(vb);
+        if (c == kEpiCols / 32 - 1) {
+          // all TMEM reads of this tile have landed: the issuers may overwrite the accumulators
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_a(acc_empty);
+        }
+        if (row < p.M) {
+          const int32_t n_first = n0 + col0 + c * 32;
+          if (p.out_dtype == SGLB200_BF16) {
+            store32<__nv_bfloat16>(va, vb, two, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + n_first,
+                                   n_first, p.N);
+          } else {
+            store32<__half>(va, vb, two, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
+          }
+        }
+      }
+      if (ctl->abort_flag) break;
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      ptr = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+int make_map2d(CUtensorMap* map, const void* base, uint64_t k, uint64_t rows, uint64_t ld, uint32_t box_rows,
+               CUtensorMapL2promotion promo) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  cuuint64_t gdim[2] = {k, rows};
+  cuuint64_t gstr[1] = {ld};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SGLB200_OK;
+}
+
+}  // namespace
+}  // namespace sglb
+
+using namespace sglb;
+
+// Debug hook (not in the public header): mirror time-out codes of the UE8M0 GEMM into host-mapped memory.
+extern "C" int sglb200_debug_set_status_mirror(int* device_visible_host_ptr) {
+  return (int)cudaMemcpyToSymbol(g_ue8m0_mirror, &device_visible_host_ptr, sizeof(int*));
+}
+
+extern "C" int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb,
+                                           void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                           int64_t ldc, int64_t sfa_ld, int64_t sfb_stride_n, int64_t sfb_stride_k,
+                                           int out_dtype, void* stream) {
+  SGLB_REQUIRE(M >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size", (long long)M,
+               (long long)N, (long long)K);
+  SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE,
+               "out_dtype=%d: only bf16 (0) and f16 (1)", out_dtype);
+  SGLB_REQUIRE(M < ((int64_t)1 << 31) - 256 && N < ((int64_t)1 << 31) - 256 && K < ((int64_t)1 << 31) - 256,
+               SGLB200_ERR_SHAPE, "a dimension exceeds 2^31");
+  SGLB_REQUIRE(K > 0 || M == 0 || N == 0, SGLB200_ERR_SHAPE, "K must be positive");
+  SGLB_REQUIRE(K % 16 == 0, SGLB200_ERR_SHAPE, "K=%lld must be a multiple of 16", (long long)K);
+  SGLB_REQUIRE(N % 8 == 0, SGLB200_ERR_SHAPE, "N=%lld must be a multiple of 8 (16-byte output rows)", (long long)N);
+  if (M == 0 || N == 0) return SGLB200_OK;
+  SGLB_REQUIRE(a && b && sfa && sfb && out, SGLB200_ERR_NULL, "a/b/sfa/sfb/out must not be NULL");
+  SGLB_REQUIRE(lda >= K && lda % 16 == 0 && ldb >= K && ldb % 16 == 0, SGLB200_ERR_ALIGN,
+               "lda=%lld / ldb=%lld must be >= K and multiples of 16", (long long)lda, (long long)ldb);
+  SGLB_REQUIRE(ldc >= N && (ldc * 2) % 16 == 0, SGLB200_ERR_ALIGN, "ldc=%lld must be >= N and a multiple of 8",
+               (long long)ldc);
+  SGLB_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(out, 16) && aligned(sfa, 4) && aligned(sfb, 4),
+               SGLB200_ERR_ALIGN, "a, b, out must be 16-byte aligned and the scale pointers 4-byte aligned");
+  SGLB_REQUIRE(sfa_ld >= M, SGLB200_ERR_SHAPE, "sfa_ld=%lld must be >= M (scale words of a row group are contiguous)",
+               (long long)sfa_ld);
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
+               di.cc_major, di.cc_minor);
+
+  alignas(64) CUtensorMap map_a, map_b;
+  if (int rc = make_map2d(&map_a, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
+    return rc;
+  if (int rc = make_map2d(&map_b, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
+    return rc;
+
+  Params p;
+  p.sfa = sfa;
+  p.sfb = sfb;
+  p.out = out;
+  p.M = (int32_t)M;
+  p.N = (int32_t)N;
+  p.K = (int32_t)K;
+  p.m_tiles = (int32_t)((M + BM - 1) / BM);
+  p.n_tiles = (int32_t)((N + BN - 1) / BN);
+  p.k_tiles = (int32_t)((K + BK - 1) / BK);
+  p.k_groups = (p.k_tiles + 3) / 4;
+  p.ldc = ldc;
+  p.sfa_ld = sfa_ld;
+  p.sfb_stride_n = sfb_stride_n;
+  p.sfb_stride_k = sfb_stride_k;
+  p.out_dtype = out_dtype;
+
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fp8_ue8m0_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kSmemBytes);
+    if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done[dev] = true;
+  }
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
+  fp8_ue8m0_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  SGLB_CHECK_LAUNCH("fp8_ue8m0_gemm_kernel");
+  return SGLB200_OK;
+}

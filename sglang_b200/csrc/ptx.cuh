@@ -56,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > limit_ns) {
+      } else if ((int64_t)(now - t0) > (int64_t)limit_ns) {  // signed: a timer that steps back must not look like a time-out
         return false;
       }
     }
@@ -85,7 +85,7 @@ __device__ __forceinline__ bool mbar_try_wait_a(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait (see mbar_wait).  The time-out path is out of line so the ready path stays short.
-__device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+static __device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
   uint64_t t0 = 0;
   uint32_t polls = 0;
   while (!mbar_try_wait_a(bar, parity)) {
@@ -93,7 +93,7 @@ __device__ __noinline__ bool mbar_wait_slow_a(uint32_t bar, uint32_t parity, uin
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > limit_ns) {
+      } else if ((int64_t)(now - t0) > (int64_t)limit_ns) {  // signed: a timer that steps back must not look like a time-out
         return false;
       }
     }
@@ -198,6 +198,48 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
                  "+r"(r[30]), "+r"(r[31])
                :
                : "memory");
+}
+
+// ---- hardware block scaling (kind::mxf8f6f4.block_scale): UE8M0 scale factors live in TMEM
+// Copies 32 rows x 16 bytes from shared memory (described by a no-swizzle matrix descriptor) into four TMEM
+// columns of lanes 0..31 and replicates them into the other three lane quarters.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Descriptor of a scale-factor block in shared memory: 32 rows of 16 bytes, contiguous, no swizzle
+// (8-row atoms 128 bytes apart), descriptor version 1.
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)(128u >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+// D[tmem] (+)= (A * 2^sfa) (B * 2^sfb): e4m3 operands with one UE8M0 scale per row per 32 elements of K.
+// sfa / sfb are TMEM addresses of the scale columns; the byte used inside each 32-bit scale word is chosen by the
+// a_sf_id / b_sf_id fields of idesc.
+__device__ __forceinline__ void mma_mxf8_block_scaled(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                      uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptor for the block-scaled kind: e4m3 x e4m3, K-major, UE8M0 scales, shape M x N x 32;
+// sf_id (0..3) selects the byte of the scale words for both operands.
+__host__ __device__ constexpr uint32_t make_idesc_mxf8(uint32_t m, uint32_t n, uint32_t sf_id) {
+  return (sf_id << 4)         // B scale byte
+         | (0u << 7)          // A format: e4m3
+         | (0u << 10)         // B format: e4m3
+         | ((n >> 3) << 17)   // N / 8
+         | (1u << 23)         // scale format: UE8M0
+         | ((m >> 4) << 24)   // M / 16
+         | (sf_id << 29);     // A scale byte
 }
 
 // Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes, stored with the

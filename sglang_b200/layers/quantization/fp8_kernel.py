@@ -9,7 +9,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from ...sgl_kernel import fp8_blockwise_scaled_mm, sgl_per_token_group_quant_8bit
-from ..._lib import blockwise_mm, dtype_code
+from ..._lib import blockwise_mm, check, dtype_code, lib
 
 fp8_dtype = torch.float8_e4m3fn
 fp8_max = torch.finfo(fp8_dtype).max
@@ -97,4 +97,46 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
         blockwise_mm(A2.data_ptr(), B.data_ptr(), As2.data_ptr(), Bs.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
                      As2.stride(0), As2.stride(1), Bs.stride(0), Bs.stride(1), dtype_code(output_dtype), A.device,
                      torch.cuda.current_stream(A.device).cuda_stream)
+    return C
+
+
+def pack_ue8m0_scales(scales: torch.Tensor) -> torch.Tensor:
+    """Pack power-of-two fp32 scales ``[R, KB]`` into the UE8M0 word layout the block-scaled GEMM reads:
+    int32 ``[R, ceil(KB/4)]``, byte ``j`` of word ``(r, g)`` = biased exponent of ``scales[r, 4g + j]``
+    (missing k-blocks are padded with exponent 127 = 1.0).  Offline / load-time helper."""
+    assert scales.dtype == torch.float32 and scales.dim() == 2
+    bits = scales.contiguous().view(torch.int32)
+    if bool((bits & 0x7FFFFF).ne(0).any()) or bool((bits <= 0).any()):
+        raise ValueError("UE8M0 scales must be positive powers of two")
+    R, KB = scales.shape
+    KG = (KB + 3) // 4
+    e = torch.full((R, KG * 4), 127, dtype=torch.int32, device=scales.device)
+    e[:, :KB] = (bits >> 23) & 0xFF
+    e = e.view(R, KG, 4)
+    return (e[..., 0] | (e[..., 1] << 8) | (e[..., 2] << 16) | (e[..., 3] << 24)).to(torch.int32).contiguous()
+
+
+def w8a8_block_fp8_matmul_ue8m0(A: torch.Tensor, B: torch.Tensor, As_packed: torch.Tensor, Bs_packed: torch.Tensor,
+                                output_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Block-FP8 GEMM with UE8M0 scales on the tensor core's block-scaling path, the counterpart of
+    ``w8a8_block_fp8_matmul_deepgemm`` on Blackwell (``fp8_kernel.py:1047-1065``).
+
+    A ``[M, K]`` e4m3; As_packed int32 ``[M, ceil(K/512)]`` with ``stride(0) == 1`` as returned by
+    ``sglang_per_token_group_quant_fp8(..., column_major_scales=True, scale_tma_aligned=True, scale_ue8m0=True)``;
+    B ``[N, K]`` e4m3; Bs_packed int32 ``[ceil(N/128), ceil(K/512)]`` from :func:`pack_ue8m0_scales`."""
+    assert A.dim() == 2 and A.is_contiguous() and B.dim() == 2 and B.is_contiguous() and A.shape[1] == B.shape[1]
+    M, K = A.shape
+    N = B.shape[0]
+    KG = (-(-K // 128) + 3) // 4
+    assert As_packed.dtype == torch.int32 and As_packed.shape == (M, KG) and (M <= 1 or As_packed.stride(0) == 1)
+    assert Bs_packed.dtype == torch.int32 and Bs_packed.shape == (-(-N // 128), KG)
+    C = torch.empty(M, N, device=A.device, dtype=output_dtype)
+    if M == 0:
+        return C
+    sfa_ld = As_packed.stride(1) if KG > 1 else max(As_packed.stride(1), M)
+    with torch.cuda.device(A.device):
+        check(lib().sglb200_fp8_ue8m0_scaled_mm(
+            A.data_ptr(), B.data_ptr(), As_packed.data_ptr(), Bs_packed.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
+            sfa_ld, Bs_packed.stride(0), Bs_packed.stride(1), dtype_code(output_dtype),
+            torch.cuda.current_stream(A.device).cuda_stream), "w8a8_block_fp8_matmul_ue8m0")
     return C
