@@ -215,7 +215,7 @@ def main():
     ap.add_argument("--cpu-m", type=int, default=1024, help="rows of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE section (11.3 GB of expert weights)")
-    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant"],
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant", "ue8m0"],
                     help="profiling aid: run only the linear sweep ('gemm') or only the quant bandwidth case")
     ap.add_argument("--shape", default=None, help="profiling aid: restrict the sweep to one layer name")
     args = ap.parse_args()
@@ -243,8 +243,9 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from sglang_b200.layers.quantization import (Fp8Config, Fp8LinearMethod, sglang_per_token_group_quant_fp8,
-                                                 w8a8_block_fp8_matmul)
+    from sglang_b200.layers.quantization import (Fp8Config, Fp8LinearMethod, pack_ue8m0_scales,
+                                                 sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul,
+                                                 w8a8_block_fp8_matmul_ue8m0)
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the product path)")
@@ -260,7 +261,7 @@ def main():
     layers = []
     gen = torch.Generator(device=dev).manual_seed(0)
 
-    def block_quant(w):
+    def block_quant(w, ue8m0=False):
         n, k = w.shape
         n_p, k_p = -(-n // 128) * 128, -(-k // 128) * 128
         wp = torch.zeros(n_p, k_p, device=dev)
@@ -268,6 +269,9 @@ def main():
         v = wp.view(n_p // 128, 128, k_p // 128, 128)
         s = v.abs().amax(dim=(1, 3), keepdim=True) / 448.0
         s = torch.where(s == 0, torch.ones_like(s), s)
+        if ue8m0:  # power-of-two block scales (a UE8M0 checkpoint)
+            mant, exp = torch.frexp(s)
+            s = torch.ldexp(torch.ones_like(s), torch.where(mant == 0.5, exp - 1, exp))
         q = (v / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(n_p, k_p)[:n, :k].contiguous()
         return q, s.view(n_p // 128, k_p // 128).contiguous()
 
@@ -284,6 +288,7 @@ def main():
             k_loc = K // world
         w = torch.randn(n_loc, k_loc, device=dev, generator=gen) * 0.02
         wq, ws = block_quant(w)
+        wq_u, ws_u = block_quant(w, ue8m0=True)
         del w
         layer = torch.nn.Module()
         method.create_weights(layer, k_loc, [n_loc], K, N, torch.bfloat16, device=dev)
@@ -292,7 +297,7 @@ def main():
         x = torch.randn(M, k_loc, device=dev, generator=gen)
         x = torch.where(torch.rand(M, k_loc, device=dev, generator=gen) < 0.01, x * 50.0, x).bfloat16()
         layers.append({"name": name, "N": N, "K": K, "mode": mode, "n_loc": n_loc, "k_loc": k_loc, "layer": layer,
-                       "x": x, "gemm_ms": []})
+                       "x": x, "gemm_ms": [], "wq_u": wq_u, "ws_u": pack_ue8m0_scales(ws_u), "ev_u": []})
 
     def step(record=False):
         for L in layers:
@@ -313,18 +318,17 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup if args.only != "quant" else 0):
+    for _ in range(args.warmup if args.only not in ("quant", "ue8m0") else 0):
         step()
     for L in layers:
         L["ev"] = []
-    if args.only == "quant":
-        args.steps = 1
+    main_steps = args.steps if args.only not in ("quant", "ue8m0") else 1
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
     fence()
     sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0.record()
-    for _ in range(args.steps):
+    for _ in range(main_steps):
         step(record=True)
     t1.record()
     fence()
@@ -332,7 +336,7 @@ def main():
     ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms) / args.steps
+    ms_per_step = float(ms) / main_steps
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     # GEMM kernel alone: CUDA events around every launch in the timed region
@@ -354,12 +358,63 @@ def main():
                 "traffic_note": "bytes per launch averaged over the layers; ncu ratio 1.05 on a smaller M scaled up",
                 "kernel": "fp8_block_gemm_kernel",
                 "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
-                "frac_of_nominal_fp8": achieved / 4500.0, "launches": args.steps * len(layers),
-                "avg_launch_ms": gemm_ms / (args.steps * len(layers))}
+                "frac_of_nominal_fp8": achieved / 4500.0, "launches": main_steps * len(layers),
+                "avg_launch_ms": gemm_ms / (main_steps * len(layers))}
+
+    # ---- the same sweep on a UE8M0 checkpoint (power-of-two weight block scales, power-of-two activation group
+    # scales): the tensor core applies the scales itself (tcgen05.mma kind::mxf8f6f4.block_scale)
+    def step_u(record=False):
+        for L in layers:
+            q, s = sglang_per_token_group_quant_fp8(L["x"], 128, column_major_scales=True, scale_tma_aligned=True,
+                                                    scale_ue8m0=True)
+            if record:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            y = w8a8_block_fp8_matmul_ue8m0(q, L["wq_u"], s, L["ws_u"], torch.bfloat16)
+            if record:
+                e1.record()
+                L["ev_u"].append((e0, e1))
+            if world > 1 and L["mode"] == "row":
+                dist.all_reduce(y)
+        return y
+
+    ue8m0 = None
+    if args.only in ("all", "ue8m0"):
+        for _ in range(args.warmup):
+            step_u()
+        sampler_u = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
+        fence()
+        sampler_u.start()
+        u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        u0.record()
+        for _ in range(args.steps):
+            step_u(record=True)
+        u1.record()
+        fence()
+        clocks_u = sampler_u.stop()
+        ms_u = torch.tensor([u0.elapsed_time(u1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms_u, op=dist.ReduceOp.MAX)
+        ms_u_step = float(ms_u) / args.steps
+        g_ms, g_fl, shp = 0.0, 0.0, {}
+        for L in layers:
+            tt = [a.elapsed_time(b) for a, b in L["ev_u"]]
+            f = 2.0 * M * L["n_loc"] * L["k_loc"]
+            g_ms += sum(tt)
+            g_fl += f * len(tt)
+            shp[L["name"]] = {"gemm_ms": statistics.median(tt), "gemm_tflops": f / (statistics.median(tt) * 1e-3) / 1e12}
+        ach_u = g_fl / (g_ms * 1e-3) / 1e12
+        ue8m0 = {"workload": "same five layers, UE8M0 checkpoint: power-of-two weight block scales and activation "
+                             "group scales, hardware block-scaled MMA",
+                 "value": total_flops / (ms_u_step * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_u_step,
+                 "roofline": {"bound": "tensor", "achieved": ach_u, "peak": 2.0 * peaks["bf16_tflops_sustained"],
+                              "unit": "TFLOP/s", "frac": ach_u / (2.0 * peaks["bf16_tflops_sustained"]),
+                              "frac_of_nominal_fp8": ach_u / 4500.0, "kernel": "fp8_ue8m0_gemm_kernel"},
+                 "per_shape": shp, "clocks": clocks_u, "gpu_launches": args.steps * len(layers) * 2}
 
     # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed between launches
     quant = None
-    if rank == 0 and args.only != "gemm":
+    if rank == 0 and args.only not in ("gemm", "ue8m0"):
         xq = torch.randn(16384, 7168, device=dev, generator=gen)
         xq = (xq * 10 ** (torch.rand(16384, 1, device=dev, generator=gen) * 4 - 2)).bfloat16()
         flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
@@ -385,7 +440,8 @@ def main():
         if rank == 0:
             print(json.dumps({"metric": METRIC, "only": args.only, "value": value, "unit": "TFLOP/s", "n_gpus": world,
                               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "config": config,
-                              "clocks": clocks, "roofline": roofline, "quant": quant, "per_shape": per_shape}))
+                              "clocks": clocks, "roofline": roofline, "quant": quant, "per_shape": per_shape,
+                              "ue8m0": ue8m0}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -439,7 +495,7 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks,
                 "e2e": e2e, "gpu_launches": args.steps * len(layers) * 2, "roofline": roofline,
-                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "impl": "ours"}
+                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "ue8m0": ue8m0, "impl": "ours"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

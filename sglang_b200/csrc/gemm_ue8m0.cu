@@ -10,17 +10,18 @@
 // deep_gemm_wrapper/configurer.py:24-25).
 //
 // One CTA per SM, 416 threads:
-//   warps 0-1   TMA producers (k-blocks alternate): A tile 128 x 128 B and B tile 192 x 128 B into a 5-stage ring.
-//   warps 2-3   MMA issuers (k-blocks of a tile alternate; issuing an MMA blocks the thread for its duration, so two
-//               issuers keep the pipe fed while the other one handles its barriers).  Each issuer accumulates its
-//               k-blocks in its OWN 192-column TMEM accumulator, so no ordering between the two is needed; the
-//               epilogue adds the two.  Before the first k-block of every group of four, an issuer copies that
-//               group's scale words from shared memory into its own TMEM scale columns (tcgen05.cp).
+//   warps 0-1   TMA producers (k-blocks alternate): A tile 128 x 128 B and B tile 224 x 128 B into a 4-stage ring.
+//   warp 2      the MMA issuer (one thread): per k-block four 128 x 224 x 32 block-scaled MMAs into one of TWO
+//               224-column TMEM accumulators (tiles alternate, so the epilogue of a tile overlaps the next tile's
+//               MMAs).  Before the first k-block of every group of four it copies that group's scale words from shared
+//               memory into TMEM scale columns (tcgen05.cp; two sets, alternating).  All tensor-pipe work comes from
+//               this one thread, so copies and MMAs execute in the order they were issued.
+//   warp 3      idle.
 //   warp 4      scale loader: per tile and per group of four k-blocks, 128 packed scale words of A (one int32 holds the
-//               four exponent bytes of a row, the layout the quantiser writes) and 192 of B, written to shared memory
+//               four exponent bytes of a row, the layout the quantiser writes) and 224 of B, written to shared memory
 //               in the 32 x 16 B arrangement tcgen05.cp.32x128b.warpx4 expects (lane l: rows l, l+32, l+64, l+96).
 //               The k-block inside the group picks the byte through the instruction descriptor's scale ids.
-//   warps 5-12  epilogue: after the last k-block, D0 + D1 -> bf16/f16 rows.
+//   warps 5-12  epilogue: after the last k-block of a tile, its accumulator -> bf16/f16 rows.
 // Every mbarrier wait is bounded; on time-out the CTA records a code in g_device_status and winds down.
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -51,17 +52,17 @@ int ue8m0_take_device_status() {
 
 namespace {
 
-constexpr int BM = 128, BN = 192, BK = 128;
-constexpr int kStages = 5;
+constexpr int BM = 128, BN = 224, BK = 128;
+constexpr int kStages = 4;
 constexpr int kSfBufs = 4;
 constexpr int kThreads = 13 * 32;
 constexpr int kEpiWarp0 = 5, kEpiWarps = 8;
-constexpr int kEpiCols = BN / 2;  // 96 columns per epilogue warp
+constexpr int kEpiCols = BN / 2;  // 112 columns per epilogue warp: three loads of 32 and one of 16
 constexpr uint32_t kTileABytes = BM * BK, kTileBBytes = BN * BK, kStageBytes = kTileABytes + kTileBBytes;
 constexpr uint32_t kSfABytes = 512, kSfBBytes = 1024, kSfBufBytes = kSfABytes + kSfBBytes;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kSfTmemBase = 2 * BN;  // 384: scale columns start after the two accumulators
-constexpr uint32_t kSfTmemPerSet = 12;    // 4 columns for A's scales + 8 for B's (192 rows -> two copies of 128)
+constexpr uint32_t kSfTmemBase = 2 * BN;  // 448: scale columns start after the two accumulators
+constexpr uint32_t kSfTmemPerSet = 12;    // 4 columns for A's scales + 8 for B's (224 rows -> two copies of 128)
 constexpr int kGroupM = 16;
 constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + (size_t)kSfBufs * kSfBufBytes + 256;
 
@@ -80,8 +81,8 @@ struct Ctl {
   uint64_t empty[kStages];
   uint64_t sf_full[kSfBufs];
   uint64_t sf_empty[kSfBufs];
-  uint64_t acc_full;
-  uint64_t acc_empty;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int32_t abort_flag;
 };
@@ -158,10 +159,12 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     }
     for (int i = 0; i < kSfBufs; ++i) {
       ptx::mbar_init(&ctl->sf_full[i], 1);
-      ptx::mbar_init(&ctl->sf_empty[i], 2);  // both issuers copy the block into their own TMEM columns
+      ptx::mbar_init(&ctl->sf_empty[i], 1);
     }
-    ptx::mbar_init(&ctl->acc_full, 2);  // one commit per issuer
-    ptx::mbar_init(&ctl->acc_empty, kEpiWarps);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&ctl->acc_full[i], 1);
+      ptx::mbar_init(&ctl->acc_empty[i], kEpiWarps);
+    }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -182,8 +185,8 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
   const uint32_t sf_full0 = ptx::smem_u32(&ctl->sf_full[0]);
   const uint32_t sf_empty0 = ptx::smem_u32(&ctl->sf_empty[0]);
-  const uint32_t acc_full = ptx::smem_u32(&ctl->acc_full);
-  const uint32_t acc_empty = ptx::smem_u32(&ctl->acc_empty);
+  const uint32_t acc_full0 = ptx::smem_u32(&ctl->acc_full[0]);
+  const uint32_t acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
   const uint32_t stage0 = ptx::smem_u32(smem);
   const uint32_t sf0 = ptx::smem_u32(sf_smem);
 
@@ -221,15 +224,15 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (++stage == kStages) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp < 4) {
-    // ===== MMA issuers: issuer w takes the k-blocks kb with kb % 2 == w of every tile into accumulator w
-    const uint32_t w = warp - 2;
+  } else if (warp == 2) {
+    // ===== MMA issuer
     const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
-    const uint32_t d_tmem = tmem_base + w * BN;
     uint32_t stage = 0, phase = 0, q = 0, tile_i = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_i) {
-      bool ok = ptx::mbar_wait_a(acc_empty, (tile_i & 1) ^ 1);
+      const uint32_t as = tile_i & 1;  // accumulator of this tile
+      bool ok = ptx::mbar_wait_a(acc_empty0 + as * 8, ((tile_i >> 1) & 1) ^ 1);
       if (!ok) timeout(ctl, 12);
+      const uint32_t d_tmem = tmem_base + as * BN;
       for (int32_t kg = 0; kg < p.k_groups && ok; ++kg, ++q) {
         const uint32_t buf = q % kSfBufs;
         if (!ptx::mbar_wait_a(sf_full0 + buf * 8, (q / kSfBufs) & 1)) {
@@ -238,7 +241,7 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           break;
         }
         ptx::tc_fence_after();
-        const uint32_t sf_col = tmem_base + kSfTmemBase + (w * 2 + (q & 1)) * kSfTmemPerSet;
+        const uint32_t sf_col = tmem_base + kSfTmemBase + (q & 1) * kSfTmemPerSet;
         if (lane == 0) {
           const uint32_t src = sf0 + buf * kSfBufBytes;
           ptx::tmem_cp_32x128b_warpx4(sf_col, ptx::make_sf_desc(src));
@@ -248,33 +251,27 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
         const int32_t kb_end = min(kg * 4 + 4, p.k_tiles);
         for (int32_t kb = kg * 4; kb < kb_end; ++kb) {
-          if ((uint32_t)(kb & 1) == w) {
-            if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
-              timeout(ctl, 14);
-              ok = false;
-              break;
-            }
-            ptx::tc_fence_after();
-            if (lane == 0) {
-              const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
-              const uint64_t b_desc = a_desc + (kTileABytes >> 4);
-              const uint32_t idesc = ptx::make_idesc_mxf8(BM, BN, (uint32_t)(kb & 3));
-              ptx::mma_mxf8_block_scaled(d_tmem, a_desc, b_desc, idesc, sf_col, sf_col + 4, kb >= 2 ? 1u : 0u);
+          if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
+            timeout(ctl, 14);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
+            const uint64_t b_desc = a_desc + (kTileABytes >> 4);
+            const uint32_t idesc = ptx::make_idesc_mxf8(BM, BN, (uint32_t)(kb & 3));
+            ptx::mma_mxf8_block_scaled(d_tmem, a_desc, b_desc, idesc, sf_col, sf_col + 4, kb > 0 ? 1u : 0u);
 #pragma unroll
-              for (uint32_t k = 1; k < BK / 32; ++k)
-                ptx::mma_mxf8_block_scaled(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sf_col, sf_col + 4, 1u);
-              ptx::mma_commit_a(empty0 + stage * 8);
-            }
+            for (uint32_t k = 1; k < BK / 32; ++k)
+              ptx::mma_mxf8_block_scaled(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, sf_col, sf_col + 4, 1u);
+            ptx::mma_commit_a(empty0 + stage * 8);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
       if (!ok || ctl->abort_flag) break;
-      // this issuer's share of the tile is in flight: publish it when it is done (an issuer without any k-block,
-      // which happens only when the tile has a single k-block, still has to arrive)
-      if (lane == 0) {
-        if (p.k_tiles > (int32_t)w) ptx::mma_commit_a(acc_full); else ptx::mbar_arrive_a(acc_full);
-      }
+      if (lane == 0) ptx::mma_commit_a(acc_full0 + as * 8);  // the tile is complete when everything issued so far is
     }
   } else if (warp == 4) {
     // ===== scale loader
@@ -321,42 +318,44 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (!ptx::mbar_wait_a(sf_empty0 + (q % kSfBufs) * 8, ((q / kSfBufs) & 1) ^ 1)) { timeout(ctl, 18); break; }
       }
     }
-  } else {
+  } else if (warp >= kEpiWarp0) {
     // ===== epilogue (warps 5..12): TMEM lane quarter = warp % 4, column half = (warp - 5) / 4
     const int qd = warp & 3;
     const int col0 = ((warp - kEpiWarp0) >> 2) * kEpiCols;
-    const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16) + col0;
-    const bool two = p.k_tiles > 1;
     uint32_t tile_i = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_i) {
       int32_t m0, n0;
       tile_coords(p, t, m0, n0);
-      if (!ptx::mbar_wait_a(acc_full, tile_i & 1)) {
+      const uint32_t as = tile_i & 1;
+      if (!ptx::mbar_wait_a(acc_full0 + as * 8, (tile_i >> 1) & 1)) {
         timeout(ctl, 16);
         break;
       }
       ptx::tc_fence_after();
+      const uint32_t tlane = tmem_base + ((uint32_t)(qd * 32) << 16) + as * BN + col0;
       const int32_t row = m0 + qd * 32 + lane;
+      // 112 columns = 32 + 32 + 32 + 16; the last load reads 32 columns of which the first 16 are this warp's
+      // (the other 16 belong to the neighbouring half or to the other accumulator and are not stored)
 #pragma unroll
-      for (int c = 0; c < kEpiCols / 32; ++c) {
-        uint32_t va[32], vb[32];
+      for (int c = 0; c < 4; ++c) {
+        uint32_t va[32];
         ptx::tmem_ld_32x32(tlane + c * 32, va);
-        ptx::tmem_ld_32x32(tlane + BN + c * 32, vb);
         ptx::tmem_ld_wait(va);
-        ptx::tmem_ld_wait(vb);
-        if (c == kEpiCols / 32 - 1) {
-          // all TMEM reads of this tile have landed: the issuers may overwrite the accumulators
+        if (c == 3) {
+          // all TMEM reads of this tile have landed: the issuer may overwrite this accumulator
           ptx::tc_fence_before();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive_a(acc_empty);
+          if (lane == 0) ptx::mbar_arrive_a(acc_empty0 + as * 8);
         }
         if (row < p.M) {
           const int32_t n_first = n0 + col0 + c * 32;
+          const int32_t n_limit = min(p.N, n0 + col0 + kEpiCols);  // do not store beyond this warp's 112 columns
           if (p.out_dtype == SGLB200_BF16) {
-            store32<__nv_bfloat16>(va, vb, two, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + n_first,
-                                   n_first, p.N);
+            store32<__nv_bfloat16>(va, va, false, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + n_first,
+                                   n_first, n_limit);
           } else {
-            store32<__half>(va, vb, two, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
+            store32<__half>(va, va, false, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + n_first, n_first,
+                            n_limit);
           }
         }
       }

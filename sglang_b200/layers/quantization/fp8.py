@@ -17,7 +17,7 @@ class Fp8Config:
     """Quantisation config of a block-FP8 checkpoint (``fp8.py:95-178``)."""
 
     def __init__(self, is_checkpoint_fp8_serialized: bool = True, activation_scheme: str = "dynamic",
-                 weight_block_size: Optional[List[int]] = None):
+                 weight_block_size: Optional[List[int]] = None, requant_weight_ue8m0: bool = False):
         if activation_scheme != "dynamic":
             raise ValueError("The block-wise quantization only supports dynamic activation scheme for now.")
         if weight_block_size is None:
@@ -29,6 +29,10 @@ class Fp8Config:
         self.is_checkpoint_fp8_serialized = True
         self.activation_scheme = activation_scheme
         self.weight_block_size = list(weight_block_size)
+        # Requantise weights whose block scales are not powers of two to UE8M0 scales at load time, as the reference
+        # does for its Blackwell DeepGEMM path (fp8_utils.py:416-507); changes the weight codes, so results move by
+        # the requantisation error.  Off by default: such weights then use the fp32-scale GEMM, which is exact.
+        self.requant_weight_ue8m0 = requant_weight_ue8m0
 
     @classmethod
     def get_name(cls) -> str:
@@ -85,11 +89,33 @@ class Fp8LinearMethod:
         layer.register_parameter("input_scale", None)
 
     def process_weights_after_loading(self, layer: Module) -> None:
-        """Nothing to do on CUDA for block quantisation (``fp8.py:340-363``)."""
+        """Pick the GEMM for this layer once the weights are in place (``fp8.py:340-363``; the UE8M0 handling
+        mirrors ``fp8_utils.py:416-507``).  If every block scale is a power of two (a UE8M0 checkpoint), or after
+        ``requant_weight_ue8m0``, the exponents are packed for the tensor core's block-scaling path; otherwise the
+        layer keeps the fp32-scale GEMM.  One host synchronisation, at load time only."""
+        from .fp8_kernel import pack_ue8m0_scales
+        from .fp8_utils import requant_weight_ue8m0
+        layer.weight_scale_ue8m0 = None
+        ws = layer.weight_scale_inv.data
+        if not ws.is_cuda:
+            return None
+        bits = ws.contiguous().view(torch.int32)
+        pow2 = bool(((bits & 0x7FFFFF) == 0).all()) and bool((bits > 0).all())
+        if not pow2 and self.quant_config.requant_weight_ue8m0:
+            wq, ws = requant_weight_ue8m0(layer.weight.data, ws, self.quant_config.weight_block_size)
+            layer.weight.data = wq
+            layer.weight_scale_inv.data = ws
+            pow2 = True
+        if pow2:
+            layer.weight_scale_ue8m0 = pack_ue8m0_scales(ws)
         return None
 
     def apply(self, layer: Module, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``Fp8LinearMethod.apply`` (``fp8.py:453-499``, block-quant branch ``:482-489``)."""
+        packed = getattr(layer, "weight_scale_ue8m0", None)
+        if packed is not None:
+            from .fp8_utils import w8a8_block_fp8_linear_ue8m0
+            return w8a8_block_fp8_linear_ue8m0(x, layer.weight, packed, bias)
         return self.w8a8_block_fp8_linear(input=x, weight=layer.weight,
                                           block_size=self.quant_config.weight_block_size,
                                           weight_scale=layer.weight_scale_inv, input_scale=None, bias=bias)

@@ -6,7 +6,7 @@ from typing import List, Optional
 
 import torch
 
-from .fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+from .fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul, w8a8_block_fp8_matmul_ue8m0
 
 
 def w8a8_block_fp8_linear(input: torch.Tensor, weight: torch.Tensor, block_size: List[int],
@@ -44,3 +44,42 @@ def block_quant_dequant(x_q_block: torch.Tensor, x_s: torch.Tensor, block_size: 
     *_, n, k = x_q_block.shape
     rep = x_s.repeat_interleave(block_n, dim=-2).repeat_interleave(block_k, dim=-1)[..., :n, :k]
     return (x_q_block.to(torch.float32) * rep).to(dtype)
+
+
+def w8a8_block_fp8_linear_ue8m0(input: torch.Tensor, weight: torch.Tensor, weight_scale_packed: torch.Tensor,
+                                bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The linear for UE8M0 checkpoints, the counterpart of ``deepgemm_w8a8_block_fp8_linear_with_fallback`` on
+    Blackwell (``fp8_utils.py:217-255``): activations quantised with power-of-two group scales (packed int32,
+    M-major), then the hardware block-scaled GEMM.  ``weight_scale_packed`` comes from ``pack_ue8m0_scales``."""
+    input_2d = input.view(-1, input.shape[-1])
+    if not input_2d.is_contiguous():
+        input_2d = input_2d.contiguous()
+    output_shape = [*input.shape[:-1], weight.shape[0]]
+    q_input, x_scale = sglang_per_token_group_quant_fp8(input_2d, 128, column_major_scales=True,
+                                                        scale_tma_aligned=True, scale_ue8m0=True)
+    output = w8a8_block_fp8_matmul_ue8m0(q_input, weight, x_scale, weight_scale_packed, output_dtype=input_2d.dtype)
+    if bias is not None:
+        output += bias
+    return output.view(*output_shape)
+
+
+def ceil_to_ue8m0(x: torch.Tensor) -> torch.Tensor:
+    """Smallest power of two >= x (``fp8_utils.py:511-512``), computed on the exponent bits."""
+    mant, exp = torch.frexp(x.to(torch.float32).abs())
+    return torch.ldexp(torch.ones_like(mant), torch.where(mant == 0.5, exp - 1, exp))
+
+
+def requant_weight_ue8m0(weight: torch.Tensor, weight_scale: torch.Tensor, block_size: List[int]):
+    """Dequantise a block-FP8 weight and quantise it again with power-of-two block scales
+    (``requant_weight_ue8m0`` / ``per_block_cast_to_fp8``, ``fp8_utils.py:416-507``).  Offline, torch ops."""
+    bn, bk = block_size
+    n, k = weight.shape
+    w = block_quant_dequant(weight, weight_scale, block_size, torch.float32)
+    n_p, k_p = -(-n // bn) * bn, -(-k // bk) * bk
+    wp = torch.zeros(n_p, k_p, dtype=torch.float32, device=weight.device)
+    wp[:n, :k] = w
+    v = wp.view(n_p // bn, bn, k_p // bk, bk)
+    amax = v.abs().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
+    sf = ceil_to_ue8m0(amax / 448.0)
+    q = (v * (1.0 / sf)).to(torch.float8_e4m3fn).view(n_p, k_p)[:n, :k].contiguous()
+    return q, sf.view(n_p // bn, k_p // bk).contiguous()

@@ -72,8 +72,24 @@ def make_weight(N, K, seed=1, std=0.02):
     return oracle.block_quant_weight(torch.randn(N, K, generator=g) * std)
 
 
-def assert_gemm_close(out, ref, what=""):
-    """The tolerance of the GEMM / MoE outputs: rel-L2 <= 1e-2 and max-abs <= 2e-2 x RMS(ref)."""
-    r, m = rel_l2(out.float().cpu(), ref.float().cpu()), max_abs_over_rms(out.float().cpu(), ref.float().cpu())
-    assert r <= 1e-2 and m <= 2e-2, f"{what}: rel-L2 {r:.3e} (<=1e-2), max-abs/RMS {m:.3e} (<=2e-2)"
+def assert_gemm_close(out, ref, what="", allow_one_ulp=False):
+    """The tolerance of the GEMM / MoE outputs: rel-L2 <= 1e-2 and max-abs <= 2e-2 x RMS(ref).
+
+    ``allow_one_ulp``: an element may also differ from the reference by one unit in the last place of its 16-bit
+    format.  One bf16 ulp of an element five times the RMS is already 2-4 % of the RMS, so an implementation whose
+    fp32 sums differ from the oracle's in the last bits (another accumulation order inside the tensor core) cannot
+    meet the max-abs bar on millions of outputs; the rel-L2 bar is unaffected."""
+    o, r_ = out.float().cpu(), ref.float().cpu()
+    r = rel_l2(o, r_)
+    diff = (o.double() - r_.double()).abs()
+    rms = r_.double().pow(2).mean().sqrt().clamp(min=1e-30)
+    bound = torch.full_like(diff, 2e-2 * float(rms))
+    if allow_one_ulp:
+        mant_bits = 7 if ref.dtype == torch.bfloat16 else 10
+        ulp = torch.ldexp(torch.ones_like(diff), torch.frexp(r_.double().abs().clamp(min=1e-30))[1] - 1 - mant_bits)
+        bound = torch.maximum(bound, ulp * 1.001)
+    m = float((diff / rms).max())
+    bad = int((diff > bound).sum())
+    assert r <= 1e-2 and bad == 0, (f"{what}: rel-L2 {r:.3e} (<=1e-2), max-abs/RMS {m:.3e} (<=2e-2"
+                                    f"{' or one ulp' if allow_one_ulp else ''}), {bad} elements over")
     return r, m
