@@ -228,6 +228,50 @@ int sglb200_silu_and_mul(const void* input, void* output, int64_t num_rows, int6
                          void* stream);
 
 /*
+ * Router front end: probabilities = softmax(gating_output[t, :]) in fp32, then the topk largest in
+ * descending order (ties go to the lower expert index); with renormalize != 0 the selected weights are
+ * divided by their sum.
+ *   gating_output [num_tokens, num_experts] contiguous, dtype = SGLB200_BF16 | SGLB200_F16 | SGLB200_F32
+ *   topk_weights  [num_tokens, topk] fp32, topk_ids [num_tokens, topk] int32, both contiguous
+ *   1 <= num_experts <= 1024 (any value, no power-of-two rule and no workspace), 1 <= topk <= num_experts.
+ * Replaces: topk_softmax  sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:512-590
+ *           (schema common_extension.cc:259-260; caller python/sglang/srt/layers/moe/topk.py fused_topk).
+ */
+int sglb200_topk_softmax(const void* gating_output, int dtype, float* topk_weights, int32_t* topk_ids,
+                         int64_t num_tokens, int64_t num_experts, int64_t topk, int renormalize, void* stream);
+
+/*
+ * Block-aligned counting sort of the flattened expert ids, the routing table of the tile-gather MoE runner.
+ * Bucket b (0 <= b < num_buckets) collects the slots whose id is b - 1; bucket 0 therefore holds id -1
+ * (slots of experts another rank owns).  Each bucket is padded to a multiple of block_size.
+ *   topk_ids            [numel] int32, values in [-1, num_buckets - 2]
+ *   sorted_token_ids    [>= numel + num_buckets * (block_size - 1)] int32: slot indices bucket by bucket, inside a
+ *                       bucket in ASCENDING slot order (the reference's order inside a bucket is whatever its
+ *                       atomics produce); with pad_sorted_token_ids != 0 the padding entries below
+ *                       num_tokens_post_pad are set to numel, otherwise the caller pre-fills the array
+ *   expert_ids          [>= capacity / block_size] int32: bucket index - 1 of each block
+ *   num_tokens_post_pad [1] int32: total padded length
+ *   cumsum              [num_buckets + 1] int32 or NULL: padded start of every bucket, then the total (the
+ *                       reference leaves its sort cursors there; no caller reads them)
+ * Limits: numel <= 2^24, num_buckets <= 1024, block_size <= 4096.
+ * Replaces: moe_align_block_size  sgl-kernel/csrc/moe/moe_align_kernel.cu:302-364 (kernels :28-300;
+ *           schema common_extension.cc:253-257); the caller passes num_experts + 1 as num_buckets
+ *           (python/sglang/srt/layers/moe/fused_moe_triton/moe_align_block_size.py:17-88).
+ */
+int sglb200_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int64_t num_buckets, int64_t block_size,
+                                 int32_t* sorted_token_ids, int32_t* expert_ids, int32_t* num_tokens_post_pad,
+                                 int32_t* cumsum, int pad_sorted_token_ids, void* stream);
+
+/*
+ * output[t, :] = cast(routed_scaling_factor * sum_j input[t, j, :]); fp32 sum in ascending j.
+ *   input [num_tokens, topk, hidden], output [num_tokens, hidden], contiguous, dtype = SGLB200_BF16 | SGLB200_F16,
+ *   hidden % 8 == 0, 16-byte aligned pointers.
+ * Replaces: moe_sum_reduce  sgl-kernel/csrc/moe/moe_sum_reduce.cu:227-403 (schema common_extension.cc:262-263).
+ */
+int sglb200_moe_sum_reduce(const void* input, void* output, int64_t num_tokens, int64_t topk, int64_t hidden,
+                           int dtype, float routed_scaling_factor, void* stream);
+
+/*
  * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
  * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps).  Reading clears it.  This call SYNCHRONISES the
  * device (cudaMemcpyFromSymbol); it is for tests and debugging, not for the serving path.  Returns -1 if the

@@ -10,7 +10,10 @@ torch-native functions (``native_per_token_group_quant_fp8``,
 ``tests/golden/``; ``tests/test_oracle_golden.py`` checks this restatement against those
 files bit for bit.  The UE8M0 scale variant is defined by composition
 (``ceil_to_ue8m0(amax / 448)`` from ``fp8_utils.py:511-512`` applied inside the native
-quant function); no reference test pins it on random data.
+quant function); no reference test pins it on random data.  The routing helpers (``topk_softmax``,
+``moe_align_block_size``, ``moe_sum_reduce``) are pinned by ``tests/golden/make_golden_routing.py``, which runs
+``fused_topk_torch_native`` (``python/sglang/srt/layers/moe/topk.py:402-431``) and the reference test's staged
+block-aligned sort (``sgl-kernel/tests/test_moe_align.py:17-148``) into ``tests/golden/routing.npz``.
 """
 
 from .block_fp8 import (  # noqa: F401
@@ -19,11 +22,14 @@ from .block_fp8 import (  # noqa: F401
     block_quant_weight,
     ceil_to_ue8m0,
     fused_experts_block_fp8,
+    moe_align_block_size,
     moe_block_fp8_from_scores,
+    moe_sum_reduce,
     pack_scales,
     per_token_group_quant_fp8,
     prepare_moe_input,
     shuffle_rows,
     silu_and_mul,
+    topk_softmax,
     w8a8_block_fp8_matmul,
 )

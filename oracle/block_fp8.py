@@ -247,3 +247,53 @@ def apply_shuffle_mul_sum(c2: torch.Tensor, c_map: np.ndarray, factors: torch.Te
         term = rows if f is None else rows * f[:, j:j + 1]
         acc = acc + torch.where(ok[:, None], term, torch.zeros_like(term))
     return acc.to(c2.dtype)
+
+
+def topk_softmax(gating_output: torch.Tensor, topk: int, renormalize: bool = False):
+    """``topk_softmax`` as the torch-native router states it (``python/sglang/srt/layers/moe/topk.py:426-431``;
+    the kernel ``sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:512-590`` is tested against the same two torch
+    calls, ``sgl-kernel/tests/test_moe_topk_softmax.py:33-44``).  Returns ``(weights fp32 [T, topk],
+    ids int32 [T, topk])``; equal probabilities go to the lower expert index, the kernel's rule
+    (``moe_topk_softmax_kernels.cu:372``; ``torch.topk`` leaves that order open)."""
+    p = torch.softmax(gating_output.float(), dim=-1)
+    # stable descending sort = torch.topk's order, with the tie rule made explicit
+    order = torch.sort(p, dim=-1, descending=True, stable=True).indices[:, :topk]
+    w = p.gather(1, order)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w, order.to(torch.int32)
+
+
+def moe_align_block_size(topk_ids: np.ndarray, block_size: int, num_experts: int):
+    """``moe_align_block_size`` (``sgl-kernel/csrc/moe/moe_align_kernel.cu:56-229,302-364`` with the caller's
+    ``num_experts + 1`` buckets, ``moe_align_block_size.py:57-85``): bucket ``id + 1`` per slot, every bucket
+    padded to a multiple of ``block_size``; ``expert_ids[block] = bucket - 1``; padding entries hold ``numel``.
+    Inside a bucket the slots are in ascending order (the order of the reference test's second implementation,
+    ``sgl-kernel/tests/test_moe_align.py:71-97``; the CUDA kernel's order there is unspecified).
+    Returns ``(sorted_token_ids [capacity], expert_ids [post_pad / block_size], post_pad, cumsum [B + 1])``."""
+    flat = np.asarray(topk_ids, dtype=np.int64).reshape(-1)
+    numel, B = flat.shape[0], num_experts + 1
+    counts = np.bincount(flat + 1, minlength=B)[:B]
+    padded = (counts + block_size - 1) // block_size * block_size
+    cumsum = np.concatenate([[0], np.cumsum(padded)]).astype(np.int32)
+    post_pad = int(cumsum[-1])
+    cap = numel + B * (block_size - 1)
+    sorted_ids = np.full(cap, numel, dtype=np.int32)
+    expert_ids = np.zeros(post_pad // block_size, dtype=np.int32)
+    order = np.argsort(flat, kind="stable")
+    pos = 0
+    for b in range(B):
+        c = int(counts[b])
+        sorted_ids[cumsum[b]:cumsum[b] + c] = order[pos:pos + c]
+        pos += c
+        expert_ids[cumsum[b] // block_size:cumsum[b + 1] // block_size] = b - 1
+    return sorted_ids, expert_ids, post_pad, cumsum
+
+
+def moe_sum_reduce(x: torch.Tensor, routed_scaling_factor: float = 1.0) -> torch.Tensor:
+    """``moe_sum_reduce`` (``sgl-kernel/csrc/moe/moe_sum_reduce.cu:146-170``): fp32 sum over the top-k axis in
+    ascending order, one multiplication by the factor, one cast."""
+    acc = torch.zeros(x.shape[0], x.shape[2], dtype=torch.float32)
+    for j in range(x.shape[1]):
+        acc = acc + x[:, j].float()
+    return (acc * torch.tensor(routed_scaling_factor, dtype=torch.float32)).to(x.dtype)

@@ -34,6 +34,9 @@ SIGNATURES = {
     "sglb200_shuffle_rows": [_P, _P, _P, _L, _L, _P],
     "sglb200_apply_shuffle_mul_sum": [_P, _P, _P, _P, _L, _L, _L, _I, _I, _P],
     "sglb200_silu_and_mul": [_P, _P, _L, _L, _I, _P],
+    "sglb200_topk_softmax": [_P, _I, _P, _P, _L, _L, _L, _I, _P],
+    "sglb200_moe_align_block_size": [_P, _L, _L, _L, _P, _P, _P, _P, _I, _P],
+    "sglb200_moe_sum_reduce": [_P, _P, _L, _L, _L, _I, _F, _P],
     "sglb200_read_device_status": [],
     "sglb200_status_string": [_I],
     "sglb200_last_error_detail": [],

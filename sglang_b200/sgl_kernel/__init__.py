@@ -14,6 +14,9 @@ from .gemm import (  # noqa: F401
 from .moe import (  # noqa: F401
     apply_shuffle_mul_sum,
     fp8_blockwise_scaled_grouped_mm,
+    moe_align_block_size,
+    moe_sum_reduce,
     prepare_moe_input,
     shuffle_rows,
+    topk_softmax,
 )

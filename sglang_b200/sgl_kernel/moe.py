@@ -1,4 +1,4 @@
-"""``sgl_kernel.moe`` ops on the block-FP8 path (``sgl-kernel/python/sgl_kernel/moe.py:96-172``)."""
+"""``sgl_kernel.moe`` ops on the block-FP8 path (``sgl-kernel/python/sgl_kernel/moe.py:6-48,96-172``)."""
 
 from __future__ import annotations
 
@@ -120,3 +120,71 @@ def fp8_blockwise_scaled_grouped_mm(output, a_ptrs, b_ptrs, out_ptrs, a_scales_p
             a.stride(0), b.stride(2), b.stride(0), output.stride(0),
             scales_a.stride(0), scales_a.stride(1), scales_b.stride(0), scales_b.stride(2), scales_b.stride(1),
             dtype_code(output.dtype), _stream(a)), "fp8_blockwise_scaled_grouped_mm")
+
+
+def topk_softmax(topk_weights: torch.Tensor, topk_ids: torch.Tensor, gating_output: torch.Tensor,
+                 renormalize: bool = False) -> None:
+    """Softmax over the experts, then the ``topk`` largest probabilities in descending order
+    (``sgl-kernel/python/sgl_kernel/moe.py:28-36``; checks as
+    ``sgl-kernel/csrc/moe/moe_topk_softmax_kernels.cu:512-545``).  Any expert count up to 1024 runs in one
+    kernel; no softmax workspace is allocated."""
+    _req(gating_output.dtype in (torch.float32, torch.float16, torch.bfloat16),
+         "gating_output must be float32, float16, or bfloat16")
+    _req(gating_output.dim() == 2, "gating_output must be 2D tensor [num_tokens, num_experts]")
+    _req(topk_weights.dim() == 2, "topk_weights must be 2D tensor [num_tokens, topk]")
+    _req(topk_ids.dim() == 2, "topk_indices must be 2D tensor [num_tokens, topk]")
+    _req(gating_output.size(0) == topk_weights.size(0),
+         "First dimension of topk_weights must match num_tokens in gating_output")
+    _req(gating_output.size(0) == topk_ids.size(0),
+         "First dimension of topk_indices must match num_tokens in gating_output")
+    _req(topk_weights.size(-1) == topk_ids.size(-1), "Second dimension of topk_indices must match topk in topk_weights")
+    _req(topk_weights.size(-1) <= gating_output.size(-1), "topk must be less than or equal to num_experts")
+    _req(topk_weights.dtype == torch.float32 and topk_ids.dtype == torch.int32,
+         "topk_weights must be float32 and topk_indices int32")
+    _req(gating_output.is_cuda and gating_output.is_contiguous() and topk_weights.is_contiguous()
+         and topk_ids.is_contiguous(), "tensors must be contiguous CUDA tensors")
+    with torch.cuda.device(gating_output.device):
+        check(lib().sglb200_topk_softmax(gating_output.data_ptr(), dtype_code(gating_output.dtype),
+                                         topk_weights.data_ptr(), topk_ids.data_ptr(), gating_output.size(0),
+                                         gating_output.size(1), topk_weights.size(1), int(bool(renormalize)),
+                                         _stream(gating_output)), "topk_softmax")
+
+
+def moe_align_block_size(topk_ids, num_experts, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad,
+                         cumsum_buffer, pad_sorted_token_ids=False) -> None:
+    """Block-aligned sort of the routed slots (``sgl-kernel/python/sgl_kernel/moe.py:6-25``, kernel
+    ``sgl-kernel/csrc/moe/moe_align_kernel.cu:302-364``).  ``num_experts`` is the number of BUCKETS, i.e. the
+    caller's expert count + 1 (bucket 0 takes id -1).  Slots of one bucket come out in ascending order."""
+    _req(topk_ids.is_cuda and topk_ids.dtype == torch.int32 and topk_ids.is_contiguous(),
+         "topk_ids must be a contiguous int32 CUDA tensor")
+    numel = topk_ids.numel()
+    cap = numel + num_experts * (block_size - 1)
+    for name, t, n in (("sorted_token_ids", sorted_token_ids, cap), ("experts_ids", experts_ids, -(-cap // block_size)),
+                       ("num_tokens_post_pad", num_tokens_post_pad, 1), ("cumsum_buffer", cumsum_buffer, num_experts + 1)):
+        _req(t.is_cuda and t.dtype == torch.int32 and t.is_contiguous() and t.numel() >= n,
+             f"{name} must be a contiguous int32 CUDA tensor with at least {n} elements")
+    with torch.cuda.device(topk_ids.device):
+        check(lib().sglb200_moe_align_block_size(topk_ids.data_ptr(), numel, num_experts, block_size,
+                                                 sorted_token_ids.data_ptr(), experts_ids.data_ptr(),
+                                                 num_tokens_post_pad.data_ptr(), cumsum_buffer.data_ptr(),
+                                                 int(bool(pad_sorted_token_ids)), _stream(topk_ids)),
+              "moe_align_block_size")
+
+
+def moe_sum_reduce(input_tensor, output_tensor, routed_scaling_factor=0) -> None:
+    """``output[t] = routed_scaling_factor * sum_j input[t, j]`` with an fp32 sum
+    (``sgl-kernel/python/sgl_kernel/moe.py:39-48``, ``sgl-kernel/csrc/moe/moe_sum_reduce.cu:227-403``).
+    bf16 / f16 only; ``hidden`` must be a multiple of 8."""
+    _req(input_tensor.is_cuda, "input must be CUDA tensor")
+    _req(output_tensor.is_cuda, "output must be CUDA tensor")
+    _req(input_tensor.dim() == 3, "input must be a 3D tensor like [token_num, topk_num, hidden_dim]")
+    _req(output_tensor.dim() == 2, "output must be [token_num, hidden_dim]")
+    _req(input_tensor.size(0) == output_tensor.size(0), "token dim mismatch")
+    _req(input_tensor.size(2) == output_tensor.size(1), "hidden_dim mismatch")
+    _req(input_tensor.is_contiguous(), "expect input to be contiguous")
+    _req(output_tensor.is_contiguous(), "expect output to be contiguous")
+    _req(input_tensor.dtype == output_tensor.dtype, "input/output dtype mismatch")
+    with torch.cuda.device(input_tensor.device):
+        check(lib().sglb200_moe_sum_reduce(input_tensor.data_ptr(), output_tensor.data_ptr(), input_tensor.size(0),
+                                           input_tensor.size(1), input_tensor.size(2), dtype_code(input_tensor.dtype),
+                                           float(routed_scaling_factor), _stream(input_tensor)), "moe_sum_reduce")

@@ -2,6 +2,7 @@
 (tests/golden/make_golden.py), plus the oracle's own layout and integer helpers."""
 
 import hashlib
+import os
 
 import numpy as np
 import pytest
@@ -126,3 +127,53 @@ def test_shuffle_and_combine_roundtrip():
     assert torch.equal(y, want)
     q = oracle.shuffle_rows(x.to(FP8), a_map)
     assert q.dtype == FP8 and torch.equal(q.view(torch.uint8)[0], x.to(FP8).view(torch.uint8)[a_map[0]])
+
+
+# ---- routing helpers: tests/golden/routing.npz (made by tests/golden/make_golden_routing.py) ----------
+ROUTING = np.load(os.path.join(os.path.dirname(__file__), "golden", "routing.npz"))
+TOPK_CASES = {"t33_e8_k2": (torch.float32, False), "t17_e64_k6_rn": (torch.float32, True),
+              "t29_e256_k8_rn": (torch.bfloat16, True), "t5_e160_k4": (torch.float16, False)}
+ALIGN_CASES = {"t1_k1_e8_b4": (8, 4), "t13_k2_e8_b4": (8, 4), "t40_k4_e16_b16": (16, 16),
+               "t64_k8_e64_b32": (64, 32), "t7_k3_e33_b64": (33, 64)}
+SUM_CASES = {"t33_k6_h128": torch.bfloat16, "t7_k8_h256_s": torch.bfloat16, "t5_k2_h64_f16": torch.float16}
+
+
+@pytest.mark.parametrize("name", sorted(TOPK_CASES))
+def test_oracle_topk_softmax_matches_reference(name):
+    dtype, renorm = TOPK_CASES[name]
+    g = torch.from_numpy(ROUTING[f"topk_{name}_g"]).to(dtype)
+    w_ref, ids_ref = ROUTING[f"topk_{name}_w"], ROUTING[f"topk_{name}_ids"]
+    k = ids_ref.shape[1]
+    w, ids = oracle.topk_softmax(g, k, renorm)
+    assert np.array_equal(w.numpy(), w_ref)
+    # torch.topk leaves the order of equal probabilities open (they occur with 16-bit logits); the kernel
+    # takes the lower index first (moe_topk_softmax_kernels.cu:372).  Rows without a tie must agree exactly.
+    top = torch.sort(torch.softmax(g.float(), -1), dim=-1, descending=True).values[:, :k + 1].numpy()
+    untied = (np.diff(top, axis=1) != 0).all(axis=1)
+    assert untied.sum() >= len(untied) // 2
+    assert np.array_equal(ids.numpy()[untied], ids_ref[untied])
+    p = torch.softmax(g.float(), -1).numpy()
+    assert np.array_equal(np.take_along_axis(p, ids.numpy().astype(np.int64), 1),
+                          np.take_along_axis(p, ids_ref.astype(np.int64), 1))
+
+
+@pytest.mark.parametrize("name", sorted(ALIGN_CASES))
+def test_oracle_moe_align_matches_reference(name):
+    E, bs = ALIGN_CASES[name]
+    ids = ROUTING[f"align_{name}_ids"]
+    sorted_ids, expert_ids, post, cumsum = oracle.moe_align_block_size(ids, bs, E)
+    assert post == int(ROUTING[f"align_{name}_post"][0])
+    assert np.array_equal(expert_ids, ROUTING[f"align_{name}_experts"])
+    assert np.array_equal(sorted_ids, ROUTING[f"align_{name}_sorted"])
+    assert cumsum[0] == 0 and cumsum[1] == 0  # bucket 0 (id -1) is empty without expert parallelism
+
+
+@pytest.mark.parametrize("name", sorted(SUM_CASES))
+def test_oracle_moe_sum_reduce_matches_fixture(name):
+    dtype = SUM_CASES[name]
+    x = torch.from_numpy(ROUTING[f"sum_{name}_x"]).view(dtype)
+    y = oracle.moe_sum_reduce(x, float(ROUTING[f"sum_{name}_scale"]))
+    assert np.array_equal(y.view(torch.int16).numpy(), ROUTING[f"sum_{name}_y"])
+    # the reference test's bar (sgl-kernel/tests/test_moe_align.py:261-268) against torch's own sum
+    if float(ROUTING[f"sum_{name}_scale"]) == 1.0:
+        torch.testing.assert_close(y, x.sum(dim=1), atol=2e-2, rtol=0)
