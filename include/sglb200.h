@@ -241,6 +241,26 @@ int sglb200_topk_softmax(const void* gating_output, int dtype, float* topk_weigh
                          int64_t num_tokens, int64_t num_experts, int64_t topk, int renormalize, void* stream);
 
 /*
+ * Sigmoid router with a selection bias and two-level top-k (the DeepSeek-V3 gate), always renormalised:
+ *   s = sigmoid(input[t, e]); b = s + bias[e] (both rounded to the input type);
+ *   score of a group (num_experts / num_expert_group consecutive experts) = sum of its two largest b;
+ *   the topk_group best groups stay (ties: lower group); inside them the topk - num_fused_shared_experts best b are
+ *   taken in descending order (ties: lower expert) with weight s; slots after them get the ids num_experts,
+ *   num_experts + 1, ... and the weight sum / routed_scaling_factor; every weight is then divided by the sum of the
+ *   routed weights and, with apply_routed_scaling_factor_on_output != 0, multiplied by routed_scaling_factor.
+ *   input [num_tokens, num_experts] and bias [num_experts] share dtype (SGLB200_BF16 | F16 | F32), contiguous;
+ *   topk_weights [num_tokens, topk] fp32, topk_ids [num_tokens, topk] int32.
+ * Limits: num_experts <= 1024 (any value divisible by num_expert_group, no power-of-two rule), num_expert_group <= 32,
+ *   at least 2 experts per group, topk <= 32.
+ * Replaces: moe_fused_gate  sgl-kernel/csrc/moe/moe_fused_gate.cu:52-262,378-525 (schema common_extension.cc:268-272);
+ *           torch-native twin biased_grouped_topk_impl  python/sglang/srt/layers/moe/topk.py:595-665.
+ */
+int sglb200_moe_fused_gate(const void* input, const void* bias, int dtype, float* topk_weights, int32_t* topk_ids,
+                           int64_t num_tokens, int64_t num_experts, int64_t num_expert_group, int64_t topk_group,
+                           int64_t topk, int64_t num_fused_shared_experts, float routed_scaling_factor,
+                           int apply_routed_scaling_factor_on_output, void* stream);
+
+/*
  * Block-aligned counting sort of the flattened expert ids, the routing table of the tile-gather MoE runner.
  * Bucket b (0 <= b < num_buckets) collects the slots whose id is b - 1; bucket 0 therefore holds id -1
  * (slots of experts another rank owns).  Each bucket is padded to a multiple of block_size.

@@ -11,8 +11,8 @@ torch-native functions (``native_per_token_group_quant_fp8``,
 files bit for bit.  The UE8M0 scale variant is defined by composition
 (``ceil_to_ue8m0(amax / 448)`` from ``fp8_utils.py:511-512`` applied inside the native
 quant function); no reference test pins it on random data.  The routing helpers (``topk_softmax``,
-``moe_align_block_size``, ``moe_sum_reduce``) are pinned by ``tests/golden/make_golden_routing.py``, which runs
-``fused_topk_torch_native`` (``python/sglang/srt/layers/moe/topk.py:402-431``) and the reference test's staged
+``moe_fused_gate``, ``moe_align_block_size``, ``moe_sum_reduce``) are pinned by ``tests/golden/make_golden_routing.py``, which runs
+``fused_topk_torch_native`` and ``biased_grouped_topk_impl`` (``python/sglang/srt/layers/moe/topk.py:402-431,594-665``) and the reference test's staged
 block-aligned sort (``sgl-kernel/tests/test_moe_align.py:17-148``) into ``tests/golden/routing.npz``.
 """
 
@@ -24,6 +24,7 @@ from .block_fp8 import (  # noqa: F401
     fused_experts_block_fp8,
     moe_align_block_size,
     moe_block_fp8_from_scores,
+    moe_fused_gate,
     moe_sum_reduce,
     pack_scales,
     per_token_group_quant_fp8,

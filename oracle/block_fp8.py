@@ -297,3 +297,38 @@ def moe_sum_reduce(x: torch.Tensor, routed_scaling_factor: float = 1.0) -> torch
     for j in range(x.shape[1]):
         acc = acc + x[:, j].float()
     return (acc * torch.tensor(routed_scaling_factor, dtype=torch.float32)).to(x.dtype)
+
+
+def moe_fused_gate(x: torch.Tensor, bias: torch.Tensor, num_expert_group: int, topk_group: int, topk: int,
+                   num_fused_shared_experts: int = 0, routed_scaling_factor: float = 0.0,
+                   apply_routed_scaling_factor_on_output: bool = False):
+    """``moe_fused_gate`` (``sgl-kernel/csrc/moe/moe_fused_gate.cu:104-258``; torch-native twin
+    ``biased_grouped_topk_impl``, ``python/sglang/srt/layers/moe/topk.py:611-661``): sigmoid, plus bias, group score =
+    sum of the two largest biased scores of a group, the ``topk_group`` best groups stay, the best biased scores
+    inside them are taken and weighted by the unbiased sigmoid, shared-expert slots get ``sum / factor``, everything
+    is divided by the routed sum.  Ties follow the kernel: lower group (``:147-150``), lower expert (``:192-196``);
+    the shared slots get the ids ``E, E + 1, ...`` (``:226-243``)."""
+    T, E = x.shape
+    s = torch.sigmoid(x.float()).to(x.dtype)
+    b = (s + bias.unsqueeze(0)).to(x.dtype)
+    gsz = E // num_expert_group
+    top2 = torch.sort(b.view(T, num_expert_group, gsz).float(), dim=-1, descending=True).values[..., :2]
+    gscore = (top2[..., 0].to(x.dtype) + top2[..., 1].to(x.dtype)).float()
+    gorder = torch.sort(gscore, dim=-1, descending=True, stable=True).indices[:, :topk_group]
+    gmask = torch.zeros(T, num_expert_group, dtype=torch.bool)
+    gmask.scatter_(1, gorder, True)
+    masked = b.float().masked_fill(~gmask.repeat_interleave(gsz, dim=1), float("-inf"))
+    k_real = topk - num_fused_shared_experts
+    ids = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, :k_real]
+    w = s.float().gather(1, ids)
+    total = torch.zeros(T, dtype=torch.float32)
+    for j in range(k_real):  # the kernel adds the weights in selection order
+        total = total + w[:, j]
+    if num_fused_shared_experts:
+        shared_w = (total / torch.tensor(routed_scaling_factor, dtype=torch.float32))[:, None]
+        w = torch.cat([w, shared_w.expand(T, num_fused_shared_experts)], dim=1)
+        ids = torch.cat([ids, (E + torch.arange(num_fused_shared_experts)).expand(T, -1)], dim=1)
+    w = w / total[:, None]
+    if apply_routed_scaling_factor_on_output:
+        w = w * torch.tensor(routed_scaling_factor, dtype=torch.float32)
+    return w, ids.to(torch.int32)

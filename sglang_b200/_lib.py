@@ -35,6 +35,7 @@ SIGNATURES = {
     "sglb200_apply_shuffle_mul_sum": [_P, _P, _P, _P, _L, _L, _L, _I, _I, _P],
     "sglb200_silu_and_mul": [_P, _P, _L, _L, _I, _P],
     "sglb200_topk_softmax": [_P, _I, _P, _P, _L, _L, _L, _I, _P],
+    "sglb200_moe_fused_gate": [_P, _P, _I, _P, _P, _L, _L, _L, _L, _L, _L, _F, _I, _P],
     "sglb200_moe_align_block_size": [_P, _L, _L, _L, _P, _P, _P, _P, _I, _P],
     "sglb200_moe_sum_reduce": [_P, _P, _L, _L, _L, _I, _F, _P],
     "sglb200_read_device_status": [],

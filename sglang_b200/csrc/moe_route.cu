@@ -95,6 +95,111 @@ topk_softmax_kernel(const T* __restrict__ logits, float* __restrict__ weights, i
 }
 
 // ------------------------------------------------------------------------------------------
+// moe_fused_gate: sigmoid router with a selection bias and two-level (group, then expert) top-k, one warp per
+// token.  s = sigmoid(x), b = s + bias (both rounded to the input type); a group's score is the sum of its two
+// largest b; the topk_group best groups stay (ties: lower group); inside them the topk best b (ties: lower
+// expert) are taken and weighted by s; weights are divided by their sum.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float round_to(float x);
+template <>
+__device__ __forceinline__ float round_to<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float round_to<__nv_bfloat16>(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+template <>
+__device__ __forceinline__ float round_to<__half>(float x) { return __half2float(__float2half_rn(x)); }
+
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(256)
+fused_gate_kernel(const T* __restrict__ logits, const T* __restrict__ bias, float* __restrict__ weights,
+                  int32_t* __restrict__ ids, int32_t num_tokens, int32_t E, int32_t G, int32_t topk_group,
+                  int32_t topk, int32_t n_shared, float rsf, int apply_rsf) {
+  extern __shared__ float gate_sm[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t token = (int64_t)blockIdx.x * (blockDim.x >> 5) + warp;
+  if (token >= num_tokens) return;
+  float* sb = gate_sm + (size_t)warp * E;
+  const T* row = logits + token * E;
+  float s[PER_LANE], b[PER_LANE];
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = i * 32 + lane;
+    s[i] = 0.f;
+    b[i] = -INFINITY;
+    if (e < E) {
+      s[i] = round_to<T>(__fdiv_rn(1.0f, 1.0f + expf(-to_f32<T>(row[e]))));
+      b[i] = round_to<T>(s[i] + to_f32<T>(bias[e]));
+      sb[e] = b[i];
+    }
+  }
+  __syncwarp();
+  const int gsz = E / G;
+  float gscore = -INFINITY;
+  if (lane < G) {
+    float m1 = -FLT_MAX, m2 = -FLT_MAX;
+    for (int j = 0; j < gsz; ++j) {
+      const float v = sb[lane * gsz + j];
+      if (v > m1) { m2 = m1; m1 = v; }
+      else if (v > m2) m2 = v;
+    }
+    gscore = round_to<T>(m1 + m2);
+  }
+  uint32_t keep = 0;
+  for (int t = 0; t < topk_group; ++t) {
+    float best = gscore;
+    int who = lane;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+      const int ow = __shfl_xor_sync(0xffffffffu, who, d);
+      if (ob > best || (ob == best && ow < who)) { best = ob; who = ow; }
+    }
+    keep |= 1u << who;
+    if (lane == who) gscore = -INFINITY;
+  }
+#pragma unroll
+  for (int i = 0; i < PER_LANE; ++i) {
+    const int e = i * 32 + lane;
+    if (e < E && !((keep >> (e / gsz)) & 1u)) b[i] = -INFINITY;
+  }
+  const int32_t topk_real = topk - n_shared;
+  float sum = 0.f, my_w = 0.f;
+  int32_t my_id = 0;
+  for (int32_t j = 0; j < topk_real; ++j) {
+    float best = -INFINITY;
+    int32_t best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+      const int e = i * 32 + lane;
+      if (b[i] > best) { best = b[i]; best_e = e; }  // taken and masked entries sit at -INFINITY and never win
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, d);
+      const int32_t oe = __shfl_xor_sync(0xffffffffu, best_e, d);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    float sw = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i)
+      if (i == (best_e >> 5)) { sw = s[i]; if ((best_e & 31) == lane) b[i] = -INFINITY; }
+    sw = __shfl_sync(0xffffffffu, sw, best_e & 31);
+    sum += sw;
+    if (lane == j) { my_w = sw; my_id = best_e; }
+  }
+  if (lane >= topk_real && lane < topk) {
+    my_w = __fdiv_rn(sum, rsf);
+    my_id = E + (lane - topk_real);
+  }
+  if (lane < topk) {
+    float r = __fdiv_rn(my_w, sum);
+    if (apply_rsf) r *= rsf;
+    weights[token * topk + lane] = r;
+    ids[token * topk + lane] = my_id;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // moe_align_block_size: stable counting sort of the flattened expert ids into buckets padded to a multiple of
 // block_size.  Bucket b holds id b - 1 (bucket 0 = id -1, the experts another rank owns).  One block.
 // ------------------------------------------------------------------------------------------
@@ -239,6 +344,27 @@ int launch_topk(const void* logits, float* w, int32_t* ids, int64_t tokens, int3
   return SGLB200_OK;
 }
 
+template <typename T>
+int launch_gate(const void* logits, const void* bias, float* w, int32_t* ids, int64_t tokens, int32_t E, int32_t G,
+                int32_t topk_group, int32_t topk, int32_t n_shared, float rsf, int apply_rsf, cudaStream_t st) {
+  const int per_lane = (E + 31) / 32;
+  const int blocks = (int)((tokens + 7) / 8);
+  const size_t smem = (size_t)8 * E * sizeof(float);
+#define SGLB_GATE(P)                                                                                        \
+  fused_gate_kernel<T, P><<<blocks, 256, smem, st>>>(static_cast<const T*>(logits), static_cast<const T*>(bias), w, \
+                                                     ids, (int32_t)tokens, E, G, topk_group, topk, n_shared, rsf,  \
+                                                     apply_rsf)
+  if (per_lane <= 1) SGLB_GATE(1);
+  else if (per_lane <= 2) SGLB_GATE(2);
+  else if (per_lane <= 4) SGLB_GATE(4);
+  else if (per_lane <= 8) SGLB_GATE(8);
+  else if (per_lane <= 16) SGLB_GATE(16);
+  else SGLB_GATE(32);
+#undef SGLB_GATE
+  SGLB_CHECK_LAUNCH("fused_gate_kernel");
+  return SGLB200_OK;
+}
+
 }  // namespace
 }  // namespace sglb
 
@@ -268,6 +394,49 @@ extern "C" int sglb200_topk_softmax(const void* gating_output, int dtype, float*
     default:
       return launch_topk<float>(gating_output, topk_weights, topk_ids, num_tokens, (int32_t)num_experts, (int32_t)topk,
                                 renormalize, st);
+  }
+}
+
+extern "C" int sglb200_moe_fused_gate(const void* input, const void* bias, int dtype, float* topk_weights,
+                                      int32_t* topk_ids, int64_t num_tokens, int64_t num_experts,
+                                      int64_t num_expert_group, int64_t topk_group, int64_t topk,
+                                      int64_t num_fused_shared_experts, float routed_scaling_factor,
+                                      int apply_routed_scaling_factor_on_output, void* stream) {
+  SGLB_REQUIRE(num_tokens >= 0 && num_tokens < ((int64_t)1 << 31), SGLB200_ERR_SHAPE, "num_tokens=%lld",
+               (long long)num_tokens);
+  SGLB_REQUIRE(num_experts >= 2 && num_experts <= 1024, SGLB200_ERR_SHAPE, "num_experts=%lld (2..1024)",
+               (long long)num_experts);
+  SGLB_REQUIRE(num_expert_group >= 1 && num_expert_group <= 32 && num_experts % num_expert_group == 0 &&
+                   num_experts / num_expert_group >= 2,
+               SGLB200_ERR_SHAPE, "num_expert_group=%lld must be 1..32, divide num_experts=%lld, and leave >= 2 experts per group",
+               (long long)num_expert_group, (long long)num_experts);
+  SGLB_REQUIRE(topk_group >= 1 && topk_group <= num_expert_group, SGLB200_ERR_SHAPE, "topk_group=%lld (1..%lld)",
+               (long long)topk_group, (long long)num_expert_group);
+  SGLB_REQUIRE(num_fused_shared_experts >= 0 && num_fused_shared_experts < topk, SGLB200_ERR_SHAPE,
+               "num_fused_shared_experts=%lld must be in 0..topk-1", (long long)num_fused_shared_experts);
+  SGLB_REQUIRE(topk >= 1 && topk <= 32 &&
+                   topk - num_fused_shared_experts <= topk_group * (num_experts / num_expert_group),
+               SGLB200_ERR_SHAPE, "topk=%lld must be 1..32 and fit into the selected groups", (long long)topk);
+  SGLB_REQUIRE(num_fused_shared_experts == 0 || routed_scaling_factor != 0.f, SGLB200_ERR_SHAPE,
+               "routed_scaling_factor must not be 0 with fused shared experts");
+  SGLB_REQUIRE(dtype == SGLB200_BF16 || dtype == SGLB200_F16 || dtype == SGLB200_F32, SGLB200_ERR_DTYPE, "dtype=%d",
+               dtype);
+  if (num_tokens == 0) return SGLB200_OK;
+  SGLB_REQUIRE(input && bias && topk_weights && topk_ids, SGLB200_ERR_NULL, "pointers must not be NULL");
+  if (int rc = arch_ok()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int32_t E = (int32_t)num_experts, G = (int32_t)num_expert_group, tg = (int32_t)topk_group, k = (int32_t)topk,
+                ns = (int32_t)num_fused_shared_experts;
+  switch (dtype) {
+    case SGLB200_BF16:
+      return launch_gate<__nv_bfloat16>(input, bias, topk_weights, topk_ids, num_tokens, E, G, tg, k, ns,
+                                        routed_scaling_factor, apply_routed_scaling_factor_on_output, st);
+    case SGLB200_F16:
+      return launch_gate<__half>(input, bias, topk_weights, topk_ids, num_tokens, E, G, tg, k, ns,
+                                 routed_scaling_factor, apply_routed_scaling_factor_on_output, st);
+    default:
+      return launch_gate<float>(input, bias, topk_weights, topk_ids, num_tokens, E, G, tg, k, ns,
+                                routed_scaling_factor, apply_routed_scaling_factor_on_output, st);
   }
 }
 

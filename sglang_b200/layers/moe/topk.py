@@ -41,3 +41,24 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int,
     _sgl_moe_align_block_size(topk_ids.contiguous(), num_experts + 1, block_size, sorted_ids, expert_ids,
                               num_tokens_post_pad, cumsum_buffer, True)
     return sorted_ids, expert_ids, num_tokens_post_pad
+
+
+def biased_grouped_topk(hidden_states: torch.Tensor, gating_output: torch.Tensor, correction_bias: torch.Tensor,
+                        topk: int, renormalize: bool, num_expert_group: Optional[int] = None,
+                        topk_group: Optional[int] = None, num_fused_shared_experts: int = 0,
+                        routed_scaling_factor: Optional[float] = None,
+                        num_token_non_padded: Optional[torch.Tensor] = None, expert_location_dispatch_info=None,
+                        apply_routed_scaling_factor_on_output: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The DeepSeek-V3 gate (``python/sglang/srt/layers/moe/topk.py:691-768``): sigmoid scores, selection bias,
+    group-limited top-k, renormalised weights.  One kernel for every expert count; like the reference's fused
+    kernel it always renormalises, so ``renormalize=False`` is refused."""
+    assert hidden_states.shape[0] == gating_output.shape[0], "Number of tokens mismatch"
+    if not renormalize:
+        raise RuntimeError("biased_grouped_topk: only renormalize=True is implemented (the fused gate renormalises)")
+    if num_token_non_padded is not None or expert_location_dispatch_info is not None:
+        raise RuntimeError("num_token_non_padded / expert_location_dispatch_info are not implemented")
+    from ...sgl_kernel import moe_fused_gate
+    return moe_fused_gate(gating_output.contiguous(), correction_bias.to(gating_output.dtype), num_expert_group,
+                          topk_group, topk, num_fused_shared_experts,
+                          routed_scaling_factor if routed_scaling_factor is not None else 0.0,
+                          apply_routed_scaling_factor_on_output)

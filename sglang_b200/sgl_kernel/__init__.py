@@ -15,6 +15,7 @@ from .moe import (  # noqa: F401
     apply_shuffle_mul_sum,
     fp8_blockwise_scaled_grouped_mm,
     moe_align_block_size,
+    moe_fused_gate,
     moe_sum_reduce,
     prepare_moe_input,
     shuffle_rows,

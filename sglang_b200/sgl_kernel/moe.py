@@ -188,3 +188,25 @@ def moe_sum_reduce(input_tensor, output_tensor, routed_scaling_factor=0) -> None
         check(lib().sglb200_moe_sum_reduce(input_tensor.data_ptr(), output_tensor.data_ptr(), input_tensor.size(0),
                                            input_tensor.size(1), input_tensor.size(2), dtype_code(input_tensor.dtype),
                                            float(routed_scaling_factor), _stream(input_tensor)), "moe_sum_reduce")
+
+
+def moe_fused_gate(input_tensor, bias, num_expert_group, topk_group, topk, num_fused_shared_experts=0,
+                   routed_scaling_factor=0, apply_routed_scaling_factor_on_output=False):
+    """Sigmoid + bias + grouped top-k gate of DeepSeek-V3, renormalised; returns ``(weights fp32, ids int32)``
+    (``sgl-kernel/python/sgl_kernel/moe.py:61-93``, kernel ``sgl-kernel/csrc/moe/moe_fused_gate.cu:378-525``).
+    Unlike the reference the expert count need not be a power of two and a group may hold more than 32 experts."""
+    _req(input_tensor.is_cuda and input_tensor.dim() == 2 and input_tensor.is_contiguous(),
+         "input must be a contiguous 2D CUDA tensor [num_tokens, num_experts]")
+    _req(bias.dim() == 1 and bias.size(0) == input_tensor.size(1), "input and bias should have the same num_experts")
+    _req(bias.dtype == input_tensor.dtype, "input and bias should have the same dtype")
+    num_rows, num_experts = input_tensor.shape
+    output = torch.empty(num_rows, topk, dtype=torch.float32, device=input_tensor.device)
+    indices = torch.empty(num_rows, topk, dtype=torch.int32, device=input_tensor.device)
+    with torch.cuda.device(input_tensor.device):
+        check(lib().sglb200_moe_fused_gate(input_tensor.data_ptr(), bias.contiguous().data_ptr(),
+                                           dtype_code(input_tensor.dtype), output.data_ptr(), indices.data_ptr(),
+                                           num_rows, num_experts, num_expert_group, topk_group, topk,
+                                           num_fused_shared_experts, float(routed_scaling_factor),
+                                           int(bool(apply_routed_scaling_factor_on_output)), _stream(input_tensor)),
+              "moe_fused_gate")
+    return output, indices

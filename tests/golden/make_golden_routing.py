@@ -8,6 +8,9 @@
   are the reference test's second implementation of the block-aligned sort.  They only use scalar
   ``tl.load`` / ``tl.store`` / ``tl.program_id`` / ``tl.cdiv`` / ``tl.minimum``, so they are executed
   unchanged with a few-line stand-in for those five names (one Python call per program id).
+* ``biased_grouped_topk_impl`` (``python/sglang/srt/layers/moe/topk.py:594-665``), the torch-native twin the
+  reference tests ``moe_fused_gate`` against (``sgl-kernel/tests/test_moe_fused_gate.py:44-56``), is executed
+  unchanged without its ``torch.compile`` decorator; the two id post-processing hooks it calls are identity here.
 * ``moe_sum_reduce``: the reference test's expectation is ``input.sum(dim=1)`` (``test_moe_align.py:261-268``);
   the kernel's own order (fp32, ascending j, then the factor, ``moe_sum_reduce.cu:146-170``) is stored.
 
@@ -87,6 +90,20 @@ def load_topk(ref_root):
     return ns["fused_topk_torch_native"]
 
 
+def load_gate(ref_root):
+    from typing import Optional
+    path = os.path.join(ref_root, "python/sglang/srt/layers/moe/topk.py")
+    tree = ast.parse(open(path).read())
+    ns = {"torch": torch, "Optional": Optional, "ExpertLocationDispatchInfo": object,
+          "topk_ids_logical_to_physical": lambda ids, info: ids,
+          "_mask_topk_ids_padded_region": lambda ids, n: None}
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name == "biased_grouped_topk_impl":
+            node.decorator_list = []
+            exec(compile(ast.Module([node], []), path, "exec"), ns)
+    return ns["biased_grouped_topk_impl"]
+
+
 def main(ref_root):
     gen = torch.Generator().manual_seed(1)
     out = {}
@@ -118,6 +135,23 @@ def main(ref_root):
         out[f"align_{name}_sorted"] = sorted_ids.numpy()
         out[f"align_{name}_experts"] = expert_ids.numpy()[: int(post) // bs]
         out[f"align_{name}_post"] = post.numpy()
+
+    # ---- moe_fused_gate (always renormalised, as the kernel)
+    gate_ref = load_gate(ref_root)
+    for name, T, E, G, tg, k, ns_, rsf, apply, dtype, kind in [
+            ("t37_e256_g8_tg4_k8", 37, 256, 8, 4, 8, 0, 2.5, False, torch.float32, "rand"),
+            ("t21_e256_g8_tg4_k9_s1", 21, 256, 8, 4, 9, 1, 2.5, True, torch.float32, "randn"),
+            ("t9_e128_g4_tg2_k4", 9, 128, 4, 2, 4, 0, 2.5, True, torch.float32, "randn"),
+            ("t13_e512_g16_tg8_k16", 13, 512, 16, 8, 16, 0, 1.0, False, torch.float32, "rand"),
+            ("t11_e96_g6_tg3_k5", 11, 96, 6, 3, 5, 0, 2.5, False, torch.float32, "randn")]:
+        x = (torch.rand(T, E, generator=gen) if kind == "rand" else torch.randn(T, E, generator=gen)).to(dtype)
+        bias = (torch.rand(E, generator=gen) * (1.0 if kind == "rand" else 0.1)).to(dtype)
+        torch.manual_seed(0)  # the shared-expert id of the torch-native function is random
+        w, ids = gate_ref(x, x, bias, k, True, G, tg, ns_, rsf, None, None, apply)
+        out[f"gate_{name}_x"] = x.float().numpy()
+        out[f"gate_{name}_bias"] = bias.float().numpy()
+        out[f"gate_{name}_w"] = w.float().numpy()
+        out[f"gate_{name}_ids"] = ids.to(torch.int32).numpy()
 
     # ---- moe_sum_reduce
     for name, T, k, H, scale, dtype in [("t33_k6_h128", 33, 6, 128, 1.0, torch.bfloat16),

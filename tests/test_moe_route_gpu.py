@@ -217,3 +217,105 @@ def test_routed_moe_from_logits_golden(name, topk):
     s_ref, e_ref, post_ref, _ = oracle.moe_align_block_size(ids.cpu().numpy(), 16, E)
     assert int(post) == post_ref and np.array_equal(s.cpu().numpy()[:post_ref], s_ref[:post_ref])
     assert np.array_equal(e.cpu().numpy()[:post_ref // 16], e_ref)
+
+
+def _gate(x, bias, G, tg, k, n_shared=0, rsf=2.5, apply=False):
+    from sglang_b200.sgl_kernel import moe_fused_gate
+    w, ids = moe_fused_gate(x.cuda(), bias.cuda(), G, tg, k, n_shared, rsf, apply)
+    torch.cuda.synchronize()
+    return w.cpu(), ids.cpu()
+
+
+def _check_gate(x, bias, G, tg, k, n_shared, rsf, apply):
+    w, ids = _gate(x, bias, G, tg, k, n_shared, rsf, apply)
+    w_ref, ids_ref = oracle.moe_fused_gate(x, bias, G, tg, k, n_shared, rsf, apply)
+    E = x.size(1)
+    k_real = k - n_shared
+    assert torch.equal(ids[:, k_real:], ids_ref[:, k_real:])  # shared slots: E, E + 1, ...
+    # rows whose group choice and expert choice are decided by gaps above 1e-6 must agree id for id
+    s = torch.sigmoid(x.float()).to(x.dtype)
+    b = (s + bias).to(x.dtype).float()
+    gs = torch.sort(b.view(x.size(0), G, E // G), dim=-1, descending=True).values[..., :2].sum(-1)
+    gsorted = torch.sort(gs, dim=-1, descending=True).values
+    clear = torch.ones(x.size(0), dtype=torch.bool)
+    if tg < G:
+        d = gsorted[:, tg - 1] - gsorted[:, tg]
+        clear &= (d > 1e-6 * gsorted[:, tg - 1].abs()) | (d == 0)
+    rows = torch.arange(x.size(0))
+    picked = b[rows[:, None], ids_ref[:, :k_real].long()]
+    kept = torch.zeros(x.size(0), G, dtype=torch.bool)
+    kept.scatter_(1, torch.sort(gs, dim=-1, descending=True, stable=True).indices[:, :tg], True)
+    rest = b.masked_fill(~kept.repeat_interleave(E // G, dim=1), -float("inf"))
+    rest[rows[:, None], ids_ref[:, :k_real].long()] = -float("inf")
+    seq = torch.cat([picked, rest.max(-1, keepdim=True).values], dim=1)
+    d = seq[:, :-1] - seq[:, 1:]
+    if x.dtype == torch.float32:
+        clear &= ((d > 1e-6 * seq[:, :-1].abs()) | (d == 0)).all(dim=1)
+    assert clear.float().mean() > 0.8 or x.size(0) < 16
+    if x.dtype == torch.float32:
+        assert torch.equal(ids[clear], ids_ref[clear])
+        torch.testing.assert_close(w[clear], w_ref[clear], rtol=1e-5, atol=1e-7)
+    else:
+        # a sigmoid within an fp32 ulp of a 16-bit rounding boundary may round the other way on the GPU and move
+        # one selection: nearly all rows must agree id for id, and those rows within one 16-bit ulp in weight
+        same = (ids == ids_ref).all(dim=1) & clear
+        assert same.float().mean() > 0.97
+        torch.testing.assert_close(w[same], w_ref[same], rtol=1e-2, atol=1e-7)
+    total = w[:, :k_real].sum(-1) / (rsf if apply else 1.0)
+    torch.testing.assert_close(total, torch.ones_like(total), rtol=1e-5, atol=0)
+    assert (ids[:, :k_real] >= 0).all() and (ids[:, :k_real] < E).all()
+
+
+@pytest.mark.parametrize("name,G,tg,n_shared,rsf,apply", [
+    ("t37_e256_g8_tg4_k8", 8, 4, 0, 2.5, False), ("t21_e256_g8_tg4_k9_s1", 8, 4, 1, 2.5, True),
+    ("t9_e128_g4_tg2_k4", 4, 2, 0, 2.5, True), ("t13_e512_g16_tg8_k16", 16, 8, 0, 1.0, False),
+    ("t11_e96_g6_tg3_k5", 6, 3, 0, 2.5, False)])
+def test_moe_fused_gate_golden(name, G, tg, n_shared, rsf, apply):
+    x, bias = torch.from_numpy(ROUTING[f"gate_{name}_x"]), torch.from_numpy(ROUTING[f"gate_{name}_bias"])
+    w_ref, ids_ref = ROUTING[f"gate_{name}_w"], ROUTING[f"gate_{name}_ids"]
+    w, ids = _gate(x, bias, G, tg, ids_ref.shape[1], n_shared, rsf, apply)
+    o = np.argsort(ids.numpy(), axis=1, kind="stable")
+    o_ref = np.argsort(ids_ref, axis=1, kind="stable")
+    assert np.array_equal(np.take_along_axis(ids.numpy(), o, 1), np.take_along_axis(ids_ref, o_ref, 1))
+    np.testing.assert_allclose(np.take_along_axis(w.numpy(), o, 1), np.take_along_axis(w_ref, o_ref, 1), rtol=1e-5)
+
+
+@pytest.mark.parametrize("T", [1, 7, 64, 1024, 8192])
+@pytest.mark.parametrize("E,G,tg,k", [(128, 4, 2, 4), (256, 8, 4, 8), (512, 16, 8, 16), (96, 6, 3, 5), (1024, 32, 4, 32),
+                                      (64, 1, 1, 6)])
+@pytest.mark.parametrize("n_shared", [0, 1, 2])
+@pytest.mark.parametrize("apply", [False, True])
+def test_moe_fused_gate_parity(T, E, G, tg, k, n_shared, apply):
+    gen = torch.Generator().manual_seed(T + E + n_shared)
+    x = torch.rand(T, E, generator=gen) if (T & 1) else torch.randn(T, E, generator=gen)
+    bias = torch.rand(E, generator=gen)
+    if k + n_shared > 32:
+        k -= n_shared
+    _check_gate(x, bias, G, tg, k + n_shared, n_shared, 2.5, apply)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_moe_fused_gate_16bit(dtype):
+    gen = torch.Generator().manual_seed(11)
+    x = torch.randn(512, 256, generator=gen).to(dtype)
+    bias = (torch.rand(256, generator=gen) * 0.1).to(dtype)
+    _check_gate(x, bias, 8, 4, 8, 0, 2.5, False)
+
+
+def test_moe_fused_gate_rejects_and_layer_entry():
+    from sglang_b200.layers.moe.topk import biased_grouped_topk
+    from sglang_b200.sgl_kernel import moe_fused_gate
+    x = torch.zeros(4, 256, device="cuda")
+    bias = torch.zeros(256, device="cuda")
+    with pytest.raises(RuntimeError, match="num_expert_group"):
+        moe_fused_gate(x, bias, 7, 4, 8)
+    with pytest.raises(RuntimeError, match="fit into the selected groups"):
+        moe_fused_gate(x, bias, 32, 1, 9)
+    with pytest.raises(RuntimeError, match="same num_experts"):
+        moe_fused_gate(x, bias[:128], 8, 4, 8)
+    # identical scores everywhere: groups 0..3, experts 0..7, equal weights
+    w, ids = biased_grouped_topk(x, x, bias, 8, True, 8, 4, routed_scaling_factor=2.5)
+    assert torch.equal(ids.cpu(), torch.arange(8, dtype=torch.int32).repeat(4, 1))
+    torch.testing.assert_close(w.cpu(), torch.full((4, 8), 0.125))
+    with pytest.raises(RuntimeError, match="renormalize"):
+        biased_grouped_topk(x, x, bias, 8, False, 8, 4)

@@ -177,3 +177,33 @@ def test_oracle_moe_sum_reduce_matches_fixture(name):
     # the reference test's bar (sgl-kernel/tests/test_moe_align.py:261-268) against torch's own sum
     if float(ROUTING[f"sum_{name}_scale"]) == 1.0:
         torch.testing.assert_close(y, x.sum(dim=1), atol=2e-2, rtol=0)
+
+
+GATE_CASES = {"t37_e256_g8_tg4_k8": (8, 4, 0, 2.5, False), "t21_e256_g8_tg4_k9_s1": (8, 4, 1, 2.5, True),
+              "t9_e128_g4_tg2_k4": (4, 2, 0, 2.5, True), "t13_e512_g16_tg8_k16": (16, 8, 0, 1.0, False),
+              "t11_e96_g6_tg3_k5": (6, 3, 0, 2.5, False)}
+
+
+def by_id(w, ids):
+    """Rows sorted by expert id: the torch-native gate returns its selection in no particular order."""
+    order = np.argsort(ids, axis=1, kind="stable")
+    return np.take_along_axis(w, order, 1), np.take_along_axis(ids, order, 1)
+
+
+@pytest.mark.parametrize("name", sorted(GATE_CASES))
+def test_oracle_moe_fused_gate_matches_reference(name):
+    G, tg, n_shared, rsf, apply = GATE_CASES[name]
+    x, bias = torch.from_numpy(ROUTING[f"gate_{name}_x"]), torch.from_numpy(ROUTING[f"gate_{name}_bias"])
+    w_ref, ids_ref = ROUTING[f"gate_{name}_w"], ROUTING[f"gate_{name}_ids"]
+    w, ids = oracle.moe_fused_gate(x, bias, G, tg, ids_ref.shape[1], n_shared, rsf, apply)
+    w, ids = w.numpy(), ids.numpy()
+    assert (ids_ref[:, ids_ref.shape[1] - n_shared:] >= x.shape[1]).all()
+    w_s, ids_s = by_id(w, ids)
+    w_rs, ids_rs = by_id(w_ref, ids_ref)
+    assert np.array_equal(ids_s, ids_rs)
+    np.testing.assert_allclose(w_s, w_rs, rtol=2e-6, atol=0)  # the sum is taken in a different order
+    # the kernel's order: descending biased score among the routed slots
+    k_real = ids.shape[1] - n_shared
+    b = (torch.sigmoid(x) + bias).numpy()
+    picked = np.take_along_axis(b, ids[:, :k_real].astype(np.int64), 1)
+    assert (np.diff(picked, axis=1) <= 0).all()
