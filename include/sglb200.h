@@ -292,8 +292,53 @@ int sglb200_moe_sum_reduce(const void* input, void* output, int64_t num_tokens, 
                            int dtype, float routed_scaling_factor, void* stream);
 
 /*
+ * GEMM + all-reduce over peer memory for the row-parallel linear at small M (each rank holds a K-slice and produces a
+ * full [M, N] partial sum).  Two launches per rank, no collective library call:
+ *   1. sglb200_fp8_blockwise_scaled_mm_push: the GEMM of sglb200_fp8_blockwise_scaled_mm whose epilogue stores every
+ *      output tile straight into the receive buffer of EVERY rank (peer stores over NVLink; slot [epoch & 1][rank])
+ *      and then raises that tile's flag words there, so the transfer runs tile by tile under the remaining math.
+ *   2. sglb200_peer_reduce: waits (bounded) per tile until all `world` ranks' flag words reached `epoch`, adds the
+ *      `world` slots in fp32 in ascending rank order (every rank gets the same bits) and writes `out`.
+ * Memory, per rank, mapped by every rank (sglb200_peer_alloc / sglb200_peer_open, or any peer-accessible allocation):
+ *   receive buffer  sglb200_peer_recv_bytes(slot_elems) bytes = [2][8][slot_elems] 16-bit elements, M * N <= slot_elems;
+ *   flag words      sglb200_peer_flag_bytes() bytes, zero before the first call.
+ * peer_recv / peer_flags are HOST arrays of `world` device pointers, entry r = rank r's buffer as mapped in this
+ * process.  `epoch` starts at 1 and grows by 1 per exchange, the same value on every rank.  Rules: all ranks issue the
+ * same sequence of exchanges, each on ONE stream per rank (the two alternating slot sets are safe exactly because a
+ * rank's exchange e + 1 is enqueued after its exchange e); at most 1024 output tiles of 128 x 128; world <= 8.
+ * A wait that runs out (a rank that never pushed) leaves the tile unwritten and sets device status 5
+ * (sglb200_read_device_status); timeout_ns <= 0 selects 2 s.
+ * Replaces: the one-shot path of the custom all-reduce the reference uses under its row-parallel linear at small sizes
+ *           (sgl-kernel/csrc/allreduce/custom_all_reduce.cuh:203-266, python/sglang/srt/layers/linear.py:1379-1380,
+ *           python/sglang/srt/distributed/device_communicators/custom_all_reduce.py), fused with the GEMM before it.
+ */
+int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b, const float* sa, const float* sb, int64_t M,
+                                         int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t sa_stride_m,
+                                         int64_t sa_stride_k, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
+                                         void* const* peer_recv, void* const* peer_flags, int rank, int world,
+                                         uint32_t epoch, int64_t slot_elems, void* stream);
+int sglb200_peer_reduce(const void* recv_local, const void* flags_local, void* out, int64_t M, int64_t N, int64_t ldc,
+                        int out_dtype, int world, uint32_t epoch, int64_t slot_elems, int64_t timeout_ns,
+                        void* stream);
+int64_t sglb200_peer_flag_bytes(void);
+int64_t sglb200_peer_recv_bytes(int64_t slot_elems);
+
+/*
+ * Set-up calls for the buffers above; the only entry points that ALLOCATE device memory, and they synchronise.
+ * sglb200_peer_alloc: cudaMalloc + zero fill on the current device, and the 64-byte CUDA IPC handle another process
+ * passes to sglb200_peer_open to map the same memory (peer access is enabled on first use).  sglb200_peer_close
+ * unmaps an opened pointer, sglb200_peer_free releases an allocated one.
+ * Replaces: the IPC buffer set-up of custom_all_reduce.py (create_shared_buffer / free_shared_buffer) and
+ *           sgl-kernel/csrc/allreduce/custom_all_reduce.cu (init_custom_ar, register_buffer).
+ */
+int sglb200_peer_alloc(int64_t bytes, void** dev_ptr, unsigned char* handle64);
+int sglb200_peer_open(const unsigned char* handle64, void** dev_ptr);
+int sglb200_peer_close(void* dev_ptr);
+int sglb200_peer_free(void* dev_ptr);
+
+/*
  * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
- * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps).  Reading clears it.  This call SYNCHRONISES the
+ * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce).  Reading clears it.  This call SYNCHRONISES the
  * device (cudaMemcpyFromSymbol); it is for tests and debugging, not for the serving path.  Returns -1 if the
  * read itself failed.  No counterpart in the reference (its kernels have no bounded waits).
  */

@@ -50,6 +50,20 @@ constexpr int kGroupM = 16;  // m-tiles per raster group (dense)
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/ +
                               (kMaxExperts + 1) * sizeof(int32_t);
 
+// Push epilogue (dense, one tile per (m, n)): instead of writing `out`, every output tile is stored into the receive
+// buffer of every rank, in the slot of this rank, and flagged there.  Receive buffer of a rank:
+// [2 sets][kMaxPeers sources][slot_elems] elements; flags: [2][kMaxPeers][kPushMaxTiles][kEpiWarps] words holding the
+// epoch of the last completed store.  set = epoch & 1.
+constexpr int kMaxPeers = 8;
+constexpr int kPushMaxTiles = 1024;
+struct PushParams {
+  void* dst[kMaxPeers];
+  uint32_t* flag[kMaxPeers];
+  int32_t world, rank;
+  uint32_t epoch;
+  int64_t slot_elems;
+};
+
 struct GemmParams {
   const float* sa;
   const float* sb;
@@ -66,6 +80,7 @@ struct GemmParams {
   // its fp32 partial sums to partial[split][row][col] (row stride N) and a second kernel adds the splits up
   float* partial;
   int32_t k_splits, kb_per_split;
+  PushParams push;
 };
 
 struct Tile {
@@ -174,7 +189,7 @@ __device__ __forceinline__ void fma32(float2* acc, const uint32_t (&v)[32], floa
     acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), scale2, acc[j]);
 }
 
-template <bool GROUPED>
+template <bool GROUPED, bool PUSH>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const GemmParams p) {
@@ -389,7 +404,34 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         }
       }
       if (!ok || ctl->abort_flag) break;
-      if (row < tl.row_end) {
+      if constexpr (PUSH) {
+        const int32_t n_first = tl.n0 + col0;
+        const uint32_t set = p.push.epoch & 1u;
+        const int64_t slot = ((int64_t)set * kMaxPeers + p.push.rank) * p.push.slot_elems;
+        if (row < tl.row_end) {
+          for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
+            int pr = p.push.rank + 1 + i;
+            if (pr >= p.push.world) pr -= p.push.world;
+            if (p.out_dtype == SGLB200_BF16) {
+              store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first,
+                                       n_first, p.N);
+            } else {
+              store_row<__half>(acc, static_cast<__half*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first, n_first,
+                                p.N);
+            }
+          }
+        }
+        // the warp's 32 rows x 64 columns are on their way: order them before the flag, one flag word per warp
+        __syncwarp();
+        if (lane < p.push.world) {
+          const int32_t tile_id = (tl.row0 / BM) * p.n_tiles + tl.n0 / BN;
+          uint32_t* f = p.push.flag[lane] +
+                        (((int64_t)set * kMaxPeers + p.push.rank) * kPushMaxTiles + tile_id) * kEpiWarps +
+                        (warp - 2 * kIssuers);
+          __threadfence_system();
+          ptx::st_release_sys_u32(f, p.push.epoch);
+        }
+      } else if (row < tl.row_end) {
         const int32_t n_first = tl.n0 + col0;
         if (p.partial != nullptr) {
           float* dst = p.partial + ((int64_t)tl.split * p.total_rows + row) * p.N + n_first;
@@ -445,6 +487,65 @@ splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, 
   }
 }
 
+// Receiving side of the push epilogue: out[m, n] = cast(sum over source ranks of their slot), fp32, ascending rank (so
+// every rank computes the same bits).  One tile per loop step; 8 * world threads wait (bounded) for the tile's flag
+// words to reach `epoch`.  On a time-out the block records status 5 and returns without writing the tile.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+peer_reduce_kernel(const OutT* recv, const uint32_t* flags, OutT* __restrict__ out, int32_t M, int32_t N, int64_t ldc,
+                   int32_t n_tiles, int32_t total_tiles, int32_t world, uint32_t epoch, int64_t slot_elems,
+                   uint64_t limit_ns) {
+  __shared__ int s_ok;
+  const uint32_t set = epoch & 1u;
+  for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < world * kEpiWarps) {
+      const int src = threadIdx.x / kEpiWarps, w = threadIdx.x % kEpiWarps;
+      const uint32_t* f = flags + (((int64_t)set * kMaxPeers + src) * kPushMaxTiles + t) * kEpiWarps + w;
+      uint64_t t0 = 0;
+      uint32_t polls = 0;
+      while ((int32_t)(ptx::ld_acquire_sys_u32(f) - epoch) < 0) {
+        if ((++polls & 255u) == 0) {
+          const uint64_t now = ptx::global_timer_ns();
+          if (t0 == 0) {
+            t0 = now;
+          } else if ((int64_t)(now - t0) > (int64_t)limit_ns) {
+            s_ok = 0;
+            atomicCAS(&g_device_status, 0, 5);
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
+    const int32_t rows = min(BM, M - mt * BM), vecs = min(BN, N - nt * BN) / 8;
+    for (int32_t i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
+      const int32_t r = i / vecs, c = (i - r * vecs) * 8;
+      const int64_t off = (int64_t)(mt * BM + r) * N + nt * BN + c;
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+      for (int src = 0; src < world; ++src) {
+        // written by another GPU since this SM may last have cached the line: bypass L1
+        const uint4 u = __ldcv(reinterpret_cast<const uint4*>(recv + ((int64_t)set * kMaxPeers + src) * slot_elems + off));
+        const OutT* h = reinterpret_cast<const OutT*>(&u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) a[j] += static_cast<float>(h[j]);
+      }
+      uint4 o;
+      o.x = pack2<OutT>(a[0], a[1]);
+      o.y = pack2<OutT>(a[2], a[3]);
+      o.z = pack2<OutT>(a[4], a[5]);
+      o.w = pack2<OutT>(a[6], a[7]);
+      *reinterpret_cast<uint4*>(out + (int64_t)(mt * BM + r) * ldc + nt * BN + c) = o;
+    }
+    __syncthreads();
+  }
+}
+
 // ------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -492,13 +593,13 @@ int splitk_choice(int64_t M, int64_t N, int64_t K, int sm_count) {
   return splits < 2 ? 1 : (int)splits;
 }
 
-template <bool GROUPED>
+template <bool GROUPED, bool PUSH>
 int set_smem_attr_once() {
   static bool done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<GROUPED, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kSmemBytes);
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     done[dev] = true;
@@ -510,7 +611,7 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
                 const int32_t* expert_offsets, const int32_t* problem_sizes, int64_t total_rows, int64_t num_experts, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
                 int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream,
-                float* workspace = nullptr, int64_t workspace_floats = 0) {
+                float* workspace = nullptr, int64_t workspace_floats = 0, const PushParams* push = nullptr) {
   const bool grouped = expert_offsets != nullptr;
   SGLB_REQUIRE(total_rows >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size",
                (long long)total_rows, (long long)N, (long long)K);
@@ -576,7 +677,8 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   p.partial = nullptr;
   p.k_splits = 1;
   p.kb_per_split = p.k_tiles;
-  if (!grouped && workspace != nullptr) {
+  if (push) p.push = *push;
+  if (!grouped && workspace != nullptr && !push) {
     const int splits = splitk_choice(total_rows, N, K, di.sm_count);
     if (splits > 1 && (int64_t)splits * total_rows * N <= workspace_floats) {
       p.partial = workspace;
@@ -587,16 +689,21 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (grouped) {
-    if (int rc = set_smem_attr_once<true>()) return rc;
+    if (int rc = set_smem_attr_once<true, false>()) return rc;
     // an upper bound on the tile count without reading the device: every expert can add one ragged m-tile
     const int64_t max_tiles = ((total_rows + BM - 1) / BM + num_experts) * p.n_tiles;
     const int grid = (int)(max_tiles < di.sm_count ? max_tiles : di.sm_count);
-    fp8_block_gemm_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+    fp8_block_gemm_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+  } else if (push) {
+    if (int rc = set_smem_attr_once<false, true>()) return rc;
+    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+    const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
+    fp8_block_gemm_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
   } else {
-    if (int rc = set_smem_attr_once<false>()) return rc;
+    if (int rc = set_smem_attr_once<false, false>()) return rc;
     const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-    fp8_block_gemm_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+    fp8_block_gemm_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
     if (p.partial != nullptr) {
       SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
       const int64_t vecs = total_rows * (N / 8);
@@ -726,6 +833,89 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void
 // Reads (and clears) the device-side status word: 0, or the code of the first bounded wait that
 // timed out (1 producer, 2/3 MMA issuer, 4 promotion warps).  Synchronises the device: for tests
 // and debugging, not for the serving path.
+extern "C" int64_t sglb200_peer_flag_bytes(void) {
+  return (int64_t)2 * sglb::kMaxPeers * sglb::kPushMaxTiles * sglb::kEpiWarps * (int64_t)sizeof(uint32_t);
+}
+
+extern "C" int64_t sglb200_peer_recv_bytes(int64_t slot_elems) {
+  return (int64_t)2 * sglb::kMaxPeers * slot_elems * 2;
+}
+
+namespace sglb {
+namespace {
+int check_push_args(int64_t M, int64_t N, int world, int rank, uint32_t epoch, int64_t slot_elems) {
+  SGLB_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, SGLB200_ERR_SHAPE,
+               "world=%d (1..%d) rank=%d", world, kMaxPeers, rank);
+  SGLB_REQUIRE(epoch != 0, SGLB200_ERR_SHAPE, "epoch must start at 1 (the flag words start at 0)");
+  SGLB_REQUIRE(slot_elems % 8 == 0 && M * N <= slot_elems, SGLB200_ERR_WORKSPACE,
+               "M*N=%lld does not fit a receive slot of %lld elements (a multiple of 8)", (long long)(M * N),
+               (long long)slot_elems);
+  SGLB_REQUIRE(((M + BM - 1) / BM) * ((N + BN - 1) / BN) <= kPushMaxTiles, SGLB200_ERR_WORKSPACE,
+               "more than %d output tiles: too large for the one-shot exchange", kPushMaxTiles);
+  return SGLB200_OK;
+}
+}  // namespace
+}  // namespace sglb
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b, const float* sa, const float* sb,
+                                                    int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                                    int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                                                    int64_t sb_stride_k, int out_dtype, void* const* peer_recv,
+                                                    void* const* peer_flags, int rank, int world, uint32_t epoch,
+                                                    int64_t slot_elems, void* stream) {
+  using namespace sglb;
+  if (int rc = check_push_args(M, N, world, rank, epoch, slot_elems)) return rc;
+  SGLB_REQUIRE(peer_recv && peer_flags, SGLB200_ERR_NULL, "peer_recv / peer_flags must not be NULL");
+  PushParams push;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    push.dst[i] = i < world ? peer_recv[i] : nullptr;
+    push.flag[i] = i < world ? static_cast<uint32_t*>(peer_flags[i]) : nullptr;
+    SGLB_REQUIRE(i >= world || (push.dst[i] && push.flag[i] && aligned(push.dst[i], 16) && aligned(push.flag[i], 4)),
+                 SGLB200_ERR_NULL, "peer %d: receive buffer / flags missing or misaligned", i);
+  }
+  push.world = world;
+  push.rank = rank;
+  push.epoch = epoch;
+  push.slot_elems = slot_elems;
+  return gemm_common(a, b, sa, sb, push.dst[rank], nullptr, nullptr, M, 1, N, K, lda, ldb, 0, N, sa_stride_m, sa_stride_k,
+                     0, sb_stride_n, sb_stride_k, out_dtype, stream, nullptr, 0, &push);
+}
+
+extern "C" int sglb200_peer_reduce(const void* recv_local, const void* flags_local, void* out, int64_t M, int64_t N,
+                                   int64_t ldc, int out_dtype, int world, uint32_t epoch, int64_t slot_elems,
+                                   int64_t timeout_ns, void* stream) {
+  using namespace sglb;
+  SGLB_REQUIRE(M >= 0 && N >= 0 && N % 8 == 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld (N must be a multiple of 8)",
+               (long long)M, (long long)N);
+  if (int rc = check_push_args(M, N, world, 0, epoch, slot_elems)) return rc;
+  SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "out_dtype=%d", out_dtype);
+  if (M == 0 || N == 0) return SGLB200_OK;
+  SGLB_REQUIRE(recv_local && flags_local && out, SGLB200_ERR_NULL, "recv_local / flags_local / out must not be NULL");
+  SGLB_REQUIRE(ldc >= N && ldc % 8 == 0 && aligned(out, 16) && aligned(recv_local, 16), SGLB200_ERR_ALIGN,
+               "ldc=%lld must be >= N and a multiple of 8; out and recv_local 16-byte aligned", (long long)ldc);
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
+               di.cc_major, di.cc_minor);
+  const int32_t n_tiles = (int32_t)((N + BN - 1) / BN);
+  const int32_t tiles = (int32_t)((M + BM - 1) / BM) * n_tiles;
+  const int grid = tiles < 2 * di.sm_count ? tiles : 2 * di.sm_count;
+  const uint64_t limit = timeout_ns > 0 ? (uint64_t)timeout_ns : 2000000000ull;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == SGLB200_BF16) {
+    peer_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(recv_local), static_cast<const uint32_t*>(flags_local),
+        static_cast<__nv_bfloat16*>(out), (int32_t)M, (int32_t)N, ldc, n_tiles, tiles, world, epoch, slot_elems, limit);
+  } else {
+    peer_reduce_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(recv_local),
+                                                    static_cast<const uint32_t*>(flags_local), static_cast<__half*>(out),
+                                                    (int32_t)M, (int32_t)N, ldc, n_tiles, tiles, world, epoch,
+                                                    slot_elems, limit);
+  }
+  SGLB_CHECK_LAUNCH("peer_reduce_kernel");
+  return SGLB200_OK;
+}
+
 namespace sglb {
 int ue8m0_take_device_status();  // gemm_ue8m0.cu
 }

@@ -77,20 +77,34 @@ class ColumnParallelBlockFp8Linear(_ParallelBase):
 class RowParallelBlockFp8Linear(_ParallelBase):
     """``Y = sum_r X_r W_r^T``: each rank owns ``K / tp`` input features of the weight and the
     matching slice of the activations; the partial outputs are summed with one all-reduce
-    (``linear.py:1361-1386``).  The bias is added once, on rank 0, before the reduction."""
+    (``linear.py:1361-1386``).  The bias is added once, on rank 0, before the reduction.
+
+    With a ``peer_exchange`` (:class:`~sglang_b200.distributed.peer_allreduce.PeerExchange`) and an output that fits
+    its receive slot, the GEMM pushes its tiles into every rank's memory and the sum is taken there: no NCCL call
+    (the reference switches to its custom all-reduce below a size threshold the same way,
+    ``custom_all_reduce.py: should_custom_ar``).  Larger outputs take the NCCL all-reduce."""
 
     def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
                  input_is_parallel: bool = True, reduce_results: bool = True,
-                 apply_fn: Optional[Callable] = None, group=None):
+                 apply_fn: Optional[Callable] = None, group=None, peer_exchange=None):
         w, s = shard_block_fp8_weight(weight, scale, rank, world, 1)
         super().__init__(w, s, bias if rank == 0 else None, apply_fn, group)
         self.rank, self.world = rank, world
         self.input_is_parallel, self.reduce_results = input_is_parallel, reduce_results
+        self.peer_exchange = peer_exchange
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.input_is_parallel:
             per = x.shape[-1] // self.world
             x = x.narrow(-1, self.rank * per, per).contiguous()
+        ex = self.peer_exchange
+        if (ex is not None and self.reduce_results and self.world > 1 and x.is_cuda
+                and ex.fits(x.numel() // x.shape[-1], self.weight.shape[0])):
+            from .peer_allreduce import fused_row_parallel_linear
+            y = fused_row_parallel_linear(ex, x, self.weight, self.weight_scale_inv, None)
+            if self.bias is not None:  # held by rank 0 only: every rank needs it after the sum
+                raise RuntimeError("peer_exchange with a bias is not implemented")
+            return y
         y = self._apply(self, x, self.bias)
         if self.reduce_results:
             y = tensor_model_parallel_all_reduce(y, self.group)

@@ -58,6 +58,28 @@ def _worker(rank, world, port, q):
         refm = oracle.fused_experts_block_fp8(xm, w1q, w2q, w1s, w2s, tw, ti)
         rel = float((out.cpu().float() - refm.float()).norm() / refm.float().norm())
         assert rel <= 1e-2, f"ep moe rel-L2 {rel}"
+        # ---- row-parallel linear with the GEMM pushing its tiles into every rank's memory (no NCCL on the path)
+        from sglang_b200.distributed import PeerExchange
+        ex = PeerExchange(slot_elems=128 * H)
+        try:
+            fused = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, peer_exchange=ex)
+            for it, Ms in enumerate([64, 1, 128, 33, 64, 64, 100]):
+                xs = torch.randn(Ms, I, generator=g).bfloat16()
+                xr = xs[:, rank * (I // world):(rank + 1) * (I // world)].contiguous().cuda()
+                y_f = fused(xr)
+                y_n = down(xr)  # the same shard through NCCL
+                torch.cuda.synchronize()
+                assert ex.epoch == it + 1
+                qs, as_ = oracle.per_token_group_quant_fp8(xs, 128)
+                assert_gemm_close(y_f, oracle.w8a8_block_fp8_matmul(qs, w_dn, as_, s_dn), f"fused row-parallel {it}")
+                assert_gemm_close(y_f, y_n.cpu(), f"fused vs nccl {it}")
+                both = [torch.empty_like(y_f) for _ in range(world)]
+                dist.all_gather(both, y_f)
+                assert torch.equal(both[0], both[1]), "ranks must hold identical bits"
+            big = fused(torch.randn(512, I // world, generator=g).bfloat16().cuda())  # does not fit: NCCL path
+            assert big.shape == (512, H) and ex.epoch == 7
+        finally:
+            ex.close()
         from sglang_b200._lib import lib
         assert lib().sglb200_read_device_status() == 0
         q.put((rank, "ok"))
