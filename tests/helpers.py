@@ -93,3 +93,17 @@ def assert_gemm_close(out, ref, what="", allow_one_ulp=False):
     assert r <= 1e-2 and bad == 0, (f"{what}: rel-L2 {r:.3e} (<=1e-2), max-abs/RMS {m:.3e} (<=2e-2"
                                     f"{' or one ulp' if allow_one_ulp else ''}), {bad} elements over")
     return r, m
+
+
+def row_parallel_reference(x, wq, ws, world):
+    """Oracle of the row-parallel linear: every rank quantises its K-slice, rounds its partial product to the output
+    type, and the partial products are added (``python/sglang/srt/layers/linear.py:1361-1386``); fp32 sum here."""
+    import oracle
+    K = x.shape[1]
+    kr = K // world
+    ref = torch.zeros(x.shape[0], wq.shape[0], dtype=torch.float32)
+    for r in range(world):
+        q, s = oracle.per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous(), 128)
+        ref += oracle.w8a8_block_fp8_matmul(q, wq[:, r * kr:(r + 1) * kr].contiguous(), s,
+                                            ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous()).float()
+    return ref.to(x.dtype)

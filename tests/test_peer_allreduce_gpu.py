@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import assert_gemm_close, make_activations
+from helpers import assert_gemm_close, make_activations, row_parallel_reference
 
 pytestmark = pytest.mark.gpu
 
@@ -70,12 +70,7 @@ def test_push_and_reduce_emulated_ranks(world, M, N, K):
             assert torch.equal(outs[r], want), f"rank {r} epoch {epoch}"
         # the tensor-parallel semantic: every rank rounds its partial sum to bf16, then the partial sums are added
         # (python/sglang/srt/layers/linear.py:1361-1386); the oracle does the same on the K-slices
-        ref = torch.zeros(M, N, dtype=torch.float32)
-        for r in range(world):
-            q, s = oracle.per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous(), 128)
-            ref += oracle.w8a8_block_fp8_matmul(q, wq[:, r * kr:(r + 1) * kr].contiguous(),
-                                                s, ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous()).float()
-        assert_gemm_close(outs[0], ref.bfloat16(), f"epoch {epoch}")
+        assert_gemm_close(outs[0], row_parallel_reference(x, wq, ws, world), f"epoch {epoch}")
 
 
 def test_reduce_wait_runs_out_and_reports():
