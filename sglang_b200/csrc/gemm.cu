@@ -53,14 +53,19 @@ constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStag
 // Push epilogue (dense, one tile per (m, n)): instead of writing `out`, every output tile is stored into the receive
 // buffer of every rank, in the slot of this rank, and flagged there.  Receive buffer of a rank:
 // [2 sets][kMaxPeers sources][slot_elems] elements; flags: [2][kMaxPeers][kPushMaxTiles][kEpiWarps] words holding the
-// epoch of the last completed store.  set = epoch & 1.
+// epoch of the last completed store.  set = epoch & 1.  The epoch lives on the device: three control words of this
+// rank follow its flag words ({completed exchanges, block tickets of the reduce kernel, failure mark}); the epoch of
+// the exchange in flight is completed + 1, read by both kernels and advanced by the reduce kernel's last block, so a
+// captured CUDA graph can be replayed.
 constexpr int kMaxPeers = 8;
 constexpr int kPushMaxTiles = 1024;
+constexpr int64_t kFlagWords = (int64_t)2 * kMaxPeers * kPushMaxTiles * 8;
 struct PushParams {
   void* dst[kMaxPeers];
   uint32_t* flag[kMaxPeers];
   int32_t world, rank;
-  uint32_t epoch;
+  const uint32_t* ctl;  // this rank's control words
+  uint32_t* tickets;    // this rank's split-K arrival counters, [kPushMaxTiles][kEpiWarps], zero between launches
   int64_t slot_elems;
 };
 
@@ -80,8 +85,15 @@ struct GemmParams {
   // its fp32 partial sums to partial[split][row][col] (row stride N) and a second kernel adds the splits up
   float* partial;
   int32_t k_splits, kb_per_split;
+};
+
+struct PushGemmParams : GemmParams {
   PushParams push;
 };
+template <bool PUSH>
+struct ParamsOf { using type = GemmParams; };
+template <>
+struct ParamsOf<true> { using type = PushGemmParams; };
 
 struct Tile {
   int32_t row0;     // first row of the tile in a / out
@@ -192,7 +204,7 @@ __device__ __forceinline__ void fma32(float2* acc, const uint32_t (&v)[32], floa
 template <bool GROUPED, bool PUSH>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const GemmParams p) {
+                      const typename ParamsOf<PUSH>::type p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
@@ -354,6 +366,8 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int r_in_tile = q * 32 + lane;
     uint32_t acc_stage = 0, acc_phase = 0;
     float2 acc[kEpiCols / 2];
+    uint32_t push_epoch = 0;
+    if constexpr (PUSH) push_epoch = *reinterpret_cast<const volatile uint32_t*>(p.push.ctl) + 1u;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       const int32_t row = tl.row0 + r_in_tile;
@@ -406,30 +420,73 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       if (!ok || ctl->abort_flag) break;
       if constexpr (PUSH) {
         const int32_t n_first = tl.n0 + col0;
-        const uint32_t set = p.push.epoch & 1u;
-        const int64_t slot = ((int64_t)set * kMaxPeers + p.push.rank) * p.push.slot_elems;
-        if (row < tl.row_end) {
-          for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
-            int pr = p.push.rank + 1 + i;
-            if (pr >= p.push.world) pr -= p.push.world;
-            if (p.out_dtype == SGLB200_BF16) {
-              store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first,
-                                       n_first, p.N);
-            } else {
-              store_row<__half>(acc, static_cast<__half*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first, n_first,
-                                p.N);
+        const int32_t tile_id = (tl.row0 / BM) * p.n_tiles + tl.n0 / BN;
+        const int wi = warp - 2 * kIssuers;
+        bool last = true;
+        if (p.k_splits > 1) {
+          // split-K inside the rank: every split stores its fp32 partial sums; the warp that arrives last at this
+          // (tile, warp) counter adds all splits in ascending order (the same bits whoever is last) and pushes
+          if (row < tl.row_end) {
+            float* dst = p.partial + ((int64_t)tl.split * p.total_rows + row) * p.N + n_first;
+#pragma unroll
+            for (int c = 0; c < kEpiCols / 4; ++c) {
+              if (n_first + c * 4 < p.N)
+                *reinterpret_cast<float4*>(dst + c * 4) =
+                    make_float4(acc[2 * c].x, acc[2 * c].y, acc[2 * c + 1].x, acc[2 * c + 1].y);
+            }
+          }
+          __syncwarp();
+          uint32_t ticket = 0;
+          if (lane == 0) {
+            __threadfence();
+            ticket = atomicAdd(p.push.tickets + tile_id * kEpiWarps + wi, 1u);
+            if (ticket == (uint32_t)p.k_splits - 1u) {
+              __threadfence();
+              p.push.tickets[tile_id * kEpiWarps + wi] = 0;  // ready for the next launch
+            }
+          }
+          ticket = __shfl_sync(0xffffffffu, ticket, 0);
+          __syncwarp();
+          last = ticket == (uint32_t)p.k_splits - 1u;
+          if (last && row < tl.row_end) {
+#pragma unroll
+            for (int j = 0; j < kEpiCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
+            for (int32_t sp = 0; sp < p.k_splits; ++sp) {
+              const float* src = p.partial + ((int64_t)sp * p.total_rows + row) * p.N + n_first;
+#pragma unroll
+              for (int c = 0; c < kEpiCols / 4; ++c) {
+                if (n_first + c * 4 < p.N) {
+                  const float4 v = __ldcg(reinterpret_cast<const float4*>(src + c * 4));  // other SMs wrote it: from L2
+                  acc[2 * c].x += v.x; acc[2 * c].y += v.y; acc[2 * c + 1].x += v.z; acc[2 * c + 1].y += v.w;
+                }
+              }
             }
           }
         }
-        // the warp's 32 rows x 64 columns are on their way: order them before the flag, one flag word per warp
-        __syncwarp();
-        if (lane < p.push.world) {
-          const int32_t tile_id = (tl.row0 / BM) * p.n_tiles + tl.n0 / BN;
-          uint32_t* f = p.push.flag[lane] +
-                        (((int64_t)set * kMaxPeers + p.push.rank) * kPushMaxTiles + tile_id) * kEpiWarps +
-                        (warp - 2 * kIssuers);
-          __threadfence_system();
-          ptx::st_release_sys_u32(f, p.push.epoch);
+        if (last) {
+          const uint32_t set = push_epoch & 1u;
+          const int64_t slot = ((int64_t)set * kMaxPeers + p.push.rank) * p.push.slot_elems;
+          if (row < tl.row_end) {
+            for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
+              int pr = p.push.rank + 1 + i;
+              if (pr >= p.push.world) pr -= p.push.world;
+              if (p.out_dtype == SGLB200_BF16) {
+                store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first,
+                                         n_first, p.N);
+              } else {
+                store_row<__half>(acc, static_cast<__half*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first,
+                                  n_first, p.N);
+              }
+            }
+          }
+          // the warp's 32 rows x 64 columns are on their way: order them before the flag, one flag word per warp
+          __syncwarp();
+          if (lane < p.push.world) {
+            uint32_t* f = p.push.flag[lane] +
+                          (((int64_t)set * kMaxPeers + p.push.rank) * kPushMaxTiles + tile_id) * kEpiWarps + wi;
+            __threadfence_system();
+            ptx::st_release_sys_u32(f, push_epoch);
+          }
         }
       } else if (row < tl.row_end) {
         const int32_t n_first = tl.n0 + col0;
@@ -492,14 +549,19 @@ splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, 
 // words to reach `epoch`.  On a time-out the block records status 5 and returns without writing the tile.
 template <typename OutT>
 __global__ void __launch_bounds__(256)
-peer_reduce_kernel(const OutT* recv, const uint32_t* flags, OutT* __restrict__ out, int32_t M, int32_t N, int64_t ldc,
-                   int32_t n_tiles, int32_t total_tiles, int32_t world, uint32_t epoch, int64_t slot_elems,
+peer_reduce_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT* __restrict__ out, int32_t M, int32_t N,
+                   int64_t ldc, int32_t n_tiles, int32_t total_tiles, int32_t world, int64_t slot_elems,
                    uint64_t limit_ns) {
   __shared__ int s_ok;
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile uint32_t*>(ctl) + 1u;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch;
   const uint32_t set = epoch & 1u;
   for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
     if ((int)threadIdx.x < world * kEpiWarps) {
       const int src = threadIdx.x / kEpiWarps, w = threadIdx.x % kEpiWarps;
       const uint32_t* f = flags + (((int64_t)set * kMaxPeers + src) * kPushMaxTiles + t) * kEpiWarps + w;
@@ -519,7 +581,7 @@ peer_reduce_kernel(const OutT* recv, const uint32_t* flags, OutT* __restrict__ o
       }
     }
     __syncthreads();
-    if (!s_ok) return;
+    if (!s_ok) break;  // uniform: s_ok is only ever cleared before the barrier above
     const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
     const int32_t rows = min(BM, M - mt * BM), vecs = min(BN, N - nt * BN) / 8;
     for (int32_t i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
@@ -543,6 +605,17 @@ peer_reduce_kernel(const OutT* recv, const uint32_t* flags, OutT* __restrict__ o
       *reinterpret_cast<uint4*>(out + (int64_t)(mt * BM + r) * ldc + nt * BN + c) = o;
     }
     __syncthreads();
+  }
+  // every block takes a ticket; the last one closes the exchange: the epoch advances only if no block gave up
+  if (threadIdx.x == 0) {
+    if (!s_ok) atomicExch(&ctl[2], 1u);
+    __threadfence();
+    if (atomicAdd(&ctl[1], 1u) == gridDim.x - 1) {
+      __threadfence();
+      const uint32_t failed = atomicExch(&ctl[2], 0u);
+      ctl[1] = 0;
+      if (!failed) *reinterpret_cast<volatile uint32_t*>(ctl) = epoch;
+    }
   }
 }
 
@@ -654,7 +727,7 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     if (int rc = make_map(&map_b, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
   }
 
-  GemmParams p;
+  PushGemmParams p;
   p.sa = sa;
   p.sb = sb;
   p.out = out;
@@ -678,7 +751,7 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   p.k_splits = 1;
   p.kb_per_split = p.k_tiles;
   if (push) p.push = *push;
-  if (!grouped && workspace != nullptr && !push) {
+  if (!grouped && workspace != nullptr) {
     const int splits = splitk_choice(total_rows, N, K, di.sm_count);
     if (splits > 1 && (int64_t)splits * total_rows * N <= workspace_floats) {
       p.partial = workspace;
@@ -693,17 +766,17 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     // an upper bound on the tile count without reading the device: every expert can add one ragged m-tile
     const int64_t max_tiles = ((total_rows + BM - 1) / BM + num_experts) * p.n_tiles;
     const int grid = (int)(max_tiles < di.sm_count ? max_tiles : di.sm_count);
-    fp8_block_gemm_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+    fp8_block_gemm_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
   } else if (push) {
     if (int rc = set_smem_attr_once<false, true>()) return rc;
-    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
     fp8_block_gemm_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
   } else {
     if (int rc = set_smem_attr_once<false, false>()) return rc;
     const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-    fp8_block_gemm_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+    fp8_block_gemm_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
     if (p.partial != nullptr) {
       SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
       const int64_t vecs = total_rows * (N / 8);
@@ -834,7 +907,19 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void
 // timed out (1 producer, 2/3 MMA issuer, 4 promotion warps).  Synchronises the device: for tests
 // and debugging, not for the serving path.
 extern "C" int64_t sglb200_peer_flag_bytes(void) {
-  return (int64_t)2 * sglb::kMaxPeers * sglb::kPushMaxTiles * sglb::kEpiWarps * (int64_t)sizeof(uint32_t);
+  static_assert(sglb::kEpiWarps == 8, "kFlagWords assumes 8 flag words per tile");
+  // flag words, the control words, the split-K arrival counters
+  return (sglb::kFlagWords + 64 + (int64_t)sglb::kPushMaxTiles * sglb::kEpiWarps) * (int64_t)sizeof(uint32_t);
+}
+
+extern "C" int sglb200_peer_completed(const void* flags_local, int64_t* completed) {
+  SGLB_REQUIRE(flags_local && completed, SGLB200_ERR_NULL, "flags_local and completed must be given");
+  uint32_t v = 0;
+  cudaError_t e = cudaMemcpy(&v, static_cast<const uint32_t*>(flags_local) + sglb::kFlagWords, sizeof(v),
+                             cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return sglb::fail(SGLB200_ERR_LAUNCH, "cudaMemcpy: %s", cudaGetErrorString(e));
+  *completed = v;
+  return SGLB200_OK;
 }
 
 extern "C" int64_t sglb200_peer_recv_bytes(int64_t slot_elems) {
@@ -843,10 +928,9 @@ extern "C" int64_t sglb200_peer_recv_bytes(int64_t slot_elems) {
 
 namespace sglb {
 namespace {
-int check_push_args(int64_t M, int64_t N, int world, int rank, uint32_t epoch, int64_t slot_elems) {
+int check_push_args(int64_t M, int64_t N, int world, int rank, int64_t slot_elems) {
   SGLB_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, SGLB200_ERR_SHAPE,
                "world=%d (1..%d) rank=%d", world, kMaxPeers, rank);
-  SGLB_REQUIRE(epoch != 0, SGLB200_ERR_SHAPE, "epoch must start at 1 (the flag words start at 0)");
   SGLB_REQUIRE(slot_elems % 8 == 0 && M * N <= slot_elems, SGLB200_ERR_WORKSPACE,
                "M*N=%lld does not fit a receive slot of %lld elements (a multiple of 8)", (long long)(M * N),
                (long long)slot_elems);
@@ -861,10 +945,11 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
                                                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                                                     int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                                                     int64_t sb_stride_k, int out_dtype, void* const* peer_recv,
-                                                    void* const* peer_flags, int rank, int world, uint32_t epoch,
-                                                    int64_t slot_elems, void* stream) {
+                                                    void* const* peer_flags, int rank, int world,
+                                                    int64_t slot_elems, void* workspace, int64_t workspace_bytes,
+                                                    void* stream) {
   using namespace sglb;
-  if (int rc = check_push_args(M, N, world, rank, epoch, slot_elems)) return rc;
+  if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
   SGLB_REQUIRE(peer_recv && peer_flags, SGLB200_ERR_NULL, "peer_recv / peer_flags must not be NULL");
   PushParams push;
   for (int i = 0; i < kMaxPeers; ++i) {
@@ -875,19 +960,22 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
   }
   push.world = world;
   push.rank = rank;
-  push.epoch = epoch;
+  push.ctl = push.flag[rank] + kFlagWords;
+  push.tickets = push.flag[rank] + kFlagWords + 64;
   push.slot_elems = slot_elems;
+  SGLB_REQUIRE(workspace == nullptr || aligned(workspace, 16), SGLB200_ERR_ALIGN, "workspace must be 16-byte aligned");
   return gemm_common(a, b, sa, sb, push.dst[rank], nullptr, nullptr, M, 1, N, K, lda, ldb, 0, N, sa_stride_m, sa_stride_k,
-                     0, sb_stride_n, sb_stride_k, out_dtype, stream, nullptr, 0, &push);
+                     0, sb_stride_n, sb_stride_k, out_dtype, stream, static_cast<float*>(workspace),
+                     workspace ? workspace_bytes / (int64_t)sizeof(float) : 0, &push);
 }
 
-extern "C" int sglb200_peer_reduce(const void* recv_local, const void* flags_local, void* out, int64_t M, int64_t N,
-                                   int64_t ldc, int out_dtype, int world, uint32_t epoch, int64_t slot_elems,
-                                   int64_t timeout_ns, void* stream) {
+extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N,
+                                   int64_t ldc, int out_dtype, int world, int64_t slot_elems, int64_t timeout_ns,
+                                   void* stream) {
   using namespace sglb;
   SGLB_REQUIRE(M >= 0 && N >= 0 && N % 8 == 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld (N must be a multiple of 8)",
                (long long)M, (long long)N);
-  if (int rc = check_push_args(M, N, world, 0, epoch, slot_elems)) return rc;
+  if (int rc = check_push_args(M, N, world, 0, slot_elems)) return rc;
   SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "out_dtype=%d", out_dtype);
   if (M == 0 || N == 0) return SGLB200_OK;
   SGLB_REQUIRE(recv_local && flags_local && out, SGLB200_ERR_NULL, "recv_local / flags_local / out must not be NULL");
@@ -902,15 +990,16 @@ extern "C" int sglb200_peer_reduce(const void* recv_local, const void* flags_loc
   const int grid = tiles < 2 * di.sm_count ? tiles : 2 * di.sm_count;
   const uint64_t limit = timeout_ns > 0 ? (uint64_t)timeout_ns : 2000000000ull;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* fl = static_cast<uint32_t*>(flags_local);
   if (out_dtype == SGLB200_BF16) {
-    peer_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(recv_local), static_cast<const uint32_t*>(flags_local),
-        static_cast<__nv_bfloat16*>(out), (int32_t)M, (int32_t)N, ldc, n_tiles, tiles, world, epoch, slot_elems, limit);
+    peer_reduce_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(recv_local), fl,
+                                                           fl + kFlagWords, static_cast<__nv_bfloat16*>(out),
+                                                           (int32_t)M, (int32_t)N, ldc, n_tiles, tiles, world,
+                                                           slot_elems, limit);
   } else {
-    peer_reduce_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(recv_local),
-                                                    static_cast<const uint32_t*>(flags_local), static_cast<__half*>(out),
-                                                    (int32_t)M, (int32_t)N, ldc, n_tiles, tiles, world, epoch,
-                                                    slot_elems, limit);
+    peer_reduce_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(recv_local), fl, fl + kFlagWords,
+                                                    static_cast<__half*>(out), (int32_t)M, (int32_t)N, ldc, n_tiles,
+                                                    tiles, world, slot_elems, limit);
   }
   SGLB_CHECK_LAUNCH("peer_reduce_kernel");
   return SGLB200_OK;

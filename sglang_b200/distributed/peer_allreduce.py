@@ -37,7 +37,6 @@ class PeerExchange:
             raise RuntimeError("PeerExchange supports at most 8 ranks (one NVLink domain)")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.slot_elems = -(-int(slot_elems) // 8) * 8
-        self.epoch = 0
         L = lib()
         self._own: List[int] = []
         self._opened: List[int] = []
@@ -69,6 +68,14 @@ class PeerExchange:
         if self.world > 1:
             dist.barrier(group=group)  # nobody pushes before everybody has mapped
 
+    @property
+    def completed(self) -> int:
+        """Exchanges this rank has completed (the device control word; synchronises the stream-ordered work)."""
+        n = ctypes.c_int64()
+        with torch.cuda.device(self.device):
+            check(lib().sglb200_peer_completed(self.flag_ptrs[self.rank], ctypes.byref(n)), "peer_completed")
+        return n.value
+
     def fits(self, M: int, N: int) -> bool:
         return M * N <= self.slot_elems and -(-M // 128) * -(-N // 128) <= 1024
 
@@ -90,24 +97,28 @@ class PeerExchange:
         self._own, self._opened = [], []
 
 
-def push_mm(ex_recv_arr, ex_flag_arr, rank: int, world: int, epoch: int, slot_elems: int, a_q: torch.Tensor,
+def push_mm(ex_recv_arr, ex_flag_arr, rank: int, world: int, slot_elems: int, a_q: torch.Tensor,
             a_s: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, out_dtype: torch.dtype) -> None:
     """One rank's half of the exchange: ``a_q [M, K_r]`` e4m3 with scales ``a_s [M, K_r/128]`` times the rank's weight
     slice ``[N, K_r]``, every output tile stored into all ranks' receive buffers."""
     M, K = a_q.shape
     N = weight.shape[0]
-    check(lib().sglb200_fp8_blockwise_scaled_mm_push(
+    L = lib()
+    ws_bytes = L.sglb200_fp8_blockwise_scaled_mm_workspace_bytes(M, N, K)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a_q.device) if ws_bytes > 0 else None
+    check(L.sglb200_fp8_blockwise_scaled_mm_push(
         a_q.data_ptr(), weight.data_ptr(), a_s.data_ptr(), weight_scale.data_ptr(), M, N, K, a_q.stride(0),
         weight.stride(0), a_s.stride(0), a_s.stride(1), weight_scale.stride(0), weight_scale.stride(1),
-        dtype_code(out_dtype), ex_recv_arr, ex_flag_arr, rank, world, epoch, slot_elems,
+        dtype_code(out_dtype), ex_recv_arr, ex_flag_arr, rank, world, slot_elems,
+        ws.data_ptr() if ws is not None else None, ws_bytes,
         torch.cuda.current_stream(a_q.device).cuda_stream), "fp8_blockwise_scaled_mm_push")
 
 
-def peer_reduce(recv_ptr: int, flag_ptr: int, out: torch.Tensor, world: int, epoch: int, slot_elems: int,
+def peer_reduce(recv_ptr: int, flag_ptr: int, out: torch.Tensor, world: int, slot_elems: int,
                 timeout_ns: int = 0) -> None:
     """The receiving half: wait for every rank's tiles of this epoch and add them up into ``out [M, N]``."""
     check(lib().sglb200_peer_reduce(recv_ptr, flag_ptr, out.data_ptr(), out.size(0), out.size(1), out.stride(0),
-                                    dtype_code(out.dtype), world, epoch, slot_elems, timeout_ns,
+                                    dtype_code(out.dtype), world, slot_elems, timeout_ns,
                                     torch.cuda.current_stream(out.device).cuda_stream), "peer_reduce")
 
 
@@ -123,11 +134,9 @@ def fused_row_parallel_linear(ex: PeerExchange, x: torch.Tensor, weight: torch.T
     if M == 0:
         return out.reshape(*x.shape[:-1], N)
     a_q, a_s = sglang_per_token_group_quant_fp8(x2.contiguous(), 128, column_major_scales=False)
-    ex.epoch += 1
     with torch.cuda.device(x.device):
-        push_mm(ex._recv_arr, ex._flag_arr, ex.rank, ex.world, ex.epoch, ex.slot_elems, a_q, a_s, weight, weight_scale,
-                x.dtype)
-        peer_reduce(ex.recv_ptrs[ex.rank], ex.flag_ptrs[ex.rank], out, ex.world, ex.epoch, ex.slot_elems)
+        push_mm(ex._recv_arr, ex._flag_arr, ex.rank, ex.world, ex.slot_elems, a_q, a_s, weight, weight_scale, x.dtype)
+        peer_reduce(ex.recv_ptrs[ex.rank], ex.flag_ptrs[ex.rank], out, ex.world, ex.slot_elems)
     if bias is not None:
         out += bias
     return out.reshape(*x.shape[:-1], N)

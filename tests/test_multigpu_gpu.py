@@ -69,14 +69,14 @@ def _worker(rank, world, port, q):
                 y_f = fused(xr)
                 y_n = down(xr)  # the same shard through NCCL
                 torch.cuda.synchronize()
-                assert ex.epoch == it + 1
+                assert ex.completed == it + 1
                 assert_gemm_close(y_f, row_parallel_reference(xs, w_dn, s_dn, world), f"fused row-parallel {it}")
                 assert_gemm_close(y_f, y_n.cpu(), f"fused vs nccl {it}", allow_one_ulp=True)
                 both = [torch.empty_like(y_f) for _ in range(world)]
                 dist.all_gather(both, y_f)
                 assert torch.equal(both[0], both[1]), "ranks must hold identical bits"
             big = fused(torch.randn(512, I // world, generator=g).bfloat16().cuda())  # does not fit: NCCL path
-            assert big.shape == (512, H) and ex.epoch == 7
+            assert big.shape == (512, H) and ex.completed == 7
         finally:
             ex.close()
         from sglang_b200._lib import lib

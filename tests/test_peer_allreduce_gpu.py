@@ -24,20 +24,21 @@ def _buffers(world, slot_elems):
 
 
 def _plain_partial(a_q, a_s, w, ws):
-    """The rank's partial product through the plain entry point without split-K scratch: the same kernel, stored."""
-    from sglang_b200._lib import check, lib
+    """The rank's partial product through the plain path (split-K with its separate reduce kernel where the library
+    chooses it): the same kernel and the same order of additions as the push variant, stored instead of pushed."""
+    from sglang_b200._lib import blockwise_mm
     M, K = a_q.shape
     N = w.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    check(lib().sglb200_fp8_blockwise_scaled_mm(a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(),
-                                                M, N, K, a_q.stride(0), w.stride(0), out.stride(0), a_s.stride(0),
-                                                a_s.stride(1), ws.stride(0), ws.stride(1), 0,
-                                                torch.cuda.current_stream().cuda_stream), "mm")
+    blockwise_mm(a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(), M, N, K, a_q.stride(0),
+                 w.stride(0), out.stride(0), a_s.stride(0), a_s.stride(1), ws.stride(0), ws.stride(1), 0, a_q.device,
+                 torch.cuda.current_stream().cuda_stream)
     return out
 
 
 @pytest.mark.parametrize("world,M,N,K", [(2, 64, 512, 1024), (4, 1, 1024, 2048), (8, 130, 640, 2048), (8, 16, 7168, 2048),
-                                         (2, 128, 576, 512)])
+                                         (2, 128, 576, 512), (2, 16, 1024, 8192), (2, 100, 7168, 16384),
+                                         (4, 130, 1152, 8192)])
 def test_push_and_reduce_emulated_ranks(world, M, N, K):
     from sglang_b200._lib import lib
     from sglang_b200.distributed.peer_allreduce import peer_reduce, push_mm
@@ -53,12 +54,12 @@ def test_push_and_reduce_emulated_ranks(world, M, N, K):
         partials = []
         for r in range(world):
             a_q, a_s = sglang_per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous().cuda(), 128)
-            push_mm(recv_arr, flag_arr, r, world, epoch, slot, a_q, a_s, shards[r][0], shards[r][1], torch.bfloat16)
+            push_mm(recv_arr, flag_arr, r, world, slot, a_q, a_s, shards[r][0], shards[r][1], torch.bfloat16)
             partials.append(_plain_partial(a_q, a_s, *shards[r]))
         outs = []
         for r in range(world):
             out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
-            peer_reduce(recv[r].data_ptr(), flags[r].data_ptr(), out, world, epoch, slot)
+            peer_reduce(recv[r].data_ptr(), flags[r].data_ptr(), out, world, slot)
             outs.append(out)
         torch.cuda.synchronize()
         assert lib().sglb200_read_device_status() == 0
@@ -84,18 +85,21 @@ def test_reduce_wait_runs_out_and_reports():
     recv, flags, recv_arr, flag_arr = _buffers(world, slot)
     wq, ws = oracle.block_quant_weight(torch.randn(N, K, generator=torch.Generator().manual_seed(1)) * 0.05)
     a_q, a_s = sglang_per_token_group_quant_fp8(make_activations(M, K, seed=1, outliers=False).cuda(), 128)
-    push_mm(recv_arr, flag_arr, 0, world, 1, slot, a_q, a_s, wq.cuda(), ws.cuda(), torch.bfloat16)  # rank 1 stays silent
+    push_mm(recv_arr, flag_arr, 0, world, slot, a_q, a_s, wq.cuda(), ws.cuda(), torch.bfloat16)  # rank 1 stays silent
     out = torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda")
-    peer_reduce(recv[0].data_ptr(), flags[0].data_ptr(), out, world, 1, slot, timeout_ns=20_000_000)
+    peer_reduce(recv[0].data_ptr(), flags[0].data_ptr(), out, world, slot, timeout_ns=20_000_000)
     torch.cuda.synchronize()
     assert lib().sglb200_read_device_status() == 5
     assert lib().sglb200_read_device_status() == 0  # reading clears it
     assert (out == 7.0).all()
-    # the late rank arrives: the same exchange now completes
-    push_mm(recv_arr, flag_arr, 1, world, 1, slot, a_q, a_s, wq.cuda(), ws.cuda(), torch.bfloat16)
-    peer_reduce(recv[0].data_ptr(), flags[0].data_ptr(), out, world, 1, slot)
+    done = ctypes.c_int64(-1)
+    assert lib().sglb200_peer_completed(flags[0].data_ptr(), ctypes.byref(done)) == 0 and done.value == 0
+    # the late rank arrives: the same exchange now completes and the epoch advances
+    push_mm(recv_arr, flag_arr, 1, world, slot, a_q, a_s, wq.cuda(), ws.cuda(), torch.bfloat16)
+    peer_reduce(recv[0].data_ptr(), flags[0].data_ptr(), out, world, slot)
     torch.cuda.synchronize()
     assert lib().sglb200_read_device_status() == 0
+    assert lib().sglb200_peer_completed(flags[0].data_ptr(), ctypes.byref(done)) == 0 and done.value == 1
     assert torch.equal(out, (_plain_partial(a_q, a_s, wq.cuda(), ws.cuda()).float() * 2).bfloat16())
 
 
@@ -107,14 +111,12 @@ def test_push_rejections():
     w = torch.zeros(128, 128, dtype=torch.float8_e4m3fn, device="cuda")
     ws = torch.ones(1, 1, device="cuda")
     with pytest.raises(RuntimeError, match="does not fit a receive slot"):
-        push_mm(recv_arr, flag_arr, 0, 2, 1, 1024, a_q, a_s, w, ws, torch.bfloat16)
-    with pytest.raises(RuntimeError, match="epoch must start at 1"):
-        push_mm(recv_arr, flag_arr, 0, 2, 0, 4096, a_q, a_s, w, ws, torch.bfloat16)
+        push_mm(recv_arr, flag_arr, 0, 2, 1024, a_q, a_s, w, ws, torch.bfloat16)
     with pytest.raises(RuntimeError, match="world="):
-        push_mm(recv_arr, flag_arr, 2, 2, 1, 4096, a_q, a_s, w, ws, torch.bfloat16)
+        push_mm(recv_arr, flag_arr, 2, 2, 4096, a_q, a_s, w, ws, torch.bfloat16)
     with pytest.raises(RuntimeError, match="does not fit a receive slot"):
         peer_reduce(recv[0].data_ptr(), flags[0].data_ptr(), torch.empty(16, 128, dtype=torch.bfloat16, device="cuda"),
-                    2, 1, 1024)
+                    2, 1024)
 
 
 def test_peer_exchange_single_rank_alloc_and_linear():
@@ -132,5 +134,25 @@ def test_peer_exchange_single_rank_alloc_and_linear():
             ref = _plain_partial(*sglang_per_token_group_quant_fp8(x, 128), wq.cuda(), ws.cuda())
             torch.cuda.synchronize()
             assert torch.equal(y, ref)
+        assert ex.completed == 3
+        # the pair of launches replays from a CUDA graph: the epoch is read and advanced on the device
+        x = make_activations(64, 384, seed=9, outliers=False).cuda()
+        w_d, ws_d = wq.cuda(), ws.cuda()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fused_row_parallel_linear(ex, x, w_d, ws_d)  # warm-up on the capture stream
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y_g = fused_row_parallel_linear(ex, x, w_d, ws_d)
+        before = ex.completed
+        for _ in range(3):
+            y_g.zero_()
+            graph.replay()
+        torch.cuda.synchronize()
+        assert ex.completed == before + 3
+        assert torch.equal(y_g, _plain_partial(*sglang_per_token_group_quant_fp8(x, 128), w_d, ws_d))
     finally:
         ex.close()
