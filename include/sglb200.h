@@ -302,17 +302,13 @@ int sglb200_moe_sum_reduce(const void* input, void* output, int64_t num_tokens, 
  * Memory, per rank, mapped by every rank (sglb200_peer_alloc / sglb200_peer_open, or any peer-accessible allocation):
  *   receive buffer  sglb200_peer_recv_bytes(slot_elems) bytes = [2][8][slot_elems] 16-bit elements, M * N <= slot_elems;
  *   flag words      sglb200_peer_flag_bytes() bytes, zero before the first call; the tail holds this rank's
- *                   control words (exchanges completed, block tickets, failure mark) and split-K arrival counters.
+ *                   control words (exchanges completed, block tickets, failure mark).
  * peer_recv / peer_flags are HOST arrays of `world` device pointers, entry r = rank r's buffer as mapped in this
  * process.  The epoch of an exchange is (exchanges completed) + 1; it lives in the control words, both kernels read it
  * there and the last block of the reduce kernel advances it, so the pair of launches can be captured in a CUDA graph
  * and replayed.  Rules: all ranks issue the same sequence of exchanges, each on ONE stream per rank (the two
  * alternating slot sets are safe exactly because a rank's exchange e + 1 is enqueued after its exchange e); at most
  * 1024 output tiles of 128 x 128; world <= 8.
- * workspace / workspace_bytes: optional split-K scratch as for sglb200_fp8_blockwise_scaled_mm_ws (size from
- * sglb200_fp8_blockwise_scaled_mm_workspace_bytes for the rank's M, N, K_local; NULL = no split-K).  With it the splits
- * of a tile store fp32 partial sums, and the warp arriving last at the tile's counter adds them in ascending split
- * order and pushes the result: still one GEMM launch, deterministic bits.
  * A wait that runs out (a rank that never pushed) leaves its tile unwritten, sets device status 5
  * (sglb200_read_device_status) and does not advance the epoch, so the same exchange can be reduced again once the
  * missing rank has pushed; if only some ranks timed out the group is out of step and the buffers must be set up
@@ -325,7 +321,7 @@ int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b, const flo
                                          int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t sa_stride_m,
                                          int64_t sa_stride_k, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
                                          void* const* peer_recv, void* const* peer_flags, int rank, int world,
-                                         int64_t slot_elems, void* workspace, int64_t workspace_bytes, void* stream);
+                                         int64_t slot_elems, void* stream);
 int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N, int64_t ldc,
                         int out_dtype, int world, int64_t slot_elems, int64_t timeout_ns, void* stream);
 int64_t sglb200_peer_flag_bytes(void);

@@ -39,7 +39,7 @@ SIGNATURES = {
     "sglb200_moe_align_block_size": [_P, _L, _L, _L, _P, _P, _P, _P, _I, _P],
     "sglb200_moe_sum_reduce": [_P, _P, _L, _L, _L, _I, _F, _P],
     "sglb200_fp8_blockwise_scaled_mm_push": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _P, _I, _I,
-                                             _L, _P, _L, _P],
+                                             _L, _P],
     "sglb200_peer_reduce": [_P, _P, _P, _L, _L, _L, _I, _I, _L, _L, _P],
     "sglb200_peer_completed": [_P, _P],
     "sglb200_peer_flag_bytes": [],

@@ -65,9 +65,16 @@ struct PushParams {
   uint32_t* flag[kMaxPeers];
   int32_t world, rank;
   const uint32_t* ctl;  // this rank's control words
-  uint32_t* tickets;    // this rank's split-K arrival counters, [kPushMaxTiles][kEpiWarps], zero between launches
   int64_t slot_elems;
 };
+
+// Push epilogue staging: every promotion warp turns "one output row per lane" into "rows of contiguous bytes per store"
+// through a private [32 rows][kStageWords] patch of shared memory, 16 payload words per row and pass.
+constexpr int kStageWords = 20;  // 80-byte row stride: 16-byte aligned, conflict-free for the per-lane uint4 writes
+constexpr size_t kStagingBytes = (size_t)kEpiWarps * 32 * kStageWords * sizeof(uint32_t);
+constexpr size_t kStagingOffset = (((size_t)kStages * kStageBytes + 256 + (kMaxExperts + 1) * sizeof(int32_t)) + 15) / 16 * 16;
+constexpr size_t kSmemBytesPush = 1024 + kStagingOffset + kStagingBytes;
+static_assert(kSmemBytesPush <= 227 * 1024, "push variant exceeds the shared memory of an SM");
 
 struct GemmParams {
   const float* sa;
@@ -199,6 +206,23 @@ __device__ __forceinline__ void fma32(float2* acc, const uint32_t (&v)[32], floa
 #pragma unroll
   for (int j = 0; j < 16; ++j)
     acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), scale2, acc[j]);
+}
+
+// v holds 16 words (64 bytes) of the lane's row; emit(r, w, value) is called with r = row of the warp's 32 and w = first
+// word (0, 4, 8, 12) of a 16-byte piece, so that one call across the warp covers eight rows of 64 contiguous bytes.
+template <typename F>
+__device__ __forceinline__ void warp_rows_via_smem(uint32_t* stg, const uint32_t (&v)[16], int lane, F&& emit) {
+  __syncwarp();  // the previous pass has been read out
+  uint4* dst = reinterpret_cast<uint4*>(stg + lane * kStageWords);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  __syncwarp();
+  const int w = (lane & 3) * 4;
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    const int r = j + (lane >> 2);
+    emit(r, w, *reinterpret_cast<const uint4*>(stg + r * kStageWords + w));
+  }
 }
 
 template <bool GROUPED, bool PUSH>
@@ -422,71 +446,36 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int32_t n_first = tl.n0 + col0;
         const int32_t tile_id = (tl.row0 / BM) * p.n_tiles + tl.n0 / BN;
         const int wi = warp - 2 * kIssuers;
-        bool last = true;
-        if (p.k_splits > 1) {
-          // split-K inside the rank: every split stores its fp32 partial sums; the warp that arrives last at this
-          // (tile, warp) counter adds all splits in ascending order (the same bits whoever is last) and pushes
-          if (row < tl.row_end) {
-            float* dst = p.partial + ((int64_t)tl.split * p.total_rows + row) * p.N + n_first;
+        uint32_t* stg = reinterpret_cast<uint32_t*>(smem + kStagingOffset) + wi * 32 * kStageWords;
+        const int32_t row_base = tl.row0 + q * 32;  // the warp's rows are row_base + 0..31
+        const uint32_t set = push_epoch & 1u;
+        const int64_t slot = ((int64_t)set * kMaxPeers + p.push.rank) * p.push.slot_elems;
 #pragma unroll
-            for (int c = 0; c < kEpiCols / 4; ++c) {
-              if (n_first + c * 4 < p.N)
-                *reinterpret_cast<float4*>(dst + c * 4) =
-                    make_float4(acc[2 * c].x, acc[2 * c].y, acc[2 * c + 1].x, acc[2 * c + 1].y);
-            }
-          }
-          __syncwarp();
-          uint32_t ticket = 0;
-          if (lane == 0) {
-            __threadfence();
-            ticket = atomicAdd(p.push.tickets + tile_id * kEpiWarps + wi, 1u);
-            if (ticket == (uint32_t)p.k_splits - 1u) {
-              __threadfence();
-              p.push.tickets[tile_id * kEpiWarps + wi] = 0;  // ready for the next launch
-            }
-          }
-          ticket = __shfl_sync(0xffffffffu, ticket, 0);
-          __syncwarp();
-          last = ticket == (uint32_t)p.k_splits - 1u;
-          if (last && row < tl.row_end) {
+        for (int h = 0; h < 2; ++h) {  // 32 columns (64 bytes of a row) per pass
+          uint32_t v[16];
 #pragma unroll
-            for (int j = 0; j < kEpiCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-            for (int32_t sp = 0; sp < p.k_splits; ++sp) {
-              const float* src = p.partial + ((int64_t)sp * p.total_rows + row) * p.N + n_first;
-#pragma unroll
-              for (int c = 0; c < kEpiCols / 4; ++c) {
-                if (n_first + c * 4 < p.N) {
-                  const float4 v = __ldcg(reinterpret_cast<const float4*>(src + c * 4));  // other SMs wrote it: from L2
-                  acc[2 * c].x += v.x; acc[2 * c].y += v.y; acc[2 * c + 1].x += v.z; acc[2 * c + 1].y += v.w;
-                }
+          for (int w = 0; w < 16; ++w)
+            v[w] = p.out_dtype == SGLB200_BF16 ? pack2<__nv_bfloat16>(acc[16 * h + w].x, acc[16 * h + w].y)
+                                               : pack2<__half>(acc[16 * h + w].x, acc[16 * h + w].y);
+          warp_rows_via_smem(stg, v, lane, [&](int r, int w, uint4 val) {
+            const int32_t grow = row_base + r, c = n_first + 32 * h + 2 * w;  // 8 columns from c (N % 8 == 0)
+            if (grow < tl.row_end && c < p.N) {
+              const int64_t off = (slot + (int64_t)grow * p.N + c) * 2;
+              for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
+                int pr = p.push.rank + 1 + i;
+                if (pr >= p.push.world) pr -= p.push.world;
+                *reinterpret_cast<uint4*>(static_cast<char*>(p.push.dst[pr]) + off) = val;
               }
             }
-          }
+          });
         }
-        if (last) {
-          const uint32_t set = push_epoch & 1u;
-          const int64_t slot = ((int64_t)set * kMaxPeers + p.push.rank) * p.push.slot_elems;
-          if (row < tl.row_end) {
-            for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
-              int pr = p.push.rank + 1 + i;
-              if (pr >= p.push.world) pr -= p.push.world;
-              if (p.out_dtype == SGLB200_BF16) {
-                store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first,
-                                         n_first, p.N);
-              } else {
-                store_row<__half>(acc, static_cast<__half*>(p.push.dst[pr]) + slot + (int64_t)row * p.N + n_first,
-                                  n_first, p.N);
-              }
-            }
-          }
-          // the warp's 32 rows x 64 columns are on their way: order them before the flag, one flag word per warp
-          __syncwarp();
-          if (lane < p.push.world) {
-            uint32_t* f = p.push.flag[lane] +
-                          (((int64_t)set * kMaxPeers + p.push.rank) * kPushMaxTiles + tile_id) * kEpiWarps + wi;
-            __threadfence_system();
-            ptx::st_release_sys_u32(f, push_epoch);
-          }
+        // The warp's 32 rows x 64 columns are on their way.  One flag word per (tile, warp) and rank: the warp barrier
+        // orders every lane's stores before the release store of the flag (release is cumulative), at system scope.
+        __syncwarp();
+        if (lane < p.push.world) {
+          uint32_t* f = p.push.flag[lane] +
+                        (((int64_t)set * kMaxPeers + p.push.rank) * kPushMaxTiles + tile_id) * kEpiWarps + wi;
+          ptx::st_release_sys_u32(f, push_epoch);
         }
       } else if (row < tl.row_end) {
         const int32_t n_first = tl.n0 + col0;
@@ -550,7 +539,7 @@ splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, 
 template <typename OutT>
 __global__ void __launch_bounds__(256)
 peer_reduce_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT* __restrict__ out, int32_t M, int32_t N,
-                   int64_t ldc, int32_t n_tiles, int32_t total_tiles, int32_t world, int64_t slot_elems,
+                   int64_t ldc, int32_t n_tiles, int32_t total_items, int32_t world, int64_t slot_elems,
                    uint64_t limit_ns) {
   __shared__ int s_ok;
   __shared__ uint32_t s_epoch;
@@ -561,9 +550,15 @@ peer_reduce_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT*
   __syncthreads();
   const uint32_t epoch = s_epoch;
   const uint32_t set = epoch & 1u;
-  for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-    if ((int)threadIdx.x < world * kEpiWarps) {
-      const int src = threadIdx.x / kEpiWarps, w = threadIdx.x % kEpiWarps;
+  // work item = (tile, quarter of its rows): the rows 32q..32q+31 of a tile were pushed by the promotion warps q
+  // (columns 0..63) and q + 4 (columns 64..127) of every source rank
+  for (int32_t item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const int32_t t = item >> 2, q = item & 3;
+    const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
+    const int32_t row0 = mt * BM + q * 32;
+    if (row0 >= M) continue;  // uniform
+    if ((int)threadIdx.x < world * 2) {
+      const int src = threadIdx.x >> 1, w = q + 4 * (threadIdx.x & 1);
       const uint32_t* f = flags + (((int64_t)set * kMaxPeers + src) * kPushMaxTiles + t) * kEpiWarps + w;
       uint64_t t0 = 0;
       uint32_t polls = 0;
@@ -582,36 +577,42 @@ peer_reduce_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT*
     }
     __syncthreads();
     if (!s_ok) break;  // uniform: s_ok is only ever cleared before the barrier above
-    const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
-    const int32_t rows = min(BM, M - mt * BM), vecs = min(BN, N - nt * BN) / 8;
+    const int32_t rows = min(32, M - row0), vecs = min(BN, N - nt * BN) / 8;
     for (int32_t i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
       const int32_t r = i / vecs, c = (i - r * vecs) * 8;
-      const int64_t off = (int64_t)(mt * BM + r) * N + nt * BN + c;
+      const int64_t off = (int64_t)(row0 + r) * N + nt * BN + c;
+      uint4 u[kMaxPeers];
+#pragma unroll
+      for (int src = 0; src < kMaxPeers; ++src) {
+        // written by another GPU since this SM may last have cached the line: bypass L1
+        if (src < world)
+          u[src] = __ldcv(reinterpret_cast<const uint4*>(recv + ((int64_t)set * kMaxPeers + src) * slot_elems + off));
+      }
       float a[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) a[j] = 0.f;
-      for (int src = 0; src < world; ++src) {
-        // written by another GPU since this SM may last have cached the line: bypass L1
-        const uint4 u = __ldcv(reinterpret_cast<const uint4*>(recv + ((int64_t)set * kMaxPeers + src) * slot_elems + off));
-        const OutT* h = reinterpret_cast<const OutT*>(&u);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) a[j] += static_cast<float>(h[j]);
+      for (int src = 0; src < kMaxPeers; ++src) {
+        if (src < world) {
+          const OutT* h = reinterpret_cast<const OutT*>(&u[src]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] += static_cast<float>(h[j]);
+        }
       }
       uint4 o;
       o.x = pack2<OutT>(a[0], a[1]);
       o.y = pack2<OutT>(a[2], a[3]);
       o.z = pack2<OutT>(a[4], a[5]);
       o.w = pack2<OutT>(a[6], a[7]);
-      *reinterpret_cast<uint4*>(out + (int64_t)(mt * BM + r) * ldc + nt * BN + c) = o;
+      *reinterpret_cast<uint4*>(out + (int64_t)(row0 + r) * ldc + nt * BN + c) = o;
     }
     __syncthreads();
   }
   // every block takes a ticket; the last one closes the exchange: the epoch advances only if no block gave up
+  // (the epoch was read, and used, before this block's ticket; the counters are only ever touched by atomics)
   if (threadIdx.x == 0) {
     if (!s_ok) atomicExch(&ctl[2], 1u);
-    __threadfence();
     if (atomicAdd(&ctl[1], 1u) == gridDim.x - 1) {
-      __threadfence();
       const uint32_t failed = atomicExch(&ctl[2], 0u);
       ctl[1] = 0;
       if (!failed) *reinterpret_cast<volatile uint32_t*>(ctl) = epoch;
@@ -673,7 +674,7 @@ int set_smem_attr_once() {
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
     cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<GROUPED, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBytes);
+                                         (int)(PUSH ? kSmemBytesPush : kSmemBytes));
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     done[dev] = true;
   }
@@ -751,7 +752,7 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   p.k_splits = 1;
   p.kb_per_split = p.k_tiles;
   if (push) p.push = *push;
-  if (!grouped && workspace != nullptr) {
+  if (!grouped && workspace != nullptr && !push) {
     const int splits = splitk_choice(total_rows, N, K, di.sm_count);
     if (splits > 1 && (int64_t)splits * total_rows * N <= workspace_floats) {
       p.partial = workspace;
@@ -769,9 +770,9 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     fp8_block_gemm_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
   } else if (push) {
     if (int rc = set_smem_attr_once<false, true>()) return rc;
-    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
+    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-    fp8_block_gemm_kernel<false, true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+    fp8_block_gemm_kernel<false, true><<<grid, kThreads, kSmemBytesPush, st>>>(map_a, map_b, p);
   } else {
     if (int rc = set_smem_attr_once<false, false>()) return rc;
     const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
@@ -908,8 +909,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void
 // and debugging, not for the serving path.
 extern "C" int64_t sglb200_peer_flag_bytes(void) {
   static_assert(sglb::kEpiWarps == 8, "kFlagWords assumes 8 flag words per tile");
-  // flag words, the control words, the split-K arrival counters
-  return (sglb::kFlagWords + 64 + (int64_t)sglb::kPushMaxTiles * sglb::kEpiWarps) * (int64_t)sizeof(uint32_t);
+  return (sglb::kFlagWords + 64) * (int64_t)sizeof(uint32_t);  // flag words, then the control words
 }
 
 extern "C" int sglb200_peer_completed(const void* flags_local, int64_t* completed) {
@@ -946,8 +946,7 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
                                                     int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                                                     int64_t sb_stride_k, int out_dtype, void* const* peer_recv,
                                                     void* const* peer_flags, int rank, int world,
-                                                    int64_t slot_elems, void* workspace, int64_t workspace_bytes,
-                                                    void* stream) {
+                                                    int64_t slot_elems, void* stream) {
   using namespace sglb;
   if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
   SGLB_REQUIRE(peer_recv && peer_flags, SGLB200_ERR_NULL, "peer_recv / peer_flags must not be NULL");
@@ -961,12 +960,9 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
   push.world = world;
   push.rank = rank;
   push.ctl = push.flag[rank] + kFlagWords;
-  push.tickets = push.flag[rank] + kFlagWords + 64;
   push.slot_elems = slot_elems;
-  SGLB_REQUIRE(workspace == nullptr || aligned(workspace, 16), SGLB200_ERR_ALIGN, "workspace must be 16-byte aligned");
   return gemm_common(a, b, sa, sb, push.dst[rank], nullptr, nullptr, M, 1, N, K, lda, ldb, 0, N, sa_stride_m, sa_stride_k,
-                     0, sb_stride_n, sb_stride_k, out_dtype, stream, static_cast<float*>(workspace),
-                     workspace ? workspace_bytes / (int64_t)sizeof(float) : 0, &push);
+                     0, sb_stride_n, sb_stride_k, out_dtype, stream, nullptr, 0, &push);
 }
 
 extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N,
@@ -986,8 +982,8 @@ extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, vo
   SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
                di.cc_major, di.cc_minor);
   const int32_t n_tiles = (int32_t)((N + BN - 1) / BN);
-  const int32_t tiles = (int32_t)((M + BM - 1) / BM) * n_tiles;
-  const int grid = tiles < 2 * di.sm_count ? tiles : 2 * di.sm_count;
+  const int32_t tiles = (int32_t)((M + BM - 1) / BM) * n_tiles * 4;  // work items: (tile, quarter of its rows)
+  const int grid = tiles < 4 * di.sm_count ? tiles : 4 * di.sm_count;
   const uint64_t limit = timeout_ns > 0 ? (uint64_t)timeout_ns : 2000000000ull;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   uint32_t* fl = static_cast<uint32_t*>(flags_local);

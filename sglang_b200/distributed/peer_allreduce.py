@@ -103,14 +103,10 @@ def push_mm(ex_recv_arr, ex_flag_arr, rank: int, world: int, slot_elems: int, a_
     slice ``[N, K_r]``, every output tile stored into all ranks' receive buffers."""
     M, K = a_q.shape
     N = weight.shape[0]
-    L = lib()
-    ws_bytes = L.sglb200_fp8_blockwise_scaled_mm_workspace_bytes(M, N, K)
-    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a_q.device) if ws_bytes > 0 else None
-    check(L.sglb200_fp8_blockwise_scaled_mm_push(
+    check(lib().sglb200_fp8_blockwise_scaled_mm_push(
         a_q.data_ptr(), weight.data_ptr(), a_s.data_ptr(), weight_scale.data_ptr(), M, N, K, a_q.stride(0),
         weight.stride(0), a_s.stride(0), a_s.stride(1), weight_scale.stride(0), weight_scale.stride(1),
         dtype_code(out_dtype), ex_recv_arr, ex_flag_arr, rank, world, slot_elems,
-        ws.data_ptr() if ws is not None else None, ws_bytes,
         torch.cuda.current_stream(a_q.device).cuda_stream), "fp8_blockwise_scaled_mm_push")
 
 

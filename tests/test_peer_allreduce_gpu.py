@@ -24,15 +24,16 @@ def _buffers(world, slot_elems):
 
 
 def _plain_partial(a_q, a_s, w, ws):
-    """The rank's partial product through the plain path (split-K with its separate reduce kernel where the library
-    chooses it): the same kernel and the same order of additions as the push variant, stored instead of pushed."""
-    from sglang_b200._lib import blockwise_mm
+    """The rank's partial product through the plain entry point without split-K scratch: the same kernel and the same
+    order of additions as the push variant, stored instead of pushed."""
+    from sglang_b200._lib import check, lib
     M, K = a_q.shape
     N = w.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    blockwise_mm(a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(), M, N, K, a_q.stride(0),
-                 w.stride(0), out.stride(0), a_s.stride(0), a_s.stride(1), ws.stride(0), ws.stride(1), 0, a_q.device,
-                 torch.cuda.current_stream().cuda_stream)
+    check(lib().sglb200_fp8_blockwise_scaled_mm(a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(),
+                                                M, N, K, a_q.stride(0), w.stride(0), out.stride(0), a_s.stride(0),
+                                                a_s.stride(1), ws.stride(0), ws.stride(1), 0,
+                                                torch.cuda.current_stream().cuda_stream), "mm")
     return out
 
 
