@@ -228,6 +228,26 @@ int sglb200_silu_and_mul(const void* input, void* output, int64_t num_rows, int6
                          void* stream);
 
 /*
+ * MG in the masked layout: group g owns the rows [g * max_m, g * max_m + masked_m[g]) of a / sa / out; rows past
+ * masked_m[g] are neither read as results nor written (masked_m is clamped to [0, max_m]).
+ *   a   [num_groups * max_m, K] e4m3, row stride lda;  sa element (g, local row, kb) at
+ *       sa[g * sa_stride_g + row * sa_stride_m + kb * sa_stride_k] (row-major or MN-major per group)
+ *   b   [num_groups, N, K] e4m3, strides ldb (row) and ldb_e (group);  sb element (g, nb, kb) at
+ *       sb[g * sb_stride_e + nb * sb_stride_n + kb * sb_stride_k]
+ *   out [num_groups * max_m, N], row stride ldc elements;  masked_m [num_groups] int32 on the device.
+ * Same kernel and arithmetic as sglb200_fp8_blockwise_scaled_grouped_mm; alignment rules as there.
+ * Replaces: deep_gemm.fp8_m_grouped_gemm_nt_masked as called from
+ *           python/sglang/srt/layers/deep_gemm_wrapper/entrypoint.py:26-49 (third-party DeepGEMM, not in the tree;
+ *           semantics pinned by torch_w8a8_block_fp8_bmm, python/sglang/test/test_block_fp8.py:549-563,586-635).
+ */
+int sglb200_fp8_blockwise_scaled_masked_grouped_mm(const void* a, const void* b, const float* sa, const float* sb,
+                                                   void* out, const int32_t* masked_m, int64_t num_groups,
+                                                   int64_t max_m, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                                   int64_t ldb_e, int64_t ldc, int64_t sa_stride_g, int64_t sa_stride_m,
+                                                   int64_t sa_stride_k, int64_t sb_stride_e, int64_t sb_stride_n,
+                                                   int64_t sb_stride_k, int out_dtype, void* stream);
+
+/*
  * Router front end: probabilities = softmax(gating_output[t, :]) in fp32, then the topk largest in
  * descending order (ties go to the lower expert index); with renormalize != 0 the selected weights are
  * divided by their sum.

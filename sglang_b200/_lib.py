@@ -30,6 +30,8 @@ SIGNATURES = {
     "sglb200_fp8_ue8m0_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
     "sglb200_fp8_blockwise_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
                                                 _L, _L, _L, _I, _P],
+    "sglb200_fp8_blockwise_scaled_masked_grouped_mm": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
+                                                       _L, _L, _L, _L, _I, _P],
     "sglb200_prepare_moe_input": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P],
     "sglb200_shuffle_rows": [_P, _P, _P, _L, _L, _P],
     "sglb200_apply_shuffle_mul_sum": [_P, _P, _P, _P, _L, _L, _L, _I, _I, _P],

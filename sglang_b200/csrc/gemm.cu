@@ -80,8 +80,11 @@ struct GemmParams {
   const float* sa;
   const float* sb;
   void* out;
-  const int32_t* expert_offsets;  // null: dense
-  const int32_t* problem_sizes;   // grouped, optional [E,3]: rows of expert e = problem_sizes[3e]
+  const int32_t* expert_offsets;  // null: dense (or the masked layout, see rows_per_expert)
+  const int32_t* problem_sizes;   // grouped, optional: rows of expert e = problem_sizes[count_stride * e]
+  int32_t count_stride;           // 3 for a [E, 3] problem-size table, 1 for a plain per-expert row count
+  int32_t rows_per_expert;        // > 0: masked layout, expert e owns rows [e * rows_per_expert, + its row count)
+  int64_t sa_stride_e;            // masked layout: activation scale (e, local row, kb) at e * sa_stride_e + ...
   int32_t total_rows, N, K, num_experts;
   int32_t m_tiles, n_tiles, k_tiles;
   int64_t ldc;
@@ -153,8 +156,14 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int32_t* til
       if (tile_start[mid] <= t) lo = mid; else hi = mid;
     }
     const int32_t e = lo;
-    const int32_t r0 = __ldg(p.expert_offsets + e);
-    const int32_t r1 = p.problem_sizes ? r0 + __ldg(p.problem_sizes + 3 * e) : __ldg(p.expert_offsets + e + 1);
+    int32_t r0, r1;
+    if (p.rows_per_expert > 0) {
+      r0 = e * p.rows_per_expert;
+      r1 = r0 + max(0, min(__ldg(p.problem_sizes + p.count_stride * e), p.rows_per_expert));
+    } else {
+      r0 = __ldg(p.expert_offsets + e);
+      r1 = p.problem_sizes ? r0 + __ldg(p.problem_sizes + p.count_stride * e) : __ldg(p.expert_offsets + e + 1);
+    }
     const int32_t me = (r1 - r0 + BM - 1) / BM;
     const int32_t local = t - tile_start[e];
     const int32_t nt = local / me;
@@ -265,8 +274,10 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int32_t e = base + lane;
         int32_t v = 0;
         if (e < p.num_experts) {
-          const int32_t cnt = p.problem_sizes ? __ldg(p.problem_sizes + 3 * e)
-                                              : __ldg(p.expert_offsets + e + 1) - __ldg(p.expert_offsets + e);
+          int32_t cnt;
+          if (p.rows_per_expert > 0) cnt = max(0, min(__ldg(p.problem_sizes + p.count_stride * e), p.rows_per_expert));
+          else if (p.problem_sizes) cnt = __ldg(p.problem_sizes + p.count_stride * e);
+          else cnt = __ldg(p.expert_offsets + e + 1) - __ldg(p.expert_offsets + e);
           v = ((cnt + BM - 1) / BM) * p.n_tiles;
         }
         int32_t incl = v;
@@ -397,6 +408,11 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       const int32_t row = tl.row0 + r_in_tile;
       const int32_t row_c = min(row, p.total_rows - 1);
       const float* sa_row = p.sa + (int64_t)row_c * p.sa_stride_m;
+      if constexpr (GROUPED) {
+        if (p.rows_per_expert > 0)
+          sa_row = p.sa + (int64_t)tl.expert * p.sa_stride_e +
+                   (int64_t)(row_c - tl.expert * p.rows_per_expert) * p.sa_stride_m;
+      }
       const float* sb_blk = p.sb + (int64_t)tl.expert * p.sb_stride_e + (int64_t)(tl.n0 / BN) * p.sb_stride_n;
 #pragma unroll
       for (int j = 0; j < kEpiCols / 2; ++j) acc[j] = make_float2(0.f, 0.f);
@@ -685,8 +701,9 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
                 const int32_t* expert_offsets, const int32_t* problem_sizes, int64_t total_rows, int64_t num_experts, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
                 int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream,
-                float* workspace = nullptr, int64_t workspace_floats = 0, const PushParams* push = nullptr) {
-  const bool grouped = expert_offsets != nullptr;
+                float* workspace = nullptr, int64_t workspace_floats = 0, const PushParams* push = nullptr,
+                int64_t rows_per_expert = 0, int64_t sa_stride_e = 0) {
+  const bool grouped = expert_offsets != nullptr || rows_per_expert > 0;
   SGLB_REQUIRE(total_rows >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size",
                (long long)total_rows, (long long)N, (long long)K);
   SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE,
@@ -734,6 +751,9 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   p.out = out;
   p.expert_offsets = expert_offsets;
   p.problem_sizes = problem_sizes;
+  p.count_stride = rows_per_expert > 0 ? 1 : 3;
+  p.rows_per_expert = (int32_t)rows_per_expert;
+  p.sa_stride_e = sa_stride_e;
   p.total_rows = (int32_t)total_rows;
   p.N = (int32_t)N;
   p.K = (int32_t)K;
@@ -817,6 +837,23 @@ extern "C" int sglb200_fp8_blockwise_scaled_grouped_mm(const void* a, const void
   SGLB_REQUIRE(expert_offsets != nullptr, SGLB200_ERR_NULL, "expert_offsets must not be NULL");
   return sglb::gemm_common(a, b, sa, sb, out, expert_offsets, problem_sizes, total_rows, num_experts, N, K, lda, ldb, ldb_e, ldc,
                            sa_stride_m, sa_stride_k, sb_stride_e, sb_stride_n, sb_stride_k, out_dtype, stream);
+}
+
+extern "C" int sglb200_fp8_blockwise_scaled_masked_grouped_mm(const void* a, const void* b, const float* sa,
+                                                              const float* sb, void* out, const int32_t* masked_m,
+                                                              int64_t num_groups, int64_t max_m, int64_t N, int64_t K,
+                                                              int64_t lda, int64_t ldb, int64_t ldb_e, int64_t ldc,
+                                                              int64_t sa_stride_g, int64_t sa_stride_m,
+                                                              int64_t sa_stride_k, int64_t sb_stride_e,
+                                                              int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
+                                                              void* stream) {
+  SGLB_REQUIRE(num_groups >= 0 && max_m >= 0 && num_groups * max_m < ((int64_t)1 << 31) - 256, SGLB200_ERR_SHAPE,
+               "num_groups=%lld max_m=%lld", (long long)num_groups, (long long)max_m);
+  if (num_groups == 0 || max_m == 0) return SGLB200_OK;
+  SGLB_REQUIRE(masked_m != nullptr, SGLB200_ERR_NULL, "masked_m must not be NULL");
+  return sglb::gemm_common(a, b, sa, sb, out, nullptr, masked_m, num_groups * max_m, num_groups, N, K, lda, ldb, ldb_e, ldc,
+                           sa_stride_m, sa_stride_k, sb_stride_e, sb_stride_n, sb_stride_k, out_dtype, stream, nullptr, 0,
+                           nullptr, max_m, sa_stride_g);
 }
 
 extern "C" int64_t sglb200_fp8_blockwise_scaled_mm_workspace_bytes(int64_t M, int64_t N, int64_t K) {

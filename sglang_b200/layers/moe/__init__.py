@@ -167,3 +167,25 @@ def cutlass_fused_experts_fp8(a, w1_q, w2_q, w1_scale, w2_scale, topk_weights, t
     s1, s2 = w1_scale.transpose(1, 2), w2_scale.transpose(1, 2)
     assert w1.is_contiguous() and w2.is_contiguous(), "weights must be K-contiguous ([E, N, K] storage)"
     return fused_experts_block_fp8(a, w1, w2, s1.contiguous(), s2.contiguous(), topk_weights, topk_ids)
+
+
+def fused_experts_masked(hidden_states: torch.Tensor, hidden_states_scale: torch.Tensor, w13_weight: torch.Tensor,
+                         w13_scale: torch.Tensor, w2_weight: torch.Tensor, w2_scale: torch.Tensor,
+                         masked_m: torch.Tensor, expected_m: int, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """Expert MLP in the masked per-expert layout of the low-latency dispatcher
+    (``python/sglang/srt/layers/moe/moe_runner/deep_gemm.py:209-328``): ``hidden_states [E_local, max_m, H]`` e4m3
+    with ``hidden_states_scale [E_local, max_m, H/128]``; expert ``e`` holds ``masked_m[e]`` valid rows.  Grouped GEMM
+    (gate_up) -> fused SiLU-mul + group quant -> grouped GEMM (down); returns ``[E_local, max_m, H]``, rows past
+    ``masked_m[e]`` unspecified.  The activation kernel runs over all ``max_m`` rows of every expert (the rows past
+    ``masked_m[e]`` are unspecified in the reference as well)."""
+    from ..deep_gemm_wrapper import grouped_gemm_nt_f8f8bf16_masked
+    E, max_m, H = hidden_states.shape
+    two_i = w13_weight.shape[1]
+    gate_up = torch.empty(E, max_m, two_i, dtype=out_dtype, device=hidden_states.device)
+    grouped_gemm_nt_f8f8bf16_masked((hidden_states, hidden_states_scale), (w13_weight, w13_scale), gate_up, masked_m,
+                                    expected_m)
+    down_q, down_s = sglang_per_token_group_quant_fp8(gate_up.view(E * max_m, two_i), 128, fuse_silu_and_mul=True)
+    out = torch.empty(E, max_m, w2_weight.shape[1], dtype=out_dtype, device=hidden_states.device)
+    grouped_gemm_nt_f8f8bf16_masked((down_q.view(E, max_m, two_i // 2), down_s.view(E, max_m, two_i // 256)),
+                                    (w2_weight, w2_scale), out, masked_m, expected_m)
+    return out
