@@ -1,5 +1,6 @@
 // Shared host/device plumbing: status codes, argument checks, launch error capture.
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdint.h>
@@ -21,6 +22,20 @@ struct DeviceInfo {
   int max_smem_optin;
 };
 int device_info(DeviceInfo* out);  // returns SGLB200_OK or an error code
+
+// Tensor map of a rank-2 or rank-3 byte tensor with innermost extent dims[0] (K), 128-byte-swizzled boxes of
+// [box_rows x 128 bytes].  Defined in gemm.cu.
+int make_map_sw128(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                   uint32_t box_rows, CUtensorMapL2promotion promo);
+
+// The few-rows (M <= smallm_max_rows()) weight-streaming GEMM, gemm_smallm.cu
+int smallm_max_rows();
+int smallm_splits(int64_t N, int64_t K, int sm_count);
+int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                int64_t sb_stride_k, int out_dtype, float* partial, int64_t partial_floats, int sm_count, void* stream,
+                int* splits_used);
+int smallm_take_device_status();
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 

@@ -655,9 +655,11 @@ EncodeTiledFn encode_fn() {
   return fn;
 }
 
+}  // namespace
+
 // rank-2 or rank-3 byte tensor, innermost extent K, 128-byte-swizzled boxes of [rows x 128 B]
-int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
-             uint32_t box_rows, CUtensorMapL2promotion promo) {
+int make_map_sw128(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_bytes,
+                   uint32_t box_rows, CUtensorMapL2promotion promo) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   cuuint64_t gdim[3] = {dims[0], dims[1], rank == 3 ? dims[2] : 1};
@@ -668,6 +670,23 @@ int make_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return SGLB200_OK;
+}
+
+namespace {
+
+void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N, int64_t ldc, int splits, int out_dtype,
+                          int sm_count, void* stream) {
+  const int64_t vecs = M * (N / 8);
+  int rgrid = (int)((vecs + 255) / 256);
+  if (rgrid > sm_count * 8) rgrid = sm_count * 8;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == SGLB200_BF16) {
+    splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(partial, static_cast<__nv_bfloat16*>(out), (int32_t)M,
+                                                              (int32_t)N, ldc, splits);
+  } else {
+    splitk_reduce_kernel<__half><<<rgrid, 256, 0, st>>>(partial, static_cast<__half*>(out), (int32_t)M, (int32_t)N, ldc,
+                                                       splits);
+  }
 }
 
 // Number of k-splits for a dense problem: only when the output tiles alone cannot occupy the SMs (small M, where the
@@ -732,17 +751,28 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
                di.cc_major, di.cc_minor);
 
+  if (!grouped && !push && total_rows <= smallm_max_rows()) {
+    // few rows: the weight-streaming kernel with swapped operands (gemm_smallm.cu)
+    int splits = 1;
+    if (int rc = smallm_gemm(a, b, sa, sb, out, total_rows, N, K, lda, ldb, ldc, sa_stride_m, sa_stride_k, sb_stride_n,
+                             sb_stride_k, out_dtype, workspace, workspace_floats, di.sm_count, stream, &splits))
+      return rc;
+    if (splits > 1) launch_splitk_reduce(workspace, out, total_rows, N, ldc, splits, out_dtype, di.sm_count, stream);
+    SGLB_CHECK_LAUNCH("splitk_reduce_kernel");
+    return SGLB200_OK;
+  }
+
   alignas(64) CUtensorMap map_a, map_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)total_rows};
     const uint64_t str[1] = {(uint64_t)lda};
-    if (int rc = make_map(&map_a, a, 2, dims, str, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
   }
   {
     const uint64_t E = grouped ? (uint64_t)num_experts : 1;
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, E};
     const uint64_t str[2] = {(uint64_t)ldb, grouped ? (uint64_t)ldb_e : (uint64_t)ldb * (uint64_t)N};
-    if (int rc = make_map(&map_b, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+    if (int rc = make_map_sw128(&map_b, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
   }
 
   PushGemmParams p;
@@ -800,16 +830,7 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     fp8_block_gemm_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
     if (p.partial != nullptr) {
       SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
-      const int64_t vecs = total_rows * (N / 8);
-      int rgrid = (int)((vecs + 255) / 256);
-      if (rgrid > di.sm_count * 8) rgrid = di.sm_count * 8;
-      if (out_dtype == SGLB200_BF16) {
-        splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(p.partial, static_cast<__nv_bfloat16*>(out),
-                                                                  (int32_t)total_rows, (int32_t)N, ldc, p.k_splits);
-      } else {
-        splitk_reduce_kernel<__half><<<rgrid, 256, 0, st>>>(p.partial, static_cast<__half*>(out), (int32_t)total_rows,
-                                                           (int32_t)N, ldc, p.k_splits);
-      }
+      launch_splitk_reduce(p.partial, out, total_rows, N, ldc, p.k_splits, out_dtype, di.sm_count, stream);
     }
   }
   SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
@@ -861,7 +882,7 @@ extern "C" int64_t sglb200_fp8_blockwise_scaled_mm_workspace_bytes(int64_t M, in
   sglb::DeviceInfo di;
   int sms = 148;
   if (sglb::device_info(&di) == SGLB200_OK) sms = di.sm_count;
-  const int splits = sglb::splitk_choice(M, N, K, sms);
+  const int splits = M <= sglb::smallm_max_rows() ? sglb::smallm_splits(N, K, sms) : sglb::splitk_choice(M, N, K, sms);
   return splits > 1 ? (int64_t)splits * M * N * (int64_t)sizeof(float) : 0;
 }
 
@@ -1044,6 +1065,8 @@ int ue8m0_take_device_status();  // gemm_ue8m0.cu
 extern "C" int sglb200_read_device_status(void) {
   const int u = sglb::ue8m0_take_device_status();
   if (u != 0) return u;
+  const int sm = sglb::smallm_take_device_status();
+  if (sm != 0) return sm;
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, sglb::g_device_status, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();

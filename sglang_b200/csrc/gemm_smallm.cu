@@ -1,0 +1,409 @@
+// Block-scaled FP8 GEMM for few rows of activations (M <= 64: the decode case), weight-streaming bound.
+//
+// The roles of the operands are swapped: the tensor core computes C^T = W * A^T, a tile being 128 WEIGHT rows (the MMA's
+// M) by MT token columns (the MMA's N, MT = 16 / 32 / 64).  An accumulator stage is then only MT TMEM columns wide, so 8 to
+// 16 k-blocks are in flight between the MMA warp and the promotion warps instead of 4, and a shared-memory stage is 16 KB
+// of weights plus MT x 128 bytes of activations, so 8 to 10 stages (128 to 160 KB of weights) are in flight per SM: the
+// kernel is bound by HBM, not by the accumulator hand-off of the 128 x 128 kernel.  K can be cut into ranges that run on
+// different SMs (fp32 partial sums, added by splitk_reduce_kernel) when N / 128 tiles alone cannot occupy the SMs.
+//
+// warp 0: TMA producer; warp 1: TMEM owner + MMA issuer; warps 2..5: promotion (tcgen05.ld, acc += p * sa[token] * sb)
+// and the transposed store.  All waits are bounded.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace sglb {
+
+// device status word of this translation unit (0 = no bounded wait ran out); collected by sglb200_read_device_status
+__device__ int g_smallm_status = 0;
+
+int smallm_take_device_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_smallm_status, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (v != 0) {
+    const int z = 0;
+    cudaMemcpyToSymbol(g_smallm_status, &z, sizeof(int));
+  }
+  return v;
+}
+
+namespace {
+
+constexpr int BN = 128, BK = 128;  // weight rows per tile, K per block
+constexpr int kThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kWBytes = BN * BK;
+constexpr int kScaleAhead = 4;
+
+template <int MT>
+struct Cfg {
+  static constexpr int kStages = MT == 64 ? 8 : 10;
+  static constexpr int kAcc = (512 / MT) < 16 ? (512 / MT) : 16;
+  static constexpr uint32_t kABytes = MT * BK;
+  static constexpr uint32_t kStageBytes = kWBytes + kABytes;
+  static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + 512;
+};
+
+struct SmallParams {
+  const float* sa;
+  const float* sb;
+  void* out;
+  float* partial;  // [splits][M][N] fp32 when k_splits > 1
+  int32_t M, N, K;
+  int32_t n_tiles, k_tiles, k_splits, kb_per_split;
+  int64_t ldc;
+  int64_t sa_stride_m, sa_stride_k, sb_stride_n, sb_stride_k;
+  int32_t out_dtype;
+};
+
+struct Ctl {
+  uint64_t full[10];
+  uint64_t empty[10];
+  uint64_t acc_full[16];
+  uint64_t acc_empty[16];
+  uint32_t tmem_base;
+  volatile int32_t abort_flag;
+};
+static_assert(sizeof(Ctl) <= 512, "control block");
+
+__device__ __forceinline__ void timeout(Ctl* ctl, int code) {
+  ctl->abort_flag = 1;
+  atomicCAS(&g_smallm_status, 0, code);
+}
+
+// 32 lanes x N consecutive fp32 columns
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t* r);
+template <>
+__device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// wait for this thread's outstanding tcgen05.ld; the registers are tied to the statement so that their first use
+// cannot move above it
+template <int N>
+__device__ __forceinline__ void tmem_ld_fence(uint32_t* r) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i])::"memory");
+}
+
+template <int MT>
+__global__ void __launch_bounds__(kThreads, 1)
+fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                             const SmallParams p) {
+  using C = Cfg<MT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  Ctl* ctl = reinterpret_cast<Ctl*>(smem + (size_t)C::kStages * C::kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      ptx::mbar_init(&ctl->full[i], 1);
+      ptx::mbar_init(&ctl->empty[i], 1);
+    }
+    for (int i = 0; i < C::kAcc; ++i) {
+      ptx::mbar_init(&ctl->acc_full[i], 1);
+      ptx::mbar_init(&ctl->acc_empty[i], 4);  // one arrival per promotion warp
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&map_w);
+    ptx::prefetch_tensormap(&map_a);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const int32_t total = p.n_tiles * p.k_splits;
+  const uint32_t full0 = ptx::smem_u32(&ctl->full[0]), empty0 = ptx::smem_u32(&ctl->empty[0]);
+  const uint32_t acc_full0 = ptx::smem_u32(&ctl->acc_full[0]), acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
+  const uint32_t stage0 = ptx::smem_u32(smem);
+
+  if (warp == 0) {
+    // ===== TMA producer
+    uint32_t stage = 0, phase = 0;
+    for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
+      const int32_t split = t / p.n_tiles, nt = t - split * p.n_tiles;
+      const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+      bool ok = true;
+      for (int32_t kb = kb0; kb < kb1; ++kb) {
+        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
+          timeout(ctl, 11);
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          const uint32_t dst = stage0 + stage * C::kStageBytes;
+          ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, C::kStageBytes);
+          ptx::tma_load_2d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN);
+          ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, 0);
+        }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+      if (!ok || ctl->abort_flag) break;
+    }
+    // the last tcgen05.commit arrivals on `empty` must have landed before the CTA's shared memory is reused
+    if (!ctl->abort_flag) {
+      for (int i = 0; i < C::kStages; ++i) {
+        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { timeout(ctl, 15); break; }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer: D[128 weight rows][MT tokens] (+)= W_tile * A_tile^T, one TMEM stage per k-block
+    constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BN, MT);
+    const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+    for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
+      const int32_t split = t / p.n_tiles;
+      const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+      bool ok = true;
+      for (int32_t kb = kb0; kb < kb1; ++kb) {
+        if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) { timeout(ctl, 12); ok = false; break; }
+        if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) { timeout(ctl, 13); ok = false; break; }
+        ptx::tc_fence_after();
+        if (lane == 0) {
+          const uint64_t w_desc = desc0 + (uint64_t)(stage * (C::kStageBytes >> 4));
+          const uint64_t a_desc = w_desc + (kWBytes >> 4);
+          const uint32_t d_tmem = tmem_base + acc * MT;
+          ptx::mma_f8f6f4(d_tmem, w_desc, a_desc, idesc, 0);
+#pragma unroll
+          for (uint32_t k = 1; k < BK / 32; ++k) ptx::mma_f8f6f4(d_tmem, w_desc + 2 * k, a_desc + 2 * k, idesc, 1);
+          ptx::mma_commit_a(empty0 + stage * 8);
+          ptx::mma_commit_a(acc_full0 + acc * 8);
+        }
+        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        if (++acc == C::kAcc) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok || ctl->abort_flag) break;
+    }
+  } else {
+    // ===== promotion + transposed store; TMEM lane quarter = warp % 4 (warps 2, 3, 4, 5 -> quarters 2, 3, 0, 1)
+    const int q = warp & 3;
+    constexpr int kPerLane = MT / 32 > 0 ? MT / 32 : 1;  // tokens whose activation scale this lane fetches
+    uint32_t acc_stage = 0, acc_phase = 0;
+    float acc[MT];
+    for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
+      const int32_t split = t / p.n_tiles, nt = t - split * p.n_tiles;
+      const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+      const int32_t n = nt * BN + q * 32 + lane;
+      const float* sb_blk = p.sb + (int64_t)nt * p.sb_stride_n;
+#pragma unroll
+      for (int j = 0; j < MT; ++j) acc[j] = 0.f;
+      // lane l holds the scale of token l (and l + 32); tokens past M get 0 (their products are 0 anyway)
+      const float* sa_tok[kPerLane];
+      bool tok_ok[kPerLane];
+#pragma unroll
+      for (int h = 0; h < kPerLane; ++h) {
+        const int32_t tok = lane + 32 * h;
+        tok_ok[h] = tok < p.M && tok < MT;
+        sa_tok[h] = p.sa + (int64_t)(tok_ok[h] ? tok : 0) * p.sa_stride_m;
+      }
+      float sa_ring[kScaleAhead][kPerLane], sb_ring[kScaleAhead];
+#pragma unroll
+      for (int u = 0; u < kScaleAhead; ++u) {
+        const int32_t kc = min(kb0 + u, kb1 - 1);
+#pragma unroll
+        for (int h = 0; h < kPerLane; ++h) sa_ring[u][h] = tok_ok[h] ? __ldg(sa_tok[h] + (int64_t)kc * p.sa_stride_k) : 0.f;
+        sb_ring[u] = __ldg(sb_blk + (int64_t)kc * p.sb_stride_k);
+      }
+      bool ok = true;
+      for (int32_t kbb = kb0; kbb < kb1 && ok; kbb += kScaleAhead) {
+#pragma unroll
+        for (int u = 0; u < kScaleAhead; ++u) {
+          const int32_t kb = kbb + u;
+          if (kb >= kb1) break;
+          float s[kPerLane];
+#pragma unroll
+          for (int h = 0; h < kPerLane; ++h) s[h] = sa_ring[u][h] * sb_ring[u];
+          {
+            const int32_t kn = min(kb + kScaleAhead, kb1 - 1);
+#pragma unroll
+            for (int h = 0; h < kPerLane; ++h)
+              sa_ring[u][h] = tok_ok[h] ? __ldg(sa_tok[h] + (int64_t)kn * p.sa_stride_k) : 0.f;
+            sb_ring[u] = __ldg(sb_blk + (int64_t)kn * p.sb_stride_k);
+          }
+          if (!ptx::mbar_wait_a(acc_full0 + acc_stage * 8, acc_phase)) {
+            timeout(ctl, 14);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * MT;
+          uint32_t v[MT];
+          if constexpr (MT == 64) {
+            tmem_ld_cols<32>(taddr, v);
+            tmem_ld_cols<32>(taddr + 32, v + 32);
+          } else {
+            tmem_ld_cols<MT>(taddr, v);
+          }
+          tmem_ld_fence<MT>(v);
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive_a(acc_empty0 + acc_stage * 8);
+#pragma unroll
+          for (int j = 0; j < MT; ++j) {
+            const float sj = __shfl_sync(0xffffffffu, s[j / 32], j & 31);
+            acc[j] = fmaf(__uint_as_float(v[j]), sj, acc[j]);
+          }
+          if (++acc_stage == C::kAcc) { acc_stage = 0; acc_phase ^= 1; }
+        }
+      }
+      if (!ok || ctl->abort_flag) break;
+      // transposed store: for every token the warp writes 32 consecutive outputs
+      if (n < p.N) {
+        if (p.k_splits > 1) {
+          float* dst = p.partial + (int64_t)split * p.M * p.N + n;
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+            if (j < p.M) dst[(int64_t)j * p.N] = acc[j];
+        } else if (p.out_dtype == SGLB200_BF16) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + n;
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+            if (j < p.M) dst[(int64_t)j * p.ldc] = __float2bfloat16_rn(acc[j]);
+        } else {
+          __half* dst = static_cast<__half*>(p.out) + n;
+#pragma unroll
+          for (int j = 0; j < MT; ++j)
+            if (j < p.M) dst[(int64_t)j * p.ldc] = __float2half_rn(acc[j]);
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int MT>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams& p, int sm_count, cudaStream_t st) {
+  static bool done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)Cfg<MT>::kSmem);
+    if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    done[dev] = true;
+  }
+  const int total = p.n_tiles * p.k_splits;
+  const int grid = total < sm_count ? total : sm_count;
+  fp8_block_gemm_smallm_kernel<MT><<<grid, kThreads, Cfg<MT>::kSmem, st>>>(map_w, map_a, p);
+  SGLB_CHECK_LAUNCH("fp8_block_gemm_smallm_kernel");
+  return SGLB200_OK;
+}
+
+}  // namespace
+
+int smallm_max_rows() { return 64; }
+
+// K-splits for a small-M problem.  Cost model in units of one k-block of one work item: a split count s gives
+// ceil(n_tiles * s / SMs) waves of work items, each ceil(k_tiles / s) k-blocks deep plus a fixed cost per item (pipeline
+// fill, store), plus the second kernel that adds the partial sums when s > 1.  The cheapest s wins; ties go to fewer splits.
+int smallm_splits(int64_t N, int64_t K, int sm_count) {
+  const int64_t n_tiles = (N + BN - 1) / BN, k_tiles = (K + BK - 1) / BK;
+  constexpr int64_t kItemCost = 3, kReduceCost = 8;
+  int best = 1;
+  int64_t best_cost = ((n_tiles + sm_count - 1) / sm_count) * (k_tiles + kItemCost);
+  for (int64_t s = 2; s <= 32 && s * 2 <= k_tiles; ++s) {
+    const int64_t kb = (k_tiles + s - 1) / s;
+    const int64_t used = (k_tiles + kb - 1) / kb;  // splits that actually get k-blocks
+    if (used != s) continue;
+    const int64_t cost = ((n_tiles * s + sm_count - 1) / sm_count) * (kb + kItemCost) + kReduceCost;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = (int)s;
+    }
+  }
+  return best;
+}
+
+// Launches the small-M kernel (arguments already validated by the caller).  With `partial` != NULL and splits > 1 the
+// kernel leaves fp32 partial sums [splits][M][N] there and the caller adds them up; *splits_used reports which.
+int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N, int64_t K,
+                int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                int64_t sb_stride_k, int out_dtype, float* partial, int64_t partial_floats, int sm_count, void* stream,
+                int* splits_used) {
+  const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  alignas(64) CUtensorMap map_w, map_a;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t str[1] = {(uint64_t)ldb};
+    if (int rc = make_map_sw128(&map_w, b, 2, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t str[1] = {(uint64_t)lda};
+    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, (uint32_t)MT, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+  }
+  SmallParams p;
+  p.sa = sa;
+  p.sb = sb;
+  p.out = out;
+  p.M = (int32_t)M;
+  p.N = (int32_t)N;
+  p.K = (int32_t)K;
+  p.n_tiles = (int32_t)((N + BN - 1) / BN);
+  p.k_tiles = (int32_t)((K + BK - 1) / BK);
+  p.ldc = ldc;
+  p.sa_stride_m = sa_stride_m;
+  p.sa_stride_k = sa_stride_k;
+  p.sb_stride_n = sb_stride_n;
+  p.sb_stride_k = sb_stride_k;
+  p.out_dtype = out_dtype;
+  p.partial = nullptr;
+  p.k_splits = 1;
+  p.kb_per_split = p.k_tiles;
+  const int splits = smallm_splits(N, K, sm_count);
+  if (partial != nullptr && splits > 1 && (int64_t)splits * M * N <= partial_floats) {
+    p.partial = partial;
+    p.kb_per_split = (p.k_tiles + splits - 1) / splits;
+    p.k_splits = (p.k_tiles + p.kb_per_split - 1) / p.kb_per_split;
+  }
+  *splits_used = p.k_splits;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (MT) {
+    case 16: return launch<16>(map_w, map_a, p, sm_count, st);
+    case 32: return launch<32>(map_w, map_a, p, sm_count, st);
+    default: return launch<64>(map_w, map_a, p, sm_count, st);
+  }
+}
+
+}  // namespace sglb

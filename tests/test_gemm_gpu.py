@@ -126,9 +126,10 @@ def test_linear_method_apply():
 
 
 @pytest.mark.parametrize("M", [1, 16, 64, 128])
-@pytest.mark.parametrize("N,K", [(576, 7168), (7168, 2048), (1536, 4096)])
+@pytest.mark.parametrize("N,K", [(576, 7168), (7168, 8192), (1536, 4096)])
 def test_small_m_split_k(M, N, K):
-    """Small M: the split-K path (fp32 partial sums in a scratch buffer + reduce) against the oracle."""
+    """Small M: the split-K path (fp32 partial sums in a scratch buffer + reduce) against the oracle.  M <= 64 runs
+    the weight-streaming kernel with swapped operands, M = 128 the 128 x 128 kernel."""
     from sglang_b200._lib import lib
     a = make_activations(M, K, seed=M * 3 + N)
     aq, a_s = oracle.per_token_group_quant_fp8(a, 128)
@@ -138,3 +139,47 @@ def test_small_m_split_k(M, N, K):
     out = _run(aq, a_s, wq, ws, m_major=True)
     assert_gemm_close(out, ref, f"split-K M={M} N={N} K={K}")
     assert lib().sglb200_fp8_blockwise_scaled_mm_workspace_bytes(4096, N, K) == 0
+
+
+@pytest.mark.parametrize("M", [2, 16, 17, 32, 33, 48, 64, 65])
+@pytest.mark.parametrize("N,K", [(128, 128), (576, 1024), (1536, 384), (4096, 4096), (7168, 2048)])
+def test_few_rows_kernel_boundaries(M, N, K):
+    """The weight-streaming kernel (M <= 64, token columns padded to 16 / 32 / 64) on both sides of every padding
+    boundary, with ragged N, with and without split-K, both scale layouts; M = 65 is the first size of the 128-row
+    kernel."""
+    a = make_activations(M, K, seed=M * 7 + N + K)
+    aq, a_s = oracle.per_token_group_quant_fp8(a, 128)
+    wq, ws = make_weight(N, K, seed=N * 5 + K)
+    ref = oracle.w8a8_block_fp8_matmul(aq, wq, a_s, ws)
+    out = _run(aq, a_s, wq, ws, m_major=(M % 2 == 0))
+    assert_gemm_close(out, ref, f"few rows M={M} N={N} K={K}")
+    from sglang_b200._lib import check, lib  # the plain entry point: same kernel, never split
+    a_d, w_d, s_d, ws_d = aq.cuda(), wq.cuda(), a_s.cuda(), ws.cuda()
+    out2 = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    check(lib().sglb200_fp8_blockwise_scaled_mm(a_d.data_ptr(), w_d.data_ptr(), s_d.data_ptr(), ws_d.data_ptr(),
+                                                out2.data_ptr(), M, N, K, K, K, N, s_d.stride(0), s_d.stride(1),
+                                                ws_d.stride(0), ws_d.stride(1), 0, torch.cuda.current_stream().cuda_stream),
+          "mm")
+    torch.cuda.synchronize()
+    assert _status() == 0
+    assert_gemm_close(out2, ref, f"few rows, plain entry M={M} N={N} K={K}")
+
+
+def test_few_rows_f16_ragged_k_and_strided_output():
+    M, N, K = 24, 384, 320  # K = 2.5 blocks
+    a = make_activations(M, 384, seed=5)[:, :K].contiguous()
+    aq, a_s = oracle.per_token_group_quant_fp8(torch.nn.functional.pad(a, (0, 64)), 128)
+    aq = aq[:, :K].contiguous()
+    wq, ws = make_weight(N, K, seed=6)
+    ref = oracle.w8a8_block_fp8_matmul(aq, wq, a_s, ws, output_dtype=torch.float16)
+    out = _run(aq, a_s, wq, ws, out_dtype=torch.float16)
+    assert_gemm_close(out, ref, "few rows f16 ragged K")
+    from sglang_b200._lib import check, lib  # output rows 512 elements apart
+    a_d, w_d, s_d, ws_d = aq.cuda(), wq.cuda(), a_s.cuda(), ws.cuda()
+    wide = torch.full((M, 512), 3.0, dtype=torch.float16, device="cuda")
+    check(lib().sglb200_fp8_blockwise_scaled_mm(a_d.data_ptr(), w_d.data_ptr(), s_d.data_ptr(), ws_d.data_ptr(),
+                                                wide.data_ptr(), M, N, K, K, K, 512, s_d.stride(0), s_d.stride(1),
+                                                ws_d.stride(0), ws_d.stride(1), 1, torch.cuda.current_stream().cuda_stream),
+          "mm")
+    torch.cuda.synchronize()
+    assert torch.equal(wide[:, :N], out) and (wide[:, N:] == 3.0).all()

@@ -29,7 +29,7 @@ def test_noalloc_entry_matches_workspace_entry_twice():
     L = lib()
     assert L.sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes() == 16 * 1024 * 1024
     stream = torch.cuda.current_stream().cuda_stream
-    for call, (M, N, K, seed) in enumerate([(16, 7168, 2048, 1), (64, 1536, 4096, 2)]):
+    for call, (M, N, K, seed) in enumerate([(16, 7168, 8192, 1), (64, 1536, 4096, 2)]):
         a = make_activations(M, K, seed=seed)
         aq_c, as_c = oracle.per_token_group_quant_fp8(a, 128)
         wq_c, ws_c = make_weight(N, K, seed=seed + 10)
