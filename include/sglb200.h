@@ -329,6 +329,10 @@ int sglb200_moe_sum_reduce(const void* input, void* output, int64_t num_tokens, 
  * and replayed.  Rules: all ranks issue the same sequence of exchanges, each on ONE stream per rank (the two
  * alternating slot sets are safe exactly because a rank's exchange e + 1 is enqueued after its exchange e); at most
  * 1024 output tiles of 128 x 128; world <= 8.
+ * workspace / workspace_bytes: scratch for M <= 64 (size from sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes; 0 for
+ * larger M).  With it the few-rows weight-streaming kernel computes fp32 sums (K split over the SMs where that pays) and
+ * a second small kernel adds the splits, casts and does the pushing and flagging; without it (NULL) the 128-row kernel
+ * with the push epilogue runs.  Both produce the bits of the corresponding plain entry point.
  * A wait that runs out (a rank that never pushed) leaves its tile unwritten, sets device status 5
  * (sglb200_read_device_status) and does not advance the epoch, so the same exchange can be reduced again once the
  * missing rank has pushed; if only some ranks timed out the group is out of step and the buffers must be set up
@@ -341,7 +345,8 @@ int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b, const flo
                                          int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t sa_stride_m,
                                          int64_t sa_stride_k, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
                                          void* const* peer_recv, void* const* peer_flags, int rank, int world,
-                                         int64_t slot_elems, void* stream);
+                                         int64_t slot_elems, void* workspace, int64_t workspace_bytes, void* stream);
+int64_t sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N, int64_t ldc,
                         int out_dtype, int world, int64_t slot_elems, int64_t timeout_ns, void* stream);
 int64_t sglb200_peer_flag_bytes(void);

@@ -41,7 +41,8 @@ SIGNATURES = {
     "sglb200_moe_align_block_size": [_P, _L, _L, _L, _P, _P, _P, _P, _I, _P],
     "sglb200_moe_sum_reduce": [_P, _P, _L, _L, _L, _I, _F, _P],
     "sglb200_fp8_blockwise_scaled_mm_push": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _P, _I, _I,
-                                             _L, _P],
+                                             _L, _P, _L, _P],
+    "sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes": [_L, _L, _L],
     "sglb200_peer_reduce": [_P, _P, _P, _L, _L, _L, _I, _I, _L, _L, _P],
     "sglb200_peer_completed": [_P, _P],
     "sglb200_peer_flag_bytes": [],
@@ -57,7 +58,7 @@ SIGNATURES = {
 }
 _RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64,
              "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": c_int64,
-             "sglb200_peer_flag_bytes": c_int64, "sglb200_peer_recv_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
+             "sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes": c_int64, "sglb200_peer_flag_bytes": c_int64, "sglb200_peer_recv_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
 
 _lib = None
 

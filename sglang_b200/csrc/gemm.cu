@@ -636,6 +636,52 @@ peer_reduce_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT*
   }
 }
 
+// Sending side for the few-rows kernel: out-of-kernel epilogue of the push exchange.  Adds the fp32 partial sums of the
+// K-splits in ascending order (as splitk_reduce_kernel does), casts, stores the 16-byte vectors into every rank's receive
+// slot and raises the eight flag words of the tile.  One block per 128 x 128 output tile.
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+splitk_reduce_push_kernel(const float* __restrict__ partial, int32_t splits, int32_t M, int32_t N, int32_t n_tiles,
+                          int32_t total_tiles, const PushParams push) {
+  const uint32_t epoch = *reinterpret_cast<const volatile uint32_t*>(push.ctl) + 1u;
+  const uint32_t set = epoch & 1u;
+  const int64_t slot = ((int64_t)set * kMaxPeers + push.rank) * push.slot_elems;
+  for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
+    const int32_t rows = min(BM, M - mt * BM), vecs = min(BN, N - nt * BN) / 8;
+    for (int32_t i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
+      const int32_t r = i / vecs, c = (i - r * vecs) * 8;
+      const int64_t off = (int64_t)(mt * BM + r) * N + nt * BN + c;
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+      for (int32_t sp = 0; sp < splits; ++sp) {
+        const float4* src = reinterpret_cast<const float4*>(partial + (int64_t)sp * M * N + off);
+        const float4 x = __ldcs(src), y = __ldcs(src + 1);
+        a[0] += x.x; a[1] += x.y; a[2] += x.z; a[3] += x.w;
+        a[4] += y.x; a[5] += y.y; a[6] += y.z; a[7] += y.w;
+      }
+      uint4 u;
+      u.x = pack2<OutT>(a[0], a[1]);
+      u.y = pack2<OutT>(a[2], a[3]);
+      u.z = pack2<OutT>(a[4], a[5]);
+      u.w = pack2<OutT>(a[6], a[7]);
+      for (int k = 0; k < push.world; ++k) {  // peers first, this rank last
+        int pr = push.rank + 1 + k;
+        if (pr >= push.world) pr -= push.world;
+        *reinterpret_cast<uint4*>(static_cast<OutT*>(push.dst[pr]) + slot + off) = u;
+      }
+    }
+    // the block barrier orders every thread's stores before the release stores of the flags (release is cumulative)
+    __syncthreads();
+    if ((int)threadIdx.x < push.world * kEpiWarps) {
+      const int pr = threadIdx.x / kEpiWarps, w = threadIdx.x % kEpiWarps;
+      uint32_t* f = push.flag[pr] + (((int64_t)set * kMaxPeers + push.rank) * kPushMaxTiles + t) * kEpiWarps + w;
+      ptx::st_release_sys_u32(f, epoch);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -751,6 +797,25 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
   SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
                di.cc_major, di.cc_minor);
 
+  if (!grouped && push && total_rows <= smallm_max_rows() && workspace != nullptr &&
+      (int64_t)smallm_splits(N, K, di.sm_count) * total_rows * N <= workspace_floats) {
+    // few rows, exchanged: the weight-streaming kernel leaves fp32 sums, a second kernel casts and pushes them
+    int splits = 1;
+    if (int rc = smallm_gemm(a, b, sa, sb, out, total_rows, N, K, lda, ldb, ldc, sa_stride_m, sa_stride_k, sb_stride_n,
+                             sb_stride_k, out_dtype, workspace, workspace_floats, di.sm_count, stream, &splits, true))
+      return rc;
+    const int32_t n_tiles = (int32_t)((N + BN - 1) / BN);
+    const int32_t tiles = (int32_t)((total_rows + BM - 1) / BM) * n_tiles;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (out_dtype == SGLB200_BF16)
+      splitk_reduce_push_kernel<__nv_bfloat16><<<tiles, 256, 0, st>>>(workspace, splits, (int32_t)total_rows, (int32_t)N,
+                                                                     n_tiles, tiles, *push);
+    else
+      splitk_reduce_push_kernel<__half><<<tiles, 256, 0, st>>>(workspace, splits, (int32_t)total_rows, (int32_t)N,
+                                                              n_tiles, tiles, *push);
+    SGLB_CHECK_LAUNCH("splitk_reduce_push_kernel");
+    return SGLB200_OK;
+  }
   if (!grouped && !push && total_rows <= smallm_max_rows()) {
     // few rows: the weight-streaming kernel with swapped operands (gemm_smallm.cu)
     int splits = 1;
@@ -980,6 +1045,14 @@ extern "C" int sglb200_peer_completed(const void* flags_local, int64_t* complete
   return SGLB200_OK;
 }
 
+extern "C" int64_t sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || M > sglb::smallm_max_rows()) return 0;
+  sglb::DeviceInfo di;
+  int sms = 148;
+  if (sglb::device_info(&di) == SGLB200_OK) sms = di.sm_count;
+  return (int64_t)sglb::smallm_splits(N, K, sms) * M * N * (int64_t)sizeof(float);
+}
+
 extern "C" int64_t sglb200_peer_recv_bytes(int64_t slot_elems) {
   return (int64_t)2 * sglb::kMaxPeers * slot_elems * 2;
 }
@@ -1004,7 +1077,8 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
                                                     int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                                                     int64_t sb_stride_k, int out_dtype, void* const* peer_recv,
                                                     void* const* peer_flags, int rank, int world,
-                                                    int64_t slot_elems, void* stream) {
+                                                    int64_t slot_elems, void* workspace, int64_t workspace_bytes,
+                                                    void* stream) {
   using namespace sglb;
   if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
   SGLB_REQUIRE(peer_recv && peer_flags, SGLB200_ERR_NULL, "peer_recv / peer_flags must not be NULL");
@@ -1019,8 +1093,10 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
   push.rank = rank;
   push.ctl = push.flag[rank] + kFlagWords;
   push.slot_elems = slot_elems;
+  SGLB_REQUIRE(workspace == nullptr || aligned(workspace, 16), SGLB200_ERR_ALIGN, "workspace must be 16-byte aligned");
   return gemm_common(a, b, sa, sb, push.dst[rank], nullptr, nullptr, M, 1, N, K, lda, ldb, 0, N, sa_stride_m, sa_stride_k,
-                     0, sb_stride_n, sb_stride_k, out_dtype, stream, nullptr, 0, &push);
+                     0, sb_stride_n, sb_stride_k, out_dtype, stream, static_cast<float*>(workspace),
+                     workspace ? workspace_bytes / (int64_t)sizeof(float) : 0, &push);
 }
 
 extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N,

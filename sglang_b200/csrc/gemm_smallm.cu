@@ -284,7 +284,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
       if (!ok || ctl->abort_flag) break;
       // transposed store: for every token the warp writes 32 consecutive outputs
       if (n < p.N) {
-        if (p.k_splits > 1) {
+        if (p.partial != nullptr) {
           float* dst = p.partial + (int64_t)split * p.M * p.N + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
@@ -356,11 +356,12 @@ int smallm_splits(int64_t N, int64_t K, int sm_count) {
 }
 
 // Launches the small-M kernel (arguments already validated by the caller).  With `partial` != NULL and splits > 1 the
-// kernel leaves fp32 partial sums [splits][M][N] there and the caller adds them up; *splits_used reports which.
+// kernel leaves fp32 partial sums [splits][M][N] there and the caller adds them up; *splits_used reports which.  With
+// always_partial the fp32 sums go to `partial` even for a single split (the caller converts and moves them itself).
 int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                 int64_t sb_stride_k, int out_dtype, float* partial, int64_t partial_floats, int sm_count, void* stream,
-                int* splits_used) {
+                int* splits_used, bool always_partial) {
   const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   alignas(64) CUtensorMap map_w, map_a;
   {
@@ -396,6 +397,8 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
     p.partial = partial;
     p.kb_per_split = (p.k_tiles + splits - 1) / splits;
     p.k_splits = (p.k_tiles + p.kb_per_split - 1) / p.kb_per_split;
+  } else if (always_partial) {
+    p.partial = partial;  // one slice of fp32 sums instead of `out` (the caller checked its size)
   }
   *splits_used = p.k_splits;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -98,15 +98,21 @@ class PeerExchange:
 
 
 def push_mm(ex_recv_arr, ex_flag_arr, rank: int, world: int, slot_elems: int, a_q: torch.Tensor,
-            a_s: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, out_dtype: torch.dtype) -> None:
+            a_s: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, out_dtype: torch.dtype,
+            use_workspace: bool = True) -> None:
     """One rank's half of the exchange: ``a_q [M, K_r]`` e4m3 with scales ``a_s [M, K_r/128]`` times the rank's weight
-    slice ``[N, K_r]``, every output tile stored into all ranks' receive buffers."""
+    slice ``[N, K_r]``, every output tile stored into all ranks' receive buffers.  For ``M <= 64`` a scratch buffer
+    lets the library take the few-rows kernel (``use_workspace=False`` forces the 128-row kernel's push epilogue)."""
     M, K = a_q.shape
     N = weight.shape[0]
-    check(lib().sglb200_fp8_blockwise_scaled_mm_push(
+    L = lib()
+    ws_bytes = L.sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(M, N, K) if use_workspace else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a_q.device) if ws_bytes > 0 else None
+    check(L.sglb200_fp8_blockwise_scaled_mm_push(
         a_q.data_ptr(), weight.data_ptr(), a_s.data_ptr(), weight_scale.data_ptr(), M, N, K, a_q.stride(0),
         weight.stride(0), a_s.stride(0), a_s.stride(1), weight_scale.stride(0), weight_scale.stride(1),
         dtype_code(out_dtype), ex_recv_arr, ex_flag_arr, rank, world, slot_elems,
+        ws.data_ptr() if ws is not None else None, ws_bytes,
         torch.cuda.current_stream(a_q.device).cuda_stream), "fp8_blockwise_scaled_mm_push")
 
 

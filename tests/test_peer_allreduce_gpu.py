@@ -24,22 +24,25 @@ def _buffers(world, slot_elems):
 
 
 def _plain_partial(a_q, a_s, w, ws):
-    """The rank's partial product through the plain entry point without split-K scratch: the same kernel and the same
-    order of additions as the push variant, stored instead of pushed."""
-    from sglang_b200._lib import check, lib
+    """The rank's partial product as the plain entry points compute it: for M <= 64 the few-rows kernel with the
+    library's own K-split (scratch + reduce kernel), above that the 128-row kernel without a split - in both cases the
+    kernel and the order of additions the push variant uses, stored instead of pushed."""
+    from sglang_b200._lib import blockwise_mm, check, lib
     M, K = a_q.shape
     N = w.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
-    check(lib().sglb200_fp8_blockwise_scaled_mm(a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(),
-                                                M, N, K, a_q.stride(0), w.stride(0), out.stride(0), a_s.stride(0),
-                                                a_s.stride(1), ws.stride(0), ws.stride(1), 0,
-                                                torch.cuda.current_stream().cuda_stream), "mm")
+    args = (a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(), M, N, K, a_q.stride(0), w.stride(0),
+            out.stride(0), a_s.stride(0), a_s.stride(1), ws.stride(0), ws.stride(1), 0)
+    if M <= 64:
+        blockwise_mm(*args, a_q.device, torch.cuda.current_stream().cuda_stream)
+    else:
+        check(lib().sglb200_fp8_blockwise_scaled_mm(*args, torch.cuda.current_stream().cuda_stream), "mm")
     return out
 
 
 @pytest.mark.parametrize("world,M,N,K", [(2, 64, 512, 1024), (4, 1, 1024, 2048), (8, 130, 640, 2048), (8, 16, 7168, 2048),
                                          (2, 128, 576, 512), (2, 16, 1024, 8192), (2, 100, 7168, 16384),
-                                         (4, 130, 1152, 8192)])
+                                         (4, 130, 1152, 8192), (2, 33, 7168, 16384), (8, 64, 576, 8192)])
 def test_push_and_reduce_emulated_ranks(world, M, N, K):
     from sglang_b200._lib import lib
     from sglang_b200.distributed.peer_allreduce import peer_reduce, push_mm
@@ -73,6 +76,20 @@ def test_push_and_reduce_emulated_ranks(world, M, N, K):
         # the tensor-parallel semantic: every rank rounds its partial sum to bf16, then the partial sums are added
         # (python/sglang/srt/layers/linear.py:1361-1386); the oracle does the same on the K-slices
         assert_gemm_close(outs[0], row_parallel_reference(x, wq, ws, world), f"epoch {epoch}")
+    if M <= 64:  # the other route for few rows: the 128-row kernel's push epilogue (no scratch buffer)
+        for r in range(world):
+            a_q, a_s = sglang_per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous().cuda(), 128)
+            push_mm(recv_arr, flag_arr, r, world, slot, a_q, a_s, shards[r][0], shards[r][1], torch.bfloat16,
+                    use_workspace=False)
+        outs = []
+        for r in range(world):
+            out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+            peer_reduce(recv[r].data_ptr(), flags[r].data_ptr(), out, world, slot)
+            outs.append(out)
+        torch.cuda.synchronize()
+        assert lib().sglb200_read_device_status() == 0
+        assert all(torch.equal(o, outs[0]) for o in outs)
+        assert_gemm_close(outs[0], row_parallel_reference(x, wq, ws, world), "push epilogue route")
 
 
 def test_reduce_wait_runs_out_and_reports():
