@@ -205,6 +205,50 @@ def moe_section(torch, dev, gen, M=4096, E=256, topk=8, H=7168, I=2048):
             "kernels_per_call": 9}
 
 
+def decode_section(torch, dev, peaks):
+    """The five layers at decode batch sizes (M = 1, 16, 64): weight streaming, HBM-bound.  Each measurement is one
+    CUDA graph holding one GEMM call per weight copy (enough copies that the working set exceeds L2), replayed ten
+    times back to back; reported per call."""
+    from sglang_b200.layers.quantization import w8a8_block_fp8_matmul
+    out = {"workload": "block-FP8 linear at M = 1 / 16 / 64, per-call device time inside a replayed CUDA graph over "
+                       "rotating weight copies (working set > L2)", "unit": "us", "peak_gbs": peaks["hbm_gbs"],
+           "cases": []}
+    for name, N, K, _ in SHAPES:
+        copies = max(4, min(32, int(400e6 // (N * K)) + 1))
+        ws_ = [torch.randint(-60, 60, (N, K), device=dev, dtype=torch.int8).view(torch.float8_e4m3fn) for _ in range(copies)]
+        sc = torch.rand(-(-N // 128), K // 128, device=dev) * 0.01
+        for M in (1, 16, 64):
+            a = torch.randint(-60, 60, (M, K), device=dev, dtype=torch.int8).view(torch.float8_e4m3fn)
+            sa = torch.rand(M, K // 128, device=dev)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for w in ws_[:2]:
+                    w8a8_block_fp8_matmul(a, w, sa, sc, [128, 128], torch.bfloat16)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for w in ws_:
+                    w8a8_block_fp8_matmul(a, w, sa, sc, [128, 128], torch.bfloat16)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / 10 / copies
+            nbytes = N * K + N * K / 16384 * 4 + M * K + M * K / 128 * 4 + 2 * M * N
+            out["cases"].append({"layer": name, "N": N, "K": K, "M": M, "us": us, "gbs": nbytes / us / 1e3,
+                                 "frac": nbytes / us / 1e3 / peaks["hbm_gbs"]})
+            del graph
+        del ws_
+        torch.cuda.empty_cache()
+    return out
+
+
 def fused_allreduce_section(torch, dist, dev, world, rank, layers, iters=30):
     """Row-parallel layers at decode batch sizes: quant + GEMM + NCCL all-reduce against quant + GEMM with the push
     epilogue + peer reduce (no NCCL).  Device time per layer call, max over ranks, median over `iters` calls."""
@@ -551,6 +595,14 @@ def main():
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps,
            "api": "Fp8LinearMethod.apply on pinned-host activations, result copied back to pinned host"}
 
+    decode = None
+    if rank == 0 and world == 1:
+        try:
+            decode = decode_section(torch, dev, peaks)
+        except Exception as e:  # noqa: BLE001 - the headline must not depend on this section
+            decode = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
+
     fused_ar = None
     if world > 1:
         try:
@@ -567,7 +619,7 @@ def main():
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks,
                 "e2e": e2e, "gpu_launches": args.steps * len(layers) * 2, "roofline": roofline,
-                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "ue8m0": ue8m0, "fused_allreduce": fused_ar,
+                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "ue8m0": ue8m0, "decode": decode, "fused_allreduce": fused_ar,
                 "impl": "ours"}
         print(json.dumps(line))
     if world > 1:
