@@ -205,7 +205,7 @@ def moe_section(torch, dev, gen, M=4096, E=256, topk=8, H=7168, I=2048):
             "kernels_per_call": 9}
 
 
-def decode_section(torch, dev, peaks):
+def decode_section(torch, dev, peaks, shapes=None, ms=(1, 16, 64)):
     """The five layers at decode batch sizes (M = 1, 16, 64): weight streaming, HBM-bound.  Each measurement is one
     CUDA graph holding one GEMM call per weight copy (enough copies that the working set exceeds L2), replayed ten
     times back to back; reported per call."""
@@ -213,11 +213,11 @@ def decode_section(torch, dev, peaks):
     out = {"workload": "block-FP8 linear at M = 1 / 16 / 64, per-call device time inside a replayed CUDA graph over "
                        "rotating weight copies (working set > L2)", "unit": "us", "peak_gbs": peaks["hbm_gbs"],
            "cases": []}
-    for name, N, K, _ in SHAPES:
+    for name, N, K, _ in (shapes or SHAPES):
         copies = max(4, min(32, int(400e6 // (N * K)) + 1))
         ws_ = [torch.randint(-60, 60, (N, K), device=dev, dtype=torch.int8).view(torch.float8_e4m3fn) for _ in range(copies)]
         sc = torch.rand(-(-N // 128), K // 128, device=dev) * 0.01
-        for M in (1, 16, 64):
+        for M in ms:
             a = torch.randint(-60, 60, (M, K), device=dev, dtype=torch.int8).view(torch.float8_e4m3fn)
             sa = torch.rand(M, K // 128, device=dev)
             side = torch.cuda.Stream()
@@ -324,8 +324,9 @@ def main():
     ap.add_argument("--cpu-m", type=int, default=1024, help="rows of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE section (11.3 GB of expert weights)")
-    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant", "ue8m0"],
-                    help="profiling aid: run only the linear sweep ('gemm') or only the quant bandwidth case")
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant", "ue8m0", "decode"],
+                    help="profiling aid: run only the linear sweep ('gemm'), the quant bandwidth case, the UE8M0 sweep "
+                         "or the decode-size section (with --shape and --m for one case)")
     ap.add_argument("--shape", default=None, help="profiling aid: restrict the sweep to one layer name")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -364,6 +365,11 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     peaks = load_peaks()
     M = args.m
+    if args.only == "decode":
+        sel = [sh for sh in SHAPES if args.shape in (None, sh[0])]
+        ms_sel = (args.m,) if args.m <= 64 else (1, 16, 64)
+        print(json.dumps({"metric": METRIC, "only": "decode", "decode": decode_section(torch, dev, peaks, sel, ms_sel)}))
+        return
 
     # ---- synthetic layers, sharded for this rank
     method = Fp8LinearMethod(Fp8Config(), tp_size=world)
