@@ -205,6 +205,78 @@ def moe_section(torch, dev, gen, M=4096, E=256, topk=8, H=7168, I=2048):
             "kernels_per_call": 9}
 
 
+def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5):
+    """Tensor-parallel decoder projections at the Llama-3-70B shape (hidden 8192, intermediate 28672, 64 q / 8 kv
+    heads of 128): column-parallel QKV and gate_up, row-parallel o and down, each followed by an NCCL all-reduce of the
+    [M, 8192] bf16 output.  One step = the four linears of a layer on M tokens; device time, max over ranks."""
+    from sglang_b200.layers.quantization import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+    layers_ = [("qkv", 10240, 8192, "column"), ("o", 8192, 8192, "row"), ("gate_up", 57344, 8192, "column"),
+               ("down", 8192, 28672, "row")]
+    built, flops = [], 0.0
+    for name, N, K, mode in layers_:
+        n_loc, k_loc = (N // world, K) if mode == "column" else (N, K // world)
+        w = (torch.randn(n_loc, k_loc, device=dev, generator=gen) * 20).to(torch.float8_e4m3fn)
+        ws = torch.rand(n_loc // 128, k_loc // 128, device=dev, generator=gen) * 1e-3
+        x = torch.randn(M, k_loc, device=dev, generator=gen).bfloat16()
+        built.append((mode, w, ws, x))
+        flops += 2.0 * M * N * K
+
+    def step():
+        for mode, w, ws, x in built:
+            q, sc = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
+            y = w8a8_block_fp8_matmul(q, w, sc, ws, [128, 128], torch.bfloat16)
+            if mode == "row":
+                dist.all_reduce(y)
+
+    for _ in range(3):
+        step()
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return {"workload": f"Llama-3-70B layer projections, M={M}, tp{world}: qkv/gate_up column-parallel, o/down "
+                        "row-parallel + NCCL all-reduce", "ms_per_layer": float(ms),
+            "tflops": flops / (float(ms) * 1e-3) / 1e12, "allreduce_bytes_per_layer": 2 * M * 8192 * 2}
+
+
+def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk=8, H=7168, I=2048, iters=5):
+    """Expert-parallel fused MoE at the DeepSeek-V3 layer shape: E / ep experts and M_total / ep tokens per rank,
+    all-to-all dispatch of e4m3 rows + scales, local grouped GEMMs, all-to-all combine.  Device time, max over ranks."""
+    from sglang_b200.distributed import ep_fused_experts
+    el, m_loc = E // world, M_total // world
+    w1 = (torch.randn(el, 2 * I, H, device=dev, generator=gen) * 20).to(torch.float8_e4m3fn)
+    w2 = (torch.randn(el, H, I, device=dev, generator=gen) * 20).to(torch.float8_e4m3fn)
+    w1s = torch.rand(el, 2 * I // 128, H // 128, device=dev, generator=gen) * 1e-3
+    w2s = torch.rand(el, H // 128, I // 128, device=dev, generator=gen) * 1e-3
+    a = torch.randn(m_loc, H, device=dev, generator=gen).bfloat16()
+    tw, ti = torch.topk(torch.softmax(torch.randn(m_loc, E, device=dev, generator=gen), -1), topk)
+    ti = ti.to(torch.int32)
+    for _ in range(2):
+        ep_fused_experts(a, w1, w2, w1s, w2s, tw, ti, rank, world)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        ep_fused_experts(a, w1, w2, w1s, w2s, tw, ti, rank, world)
+    e1.record()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    flops = M_total * topk * (2.0 * H * 2 * I + 2.0 * I * H)
+    return {"workload": f"fused MoE E={E} top{topk} H={H} I={I}, {M_total} tokens over ep{world} ({m_loc} per rank), "
+                        "NCCL all-to-all dispatch/combine with host-side count exchange", "ms": float(ms),
+            "tflops": flops / (float(ms) * 1e-3) / 1e12}
+
+
 def decode_section(torch, dev, peaks, shapes=None, ms=(1, 16, 64)):
     """The five layers at decode batch sizes (M = 1, 16, 64): weight streaming, HBM-bound.  Each measurement is one
     CUDA graph holding one GEMM call per weight copy (enough copies that the working set exceeds L2), replayed ten
@@ -616,6 +688,26 @@ def main():
         except Exception as e:  # noqa: BLE001 - the headline must not depend on this section
             fused_ar = {"error": f"{type(e).__name__}: {e}"}
 
+    tp_llama, ep_moe = None, None
+    if world > 1:
+        for L in layers:  # free the sweep's weights first
+            L.clear()
+        layers_n = len(layers)
+        torch.cuda.empty_cache()
+        try:
+            tp_llama = tp_llama_section(torch, dist, dev, gen, world, rank)
+        except Exception as e:  # noqa: BLE001
+            tp_llama = {"error": f"{type(e).__name__}: {e}"}
+        torch.cuda.empty_cache()
+        if not args.no_moe:
+            try:
+                ep_moe = ep_moe_section(torch, dist, dev, gen, world, rank)
+            except Exception as e:  # noqa: BLE001
+                ep_moe = {"error": f"{type(e).__name__}: {e}"}
+            torch.cuda.empty_cache()
+    else:
+        layers_n = len(layers)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cpu_baseline = cpu_arm(3, 1, args.cpu_m)
@@ -624,8 +716,8 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks,
-                "e2e": e2e, "gpu_launches": args.steps * len(layers) * 2, "roofline": roofline,
-                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "ue8m0": ue8m0, "decode": decode, "fused_allreduce": fused_ar,
+                "e2e": e2e, "gpu_launches": args.steps * layers_n * 2, "roofline": roofline,
+                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "ue8m0": ue8m0, "decode": decode, "fused_allreduce": fused_ar, "tp_llama70b": tp_llama, "ep_moe": ep_moe,
                 "impl": "ours"}
         print(json.dumps(line))
     if world > 1:
