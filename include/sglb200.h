@@ -164,6 +164,22 @@ int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const int32_t* sfa
                                 int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream);
 
 /*
+ * MG with UE8M0 scales: the kernel above with the expert tile scheduler of
+ * sglb200_fp8_blockwise_scaled_grouped_mm.  Rows of expert e are [expert_offsets[e], expert_offsets[e + 1])
+ * (num_experts + 1 entries); b [num_experts, N, K] with strides ldb (row) and ldb_e (expert);
+ * sfa word (row, kg) at sfa[row * sfa_stride_m + kg * sfa_stride_k] (row-major after a row shuffle, or the quantiser's
+ * column-major layout); sfb word (e, nb, kg) at sfb[e * sfb_stride_e + nb * sfb_stride_n + kg * sfb_stride_k].
+ * Replaces: the grouped DeepGEMM calls of the reference's Blackwell MoE route with UE8M0 scales
+ *           (python/sglang/srt/layers/moe/moe_runner/deep_gemm.py:131-207: m_grouped_fp8_gemm_nt_contiguous via
+ *           deep_gemm_wrapper/entrypoint.py:52-66), with expert offsets instead of a per-row expert index.
+ */
+int sglb200_fp8_ue8m0_scaled_grouped_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb, void* out,
+                                        const int32_t* expert_offsets, int64_t total_rows, int64_t num_experts,
+                                        int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldb_e, int64_t ldc,
+                                        int64_t sfa_stride_m, int64_t sfa_stride_k, int64_t sfb_stride_e,
+                                        int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream);
+
+/*
  * MG — grouped (per-expert) block-scaled FP8 GEMM over rows sorted by expert.
  * Replaces: fp8_blockwise_scaled_grouped_mm  sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:650-810
  *           and its pointer-table helper sgl-kernel/csrc/moe/cutlass_moe_helper.cu:17-142

@@ -64,15 +64,18 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSfTmemBase = 2 * BN;  // 448: scale columns start after the two accumulators
 constexpr uint32_t kSfTmemPerSet = 12;    // 4 columns for A's scales + 8 for B's (224 rows -> two copies of 128)
 constexpr int kGroupM = 16;
-constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + (size_t)kSfBufs * kSfBufBytes + 256;
+constexpr int kMaxExperts = 1024;
+constexpr size_t kSmemBytes = 1024 + (size_t)kStages * kStageBytes + (size_t)kSfBufs * kSfBufBytes + 256 +
+                              (kMaxExperts + 1) * sizeof(int32_t);
 
 struct Params {
-  const int32_t* sfa;  // packed exponents of A: word (m, kg) at sfa[kg * sfa_ld + m]
-  const int32_t* sfb;  // packed exponents of B: word (nb, kg) at sfb[nb * sfb_stride_n + kg * sfb_stride_k]
+  const int32_t* sfa;  // packed exponents of A: word (m, kg) at sfa[kg * sfa_ld + m * sfa_stride_m]
+  const int32_t* sfb;  // of B: word (e, nb, kg) at sfb[e * sfb_stride_e + nb * sfb_stride_n + kg * sfb_stride_k]
   void* out;
-  int32_t M, N, K;
+  const int32_t* expert_offsets;  // grouped: rows of expert e are [expert_offsets[e], expert_offsets[e + 1])
+  int32_t M, N, K, num_experts;   // M = total rows of a / out
   int32_t m_tiles, n_tiles, k_tiles, k_groups;
-  int64_t ldc, sfa_ld, sfb_stride_n, sfb_stride_k;
+  int64_t ldc, sfa_ld, sfa_stride_m, sfb_stride_e, sfb_stride_n, sfb_stride_k;
   int32_t out_dtype;
 };
 
@@ -85,17 +88,45 @@ struct Ctl {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   volatile int32_t abort_flag;
+  int32_t total_tiles;
+};
+static_assert(sizeof(Ctl) <= 256, "control block");
+
+struct TileUe {
+  int32_t m0, row_end, n0, expert;
 };
 
-__device__ __forceinline__ void tile_coords(const Params& p, int32_t t, int32_t& m0, int32_t& n0) {
-  const int32_t per_group = kGroupM * p.n_tiles;
-  const int32_t gid = t / per_group;
-  const int32_t first_m = gid * kGroupM;
-  const int32_t gm = min(p.m_tiles - first_m, kGroupM);
-  const int32_t local = t - gid * per_group;
-  const int32_t nt = local / gm;
-  m0 = (first_m + (local - nt * gm)) * BM;
-  n0 = nt * BN;
+// dense: grouped-M raster; grouped: tile table of the experts (prefix sums in shared memory), n-major inside an expert
+template <bool GROUPED>
+__device__ __forceinline__ TileUe tile_coords(const Params& p, const int32_t* tile_start, int32_t t) {
+  TileUe tl;
+  if constexpr (!GROUPED) {
+    const int32_t per_group = kGroupM * p.n_tiles;
+    const int32_t gid = t / per_group;
+    const int32_t first_m = gid * kGroupM;
+    const int32_t gm = min(p.m_tiles - first_m, kGroupM);
+    const int32_t local = t - gid * per_group;
+    const int32_t nt = local / gm;
+    tl.m0 = (first_m + (local - nt * gm)) * BM;
+    tl.row_end = p.M;
+    tl.n0 = nt * BN;
+    tl.expert = 0;
+  } else {
+    int32_t lo = 0, hi = p.num_experts;  // last e with tile_start[e] <= t
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (tile_start[mid] <= t) lo = mid; else hi = mid;
+    }
+    const int32_t r0 = __ldg(p.expert_offsets + lo), r1 = __ldg(p.expert_offsets + lo + 1);
+    const int32_t me = (r1 - r0 + BM - 1) / BM;
+    const int32_t local = t - tile_start[lo];
+    const int32_t nt = local / me;
+    tl.m0 = r0 + (local - nt * me) * BM;
+    tl.row_end = r1;
+    tl.n0 = nt * BN;
+    tl.expert = lo;
+  }
+  return tl;
 }
 
 __device__ __forceinline__ void timeout(Ctl* ctl, int code) {
@@ -141,6 +172,7 @@ __device__ __forceinline__ void store32(const uint32_t (&a)[32], const uint32_t 
   }
 }
 
+template <bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const Params p) {
@@ -148,6 +180,7 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sf_smem = smem + (size_t)kStages * kStageBytes;
   Ctl* ctl = reinterpret_cast<Ctl*>(sf_smem + (size_t)kSfBufs * kSfBufBytes);
+  int32_t* tile_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(ctl) + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -175,11 +208,36 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
+  if constexpr (GROUPED) {
+    if (warp == 0) {  // exclusive prefix sum of tiles per expert
+      int32_t running = 0;
+      for (int32_t base = 0; base < p.num_experts; base += 32) {
+        const int32_t e = base + lane;
+        int32_t v = 0;
+        if (e < p.num_experts)
+          v = ((__ldg(p.expert_offsets + e + 1) - __ldg(p.expert_offsets + e) + BM - 1) / BM) * p.n_tiles;
+        int32_t incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += o;
+        }
+        if (e < p.num_experts) tile_start[e] = running + incl - v;
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) {
+        tile_start[p.num_experts] = running;
+        ctl->total_tiles = running;
+      }
+    }
+  } else {
+    if (threadIdx.x == 0) ctl->total_tiles = p.m_tiles * p.n_tiles;
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
-  const int32_t total_tiles = p.m_tiles * p.n_tiles;
+  const int32_t total_tiles = ctl->total_tiles;
 
   const uint32_t full0 = ptx::smem_u32(&ctl->full[0]);
   const uint32_t empty0 = ptx::smem_u32(&ctl->empty[0]);
@@ -194,8 +252,7 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // ===== TMA producers
     uint32_t stage = 0, phase = 0, g = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      int32_t m0, n0;
-      tile_coords(p, t, m0, n0);
+      const TileUe tl = tile_coords<GROUPED>(p, tile_start, t);
       bool ok = true;
       for (int32_t kb = 0; kb < p.k_tiles; ++kb, ++g) {
         if ((g & 1) == (uint32_t)warp) {
@@ -207,8 +264,8 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           if (lane == 0) {
             const uint32_t dst = stage0 + stage * kStageBytes;
             ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
-            ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, m0);
-            ptx::tma_load_2d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, n0);
+            ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.m0);
+            ptx::tma_load_3d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, tl.n0, tl.expert);
           }
         }
         if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -278,8 +335,8 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int32_t nb_last = (p.N + 127) / 128 - 1;
     uint32_t q = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-      int32_t m0, n0;
-      tile_coords(p, t, m0, n0);
+      const TileUe tl = tile_coords<GROUPED>(p, tile_start, t);
+      const int32_t m0 = tl.m0, n0 = tl.n0;
       bool ok = true;
       for (int32_t kg = 0; kg < p.k_groups; ++kg, ++q) {
         const uint32_t buf = q % kSfBufs;
@@ -291,12 +348,12 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         uint8_t* dst = sf_smem + (size_t)buf * kSfBufBytes;
         const int32_t* a_col = p.sfa + (int64_t)kg * p.sfa_ld;
         uint4 va;
-        va.x = (uint32_t)__ldg(a_col + min(m0 + lane, p.M - 1));
-        va.y = (uint32_t)__ldg(a_col + min(m0 + 32 + lane, p.M - 1));
-        va.z = (uint32_t)__ldg(a_col + min(m0 + 64 + lane, p.M - 1));
-        va.w = (uint32_t)__ldg(a_col + min(m0 + 96 + lane, p.M - 1));
+        va.x = (uint32_t)__ldg(a_col + (int64_t)min(m0 + lane, p.M - 1) * p.sfa_stride_m);
+        va.y = (uint32_t)__ldg(a_col + (int64_t)min(m0 + 32 + lane, p.M - 1) * p.sfa_stride_m);
+        va.z = (uint32_t)__ldg(a_col + (int64_t)min(m0 + 64 + lane, p.M - 1) * p.sfa_stride_m);
+        va.w = (uint32_t)__ldg(a_col + (int64_t)min(m0 + 96 + lane, p.M - 1) * p.sfa_stride_m);
         reinterpret_cast<uint4*>(dst)[lane] = va;
-        const int32_t* b_col = p.sfb + (int64_t)kg * p.sfb_stride_k;
+        const int32_t* b_col = p.sfb + (int64_t)tl.expert * p.sfb_stride_e + (int64_t)kg * p.sfb_stride_k;
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           uint4 vb;
@@ -324,8 +381,8 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int col0 = ((warp - kEpiWarp0) >> 2) * kEpiCols;
     uint32_t tile_i = 0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_i) {
-      int32_t m0, n0;
-      tile_coords(p, t, m0, n0);
+      const TileUe tl = tile_coords<GROUPED>(p, tile_start, t);
+      const int32_t m0 = tl.m0, n0 = tl.n0;
       const uint32_t as = tile_i & 1;
       if (!ptx::mbar_wait_a(acc_full0 + as * 8, (tile_i >> 1) & 1)) {
         timeout(ctl, 16);
@@ -347,7 +404,7 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive_a(acc_empty0 + as * 8);
         }
-        if (row < p.M) {
+        if (row < tl.row_end) {
           const int32_t n_first = n0 + col0 + c * 32;
           const int32_t n_limit = min(p.N, n0 + col0 + kEpiCols);  // do not store beyond this warp's 112 columns
           if (p.out_dtype == SGLB200_BF16) {
@@ -371,38 +428,6 @@ fp8_ue8m0_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   }
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess) {
-      cudaGetLastError();
-      ptr = nullptr;
-    }
-    return reinterpret_cast<EncodeTiledFn>(ptr);
-  }();
-  return fn;
-}
-
-int make_map2d(CUtensorMap* map, const void* base, uint64_t k, uint64_t rows, uint64_t ld, uint32_t box_rows,
-               CUtensorMapL2promotion promo) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available from the CUDA driver");
-  cuuint64_t gdim[2] = {k, rows};
-  cuuint64_t gstr[1] = {ld};
-  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), gdim, gstr, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(SGLB200_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return SGLB200_OK;
-}
-
 }  // namespace
 }  // namespace sglb
 
@@ -413,10 +438,13 @@ extern "C" int sglb200_debug_set_status_mirror(int* device_visible_host_ptr) {
   return (int)cudaMemcpyToSymbol(g_ue8m0_mirror, &device_visible_host_ptr, sizeof(int*));
 }
 
-extern "C" int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb,
-                                           void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                                           int64_t ldc, int64_t sfa_ld, int64_t sfb_stride_n, int64_t sfb_stride_k,
-                                           int out_dtype, void* stream) {
+namespace sglb {
+namespace {
+int ue8m0_common(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb, void* out,
+                 const int32_t* expert_offsets, int64_t M, int64_t num_experts, int64_t N, int64_t K, int64_t lda,
+                 int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sfa_ld, int64_t sfa_stride_m, int64_t sfb_stride_e,
+                 int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream) {
+  const bool grouped = expert_offsets != nullptr;
   SGLB_REQUIRE(M >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size", (long long)M,
                (long long)N, (long long)K);
   SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE,
@@ -426,56 +454,104 @@ extern "C" int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const i
   SGLB_REQUIRE(K > 0 || M == 0 || N == 0, SGLB200_ERR_SHAPE, "K must be positive");
   SGLB_REQUIRE(K % 16 == 0, SGLB200_ERR_SHAPE, "K=%lld must be a multiple of 16", (long long)K);
   SGLB_REQUIRE(N % 8 == 0, SGLB200_ERR_SHAPE, "N=%lld must be a multiple of 8 (16-byte output rows)", (long long)N);
+  if (grouped)
+    SGLB_REQUIRE(num_experts >= 1 && num_experts <= kMaxExperts, SGLB200_ERR_SHAPE, "num_experts=%lld: 1..%d",
+                 (long long)num_experts, kMaxExperts);
   if (M == 0 || N == 0) return SGLB200_OK;
   SGLB_REQUIRE(a && b && sfa && sfb && out, SGLB200_ERR_NULL, "a/b/sfa/sfb/out must not be NULL");
   SGLB_REQUIRE(lda >= K && lda % 16 == 0 && ldb >= K && ldb % 16 == 0, SGLB200_ERR_ALIGN,
                "lda=%lld / ldb=%lld must be >= K and multiples of 16", (long long)lda, (long long)ldb);
+  SGLB_REQUIRE(!grouped || (ldb_e % 16 == 0 && ldb_e >= ldb), SGLB200_ERR_ALIGN,
+               "ldb_e=%lld must be a multiple of 16 and >= ldb", (long long)ldb_e);
   SGLB_REQUIRE(ldc >= N && (ldc * 2) % 16 == 0, SGLB200_ERR_ALIGN, "ldc=%lld must be >= N and a multiple of 8",
                (long long)ldc);
   SGLB_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(out, 16) && aligned(sfa, 4) && aligned(sfb, 4),
                SGLB200_ERR_ALIGN, "a, b, out must be 16-byte aligned and the scale pointers 4-byte aligned");
-  SGLB_REQUIRE(sfa_ld >= M, SGLB200_ERR_SHAPE, "sfa_ld=%lld must be >= M (scale words of a row group are contiguous)",
-               (long long)sfa_ld);
+  SGLB_REQUIRE(sfa_stride_m >= 1 && sfa_ld >= 1, SGLB200_ERR_SHAPE, "sfa_ld=%lld sfa_stride_m=%lld", (long long)sfa_ld,
+               (long long)sfa_stride_m);
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
   SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
                di.cc_major, di.cc_minor);
 
   alignas(64) CUtensorMap map_a, map_b;
-  if (int rc = make_map2d(&map_a, a, (uint64_t)K, (uint64_t)M, (uint64_t)lda, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
-    return rc;
-  if (int rc = make_map2d(&map_b, b, (uint64_t)K, (uint64_t)N, (uint64_t)ldb, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B))
-    return rc;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t str[1] = {(uint64_t)lda};
+    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, grouped ? (uint64_t)num_experts : 1};
+    const uint64_t str[2] = {(uint64_t)ldb, grouped ? (uint64_t)ldb_e : (uint64_t)ldb * (uint64_t)N};
+    if (int rc = make_map_sw128(&map_b, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+  }
 
   Params p;
   p.sfa = sfa;
   p.sfb = sfb;
   p.out = out;
+  p.expert_offsets = expert_offsets;
   p.M = (int32_t)M;
   p.N = (int32_t)N;
   p.K = (int32_t)K;
+  p.num_experts = grouped ? (int32_t)num_experts : 1;
   p.m_tiles = (int32_t)((M + BM - 1) / BM);
   p.n_tiles = (int32_t)((N + BN - 1) / BN);
   p.k_tiles = (int32_t)((K + BK - 1) / BK);
   p.k_groups = (p.k_tiles + 3) / 4;
   p.ldc = ldc;
   p.sfa_ld = sfa_ld;
+  p.sfa_stride_m = sfa_stride_m;
+  p.sfb_stride_e = grouped ? sfb_stride_e : 0;
   p.sfb_stride_n = sfb_stride_n;
   p.sfb_stride_k = sfb_stride_k;
   p.out_dtype = out_dtype;
 
-  static bool attr_done[64] = {false};
+  static bool attr_done[2][64] = {{false}};
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_ue8m0_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBytes);
+  if (dev >= 0 && dev < 64 && !attr_done[grouped][dev]) {
+    cudaError_t e = grouped ? cudaFuncSetAttribute(fp8_ue8m0_gemm_kernel<true>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes)
+                            : cudaFuncSetAttribute(fp8_ue8m0_gemm_kernel<false>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    attr_done[dev] = true;
+    attr_done[grouped][dev] = true;
   }
-  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
-  const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-  fp8_ue8m0_gemm_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(map_a, map_b, p);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (grouped) {
+    // an upper bound on the tile count without reading the device: every expert can add one ragged m-tile
+    const int64_t max_tiles = ((M + BM - 1) / BM + num_experts) * p.n_tiles;
+    const int grid = (int)(max_tiles < di.sm_count ? max_tiles : di.sm_count);
+    fp8_ue8m0_gemm_kernel<true><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+  } else {
+    const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+    const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
+    fp8_ue8m0_gemm_kernel<false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, p);
+  }
   SGLB_CHECK_LAUNCH("fp8_ue8m0_gemm_kernel");
   return SGLB200_OK;
+}
+}  // namespace
+}  // namespace sglb
+
+extern "C" int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb,
+                                           void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                           int64_t ldc, int64_t sfa_ld, int64_t sfb_stride_n, int64_t sfb_stride_k,
+                                           int out_dtype, void* stream) {
+  SGLB_REQUIRE(sfa_ld >= M, SGLB200_ERR_SHAPE, "sfa_ld=%lld must be >= M (scale words of a row group are contiguous)",
+               (long long)sfa_ld);
+  return sglb::ue8m0_common(a, b, sfa, sfb, out, nullptr, M, 1, N, K, lda, ldb, 0, ldc, sfa_ld, 1, 0, sfb_stride_n,
+                            sfb_stride_k, out_dtype, stream);
+}
+
+extern "C" int sglb200_fp8_ue8m0_scaled_grouped_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb,
+                                                   void* out, const int32_t* expert_offsets, int64_t total_rows,
+                                                   int64_t num_experts, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                                   int64_t ldb_e, int64_t ldc, int64_t sfa_stride_m, int64_t sfa_stride_k,
+                                                   int64_t sfb_stride_e, int64_t sfb_stride_n, int64_t sfb_stride_k,
+                                                   int out_dtype, void* stream) {
+  SGLB_REQUIRE(expert_offsets != nullptr, SGLB200_ERR_NULL, "expert_offsets must not be NULL");
+  return sglb::ue8m0_common(a, b, sfa, sfb, out, expert_offsets, total_rows, num_experts, N, K, lda, ldb, ldb_e, ldc,
+                            sfa_stride_k, sfa_stride_m, sfb_stride_e, sfb_stride_n, sfb_stride_k, out_dtype, stream);
 }

@@ -189,3 +189,60 @@ def fused_experts_masked(hidden_states: torch.Tensor, hidden_states_scale: torch
     grouped_gemm_nt_f8f8bf16_masked((down_q.view(E, max_m, two_i // 2), down_s.view(E, max_m, two_i // 256)),
                                     (w2_weight, w2_scale), out, masked_m, expected_m)
     return out
+
+
+def _grouped_mm_ue8m0(a_q, a_sf, w, w_sf, out, expert_offsets):
+    """``out[rows of e] = a_q[rows of e] @ w[e].T`` with power-of-two scales applied by the tensor core; ``a_sf
+    [rows, ceil(K/512)]`` int32 in any strides, ``w_sf [E, N/128, ceil(K/512)]`` int32."""
+    E, N, K = w.shape
+    with torch.cuda.device(a_q.device):
+        check(lib().sglb200_fp8_ue8m0_scaled_grouped_mm(
+            a_q.data_ptr(), w.data_ptr(), a_sf.data_ptr(), w_sf.data_ptr(), out.data_ptr(), expert_offsets.data_ptr(),
+            a_q.size(0), E, N, K, a_q.stride(0), w.stride(1), w.stride(0), out.stride(0), a_sf.stride(0),
+            a_sf.stride(1) if a_sf.size(1) > 1 else max(a_sf.stride(1), 1), w_sf.stride(0), w_sf.stride(1), w_sf.stride(2),
+            dtype_code(out.dtype), torch.cuda.current_stream(a_q.device).cuda_stream),
+            "fp8_ue8m0_scaled_grouped_mm")
+
+
+def fused_experts_block_fp8_ue8m0(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_sf: torch.Tensor,
+                                  w2_sf: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
+                                  routed_scaling_factor: Optional[float] = None) -> torch.Tensor:
+    """The expert MLP on a UE8M0 checkpoint (power-of-two weight block scales, packed by ``pack_ue8m0_scales`` per
+    expert: ``w1_sf [E, 2I/128, ceil(H/512)]``, ``w2_sf [E, H/128, ceil(I/512)]`` int32) with power-of-two activation
+    group scales: the reference's Blackwell route through DeepGEMM
+    (``python/sglang/srt/layers/moe/moe_runner/deep_gemm.py:131-207``, ``DEEPGEMM_SCALE_UE8M0``).  Same pipeline as
+    :func:`fused_experts_block_fp8`; both grouped GEMMs run on the tensor core's block-scaling path."""
+    from ...sgl_kernel import sgl_per_token_group_quant_8bit
+    assert hidden_states.dim() == 2 and hidden_states.is_contiguous()
+    M, H = hidden_states.shape
+    E, two_i, _ = w1.shape
+    I = two_i // 2
+    assert H % 128 == 0 and I % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
+    dev, out_dtype = hidden_states.device, hidden_states.dtype
+    out = torch.empty(M, H, dtype=out_dtype, device=dev)
+    if M == 0:
+        return out
+    topk = topk_ids.size(1)
+    rows = M * topk
+    kg1 = -(-(H // 128) // 4)
+    a_q = torch.empty(M, H, dtype=FP8, device=dev)
+    a_sf = torch.empty(M, kg1, dtype=torch.int32, device=dev)  # row-major words, so that rows can be shuffled
+    sgl_per_token_group_quant_8bit(hidden_states, a_q, a_sf, 128, 1e-10, -448.0, 448.0, scale_ue8m0=True)
+    ids = topk_ids.to(torch.int32).contiguous()
+    expert_offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    ps1 = torch.empty(E, 3, dtype=torch.int32, device=dev)
+    ps2 = torch.empty(E, 3, dtype=torch.int32, device=dev)
+    a_map = torch.empty(rows, dtype=torch.int32, device=dev)
+    c_map = torch.empty(rows, dtype=torch.int32, device=dev)
+    prepare_moe_input(ids, expert_offsets, ps1, ps2, a_map, c_map, E, I, H)
+    rep_q = shuffle_rows(a_q, a_map, (rows, H))
+    rep_sf = shuffle_rows(a_sf, a_map, (rows, kg1))
+    c1 = torch.empty(rows, two_i, dtype=out_dtype, device=dev)
+    _grouped_mm_ue8m0(rep_q, rep_sf, w1, w1_sf, c1, expert_offsets)
+    q2, sf2 = sglang_per_token_group_quant_fp8(c1, 128, column_major_scales=True, scale_tma_aligned=True,
+                                               scale_ue8m0=True, fuse_silu_and_mul=True)
+    c2 = torch.empty(rows, H, dtype=out_dtype, device=dev)
+    _grouped_mm_ue8m0(q2, sf2, w2, w2_sf, c2, expert_offsets)
+    factors = topk_weights if routed_scaling_factor is None else topk_weights * routed_scaling_factor
+    apply_shuffle_mul_sum(c2, out, c_map, factors.to(out_dtype).reshape(-1).contiguous(), round_products=True)
+    return out

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 import oracle
-from helpers import FP8, assert_gemm_close, rel_l2
+from helpers import FP8, assert_gemm_close, make_activations, rel_l2
 
 pytestmark = pytest.mark.gpu
 
@@ -95,3 +95,59 @@ def test_linear_method_picks_ue8m0_for_power_of_two_scales():
     q2, s2 = oracle.per_token_group_quant_fp8(x, 128)
     ref2 = oracle.w8a8_block_fp8_matmul(q2, wq2, s2, ws2)
     assert rel_l2(y2.float().cpu(), ref2.float()) < 6e-2  # requantisation error of weights and power-of-two activation scales
+
+
+def _ue8m0_experts(E, H, I, seed):
+    from sglang_b200.layers.quantization import pack_ue8m0_scales
+    g = torch.Generator().manual_seed(seed)
+    w1 = [oracle.block_quant_weight(torch.randn(2 * I, H, generator=g) * 0.05, scale_ue8m0=True) for _ in range(E)]
+    w2 = [oracle.block_quant_weight(torch.randn(H, I, generator=g) * 0.05, scale_ue8m0=True) for _ in range(E)]
+    w1q, w1s = torch.stack([w[0] for w in w1]), torch.stack([w[1] for w in w1])
+    w2q, w2s = torch.stack([w[0] for w in w2]), torch.stack([w[1] for w in w2])
+    w1p = torch.stack([pack_ue8m0_scales(s) for s in w1s])
+    w2p = torch.stack([pack_ue8m0_scales(s) for s in w2s])
+    return w1q, w1s, w2q, w2s, w1p, w2p
+
+
+@pytest.mark.parametrize("rows_per_expert,N,K", [([5, 0, 300, 128, 1], 448, 512), ([130, 129, 2], 2048, 1024),
+                                                 ([0, 0, 7], 224, 128), ([64] * 16, 4096, 7168)])
+def test_grouped_ue8m0_gemm_matches_oracle(rows_per_expert, N, K):
+    """Grouped form: ragged expert segments (empty ones included), row-major scale words as after a row shuffle."""
+    from sglang_b200.layers.moe import _grouped_mm_ue8m0
+    from sglang_b200.layers.quantization import pack_ue8m0_scales
+    E, total = len(rows_per_expert), sum(rows_per_expert)
+    x = make_activations(total, K, seed=total + N, outliers=False)
+    q, s = oracle.per_token_group_quant_fp8(x, 128, scale_ue8m0=True)
+    g = torch.Generator().manual_seed(N)
+    ws = [oracle.block_quant_weight(torch.randn(N, K, generator=g) * 0.05, scale_ue8m0=True) for _ in range(E)]
+    wq, wsc = torch.stack([w[0] for w in ws]), torch.stack([w[1] for w in ws])
+    wp = torch.stack([pack_ue8m0_scales(t) for t in wsc])
+    offs = torch.tensor([0] + list(torch.tensor(rows_per_expert).cumsum(0)), dtype=torch.int32)
+    out = torch.full((total, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    _grouped_mm_ue8m0(q.cuda(), pack_ue8m0_scales(s).cuda(), wq.cuda(), wp.cuda(), out, offs.cuda())
+    torch.cuda.synchronize()
+    from sglang_b200._lib import lib
+    assert lib().sglb200_read_device_status() == 0
+    for e in range(E):
+        r0, r1 = int(offs[e]), int(offs[e + 1])
+        if r1 > r0:
+            ref = oracle.w8a8_block_fp8_matmul(q[r0:r1], wq[e], s[r0:r1], wsc[e])
+            assert_gemm_close(out[r0:r1], ref, f"expert {e}", allow_one_ulp=True)
+
+
+@pytest.mark.parametrize("M,E,topk,H,I", [(1, 8, 2, 512, 256), (100, 16, 4, 512, 256), (700, 32, 8, 1024, 384)])
+def test_fused_experts_ue8m0_matches_oracle(M, E, topk, H, I):
+    from sglang_b200.layers.moe import fused_experts_block_fp8_ue8m0
+    a = make_activations(M, H, seed=M, outliers=False)
+    w1q, w1s, w2q, w2s, w1p, w2p = _ue8m0_experts(E, H, I, seed=E)
+    g = torch.Generator().manual_seed(M + 1)
+    w, ids = torch.topk(torch.softmax(torch.randn(M, E, generator=g), dim=-1), topk)
+    ids = ids.to(torch.int32)
+    if M >= 100:
+        ids[5, 1] = -1
+    ref = oracle.fused_experts_block_fp8(a, w1q, w2q, w1s, w2s, w, ids, scale_ue8m0=True)
+    out = fused_experts_block_fp8_ue8m0(a.cuda(), w1q.cuda(), w2q.cuda(), w1p.cuda(), w2p.cuda(), w.cuda(), ids.cuda())
+    torch.cuda.synchronize()
+    from sglang_b200._lib import lib
+    assert lib().sglb200_read_device_status() == 0
+    assert_gemm_close(out, ref, "fused experts, UE8M0", allow_one_ulp=True)
