@@ -83,6 +83,20 @@ int sglb200_silu_mul_group_quant_fp8(const void* input, int in_dtype, void* out_
                                      int64_t s_stride_row, int64_t s_stride_group, void* stream);
 
 /*
+ * Q in the batched / masked layout of the low-latency MoE path: input [num_batches, rows_per_batch, hidden] (with
+ * fuse_silu_and_mul != 0: [.., 2 * hidden], gate first), out_q [num_batches, rows_per_batch, hidden]; the scale of
+ * (batch b, row r, group g) at out_s[b * s_stride_batch + r * s_stride_row + g * s_stride_group] (UE8M0: int32 words,
+ * g / 4, as above).  With masked_m != NULL (int32 [num_batches], device) only rows r < masked_m[b] are read and
+ * written.  bf16 / f16 input.  Same arithmetic as sglb200_per_token_group_quant_fp8.
+ * Replaces: sgl_per_token_group_quant_8bit_v2 with masked_m
+ *           sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:194-238,394-514 (schema common_extension.cc:178-181).
+ */
+int sglb200_group_quant_fp8_batched(const void* input, int in_dtype, void* out_q, void* out_s, int64_t num_batches,
+                                    int64_t rows_per_batch, int64_t hidden, int group_size, float eps, float fp8_min,
+                                    float fp8_max, int scale_ue8m0, int fuse_silu_and_mul, const int32_t* masked_m,
+                                    int64_t s_stride_batch, int64_t s_stride_row, int64_t s_stride_group, void* stream);
+
+/*
  * G — block-scaled FP8 GEMM:  out[m, n] = cast( sum_kb ( sum_{k in kb} a[m,k] * b[n,k] ) * sa[m,kb] * sb[n/128,kb] ).
  * Replaces: fp8_blockwise_scaled_mm  sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:368-465
  *           (schema common_extension.cc:168-171) and the Triton twin w8a8_block_fp8_matmul_triton

@@ -22,6 +22,7 @@ _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 SIGNATURES = {
     "sglb200_per_token_group_quant_fp8": [_P, _I, _P, _P, _L, _L, _I, _F, _F, _F, _I, _L, _L, _P],
     "sglb200_silu_mul_group_quant_fp8": [_P, _I, _P, _P, _P, _L, _L, _I, _F, _F, _F, _I, _L, _L, _P],
+    "sglb200_group_quant_fp8_batched": [_P, _I, _P, _P, _L, _L, _L, _I, _F, _F, _F, _I, _I, _P, _L, _L, _L, _P],
     "sglb200_fp8_blockwise_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
     "sglb200_fp8_blockwise_scaled_mm_ws": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _L, _P],
     "sglb200_fp8_blockwise_scaled_mm_workspace_bytes": [_L, _L, _L],

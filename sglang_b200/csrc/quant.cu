@@ -35,6 +35,11 @@ struct QuantParams {
   uint32_t hidden;              // elements per output row
   float eps, fp8_min, fp8_max;
   int64_t s_stride_row, s_stride_group;
+  // batched / masked layout (rows_per_batch > 0; 16-bit inputs only): row = batch * rows_per_batch + local, scales at
+  // batch * s_stride_batch + local * s_stride_row, and with masked_m only local < masked_m[batch] is processed
+  const int32_t* masked_m;
+  uint32_t rows_per_batch, bdiv_mul, bdiv_shift;
+  int64_t s_stride_batch;
 };
 
 // ---- element traits: E = elements per 16-byte vector -----------------------------------------
@@ -127,6 +132,7 @@ __global__ void __launch_bounds__(kThreads) group_quant16_kernel(const QuantPara
 
   uint4 raw[kUnroll][2];
   uint32_t row[kUnroll], grp[kUnroll];
+  int64_t s_off[kUnroll];  // offset of the row's scales
   bool live[kUnroll];
 
 #pragma unroll
@@ -136,6 +142,13 @@ __global__ void __launch_bounds__(kThreads) group_quant16_kernel(const QuantPara
     const uint32_t tt = live[i] ? t : 0u;
     row[i] = (uint32_t)(((uint64_t)tt * p.div_mul) >> p.div_shift);
     grp[i] = tt - row[i] * p.groups_per_row;
+    s_off[i] = (int64_t)row[i] * p.s_stride_row;
+    if (p.rows_per_batch != 0) {
+      const uint32_t b = (uint32_t)(((uint64_t)row[i] * p.bdiv_mul) >> p.bdiv_shift);
+      const uint32_t local = row[i] - b * p.rows_per_batch;
+      s_off[i] = (int64_t)b * p.s_stride_batch + (int64_t)local * p.s_stride_row;
+      if (p.masked_m != nullptr && (int32_t)local >= __ldg(p.masked_m + b)) live[i] = false;
+    }
     raw[i][0] = raw[i][1] = make_uint4(0, 0, 0, 0);
     if (live[i]) {
       if constexpr (FUSE_SILU) {
@@ -210,15 +223,14 @@ __global__ void __launch_bounds__(kThreads) group_quant16_kernel(const QuantPara
 
     if (lane == 0) {
       if constexpr (UE8M0) {
-        uint8_t* wp = reinterpret_cast<uint8_t*>(p.out_s) +
-                      4 * ((int64_t)row[i] * p.s_stride_row + (int64_t)(grp[i] >> 2) * p.s_stride_group);
+        uint8_t* wp = reinterpret_cast<uint8_t*>(p.out_s) + 4 * (s_off[i] + (int64_t)(grp[i] >> 2) * p.s_stride_group);
         const uint32_t b = grp[i] & 3u;
         wp[b] = (uint8_t)(__float_as_uint(s) >> 23);
         if (grp[i] + 1 == p.groups_per_row) {
           for (uint32_t z = b + 1; z < 4; ++z) wp[z] = 0;  // bytes of the word past the last group
         }
       } else {
-        static_cast<float*>(p.out_s)[(int64_t)row[i] * p.s_stride_row + (int64_t)grp[i] * p.s_stride_group] = s;
+        static_cast<float*>(p.out_s)[s_off[i] + (int64_t)grp[i] * p.s_stride_group] = s;
       }
     }
   }
@@ -337,7 +349,11 @@ int launch_t32(const QuantParams& p, int group_size, bool ue8m0, cudaStream_t st
 template <bool FUSE>
 int quant_entry(const void* input, int in_dtype, void* out_q, void* out_s, void* out_act, int64_t num_rows,
                 int64_t hidden, int group_size, float eps, float fp8_min, float fp8_max, int scale_ue8m0,
-                int64_t s_stride_row, int64_t s_stride_group, void* stream) {
+                int64_t s_stride_row, int64_t s_stride_group, void* stream, int64_t rows_per_batch = 0,
+                int64_t s_stride_batch = 0, const int32_t* masked_m = nullptr) {
+  SGLB_REQUIRE(rows_per_batch == 0 || (in_dtype != SGLB200_F32 && rows_per_batch > 0 && num_rows % rows_per_batch == 0),
+               SGLB200_ERR_SHAPE, "batched layout: 16-bit input and num_rows a multiple of rows_per_batch=%lld",
+               (long long)rows_per_batch);
   SGLB_REQUIRE(num_rows >= 0 && hidden >= 0, SGLB200_ERR_SHAPE, "num_rows=%lld hidden=%lld: negative size",
                (long long)num_rows, (long long)hidden);
   SGLB_REQUIRE(group_size == 16 || group_size == 32 || group_size == 64 || group_size == 128, SGLB200_ERR_SHAPE,
@@ -382,6 +398,16 @@ int quant_entry(const void* input, int in_dtype, void* out_q, void* out_s, void*
   p.fp8_max = fp8_max;
   p.s_stride_row = s_stride_row;
   p.s_stride_group = s_stride_group;
+  p.masked_m = masked_m;
+  p.rows_per_batch = (uint32_t)rows_per_batch;
+  p.bdiv_mul = p.bdiv_shift = 0;
+  p.s_stride_batch = s_stride_batch;
+  if (rows_per_batch > 0) {  // same round-up magic number as for the groups
+    uint32_t sh = 0;
+    while (((uint64_t)1 << sh) < (uint64_t)rows_per_batch) ++sh;
+    p.bdiv_shift = 31 + sh;
+    p.bdiv_mul = (uint32_t)((((uint64_t)1 << (31 + sh)) + (uint64_t)rows_per_batch - 1) / (uint64_t)rows_per_batch);
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // with the e4m3 limits the saturating conversion already clamps; other limits need the explicit clamp
   const bool clamp = !(fp8_max == 448.0f && fp8_min == -448.0f);
@@ -409,4 +435,22 @@ extern "C" int sglb200_silu_mul_group_quant_fp8(const void* input, int in_dtype,
                                                 int64_t s_stride_row, int64_t s_stride_group, void* stream) {
   return sglb::quant_entry<true>(input, in_dtype, out_q, out_s, out_act, num_rows, hidden, group_size, eps, fp8_min,
                                  fp8_max, scale_ue8m0, s_stride_row, s_stride_group, stream);
+}
+
+extern "C" int sglb200_group_quant_fp8_batched(const void* input, int in_dtype, void* out_q, void* out_s,
+                                               int64_t num_batches, int64_t rows_per_batch, int64_t hidden,
+                                               int group_size, float eps, float fp8_min, float fp8_max,
+                                               int scale_ue8m0, int fuse_silu_and_mul, const int32_t* masked_m,
+                                               int64_t s_stride_batch, int64_t s_stride_row, int64_t s_stride_group,
+                                               void* stream) {
+  SGLB_REQUIRE(num_batches >= 0 && rows_per_batch >= 1, SGLB200_ERR_SHAPE, "num_batches=%lld rows_per_batch=%lld",
+               (long long)num_batches, (long long)rows_per_batch);
+  const int64_t rows = num_batches * rows_per_batch;
+  if (fuse_silu_and_mul)
+    return sglb::quant_entry<true>(input, in_dtype, out_q, out_s, nullptr, rows, hidden, group_size, eps, fp8_min,
+                                   fp8_max, scale_ue8m0, s_stride_row, s_stride_group, stream, rows_per_batch,
+                                   s_stride_batch, masked_m);
+  return sglb::quant_entry<false>(input, in_dtype, out_q, out_s, nullptr, rows, hidden, group_size, eps, fp8_min, fp8_max,
+                                  scale_ue8m0, s_stride_row, s_stride_group, stream, rows_per_batch, s_stride_batch,
+                                  masked_m);
 }

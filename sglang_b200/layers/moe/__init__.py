@@ -176,18 +176,16 @@ def fused_experts_masked(hidden_states: torch.Tensor, hidden_states_scale: torch
     (``python/sglang/srt/layers/moe/moe_runner/deep_gemm.py:209-328``): ``hidden_states [E_local, max_m, H]`` e4m3
     with ``hidden_states_scale [E_local, max_m, H/128]``; expert ``e`` holds ``masked_m[e]`` valid rows.  Grouped GEMM
     (gate_up) -> fused SiLU-mul + group quant -> grouped GEMM (down); returns ``[E_local, max_m, H]``, rows past
-    ``masked_m[e]`` unspecified.  The activation kernel runs over all ``max_m`` rows of every expert (the rows past
-    ``masked_m[e]`` are unspecified in the reference as well)."""
+    ``masked_m[e]`` unspecified (neither read nor written by any of the three kernels)."""
     from ..deep_gemm_wrapper import grouped_gemm_nt_f8f8bf16_masked
     E, max_m, H = hidden_states.shape
     two_i = w13_weight.shape[1]
     gate_up = torch.empty(E, max_m, two_i, dtype=out_dtype, device=hidden_states.device)
     grouped_gemm_nt_f8f8bf16_masked((hidden_states, hidden_states_scale), (w13_weight, w13_scale), gate_up, masked_m,
                                     expected_m)
-    down_q, down_s = sglang_per_token_group_quant_fp8(gate_up.view(E * max_m, two_i), 128, fuse_silu_and_mul=True)
+    down_q, down_s = sglang_per_token_group_quant_fp8(gate_up, 128, fuse_silu_and_mul=True, masked_m=masked_m)
     out = torch.empty(E, max_m, w2_weight.shape[1], dtype=out_dtype, device=hidden_states.device)
-    grouped_gemm_nt_f8f8bf16_masked((down_q.view(E, max_m, two_i // 2), down_s.view(E, max_m, two_i // 256)),
-                                    (w2_weight, w2_scale), out, masked_m, expected_m)
+    grouped_gemm_nt_f8f8bf16_masked((down_q, down_s), (w2_weight, w2_scale), out, masked_m, expected_m)
     return out
 
 

@@ -37,7 +37,7 @@ def create_per_token_group_quant_fp8_output_scale(x_shape, device, group_size, c
         if scale_tma_aligned:
             aligned_size = align(x_shape[-2], 4)
             return torch.empty(tuple(x_shape[:-2]) + (x_shape[-1] // group_size, aligned_size), device=device,
-                               dtype=torch.float32).transpose(-1, -2)[: x_shape[-2], :]
+                               dtype=torch.float32).transpose(-1, -2)[..., : x_shape[-2], :]
         return torch.empty((x_shape[-1] // group_size,) + tuple(x_shape[:-1]), device=device,
                            dtype=torch.float32).permute(-1, -2)
     return torch.empty(tuple(x_shape[:-1]) + (x_shape[-1] // group_size,), device=device, dtype=torch.float32)
@@ -55,10 +55,13 @@ def sglang_per_token_group_quant_fp8(
     enable_v2: Optional[bool] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """``sglang_per_token_group_quant_fp8`` (``fp8_kernel.py:477-527``): returns
-    ``(x_q e4m3, x_s)`` with ``x_s`` in the requested layout."""
+    ``(x_q e4m3, x_s)`` with ``x_s`` in the requested layout.  With a 3-D ``x [E, max_m, K]`` the scales are laid out
+    per expert, and ``masked_m [E]`` (int32) limits the work to the first ``masked_m[e]`` rows of every expert; the
+    other rows of ``x_q`` / ``x_s`` are left unwritten (``per_token_group_quant_8bit_v2.cu:194-238``)."""
     assert x.shape[-1] % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`"
     assert x.is_contiguous(), "`x` is not contiguous"
-    assert x.dim() == 2, "only 2-D activations are supported"
+    assert x.dim() in (2, 3), "activations must be [M, K] or, for the masked per-expert layout, [E, max_m, K]"
+    assert masked_m is None or x.dim() == 3, "masked_m goes with the [E, max_m, K] layout"
     out_shape = (*x.shape[:-1], x.shape[-1] // (2 if fuse_silu_and_mul else 1))
     x_q = torch.empty(out_shape, device=x.device, dtype=fp8_dtype)
     x_s = create_per_token_group_quant_fp8_output_scale(out_shape, x.device, group_size, column_major_scales,

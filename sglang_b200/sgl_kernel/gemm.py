@@ -92,9 +92,12 @@ def sgl_per_token_group_quant_8bit(
     _cuda_check(input.is_contiguous(), "input must be contiguous")
     _cuda_check(output_q.is_contiguous(), "output_q must be contiguous")
     _cuda_check(output_q.dtype == FP8, "output_q must be Float8_e4m3fn (the int8 destination is not implemented)")
-    _cuda_check(masked_m is None, "masked_m (masked per-expert layout) is not implemented")
-    _cuda_check(output_s.dim() == 2, "output_s must be 2D")
     hidden_in = input.size(-1)
+    if input.dim() == 3:
+        return _quant_batched(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0,
+                              fuse_silu_and_mul, masked_m)
+    _cuda_check(masked_m is None, "masked_m needs the 3-D [E, max_m, K] layout")
+    _cuda_check(output_s.dim() == 2, "output_s must be 2D")
     hidden = hidden_in // 2 if fuse_silu_and_mul else hidden_in
     _cuda_check(hidden % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`")
     rows = input.numel() // hidden_in if hidden_in else 0
@@ -123,6 +126,37 @@ def sgl_per_token_group_quant_8bit(
             check(L.sglb200_per_token_group_quant_fp8(input.data_ptr(), dtype_code(input.dtype),
                                                       output_q.data_ptr(), output_s.data_ptr(), *args),
                   "sgl_per_token_group_quant_8bit")
+
+
+def _quant_batched(input, output_q, output_s, group_size, eps, fp8_min, fp8_max, scale_ue8m0, fuse_silu_and_mul,
+                   masked_m) -> None:
+    """The ``[E, max_m, K]`` layout of the low-latency MoE path: scales addressed per expert, optional row mask
+    (``sgl-kernel/csrc/gemm/per_token_group_quant_8bit_v2.cu:194-238,394-514``)."""
+    E, max_m, hidden_in = input.shape
+    hidden = hidden_in // 2 if fuse_silu_and_mul else hidden_in
+    _cuda_check(input.dtype in (torch.bfloat16, torch.float16), "the batched layout takes bf16 / f16 input")
+    _cuda_check(hidden % group_size == 0, "the last dimension of `x` cannot be divisible by `group_size`")
+    _cuda_check(output_q.shape == (E, max_m, hidden), "output_q shape is not matched")
+    G = hidden // group_size
+    _cuda_check(output_s.dim() == 3 and output_s.size(0) == E and output_s.size(1) == max_m
+                and output_s.size(2) == (-(-G // 4) if scale_ue8m0 else G), "output_s shape is not matched")
+    _cuda_check(output_s.dtype == (torch.int32 if scale_ue8m0 else torch.float32), "output_s has the wrong dtype")
+    mptr = None
+    if masked_m is not None:
+        _cuda_check(masked_m.dtype == torch.int32 and masked_m.is_contiguous() and masked_m.numel() == E,
+                    "masked_m must be a contiguous int32 tensor with one entry per expert")
+        mptr = masked_m.data_ptr()
+    if E == 0 or max_m == 0 or hidden == 0:
+        return
+    eps_eff = float(torch.tensor(eps, dtype=input.dtype).float())
+    if eps_eff == 0.0 and eps > 0.0:
+        eps_eff = float(eps)
+    with torch.cuda.device(input.device):
+        check(lib().sglb200_group_quant_fp8_batched(
+            input.data_ptr(), dtype_code(input.dtype), output_q.data_ptr(), output_s.data_ptr(), E, max_m, hidden,
+            group_size, eps_eff, fp8_min, fp8_max, int(bool(scale_ue8m0)), int(bool(fuse_silu_and_mul)), mptr,
+            output_s.stride(0), output_s.stride(1), output_s.stride(2), _stream(input)),
+            "sgl_per_token_group_quant_8bit(masked)")
 
 
 def sgl_per_token_group_quant_fp8(input, output_q, output_s, group_size, eps, fp8_min, fp8_max,

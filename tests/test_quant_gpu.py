@@ -125,3 +125,46 @@ def test_fused_silu_mul_quant():
     d = (act.cpu().float() - ref.float()).abs()
     assert bool((d <= ref.float().abs() * 2.0 ** -7 + 1e-30).all())
     assert float((act.cpu() != ref).float().mean()) < 1e-3
+
+
+@pytest.mark.parametrize("layout", ["row", "col_tma", "ue8m0"])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_masked_per_expert_layout(layout, fuse):
+    """[E, max_m, K] with masked_m valid rows per expert: valid rows equal the flat kernel's output bit for bit (and
+    with that the oracle's), the other rows of codes and scales are not touched."""
+    from sglang_b200.layers.quantization import (create_per_token_group_quant_fp8_output_scale,
+                                                 sglang_per_token_group_quant_fp8)
+    from sglang_b200.sgl_kernel import sgl_per_token_group_quant_8bit
+    E, max_m, K = 5, 37, 512
+    masked = torch.tensor([37, 0, 1, 20, 36], dtype=torch.int32)
+    x = make_activations(E * max_m, K * (2 if fuse else 1), seed=9, outliers=False).view(E, max_m, -1).cuda()
+    ue = layout == "ue8m0"
+    kw = dict(column_major_scales=layout != "row", scale_tma_aligned=layout != "row", scale_ue8m0=ue)
+    q = torch.full((E, max_m, K), 0.5, device="cuda").to(FP8)
+    s = create_per_token_group_quant_fp8_output_scale((E, max_m, K), "cuda", 128, **kw)
+    s.fill_(77 if ue else 77.0)
+    sgl_per_token_group_quant_8bit(x, q, s, 128, 1e-10, -448.0, 448.0, ue, fuse, masked.cuda())
+    torch.cuda.synchronize()
+    sentinel_q = torch.full((1,), 0.5).to(FP8).view(torch.uint8).item()
+    for e in range(E):
+        m = int(masked[e])
+        q_ref, s_ref = sglang_per_token_group_quant_fp8(x[e].contiguous(), 128, fuse_silu_and_mul=fuse, **kw)
+        assert torch.equal(q[e, :m].view(torch.uint8), q_ref[:m].view(torch.uint8)), f"expert {e} codes"
+        assert torch.equal(s[e, :m], s_ref[:m]), f"expert {e} scales"
+        assert (q[e, m:].view(torch.uint8) == sentinel_q).all(), f"expert {e}: codes past masked_m were written"
+        if not ue:  # UE8M0 words hold four k-blocks: rows past masked_m keep the whole word
+            assert (s[e, m:] == 77.0).all(), f"expert {e}: scales past masked_m were written"
+        else:
+            assert (s[e, m:] == 77).all()
+    # the allocating wrapper, unmasked 3-D input: every expert as the flat call
+    q3, s3 = sglang_per_token_group_quant_fp8(x, 128, fuse_silu_and_mul=fuse, **kw)
+    q2, s2 = sglang_per_token_group_quant_fp8(x.view(E * max_m, -1), 128, fuse_silu_and_mul=fuse, **kw)
+    assert torch.equal(q3.view(torch.uint8).view(E * max_m, K), q2.view(torch.uint8))
+    if layout == "row":
+        assert torch.equal(s3.reshape(E * max_m, -1), s2)
+    with pytest.raises(RuntimeError, match="masked_m"):
+        sgl_per_token_group_quant_8bit(x, q, s, 128, 1e-10, -448.0, 448.0, ue, fuse, masked[:2].cuda())
+    with pytest.raises(RuntimeError, match="3-D"):
+        sgl_per_token_group_quant_8bit(x.view(E * max_m, -1), q.view(E * max_m, K),
+                                       torch.empty(E * max_m, K // 128, device="cuda"), 128, 1e-10, -448.0, 448.0,
+                                       False, fuse, masked.cuda())
