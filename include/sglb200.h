@@ -176,6 +176,13 @@ int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void* b, const 
 int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb, void* out,
                                 int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sfa_ld,
                                 int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream);
+/* The same with optional split-K scratch for M <= 64 (size: sglb200_fp8_blockwise_scaled_mm_workspace_bytes; NULL = no
+ * split).  Up to 64 rows both entries run the weight-streaming kernel of sglb200_fp8_blockwise_scaled_mm, which decodes
+ * the exponent bytes itself (the scales stay exact powers of two); above that the block-scaling kernel. */
+int sglb200_fp8_ue8m0_scaled_mm_ws(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb, void* out,
+                                   int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sfa_ld,
+                                   int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* workspace,
+                                   int64_t workspace_bytes, void* stream);
 
 /*
  * MG with UE8M0 scales: the kernel above with the expert tile scheduler of

@@ -29,6 +29,7 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_scaled_mm_noalloc": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
     "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": [],
     "sglb200_fp8_ue8m0_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
+    "sglb200_fp8_ue8m0_scaled_mm_ws": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _L, _P],
     "sglb200_fp8_ue8m0_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
                                             _I, _P],
     "sglb200_fp8_blockwise_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,

@@ -34,7 +34,9 @@ int smallm_splits(int64_t N, int64_t K, int sm_count);
 int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                 int64_t sb_stride_k, int out_dtype, float* partial, int64_t partial_floats, int sm_count, void* stream,
-                int* splits_used, bool always_partial = false);
+                int* splits_used, bool always_partial = false, bool ue8m0 = false);
+void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N, int64_t ldc, int splits, int out_dtype,
+                          int sm_count, void* stream);  // gemm.cu
 int smallm_take_device_status();
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

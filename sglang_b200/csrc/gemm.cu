@@ -718,8 +718,6 @@ int make_map_sw128(CUtensorMap* map, const void* base, int rank, const uint64_t*
   return SGLB200_OK;
 }
 
-namespace {
-
 void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N, int64_t ldc, int splits, int out_dtype,
                           int sm_count, void* stream) {
   const int64_t vecs = M * (N / 8);
@@ -734,6 +732,8 @@ void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N,
                                                        splits);
   }
 }
+
+namespace {
 
 // Number of k-splits for a dense problem: only when the output tiles alone cannot occupy the SMs (small M, where the
 // kernel streams the weights once and is HBM-bound), enough splits for about two work items per SM, each at least

@@ -52,7 +52,7 @@ struct Cfg {
 };
 
 struct SmallParams {
-  const float* sa;
+  const float* sa;  // UE8M0 variant: int32 words, four exponent bytes (k-blocks 4g .. 4g + 3) per word
   const float* sb;
   void* out;
   float* partial;  // [splits][M][N] fp32 when k_splits > 1
@@ -113,7 +113,18 @@ __device__ __forceinline__ void tmem_ld_fence(uint32_t* r) {
   for (int i = 0; i < N; ++i) asm volatile("" : "+r"(r[i])::"memory");
 }
 
-template <int MT>
+// scale of k-block kc: fp32 at base[kc * stride_k], or 2^(byte - 127) of the packed word at base[(kc / 4) * stride_k]
+template <bool UE>
+__device__ __forceinline__ float load_scale(const float* base, int32_t kc, int64_t stride_k) {
+  if constexpr (UE) {
+    const uint32_t w = (uint32_t)__ldg(reinterpret_cast<const int32_t*>(base) + (int64_t)(kc >> 2) * stride_k);
+    return __uint_as_float(((w >> (8 * (kc & 3))) & 0xffu) << 23);
+  } else {
+    return __ldg(base + (int64_t)kc * stride_k);
+  }
+}
+
+template <int MT, bool UE>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                              const SmallParams p) {
@@ -236,8 +247,8 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
       for (int u = 0; u < kScaleAhead; ++u) {
         const int32_t kc = min(kb0 + u, kb1 - 1);
 #pragma unroll
-        for (int h = 0; h < kPerLane; ++h) sa_ring[u][h] = tok_ok[h] ? __ldg(sa_tok[h] + (int64_t)kc * p.sa_stride_k) : 0.f;
-        sb_ring[u] = __ldg(sb_blk + (int64_t)kc * p.sb_stride_k);
+        for (int h = 0; h < kPerLane; ++h) sa_ring[u][h] = tok_ok[h] ? load_scale<UE>(sa_tok[h], kc, p.sa_stride_k) : 0.f;
+        sb_ring[u] = load_scale<UE>(sb_blk, kc, p.sb_stride_k);
       }
       bool ok = true;
       for (int32_t kbb = kb0; kbb < kb1 && ok; kbb += kScaleAhead) {
@@ -252,8 +263,8 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
             const int32_t kn = min(kb + kScaleAhead, kb1 - 1);
 #pragma unroll
             for (int h = 0; h < kPerLane; ++h)
-              sa_ring[u][h] = tok_ok[h] ? __ldg(sa_tok[h] + (int64_t)kn * p.sa_stride_k) : 0.f;
-            sb_ring[u] = __ldg(sb_blk + (int64_t)kn * p.sb_stride_k);
+              sa_ring[u][h] = tok_ok[h] ? load_scale<UE>(sa_tok[h], kn, p.sa_stride_k) : 0.f;
+            sb_ring[u] = load_scale<UE>(sb_blk, kn, p.sb_stride_k);
           }
           if (!ptx::mbar_wait_a(acc_full0 + acc_stage * 8, acc_phase)) {
             timeout(ctl, 14);
@@ -312,20 +323,20 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
   }
 }
 
-template <int MT>
+template <int MT, bool UE>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams& p, int sm_count, cudaStream_t st) {
   static bool done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)Cfg<MT>::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT, UE>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<MT>::kSmem);
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     done[dev] = true;
   }
   const int total = p.n_tiles * p.k_splits;
   const int grid = total < sm_count ? total : sm_count;
-  fp8_block_gemm_smallm_kernel<MT><<<grid, kThreads, Cfg<MT>::kSmem, st>>>(map_w, map_a, p);
+  fp8_block_gemm_smallm_kernel<MT, UE><<<grid, kThreads, Cfg<MT>::kSmem, st>>>(map_w, map_a, p);
   SGLB_CHECK_LAUNCH("fp8_block_gemm_smallm_kernel");
   return SGLB200_OK;
 }
@@ -358,10 +369,12 @@ int smallm_splits(int64_t N, int64_t K, int sm_count) {
 // Launches the small-M kernel (arguments already validated by the caller).  With `partial` != NULL and splits > 1 the
 // kernel leaves fp32 partial sums [splits][M][N] there and the caller adds them up; *splits_used reports which.  With
 // always_partial the fp32 sums go to `partial` even for a single split (the caller converts and moves them itself).
+// With ue8m0 the scale pointers are packed exponent words (sa: word (m, kg) at m * sa_stride_m + kg * sa_stride_k; sb
+// likewise per 128 weight rows) and the scales are the exact powers of two they encode.
 int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N, int64_t K,
                 int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                 int64_t sb_stride_k, int out_dtype, float* partial, int64_t partial_floats, int sm_count, void* stream,
-                int* splits_used, bool always_partial) {
+                int* splits_used, bool always_partial, bool ue8m0) {
   const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   alignas(64) CUtensorMap map_w, map_a;
   {
@@ -402,10 +415,17 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
   }
   *splits_used = p.k_splits;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ue8m0) {
+    switch (MT) {
+      case 16: return launch<16, true>(map_w, map_a, p, sm_count, st);
+      case 32: return launch<32, true>(map_w, map_a, p, sm_count, st);
+      default: return launch<64, true>(map_w, map_a, p, sm_count, st);
+    }
+  }
   switch (MT) {
-    case 16: return launch<16>(map_w, map_a, p, sm_count, st);
-    case 32: return launch<32>(map_w, map_a, p, sm_count, st);
-    default: return launch<64>(map_w, map_a, p, sm_count, st);
+    case 16: return launch<16, false>(map_w, map_a, p, sm_count, st);
+    case 32: return launch<32, false>(map_w, map_a, p, sm_count, st);
+    default: return launch<64, false>(map_w, map_a, p, sm_count, st);
   }
 }
 

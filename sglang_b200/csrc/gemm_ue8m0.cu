@@ -443,7 +443,8 @@ namespace {
 int ue8m0_common(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb, void* out,
                  const int32_t* expert_offsets, int64_t M, int64_t num_experts, int64_t N, int64_t K, int64_t lda,
                  int64_t ldb, int64_t ldb_e, int64_t ldc, int64_t sfa_ld, int64_t sfa_stride_m, int64_t sfb_stride_e,
-                 int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream) {
+                 int64_t sfb_stride_n, int64_t sfb_stride_k, int out_dtype, void* stream, float* workspace = nullptr,
+                 int64_t workspace_floats = 0) {
   const bool grouped = expert_offsets != nullptr;
   SGLB_REQUIRE(M >= 0 && N >= 0 && K >= 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld: negative size", (long long)M,
                (long long)N, (long long)K);
@@ -473,6 +474,18 @@ int ue8m0_common(const void* a, const void* b, const int32_t* sfa, const int32_t
   if (int rc = device_info(&di)) return rc;
   SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
                di.cc_major, di.cc_minor);
+
+  if (!grouped && M <= smallm_max_rows()) {
+    // few rows: the weight-streaming kernel with swapped operands decodes the exponent bytes itself (gemm_smallm.cu)
+    int splits = 1;
+    if (int rc = smallm_gemm(a, b, reinterpret_cast<const float*>(sfa), reinterpret_cast<const float*>(sfb), out, M, N, K,
+                             lda, ldb, ldc, sfa_stride_m, sfa_ld, sfb_stride_n, sfb_stride_k, out_dtype, workspace,
+                             workspace_floats, di.sm_count, stream, &splits, false, true))
+      return rc;
+    if (splits > 1) launch_splitk_reduce(workspace, out, M, N, ldc, splits, out_dtype, di.sm_count, stream);
+    SGLB_CHECK_LAUNCH("splitk_reduce_kernel");
+    return SGLB200_OK;
+  }
 
   alignas(64) CUtensorMap map_a, map_b;
   {
@@ -543,6 +556,19 @@ extern "C" int sglb200_fp8_ue8m0_scaled_mm(const void* a, const void* b, const i
                (long long)sfa_ld);
   return sglb::ue8m0_common(a, b, sfa, sfb, out, nullptr, M, 1, N, K, lda, ldb, 0, ldc, sfa_ld, 1, 0, sfb_stride_n,
                             sfb_stride_k, out_dtype, stream);
+}
+
+extern "C" int sglb200_fp8_ue8m0_scaled_mm_ws(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb,
+                                              void* out, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                              int64_t ldc, int64_t sfa_ld, int64_t sfb_stride_n, int64_t sfb_stride_k,
+                                              int out_dtype, void* workspace, int64_t workspace_bytes, void* stream) {
+  SGLB_REQUIRE(sfa_ld >= M, SGLB200_ERR_SHAPE, "sfa_ld=%lld must be >= M (scale words of a row group are contiguous)",
+               (long long)sfa_ld);
+  SGLB_REQUIRE(workspace_bytes >= 0 && (workspace == nullptr || sglb::aligned(workspace, 16)), SGLB200_ERR_ALIGN,
+               "workspace must be 16-byte aligned");
+  return sglb::ue8m0_common(a, b, sfa, sfb, out, nullptr, M, 1, N, K, lda, ldb, 0, ldc, sfa_ld, 1, 0, sfb_stride_n,
+                            sfb_stride_k, out_dtype, stream, static_cast<float*>(workspace),
+                            workspace ? workspace_bytes / (int64_t)sizeof(float) : 0);
 }
 
 extern "C" int sglb200_fp8_ue8m0_scaled_grouped_mm(const void* a, const void* b, const int32_t* sfa, const int32_t* sfb,

@@ -137,9 +137,13 @@ def w8a8_block_fp8_matmul_ue8m0(A: torch.Tensor, B: torch.Tensor, As_packed: tor
     if M == 0:
         return C
     sfa_ld = As_packed.stride(1) if KG > 1 else max(As_packed.stride(1), M)
+    L = lib()
     with torch.cuda.device(A.device):
-        check(lib().sglb200_fp8_ue8m0_scaled_mm(
+        ws_bytes = L.sglb200_fp8_blockwise_scaled_mm_workspace_bytes(M, N, K) if M <= 64 else 0
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=A.device) if ws_bytes > 0 else None
+        check(L.sglb200_fp8_ue8m0_scaled_mm_ws(
             A.data_ptr(), B.data_ptr(), As_packed.data_ptr(), Bs_packed.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
             sfa_ld, Bs_packed.stride(0), Bs_packed.stride(1), dtype_code(output_dtype),
+            ws.data_ptr() if ws is not None else None, ws_bytes,
             torch.cuda.current_stream(A.device).cuda_stream), "w8a8_block_fp8_matmul_ue8m0")
     return C

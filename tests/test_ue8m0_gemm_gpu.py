@@ -23,7 +23,10 @@ def _case(M, N, K, seed):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 224, 128), (1, 576, 512), (5, 128, 384), (200, 576, 2048), (1000, 1536, 4096),
-                                   (2048, 1920, 4096), (333, 7168, 1536)])
+                                   (2048, 1920, 4096), (333, 7168, 1536),
+                                   # up to 64 rows: the weight-streaming kernel, with and without split-K
+                                   (16, 7168, 8192), (17, 1536, 4096), (33, 576, 7168), (64, 4096, 7168), (48, 384, 640),
+                                   (65, 7168, 2048)])
 def test_ue8m0_gemm_matches_oracle(M, N, K):
     from sglang_b200._lib import lib
     from sglang_b200.layers.quantization import (pack_ue8m0_scales, sglang_per_token_group_quant_fp8,
