@@ -263,7 +263,7 @@ def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5):
 def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk=8, H=7168, I=2048, iters=5):
     """Expert-parallel fused MoE at the DeepSeek-V3 layer shape: E / ep experts and M_total / ep tokens per rank,
     all-to-all dispatch of e4m3 rows + scales, local grouped GEMMs, all-to-all combine.  Device time, max over ranks."""
-    from sglang_b200.distributed import ep_fused_experts
+    from sglang_b200.distributed import PeerEpExchange, ep_fused_experts, ep_fused_experts_peer
     el, m_loc = E // world, M_total // world
     w1 = (torch.randn(el, 2 * I, H, device=dev, generator=gen) * 20).to(torch.float8_e4m3fn)
     w2 = (torch.randn(el, H, I, device=dev, generator=gen) * 20).to(torch.float8_e4m3fn)
@@ -286,9 +286,31 @@ def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk
     ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     flops = M_total * topk * (2.0 * H * 2 * I + 2.0 * I * H)
-    return {"workload": f"fused MoE E={E} top{topk} H={H} I={I}, {M_total} tokens over ep{world} ({m_loc} per rank), "
-                        "NCCL all-to-all dispatch/combine with host-side count exchange", "ms": float(ms),
-            "tflops": flops / (float(ms) * 1e-3) / 1e12}
+    res = {"workload": f"fused MoE E={E} top{topk} H={H} I={I}, {M_total} tokens over ep{world} ({m_loc} per rank)",
+           "nccl": {"ms": float(ms), "tflops": flops / (float(ms) * 1e-3) / 1e12,
+                    "how": "NCCL all-to-all dispatch/combine with a host-side count exchange"}}
+    # the same layer with dispatch / combine over peer memory: no NCCL call, no host round trip
+    ex = PeerEpExchange(capacity=M_total, hidden=H, topk=topk, m_max=m_loc)
+    try:
+        for _ in range(2):
+            out_p = ep_fused_experts_peer(ex, a, w1, w2, w1s, w2s, tw, ti)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(iters):
+            out_p = ep_fused_experts_peer(ex, a, w1, w2, w1s, w2s, tw, ti)
+        e1.record()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms_p = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+        dist.all_reduce(ms_p, op=dist.ReduceOp.MAX)
+        out_n = ep_fused_experts(a, w1, w2, w1s, w2s, tw, ti, rank, world)
+        err = float((out_p.float() - out_n.float()).norm() / out_n.float().norm())
+        res["peer"] = {"ms": float(ms_p), "tflops": flops / (float(ms_p) * 1e-3) / 1e12, "rel_l2_vs_nccl": err,
+                       "how": "dispatch / combine kernels over CUDA-IPC peer memory, device-side row counts"}
+    finally:
+        ex.close()
+    return res
 
 
 def decode_section(torch, dev, peaks, shapes=None, ms=(1, 16, 64)):

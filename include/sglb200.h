@@ -392,6 +392,48 @@ int64_t sglb200_peer_recv_bytes(int64_t slot_elems);
 int sglb200_peer_completed(const void* flags_local, int64_t* completed);
 
 /*
+ * Expert-parallel token dispatch and combine over peer memory: the all-to-alls of the MoE layer without a collective
+ * library and without a host round trip for the row counts.  Every rank owns one exchange buffer of
+ * sglb200_ep_buffer_bytes(capacity, H, topk, world, m_max) bytes, zero before the first use, mapped by every rank
+ * (sglb200_peer_alloc / sglb200_peer_open); peer_bases is a HOST array of `world` device pointers, entry r = rank r's
+ * buffer as mapped in this process.  capacity = rows a rank can receive per exchange (at most the tokens of all ranks),
+ * m_max = tokens a rank may send.  sglb200_ep_buffer_offsets returns the byte offsets of {recv_q [capacity, H] e4m3,
+ * recv_s [capacity, H/128] f32, recv_meta [capacity, 2] i32, recv_ids [capacity, topk] i32, recv_w [capacity, topk] f32,
+ * comb [world, m_max, H] 16-bit, control words} inside a buffer.  One exchange, the same `epoch` (1, 2, 3, ...) on every
+ * rank, four launches on one stream per rank:
+ *   sglb200_ep_dispatch        every token of this rank (q [M, H] e4m3, scales s, topk_ids with GLOBAL expert ids, fp32
+ *                              weights) is stored once into the buffer of every rank that owns one of its experts
+ *                              (expert e lives on rank e / num_local_experts), in a row reserved there by a remote atomic.
+ *   sglb200_ep_receive         waits (bounded) until every rank has finished dispatching; rows that were not received
+ *                              get ids -1; count_out (device int32, may be NULL) = rows received.  The caller then runs
+ *                              the expert MLP on recv_q / recv_s / recv_ids / recv_w over `capacity` rows
+ *                              (sglb200 grouped GEMMs skip ids < 0) and gets one partial output row per received row.
+ *   sglb200_ep_combine_push    partial [capacity, H] (bf16 / f16): row i goes back to its source token.
+ *   sglb200_ep_combine_reduce  waits (bounded) until every rank has returned its rows; out[t] = sum of the partial rows of
+ *                              token t over the ranks that own one of its experts, ascending rank, fp32.
+ * The order of the received rows depends on timing, the result does not.  A wait that runs out sets device status 21
+ * (receive) or 22 (combine); a full receive buffer drops the row and sets 23 (sglb200_read_device_status).
+ * Replaces: DeepEP Buffer.dispatch / Buffer.combine as called from
+ *           python/sglang/srt/layers/moe/token_dispatcher/deepep.py:398-492 (third party, not in the tree), and the
+ *           reorder kernels python/sglang/srt/layers/moe/ep_moe/kernels.py:435-720.
+ */
+int64_t sglb200_ep_buffer_bytes(int64_t capacity, int64_t H, int64_t topk, int64_t world, int64_t m_max);
+int sglb200_ep_buffer_offsets(int64_t capacity, int64_t H, int64_t topk, int64_t world, int64_t m_max, int64_t* offsets7);
+int sglb200_ep_dispatch(const void* q, const float* s, int64_t s_stride_m, int64_t s_stride_k, const int32_t* topk_ids,
+                        const float* topk_weights, int64_t M, int64_t H, int64_t topk, int64_t num_local_experts,
+                        void* const* peer_bases, int rank, int world, uint32_t epoch, int64_t capacity, int64_t m_max,
+                        void* stream);
+int sglb200_ep_receive(void* const* peer_bases, int rank, int world, uint32_t epoch, int64_t H, int64_t topk,
+                       int64_t num_local_experts, int64_t capacity, int64_t m_max, int32_t* count_out, int64_t timeout_ns,
+                       void* stream);
+int sglb200_ep_combine_push(const void* partial, int dtype, void* const* peer_bases, int rank, int world, uint32_t epoch,
+                            int64_t H, int64_t topk, int64_t num_local_experts, int64_t capacity, int64_t m_max,
+                            void* stream);
+int sglb200_ep_combine_reduce(void* const* peer_bases, int rank, int world, uint32_t epoch, const int32_t* topk_ids,
+                              void* out, int dtype, int64_t M, int64_t H, int64_t topk, int64_t num_local_experts,
+                              int64_t capacity, int64_t m_max, int64_t timeout_ns, void* stream);
+
+/*
  * Set-up calls for the buffers above; the only entry points that ALLOCATE device memory, and they synchronise.
  * sglb200_peer_alloc: cudaMalloc + zero fill on the current device, and the 64-byte CUDA IPC handle another process
  * passes to sglb200_peer_open to map the same memory (peer access is enabled on first use).  sglb200_peer_close
@@ -406,7 +448,8 @@ int sglb200_peer_free(void* dev_ptr);
 
 /*
  * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
- * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce).  Reading clears it.  This call SYNCHRONISES the
+ * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce, 11-18 the same
+ * roles in the other GEMM kernels, 21-23 the expert-parallel exchange).  Reading clears it.  This call SYNCHRONISES the
  * device (cudaMemcpyFromSymbol); it is for tests and debugging, not for the serving path.  Returns -1 if the
  * read itself failed.  No counterpart in the reference (its kernels have no bounded waits).
  */

@@ -1137,12 +1137,15 @@ extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, vo
 
 namespace sglb {
 int ue8m0_take_device_status();  // gemm_ue8m0.cu
+int ep_take_device_status();     // ep_peer.cu
 }
 extern "C" int sglb200_read_device_status(void) {
   const int u = sglb::ue8m0_take_device_status();
   if (u != 0) return u;
   const int sm = sglb::smallm_take_device_status();
   if (sm != 0) return sm;
+  const int ep = sglb::ep_take_device_status();
+  if (ep != 0) return ep;
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, sglb::g_device_status, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();

@@ -21,7 +21,7 @@ def _worker(rank, world, port, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import oracle
-        from helpers import assert_gemm_close, row_parallel_reference
+        from helpers import assert_gemm_close, expert_parallel_reference, row_parallel_reference
         from sglang_b200.distributed import (ColumnParallelBlockFp8Linear, RowParallelBlockFp8Linear,
                                              ep_fused_experts)
         g = torch.Generator().manual_seed(0)
@@ -79,6 +79,22 @@ def _worker(rank, world, port, q):
             assert big.shape == (512, H) and ex.completed == 7
         finally:
             ex.close()
+        # ---- the same expert-parallel layer with dispatch / combine over peer memory (no NCCL, no host sync)
+        from sglang_b200.distributed import PeerEpExchange, ep_fused_experts_peer
+        epx = PeerEpExchange(capacity=150 + 90, hidden=Hm, topk=topk, m_max=150)
+        try:
+            for it in range(4):
+                gi = torch.Generator().manual_seed(70 + 10 * it + rank)
+                Mi = [150, 90, 1, 77][(it + rank) % 4]
+                xi = torch.randn(Mi, Hm, generator=gi).bfloat16()
+                twi, tii = torch.topk(torch.softmax(torch.randn(Mi, E, generator=gi), -1), topk)
+                out_p = ep_fused_experts_peer(epx, xi.cuda(), w1q[lo:hi].cuda(), w2q[lo:hi].cuda(), w1s[lo:hi].cuda(),
+                                              w2s[lo:hi].cuda(), twi.cuda(), tii.cuda())
+                torch.cuda.synchronize()
+                refi = expert_parallel_reference(xi, w1q, w2q, w1s, w2s, twi, tii, world)
+                assert_gemm_close(out_p, refi, f"peer ep moe {it}")
+        finally:
+            epx.close()
         from sglang_b200._lib import lib
         assert lib().sglb200_read_device_status() == 0
         q.put((rank, "ok"))
