@@ -83,14 +83,19 @@ def _worker(rank, world, port, q):
         from sglang_b200.distributed import PeerEpExchange, ep_fused_experts_peer
         epx = PeerEpExchange(capacity=150 + 90, hidden=Hm, topk=topk, m_max=150)
         try:
-            for it in range(4):
+            done = []
+            for it in range(6):
                 gi = torch.Generator().manual_seed(70 + 10 * it + rank)
                 Mi = [150, 90, 1, 77][(it + rank) % 4]
                 xi = torch.randn(Mi, Hm, generator=gi).bfloat16()
                 twi, tii = torch.topk(torch.softmax(torch.randn(Mi, E, generator=gi), -1), topk)
                 out_p = ep_fused_experts_peer(epx, xi.cuda(), w1q[lo:hi].cuda(), w2q[lo:hi].cuda(), w1s[lo:hi].cuda(),
                                               w2s[lo:hi].cuda(), twi.cuda(), tii.cuda())
-                torch.cuda.synchronize()
+                done.append((it, out_p, xi, twi, tii))
+            torch.cuda.synchronize()
+            # the references are computed after the loop: the waits inside the exchange are bounded (2 s), and seconds of
+            # CPU work on one rank between two layers would let the other rank's wait run out
+            for it, out_p, xi, twi, tii in done:
                 refi = expert_parallel_reference(xi, w1q, w2q, w1s, w2s, twi, tii, world)
                 assert_gemm_close(out_p, refi, f"peer ep moe {it}")
         finally:
