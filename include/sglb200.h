@@ -399,8 +399,9 @@ int sglb200_peer_completed(const void* flags_local, int64_t* completed);
  * buffer as mapped in this process.  capacity = rows a rank can receive per exchange (at most the tokens of all ranks),
  * m_max = tokens a rank may send.  sglb200_ep_buffer_offsets returns the byte offsets of {recv_q [capacity, H] e4m3,
  * recv_s [capacity, H/128] f32, recv_meta [capacity, 2] i32, recv_ids [capacity, topk] i32, recv_w [capacity, topk] f32,
- * comb [world, m_max, H] 16-bit, control words} inside a buffer.  One exchange, the same `epoch` (1, 2, 3, ...) on every
- * rank, four launches on one stream per rank:
+ * comb [world, m_max, H] 16-bit, control words} inside a buffer.  One exchange = four launches on one stream per rank,
+ * the same sequence on every rank; the exchange counter lives in the control words (read by all four kernels, advanced
+ * by the last block of the combine-reduce kernel), so the layer can be captured in a CUDA graph and replayed:
  *   sglb200_ep_dispatch        every token of this rank (q [M, H] e4m3, scales s, topk_ids with GLOBAL expert ids, fp32
  *                              weights) is stored once into the buffer of every rank that owns one of its experts
  *                              (expert e lives on rank e / num_local_experts), in a row reserved there by a remote atomic.
@@ -421,17 +422,17 @@ int64_t sglb200_ep_buffer_bytes(int64_t capacity, int64_t H, int64_t topk, int64
 int sglb200_ep_buffer_offsets(int64_t capacity, int64_t H, int64_t topk, int64_t world, int64_t m_max, int64_t* offsets7);
 int sglb200_ep_dispatch(const void* q, const float* s, int64_t s_stride_m, int64_t s_stride_k, const int32_t* topk_ids,
                         const float* topk_weights, int64_t M, int64_t H, int64_t topk, int64_t num_local_experts,
-                        void* const* peer_bases, int rank, int world, uint32_t epoch, int64_t capacity, int64_t m_max,
-                        void* stream);
-int sglb200_ep_receive(void* const* peer_bases, int rank, int world, uint32_t epoch, int64_t H, int64_t topk,
-                       int64_t num_local_experts, int64_t capacity, int64_t m_max, int32_t* count_out, int64_t timeout_ns,
-                       void* stream);
-int sglb200_ep_combine_push(const void* partial, int dtype, void* const* peer_bases, int rank, int world, uint32_t epoch,
-                            int64_t H, int64_t topk, int64_t num_local_experts, int64_t capacity, int64_t m_max,
-                            void* stream);
-int sglb200_ep_combine_reduce(void* const* peer_bases, int rank, int world, uint32_t epoch, const int32_t* topk_ids,
-                              void* out, int dtype, int64_t M, int64_t H, int64_t topk, int64_t num_local_experts,
-                              int64_t capacity, int64_t m_max, int64_t timeout_ns, void* stream);
+                        void* const* peer_bases, int rank, int world, int64_t capacity, int64_t m_max, void* stream);
+int sglb200_ep_receive(void* const* peer_bases, int rank, int world, int64_t H, int64_t topk, int64_t num_local_experts,
+                       int64_t capacity, int64_t m_max, int32_t* count_out, int64_t timeout_ns, void* stream);
+int sglb200_ep_combine_push(const void* partial, int dtype, void* const* peer_bases, int rank, int world, int64_t H,
+                            int64_t topk, int64_t num_local_experts, int64_t capacity, int64_t m_max, void* stream);
+int sglb200_ep_combine_reduce(void* const* peer_bases, int rank, int world, const int32_t* topk_ids, void* out, int dtype,
+                              int64_t M, int64_t H, int64_t topk, int64_t num_local_experts, int64_t capacity,
+                              int64_t m_max, int64_t timeout_ns, void* stream);
+/* Exchanges this rank has completed (its control word).  SYNCHRONISES (cudaMemcpy); for tests and debugging. */
+int sglb200_ep_completed(const void* local_base, int64_t capacity, int64_t H, int64_t topk, int64_t world, int64_t m_max,
+                         int64_t* completed);
 
 /*
  * Set-up calls for the buffers above; the only entry points that ALLOCATE device memory, and they synchronise.

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_float, c_int, c_int64, c_uint32, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_void_p
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "lib", "libsglb200.so")
@@ -50,10 +50,11 @@ SIGNATURES = {
     "sglb200_peer_reduce": [_P, _P, _P, _L, _L, _L, _I, _I, _L, _L, _P],
     "sglb200_ep_buffer_bytes": [_L, _L, _L, _L, _L],
     "sglb200_ep_buffer_offsets": [_L, _L, _L, _L, _L, _P],
-    "sglb200_ep_dispatch": [_P, _P, _L, _L, _P, _P, _L, _L, _L, _L, _P, _I, _I, c_uint32, _L, _L, _P],
-    "sglb200_ep_receive": [_P, _I, _I, c_uint32, _L, _L, _L, _L, _L, _P, _L, _P],
-    "sglb200_ep_combine_push": [_P, _I, _P, _I, _I, c_uint32, _L, _L, _L, _L, _L, _P],
-    "sglb200_ep_combine_reduce": [_P, _I, _I, c_uint32, _P, _P, _I, _L, _L, _L, _L, _L, _L, _L, _P],
+    "sglb200_ep_dispatch": [_P, _P, _L, _L, _P, _P, _L, _L, _L, _L, _P, _I, _I, _L, _L, _P],
+    "sglb200_ep_receive": [_P, _I, _I, _L, _L, _L, _L, _L, _P, _L, _P],
+    "sglb200_ep_combine_push": [_P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
+    "sglb200_ep_combine_reduce": [_P, _I, _I, _P, _P, _I, _L, _L, _L, _L, _L, _L, _L, _P],
+    "sglb200_ep_completed": [_P, _L, _L, _L, _L, _L, _P],
     "sglb200_peer_completed": [_P, _P],
     "sglb200_peer_flag_bytes": [],
     "sglb200_peer_recv_bytes": [_L],

@@ -8,7 +8,10 @@
 //   recv_ids  [capacity][topk]     expert ids relative to this rank's first expert, -1 = not here
 //   recv_w    [capacity][topk]     routing weights
 //   comb      [world][m_max][H]    partial output rows coming back: comb[r][t] = what rank r's experts add to my token t
-//   ctl       row counters (one per epoch parity), completion flags per source rank, block tickets
+//   ctl       row counters (one per epoch parity), completion flags per source rank, block tickets, and the number of
+//             exchanges this rank has completed: the epoch of an exchange is that number + 1, read by all four kernels
+//             and advanced by the last block of the combine-reduce kernel, so a captured CUDA graph of the layer can be
+//             replayed
 // dispatch:        one warp per token; for every rank that owns one of the token's experts it reserves a row there with
 //                  a remote atomic and stores the quantised row, scales, ids and weights; the last block raises this
 //                  rank's "done" flag on every peer.
@@ -48,7 +51,9 @@ constexpr int kMaxRanks = 8;
 constexpr int kMaxTopk = 32;
 // control words (uint32)
 constexpr int kCtlCount = 0;      // [2]   rows received, per epoch parity
-constexpr int kCtlTicket = 2;     // [2]   block tickets of the dispatch / combine-push kernels
+constexpr int kCtlTicket = 2;     // [3]   block tickets of the dispatch / combine-push / combine-reduce kernels
+constexpr int kCtlEpoch = 5;      //       exchanges completed by this rank; the epoch in flight is this + 1
+constexpr int kCtlFailed = 6;     //       a block of the combine-reduce kernel gave up waiting
 constexpr int kCtlDone = 8;       // [2][8] source rank r finished dispatching epoch e
 constexpr int kCtlReturned = 24;  // [2][8] expert rank r finished returning partial rows of epoch e
 constexpr int kCtlWords = 64;
@@ -76,9 +81,12 @@ struct EpParams {
   char* peer[kMaxRanks];  // every rank's buffer as mapped here; peer[rank] is this rank's own
   Layout lay;
   int32_t rank, world, H, topk, e_local, capacity, m_max;
-  uint32_t epoch;
   uint64_t limit_ns;
 };
+
+__device__ __forceinline__ uint32_t epoch_of(const EpParams& p) {
+  return *reinterpret_cast<volatile uint32_t*>(reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.lay.ctl) + kCtlEpoch) + 1u;
+}
 
 __device__ __forceinline__ uint32_t* ctl_of(const EpParams& p, int r) {
   return reinterpret_cast<uint32_t*>(p.peer[r] + p.lay.ctl);
@@ -86,7 +94,7 @@ __device__ __forceinline__ uint32_t* ctl_of(const EpParams& p, int r) {
 
 // last-block pattern: every block calls this after its stores; the last one raises flag word `which` + parity * 8 +
 // rank on every peer
-__device__ __forceinline__ void finish_and_flag(const EpParams& p, int ticket_idx, int which) {
+__device__ __forceinline__ void finish_and_flag(const EpParams& p, uint32_t epoch, int ticket_idx, int which) {
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
@@ -94,21 +102,21 @@ __device__ __forceinline__ void finish_and_flag(const EpParams& p, int ticket_id
     if (atomicAdd(&my[kCtlTicket + ticket_idx], 1u) == gridDim.x - 1) {
       my[kCtlTicket + ticket_idx] = 0;
       __threadfence_system();
-      const uint32_t par = p.epoch & 1u;
-      for (int r = 0; r < p.world; ++r) ptx::st_release_sys_u32(ctl_of(p, r) + which + par * 8 + p.rank, p.epoch);
+      const uint32_t par = epoch & 1u;
+      for (int r = 0; r < p.world; ++r) ptx::st_release_sys_u32(ctl_of(p, r) + which + par * 8 + p.rank, epoch);
     }
   }
 }
 
 // block-wide bounded wait until word base[r] reached the epoch for every r < world; false on time-out
-__device__ __forceinline__ bool wait_flags(const EpParams& p, const uint32_t* base, int code) {
+__device__ __forceinline__ bool wait_flags(const EpParams& p, uint32_t epoch, const uint32_t* base, int code) {
   __shared__ int s_ok;
   if (threadIdx.x == 0) s_ok = 1;
   __syncthreads();
   if ((int)threadIdx.x < p.world) {
     uint64_t t0 = 0;
     uint32_t polls = 0;
-    while ((int32_t)(ptx::ld_acquire_sys_u32(base + threadIdx.x) - p.epoch) < 0) {
+    while ((int32_t)(ptx::ld_acquire_sys_u32(base + threadIdx.x) - epoch) < 0) {
       if ((++polls & 255u) == 0) {
         const uint64_t now = ptx::global_timer_ns();
         if (t0 == 0) {
@@ -130,7 +138,7 @@ ep_dispatch_kernel(const EpParams p, const uint8_t* __restrict__ q, const float*
                    int64_t s_stride_k, const int32_t* __restrict__ topk_ids, const float* __restrict__ topk_w,
                    int32_t M) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t par = p.epoch & 1u;
+  const uint32_t epoch = epoch_of(p), par = epoch & 1u;
   const int G = p.H / 128, vecs = p.H / 16;
   for (int32_t t = blockIdx.x * 8 + warp; t < M; t += gridDim.x * 8) {
     int32_t id = -1;
@@ -166,13 +174,13 @@ ep_dispatch_kernel(const EpParams p, const uint8_t* __restrict__ q, const float*
       }
     }
   }
-  finish_and_flag(p, 0, kCtlDone);
+  finish_and_flag(p, epoch, 0, kCtlDone);
 }
 
 __global__ void __launch_bounds__(256) ep_receive_kernel(const EpParams p, int32_t* __restrict__ count_out) {
   uint32_t* my = ctl_of(p, p.rank);
-  const uint32_t par = p.epoch & 1u;
-  if (!wait_flags(p, my + kCtlDone + par * 8, 21)) return;
+  const uint32_t epoch = epoch_of(p), par = epoch & 1u;
+  if (!wait_flags(p, epoch, my + kCtlDone + par * 8, 21)) return;
   const uint32_t n = min(*reinterpret_cast<volatile uint32_t*>(my + kCtlCount + par), (uint32_t)p.capacity);
   int32_t* ids = reinterpret_cast<int32_t*>(p.peer[p.rank] + p.lay.ids);
   const int64_t total = (int64_t)p.capacity * p.topk;
@@ -187,7 +195,7 @@ __global__ void __launch_bounds__(256) ep_receive_kernel(const EpParams p, int32
 template <typename T>
 __global__ void __launch_bounds__(256) ep_combine_push_kernel(const EpParams p, const T* __restrict__ partial) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const uint32_t par = p.epoch & 1u;
+  const uint32_t epoch = epoch_of(p), par = epoch & 1u;
   const uint32_t n = min(*reinterpret_cast<volatile uint32_t*>(ctl_of(p, p.rank) + kCtlCount + par), (uint32_t)p.capacity);
   const int32_t* meta = reinterpret_cast<const int32_t*>(p.peer[p.rank] + p.lay.meta);
   const int vecs = p.H / 8;
@@ -198,18 +206,18 @@ __global__ void __launch_bounds__(256) ep_combine_push_kernel(const EpParams p, 
     uint4* to = reinterpret_cast<uint4*>(p.peer[src] + p.lay.comb) + ((int64_t)p.rank * p.m_max + tok) * vecs;
     for (int v = lane; v < vecs; v += 32) to[v] = __ldg(from + v);
   }
-  finish_and_flag(p, 1, kCtlReturned);
+  finish_and_flag(p, epoch, 1, kCtlReturned);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(256)
 ep_combine_reduce_kernel(const EpParams p, const int32_t* __restrict__ topk_ids, T* __restrict__ out, int32_t M) {
-  const uint32_t par = p.epoch & 1u;
-  if (!wait_flags(p, ctl_of(p, p.rank) + kCtlReturned + par * 8, 22)) return;
+  const uint32_t epoch = epoch_of(p), par = epoch & 1u;
+  const bool ok = wait_flags(p, epoch, ctl_of(p, p.rank) + kCtlReturned + par * 8, 22);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int vecs = p.H / 8;
   const uint4* comb = reinterpret_cast<const uint4*>(p.peer[p.rank] + p.lay.comb);
-  for (int32_t t = blockIdx.x * 8 + warp; t < M; t += gridDim.x * 8) {
+  for (int32_t t = blockIdx.x * 8 + warp; ok && t < M; t += gridDim.x * 8) {
     int owner = -1;
     if (lane < p.topk) {
       const int32_t id = __ldg(topk_ids + (int64_t)t * p.topk + lane);
@@ -236,17 +244,28 @@ ep_combine_reduce_kernel(const EpParams p, const int32_t* __restrict__ topk_ids,
       reinterpret_cast<uint4*>(out + (int64_t)t * p.H)[v] = o;
     }
   }
+  // every block has read the epoch by now; the last one closes the exchange (not if a block gave up: the exchange can
+  // then be reduced again once the missing rank has caught up)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* my = ctl_of(p, p.rank);
+    if (!ok) atomicExch(&my[kCtlFailed], 1u);
+    if (atomicAdd(&my[kCtlTicket + 2], 1u) == gridDim.x - 1) {
+      const uint32_t failed = atomicExch(&my[kCtlFailed], 0u);
+      my[kCtlTicket + 2] = 0;
+      if (!failed) *reinterpret_cast<volatile uint32_t*>(my + kCtlEpoch) = epoch;
+    }
+  }
 }
 
 int fill_params(EpParams* p, void* const* peer_bases, int rank, int world, int64_t H, int64_t topk, int64_t e_local,
-                int64_t capacity, int64_t m_max, uint32_t epoch, int64_t timeout_ns) {
+                int64_t capacity, int64_t m_max, int64_t timeout_ns) {
   SGLB_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, SGLB200_ERR_SHAPE, "world=%d (1..%d) rank=%d",
                world, kMaxRanks, rank);
   SGLB_REQUIRE(H > 0 && H % 128 == 0, SGLB200_ERR_SHAPE, "H=%lld must be a positive multiple of 128", (long long)H);
   SGLB_REQUIRE(topk >= 1 && topk <= kMaxTopk && e_local >= 1 && capacity >= 1 && m_max >= 1, SGLB200_ERR_SHAPE,
                "topk=%lld (1..%d) e_local=%lld capacity=%lld m_max=%lld", (long long)topk, kMaxTopk, (long long)e_local,
                (long long)capacity, (long long)m_max);
-  SGLB_REQUIRE(epoch != 0, SGLB200_ERR_SHAPE, "epoch must start at 1 (the flag words start at 0)");
   SGLB_REQUIRE(peer_bases != nullptr, SGLB200_ERR_NULL, "peer_bases must not be NULL");
   for (int r = 0; r < kMaxRanks; ++r) {
     p->peer[r] = r < world ? static_cast<char*>(peer_bases[r]) : nullptr;
@@ -261,7 +280,6 @@ int fill_params(EpParams* p, void* const* peer_bases, int rank, int world, int64
   p->e_local = (int32_t)e_local;
   p->capacity = (int32_t)capacity;
   p->m_max = (int32_t)m_max;
-  p->epoch = epoch;
   p->limit_ns = timeout_ns > 0 ? (uint64_t)timeout_ns : 2000000000ull;
   DeviceInfo di;
   if (int rc = device_info(&di)) return rc;
@@ -302,9 +320,9 @@ extern "C" int sglb200_ep_buffer_offsets(int64_t capacity, int64_t H, int64_t to
 extern "C" int sglb200_ep_dispatch(const void* q, const float* s, int64_t s_stride_m, int64_t s_stride_k,
                                    const int32_t* topk_ids, const float* topk_weights, int64_t M, int64_t H,
                                    int64_t topk, int64_t num_local_experts, void* const* peer_bases, int rank, int world,
-                                   uint32_t epoch, int64_t capacity, int64_t m_max, void* stream) {
+                                   int64_t capacity, int64_t m_max, void* stream) {
   EpParams p;
-  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, epoch, 0)) return rc;
+  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, 0)) return rc;
   SGLB_REQUIRE(M >= 0 && M <= m_max, SGLB200_ERR_SHAPE, "M=%lld must be in 0..m_max=%lld", (long long)M, (long long)m_max);
   SGLB_REQUIRE(M == 0 || (q && s && topk_ids && topk_weights && aligned(q, 16)), SGLB200_ERR_NULL,
                "q (16-byte aligned), s, topk_ids and topk_weights must be given");
@@ -314,11 +332,11 @@ extern "C" int sglb200_ep_dispatch(const void* q, const float* s, int64_t s_stri
   return SGLB200_OK;
 }
 
-extern "C" int sglb200_ep_receive(void* const* peer_bases, int rank, int world, uint32_t epoch, int64_t H, int64_t topk,
+extern "C" int sglb200_ep_receive(void* const* peer_bases, int rank, int world, int64_t H, int64_t topk,
                                   int64_t num_local_experts, int64_t capacity, int64_t m_max, int32_t* count_out,
                                   int64_t timeout_ns, void* stream) {
   EpParams p;
-  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, epoch, timeout_ns))
+  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, timeout_ns))
     return rc;
   ep_receive_kernel<<<grid_for(capacity * topk / 256 + 1), 256, 0, static_cast<cudaStream_t>(stream)>>>(p, count_out);
   SGLB_CHECK_LAUNCH("ep_receive_kernel");
@@ -326,10 +344,10 @@ extern "C" int sglb200_ep_receive(void* const* peer_bases, int rank, int world, 
 }
 
 extern "C" int sglb200_ep_combine_push(const void* partial, int dtype, void* const* peer_bases, int rank, int world,
-                                       uint32_t epoch, int64_t H, int64_t topk, int64_t num_local_experts,
-                                       int64_t capacity, int64_t m_max, void* stream) {
+                                       int64_t H, int64_t topk, int64_t num_local_experts, int64_t capacity,
+                                       int64_t m_max, void* stream) {
   EpParams p;
-  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, epoch, 0)) return rc;
+  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, 0)) return rc;
   SGLB_REQUIRE(dtype == SGLB200_BF16 || dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "dtype=%d", dtype);
   SGLB_REQUIRE(partial && aligned(partial, 16), SGLB200_ERR_NULL, "partial must be given, 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -342,12 +360,12 @@ extern "C" int sglb200_ep_combine_push(const void* partial, int dtype, void* con
   return SGLB200_OK;
 }
 
-extern "C" int sglb200_ep_combine_reduce(void* const* peer_bases, int rank, int world, uint32_t epoch,
-                                         const int32_t* topk_ids, void* out, int dtype, int64_t M, int64_t H,
-                                         int64_t topk, int64_t num_local_experts, int64_t capacity, int64_t m_max,
-                                         int64_t timeout_ns, void* stream) {
+extern "C" int sglb200_ep_combine_reduce(void* const* peer_bases, int rank, int world, const int32_t* topk_ids,
+                                         void* out, int dtype, int64_t M, int64_t H, int64_t topk,
+                                         int64_t num_local_experts, int64_t capacity, int64_t m_max, int64_t timeout_ns,
+                                         void* stream) {
   EpParams p;
-  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, epoch, timeout_ns))
+  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, timeout_ns))
     return rc;
   SGLB_REQUIRE(dtype == SGLB200_BF16 || dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "dtype=%d", dtype);
   SGLB_REQUIRE(M >= 0 && M <= m_max, SGLB200_ERR_SHAPE, "M=%lld must be in 0..m_max=%lld", (long long)M, (long long)m_max);
@@ -359,5 +377,18 @@ extern "C" int sglb200_ep_combine_reduce(void* const* peer_bases, int rank, int 
   else
     ep_combine_reduce_kernel<__half><<<grid, 256, 0, st>>>(p, topk_ids, static_cast<__half*>(out), (int32_t)M);
   SGLB_CHECK_LAUNCH("ep_combine_reduce_kernel");
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_ep_completed(const void* local_base, int64_t capacity, int64_t H, int64_t topk, int64_t world,
+                                    int64_t m_max, int64_t* completed) {
+  SGLB_REQUIRE(local_base && completed && capacity > 0 && H > 0 && topk > 0 && world > 0 && m_max > 0, SGLB200_ERR_NULL,
+               "local_base, completed and the layout arguments must be given");
+  const Layout l = make_layout(capacity, H, topk, world, m_max);
+  uint32_t v = 0;
+  cudaError_t e = cudaMemcpy(&v, static_cast<const char*>(local_base) + l.ctl + kCtlEpoch * 4, sizeof(v),
+                             cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaMemcpy: %s", cudaGetErrorString(e));
+  *completed = v;
   return SGLB200_OK;
 }

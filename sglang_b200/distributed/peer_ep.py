@@ -56,7 +56,6 @@ class PeerEpExchange:
             raise RuntimeError("PeerEpExchange supports at most 8 ranks (one NVLink domain)")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.capacity, self.hidden, self.topk, self.m_max = int(capacity), int(hidden), int(topk), int(m_max)
-        self.epoch = 0
         L = lib()
         self._opened: List[int] = []
         with torch.cuda.device(self.device):
@@ -84,6 +83,15 @@ class PeerEpExchange:
         if self.world > 1:
             dist.barrier(group=group)
 
+    @property
+    def completed(self) -> int:
+        """Exchanges this rank has completed (the device control word; synchronises the stream-ordered work)."""
+        n = ctypes.c_int64()
+        with torch.cuda.device(self.device):
+            check(lib().sglb200_ep_completed(self._own, self.capacity, self.hidden, self.topk, self.world, self.m_max,
+                                             ctypes.byref(n)), "ep_completed")
+        return n.value
+
     def close(self) -> None:
         if self._own is None:
             return
@@ -104,27 +112,27 @@ def _stream(dev) -> int:
     return torch.cuda.current_stream(dev).cuda_stream
 
 
-def ep_dispatch(arr, rank, world, epoch, capacity, m_max, a_q, a_s, topk_ids, topk_weights, e_local) -> None:
+def ep_dispatch(arr, rank, world, capacity, m_max, a_q, a_s, topk_ids, topk_weights, e_local) -> None:
     M, H = a_q.shape
     check(lib().sglb200_ep_dispatch(a_q.data_ptr(), a_s.data_ptr(), a_s.stride(0), a_s.stride(1), topk_ids.data_ptr(),
-                                    topk_weights.data_ptr(), M, H, topk_ids.size(1), e_local, arr, rank, world, epoch,
+                                    topk_weights.data_ptr(), M, H, topk_ids.size(1), e_local, arr, rank, world,
                                     capacity, m_max, _stream(a_q.device)), "ep_dispatch")
 
 
-def ep_receive(arr, rank, world, epoch, H, topk, e_local, capacity, m_max, count, timeout_ns=0) -> None:
-    check(lib().sglb200_ep_receive(arr, rank, world, epoch, H, topk, e_local, capacity, m_max,
+def ep_receive(arr, rank, world, H, topk, e_local, capacity, m_max, count, timeout_ns=0) -> None:
+    check(lib().sglb200_ep_receive(arr, rank, world, H, topk, e_local, capacity, m_max,
                                    count.data_ptr() if count is not None else None, timeout_ns,
                                    _stream(count.device if count is not None else None)), "ep_receive")
 
 
-def ep_combine_push(arr, rank, world, epoch, H, topk, e_local, capacity, m_max, partial) -> None:
-    check(lib().sglb200_ep_combine_push(partial.data_ptr(), dtype_code(partial.dtype), arr, rank, world, epoch, H, topk,
+def ep_combine_push(arr, rank, world, H, topk, e_local, capacity, m_max, partial) -> None:
+    check(lib().sglb200_ep_combine_push(partial.data_ptr(), dtype_code(partial.dtype), arr, rank, world, H, topk,
                                         e_local, capacity, m_max, _stream(partial.device)), "ep_combine_push")
 
 
-def ep_combine_reduce(arr, rank, world, epoch, topk_ids, out, e_local, capacity, m_max, timeout_ns=0) -> None:
+def ep_combine_reduce(arr, rank, world, topk_ids, out, e_local, capacity, m_max, timeout_ns=0) -> None:
     M, H = out.shape
-    check(lib().sglb200_ep_combine_reduce(arr, rank, world, epoch, topk_ids.data_ptr(), out.data_ptr(),
+    check(lib().sglb200_ep_combine_reduce(arr, rank, world, topk_ids.data_ptr(), out.data_ptr(),
                                           dtype_code(out.dtype), M, H, topk_ids.size(1), e_local, capacity, m_max,
                                           timeout_ns, _stream(out.device)), "ep_combine_reduce")
 
@@ -134,7 +142,8 @@ def ep_fused_experts_peer(ex: PeerEpExchange, hidden_states: torch.Tensor, w1: t
                           topk_ids: torch.Tensor) -> torch.Tensor:
     """The expert-parallel MoE layer for the tokens of THIS rank (same contract as
     :func:`sglang_b200.distributed.ep_fused_experts`): ``w1 / w2`` hold this rank's ``E / ep`` experts, ``topk_ids`` are
-    global expert ids.  Five launches around the local expert MLP, nothing synchronises the stream."""
+    global expert ids.  Five launches around the local expert MLP; nothing synchronises the stream and the exchange counter lives on the
+    device, so the whole layer can be captured in a CUDA graph."""
     from ..layers.moe import fused_experts_block_fp8_prequant
     from ..layers.quantization import sglang_per_token_group_quant_fp8
     M, H = hidden_states.shape
@@ -143,8 +152,7 @@ def ep_fused_experts_peer(ex: PeerEpExchange, hidden_states: torch.Tensor, w1: t
     ids = topk_ids.to(torch.int32).contiguous()
     w = topk_weights.to(torch.float32).contiguous()
     out = torch.empty(M, H, dtype=hidden_states.dtype, device=hidden_states.device)
-    ex.epoch += 1
-    args = (ex._arr, ex.rank, ex.world, ex.epoch)
+    args = (ex._arr, ex.rank, ex.world)
     with torch.cuda.device(hidden_states.device):
         if M > 0:
             a_q, a_s = sglang_per_token_group_quant_fp8(hidden_states.contiguous(), 128)

@@ -52,19 +52,19 @@ def test_ep_exchange_emulated_ranks(world, E, topk, H, I, tokens):
             else:
                 a_q = torch.empty(0, H, dtype=torch.float8_e4m3fn, device="cuda")
                 a_s = torch.empty(0, H // 128, device="cuda")
-            pe.ep_dispatch(arr, r, world, epoch, cap, m_max, a_q, a_s, ids_[r].cuda(), ws_[r].cuda(), el)
+            pe.ep_dispatch(arr, r, world, cap, m_max, a_q, a_s, ids_[r].cuda(), ws_[r].cuda(), el)
         counts = []
         for r in range(world):
             cnt = torch.zeros(1, dtype=torch.int32, device="cuda")
-            pe.ep_receive(arr, r, world, epoch, H, topk, el, cap, m_max, cnt)
+            pe.ep_receive(arr, r, world, H, topk, el, cap, m_max, cnt)
             rq, rs, rids, rw = views[r]
             partial = fused_experts_block_fp8_prequant(rq, rs, torch.bfloat16, *w_dev[r][:2], *w_dev[r][2:], rw, rids)
-            pe.ep_combine_push(arr, r, world, epoch, H, topk, el, cap, m_max, partial)
+            pe.ep_combine_push(arr, r, world, H, topk, el, cap, m_max, partial)
             counts.append(cnt)
         outs = []
         for r in range(world):
             out = torch.full((tokens[r], H), 7.0, dtype=torch.bfloat16, device="cuda")
-            pe.ep_combine_reduce(arr, r, world, epoch, ids_[r].cuda(), out, el, cap, m_max)
+            pe.ep_combine_reduce(arr, r, world, ids_[r].cuda(), out, el, cap, m_max)
             outs.append(out)
         torch.cuda.synchronize()
         assert L.sglb200_read_device_status() == 0
@@ -90,11 +90,11 @@ def test_ep_receive_wait_runs_out_and_full_buffer_reports():
     a_s = torch.ones(16, 2, device="cuda")
     ids = torch.zeros(16, topk, dtype=torch.int32, device="cuda")  # every token goes to rank 0: 16 rows into 4 slots
     w = torch.ones(16, topk, device="cuda")
-    pe.ep_dispatch(arr, 0, world, 1, cap, m_max, a_q, a_s, ids, w, el)
+    pe.ep_dispatch(arr, 0, world, cap, m_max, a_q, a_s, ids, w, el)
     torch.cuda.synchronize()
     assert L.sglb200_read_device_status() == 23  # receive buffer full: rows dropped, reported
     cnt = torch.zeros(1, dtype=torch.int32, device="cuda")
-    pe.ep_receive(arr, 0, world, 1, H, topk, el, cap, m_max, cnt, timeout_ns=20_000_000)  # rank 1 never dispatched
+    pe.ep_receive(arr, 0, world, H, topk, el, cap, m_max, cnt, timeout_ns=20_000_000)  # rank 1 never dispatched
     torch.cuda.synchronize()
     assert L.sglb200_read_device_status() == 21 and int(cnt.item()) == 0
     assert L.sglb200_read_device_status() == 0
@@ -117,5 +117,27 @@ def test_peer_ep_exchange_single_rank():
                                           ti.to(torch.int32).cuda())
             torch.cuda.synchronize()
             assert torch.equal(out, ref)
+        assert ex.completed == 3
+        # the whole layer replays from a CUDA graph: nothing on the path synchronises, the exchange counter is on the device
+        x = make_activations(M, H, seed=9, outliers=False).cuda()
+        g = torch.Generator().manual_seed(9)
+        tw, ti = torch.topk(torch.softmax(torch.randn(M, E, generator=g), -1), topk)
+        args = (x, w1q.cuda(), w2q.cuda(), w1s.cuda(), w2s.cuda(), tw.cuda(), ti.cuda())
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ep_fused_experts_peer(ex, *args)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            y_g = ep_fused_experts_peer(ex, *args)
+        before = ex.completed
+        for _ in range(3):
+            y_g.zero_()
+            graph.replay()
+        torch.cuda.synchronize()
+        assert ex.completed == before + 3
+        assert torch.equal(y_g, fused_experts_block_fp8(x, *args[1:5], tw.cuda(), ti.to(torch.int32).cuda()))
     finally:
         ex.close()
