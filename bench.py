@@ -308,6 +308,39 @@ def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk
         err = float((out_p.float() - out_n.float()).norm() / out_n.float().norm())
         res["peer"] = {"ms": float(ms_p), "tflops": flops / (float(ms_p) * 1e-3) / 1e12, "rel_l2_vs_nccl": err,
                        "how": "dispatch / combine kernels over CUDA-IPC peer memory, device-side row counts"}
+        # decode size: 64 tokens per rank.  The peer version is one CUDA graph (nothing on its path synchronises); the
+        # NCCL version needs the received-row counts on the host and cannot be captured.
+        md = 64
+        ad, twd, tid = a[:md].contiguous(), tw[:md].contiguous(), ti[:md].contiguous()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                ep_fused_experts_peer(ex, ad, w1, w2, w1s, w2s, twd, tid)
+        torch.cuda.current_stream().wait_stream(side)
+        dist.barrier()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            ep_fused_experts_peer(ex, ad, w1, w2, w1s, w2s, twd, tid)
+        times = {}
+        for name, fn in (("peer_graph", graph.replay),
+                         ("nccl_eager", lambda: ep_fused_experts(ad, w1, w2, w1s, w2s, twd, tid, rank, world))):
+            for _ in range(3):
+                fn()
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(20):
+                fn()
+            e1.record()
+            dist.barrier()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 20], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times[name] = float(t) * 1e3
+        res["decode_64_tokens_per_rank_us"] = times
+        del graph
     finally:
         ex.close()
     return res
