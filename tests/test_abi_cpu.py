@@ -121,3 +121,42 @@ def test_scale_allocator_layouts():
     assert t.shape == (6, 5) and t.stride() == (1, 8)
     u = alloc((6, 640), "cpu", 128, True, True, True)
     assert u.dtype == torch.int32 and u.shape == (6, 2) and u.stride() == (1, 8)
+
+
+def test_host_validation_of_routing_and_exchange_entries(built_lib):
+    """The routing, masked-layout and peer-exchange entry points check their arguments before touching a device too."""
+    import ctypes
+    from sglang_b200._lib import lib
+    L = lib()
+    detail = lambda: L.sglb200_last_error_detail().decode()
+    assert L.sglb200_topk_softmax(None, 2, None, None, 4, 2048, 2, 0, None) == -1 and "num_experts" in detail()
+    assert L.sglb200_topk_softmax(None, 2, None, None, 4, 8, 9, 0, None) == -1 and "topk" in detail()
+    assert L.sglb200_topk_softmax(None, 2, None, None, 0, 8, 2, 0, None) == 0
+    assert L.sglb200_moe_fused_gate(None, None, 2, None, None, 4, 256, 7, 4, 8, 0, 2.5, 0, None) == -1
+    assert "num_expert_group" in detail()
+    assert L.sglb200_moe_fused_gate(None, None, 2, None, None, 4, 256, 8, 4, 8, 2, 0.0, 0, None) == -1
+    assert "routed_scaling_factor" in detail()
+    assert L.sglb200_moe_align_block_size(None, 1 << 25, 9, 16, None, None, None, None, 0, None) == -1
+    assert L.sglb200_moe_sum_reduce(None, None, 4, 2, 100, 0, 1.0, None) == -1 and "multiple of 8" in detail()
+    assert L.sglb200_moe_sum_reduce(None, None, 0, 2, 128, 0, 1.0, None) == 0
+    assert L.sglb200_fp8_blockwise_scaled_masked_grouped_mm(None, None, None, None, None, None, 4, 64, 128, 128, 128, 128,
+                                                            128 * 128, 128, 64, 1, 1, 1, 1, 1, 0, None) == -6
+    assert "masked_m" in detail()
+    assert L.sglb200_group_quant_fp8_batched(None, 2, None, None, 4, 16, 256, 128, 1e-10, -448.0, 448.0, 0, 0, None, 32, 2,
+                                             1, None) == -1 and "16-bit" in detail()
+    ptrs = (ctypes.c_void_p * 2)(None, None)
+    assert L.sglb200_fp8_blockwise_scaled_mm_push(None, None, None, None, 64, 512, 256, 256, 256, 2, 1, 2, 1, 0, ptrs, ptrs,
+                                                  0, 2, 1024, None, 0, None) == -7 and "receive slot" in detail()
+    assert L.sglb200_fp8_blockwise_scaled_mm_push(None, None, None, None, 64, 512, 256, 256, 256, 2, 1, 2, 1, 0, ptrs, ptrs,
+                                                  3, 2, 64 * 512, None, 0, None) == -1 and "rank" in detail()
+    assert L.sglb200_peer_reduce(None, None, None, 64, 500, 512, 0, 2, 64 * 512, 0, None) == -1
+    assert L.sglb200_ep_dispatch(None, None, 2, 1, None, None, 4, 200, 2, 4, ptrs, 0, 2, 16, 16, None) == -1
+    assert "multiple of 128" in detail()
+    assert L.sglb200_ep_dispatch(None, None, 2, 1, None, None, 40, 256, 2, 4, ptrs, 0, 2, 16, 16, None) == -6
+    assert L.sglb200_ep_combine_reduce(ptrs, 0, 9, None, None, 0, 4, 256, 2, 4, 16, 16, 0, None) == -1
+    assert L.sglb200_ep_buffer_bytes(16, 256, 2, 2, 16) > 16 * 256 and L.sglb200_ep_buffer_bytes(0, 256, 2, 2, 16) == 0
+    assert L.sglb200_peer_flag_bytes() > 0 and L.sglb200_peer_recv_bytes(1024) == 2 * 8 * 1024 * 2
+    assert L.sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(128, 7168, 8192) == 0
+    h = (ctypes.c_ubyte * 64)()
+    assert L.sglb200_peer_alloc(0, None, h) == -6 and L.sglb200_peer_open(None, None) == -6
+    assert L.sglb200_peer_close(None) == 0 and L.sglb200_peer_free(None) == 0
