@@ -292,22 +292,28 @@ def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk
     # the same layer with dispatch / combine over peer memory: no NCCL call, no host round trip
     ex = PeerEpExchange(capacity=M_total, hidden=H, topk=topk, m_max=m_loc)
     try:
-        for _ in range(2):
-            out_p = ep_fused_experts_peer(ex, a, w1, w2, w1s, w2s, tw, ti)
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0.record()
-        for _ in range(iters):
-            out_p = ep_fused_experts_peer(ex, a, w1, w2, w1s, w2s, tw, ti)
-        e1.record()
-        dist.barrier()
-        torch.cuda.synchronize()
-        ms_p = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
-        dist.all_reduce(ms_p, op=dist.ReduceOp.MAX)
+        def timed_peer(fuse):
+            for _ in range(2):
+                y = ep_fused_experts_peer(ex, a, w1, w2, w1s, w2s, tw, ti, fuse_quant=fuse)
+            dist.barrier()
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(iters):
+                y = ep_fused_experts_peer(ex, a, w1, w2, w1s, w2s, tw, ti, fuse_quant=fuse)
+            e1.record()
+            dist.barrier()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t, y
+
+        ms_u, _ = timed_peer(False)
+        ms_p, out_p = timed_peer(True)
         out_n = ep_fused_experts(a, w1, w2, w1s, w2s, tw, ti, rank, world)
         err = float((out_p.float() - out_n.float()).norm() / out_n.float().norm())
         res["peer"] = {"ms": float(ms_p), "tflops": flops / (float(ms_p) * 1e-3) / 1e12, "rel_l2_vs_nccl": err,
-                       "how": "dispatch / combine kernels over CUDA-IPC peer memory, device-side row counts"}
+                       "ms_with_separate_quant_launch": float(ms_u),
+                       "how": "quantise-and-dispatch / combine kernels over CUDA-IPC peer memory, device-side row counts"}
         # decode size: 64 tokens per rank.  The peer version is one CUDA graph (nothing on its path synchronises); the
         # NCCL version needs the received-row counts on the host and cannot be captured.
         md = 64

@@ -405,6 +405,11 @@ int sglb200_peer_completed(const void* flags_local, int64_t* completed);
  *   sglb200_ep_dispatch        every token of this rank (q [M, H] e4m3, scales s, topk_ids with GLOBAL expert ids, fp32
  *                              weights) is stored once into the buffer of every rank that owns one of its experts
  *                              (expert e lives on rank e / num_local_experts), in a row reserved there by a remote atomic.
+ *   sglb200_ep_dispatch_quant  the same with the activation quantiser in front: x [M, H] bf16 / f16 (row stride ldx
+ *                              elements) is read once, quantised per 128-wide group with the e4m3 limits and fp32 scales
+ *                              (floor eps), and the codes and scales go straight into the owners' receive rows; bit-
+ *                              identical to sglb200_per_token_group_quant_fp8 followed by sglb200_ep_dispatch.  Takes the
+ *                              place of sglb200_ep_dispatch in the sequence.
  *   sglb200_ep_receive         waits (bounded) until every rank has finished dispatching; rows that were not received
  *                              get ids -1; count_out (device int32, may be NULL) = rows received.  The caller then runs
  *                              the expert MLP on recv_q / recv_s / recv_ids / recv_w over `capacity` rows
@@ -415,14 +420,18 @@ int sglb200_peer_completed(const void* flags_local, int64_t* completed);
  * The order of the received rows depends on timing, the result does not.  A wait that runs out sets device status 21
  * (receive) or 22 (combine); a full receive buffer drops the row and sets 23 (sglb200_read_device_status).
  * Replaces: DeepEP Buffer.dispatch / Buffer.combine as called from
- *           python/sglang/srt/layers/moe/token_dispatcher/deepep.py:398-492 (third party, not in the tree), and the
- *           reorder kernels python/sglang/srt/layers/moe/ep_moe/kernels.py:435-720.
+ *           python/sglang/srt/layers/moe/token_dispatcher/deepep.py:398-492 (third party, not in the tree), the
+ *           reorder kernels python/sglang/srt/layers/moe/ep_moe/kernels.py:435-720, and for the _quant form the
+ *           quantisation the dispatcher runs before it sends (token_dispatcher/deepep.py:360-371).
  */
 int64_t sglb200_ep_buffer_bytes(int64_t capacity, int64_t H, int64_t topk, int64_t world, int64_t m_max);
 int sglb200_ep_buffer_offsets(int64_t capacity, int64_t H, int64_t topk, int64_t world, int64_t m_max, int64_t* offsets7);
 int sglb200_ep_dispatch(const void* q, const float* s, int64_t s_stride_m, int64_t s_stride_k, const int32_t* topk_ids,
                         const float* topk_weights, int64_t M, int64_t H, int64_t topk, int64_t num_local_experts,
                         void* const* peer_bases, int rank, int world, int64_t capacity, int64_t m_max, void* stream);
+int sglb200_ep_dispatch_quant(const void* x, int in_dtype, int64_t ldx, const int32_t* topk_ids, const float* topk_weights,
+                              int64_t M, int64_t H, int64_t topk, int64_t num_local_experts, void* const* peer_bases,
+                              int rank, int world, int64_t capacity, int64_t m_max, float eps, void* stream);
 int sglb200_ep_receive(void* const* peer_bases, int rank, int world, int64_t H, int64_t topk, int64_t num_local_experts,
                        int64_t capacity, int64_t m_max, int32_t* count_out, int64_t timeout_ns, void* stream);
 int sglb200_ep_combine_push(const void* partial, int dtype, void* const* peer_bases, int rank, int world, int64_t H,

@@ -51,6 +51,7 @@ SIGNATURES = {
     "sglb200_ep_buffer_bytes": [_L, _L, _L, _L, _L],
     "sglb200_ep_buffer_offsets": [_L, _L, _L, _L, _L, _P],
     "sglb200_ep_dispatch": [_P, _P, _L, _L, _P, _P, _L, _L, _L, _L, _P, _I, _I, _L, _L, _P],
+    "sglb200_ep_dispatch_quant": [_P, _I, _L, _P, _P, _L, _L, _L, _L, _P, _I, _I, _L, _L, _F, _P],
     "sglb200_ep_receive": [_P, _I, _I, _L, _L, _L, _L, _L, _P, _L, _P],
     "sglb200_ep_combine_push": [_P, _I, _P, _I, _I, _L, _L, _L, _L, _L, _P],
     "sglb200_ep_combine_reduce": [_P, _I, _I, _P, _P, _I, _L, _L, _L, _L, _L, _L, _L, _P],

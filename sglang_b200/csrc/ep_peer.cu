@@ -27,6 +27,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "quant_vec.cuh"
 
 namespace sglb {
 
@@ -171,6 +172,83 @@ ep_dispatch_kernel(const EpParams p, const uint8_t* __restrict__ q, const float*
         int32_t* dm = reinterpret_cast<int32_t*>(dst + p.lay.meta) + (int64_t)slot * 2;
         dm[0] = p.rank;
         dm[1] = t;
+      }
+    }
+  }
+  finish_and_flag(p, epoch, 0, kCtlDone);
+}
+
+// Dispatch with the activation quantiser in front of it: one warp per token reads the 16-bit row once, reserves the
+// token's rows on the owning ranks (lane r asks rank r, so the remote atomics overlap), and per 128-wide group takes
+// the maximum, derives the scale and stores the sixteen codes of each lane (16 bytes) straight into every owner's
+// receive row.  Group size 128, e4m3 limits, fp32 scales: codes and scales are bit-identical to
+// sglb200_per_token_group_quant_fp8 followed by ep_dispatch_kernel, without the [M, H] e4m3 round trip through HBM.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ep_dispatch_quant_kernel(const EpParams p, const T* __restrict__ x, int64_t ldx, const int32_t* __restrict__ topk_ids,
+                         const float* __restrict__ topk_w, int32_t M, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const uint32_t epoch = epoch_of(p), par = epoch & 1u;
+  const int G = p.H / 128;
+  const int sub = lane & 7, gsel = lane >> 3;
+  const float inv_max = __frcp_rn(448.0f);
+  for (int32_t t = blockIdx.x * 8 + warp; t < M; t += gridDim.x * 8) {
+    int32_t id = -1;
+    float w = 0.f;
+    if (lane < p.topk) {
+      id = __ldg(topk_ids + (int64_t)t * p.topk + lane);
+      w = __ldg(topk_w + (int64_t)t * p.topk + lane);
+    }
+    const int owner = (id >= 0 && id / p.e_local < p.world) ? id / p.e_local : -1;
+    uint32_t mask = 0;
+    for (int r = 0; r < p.world; ++r)
+      if (__any_sync(0xffffffffu, owner == r)) mask |= 1u << r;
+    uint32_t my_slot = 0xffffffffu;
+    if (lane < p.world && ((mask >> lane) & 1u)) {
+      my_slot = atomicAdd_system(ctl_of(p, lane) + kCtlCount + par, 1u);
+      if (my_slot >= (uint32_t)p.capacity) {
+        atomicCAS(&g_ep_status, 0, 23);  // receive buffer of that rank is full: the row is dropped
+        my_slot = 0xffffffffu;
+      }
+    }
+    uint32_t slot[kMaxRanks];  // 0xffffffff: rank r gets no copy of this token
+#pragma unroll
+    for (int r = 0; r < kMaxRanks; ++r) {
+      slot[r] = __shfl_sync(0xffffffffu, my_slot, r);
+      if (slot[r] == 0xffffffffu) continue;
+      char* dst = p.peer[r];
+      if (lane < p.topk) {
+        reinterpret_cast<int32_t*>(dst + p.lay.ids)[(int64_t)slot[r] * p.topk + lane] =
+            owner == r ? id - r * p.e_local : -1;
+        reinterpret_cast<float*>(dst + p.lay.w)[(int64_t)slot[r] * p.topk + lane] = w;
+      }
+      if (lane == 0) {
+        int32_t* dm = reinterpret_cast<int32_t*>(dst + p.lay.meta) + (int64_t)slot[r] * 2;
+        dm[0] = p.rank;
+        dm[1] = t;
+      }
+    }
+    const uint4* row = reinterpret_cast<const uint4*>(x + (int64_t)t * ldx);
+#pragma unroll 2
+    for (int g0 = 0; g0 < G; g0 += 4) {
+      const int g = g0 + gsel;
+      const bool live = g < G;
+      uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
+      if (live) {
+        v0 = __ldcs(row + g * 16 + sub * 2);
+        v1 = __ldcs(row + g * 16 + sub * 2 + 1);
+      }
+      float amax = fmaxf(eps, fmaxf(Elem<T>::vec_absmax(v0), Elem<T>::vec_absmax(v1)));
+#pragma unroll
+      for (int m = 4; m >= 1; m >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, m));
+      const float s = group_scale_fast(amax, 448.0f, inv_max, false);
+      const uint4 codes = encode16_e4m3<T>(v0, v1, s);
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (slot[r] == 0xffffffffu || !live) continue;
+        char* dst = p.peer[r];
+        reinterpret_cast<uint4*>(dst + p.lay.q + (int64_t)slot[r] * p.H)[g * 8 + sub] = codes;
+        if (sub == 0) reinterpret_cast<float*>(dst + p.lay.s)[(int64_t)slot[r] * G + g] = s;
       }
     }
   }
@@ -329,6 +407,30 @@ extern "C" int sglb200_ep_dispatch(const void* q, const float* s, int64_t s_stri
   ep_dispatch_kernel<<<grid_for(M), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       p, static_cast<const uint8_t*>(q), s, s_stride_m, s_stride_k, topk_ids, topk_weights, (int32_t)M);
   SGLB_CHECK_LAUNCH("ep_dispatch_kernel");
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_ep_dispatch_quant(const void* x, int in_dtype, int64_t ldx, const int32_t* topk_ids,
+                                         const float* topk_weights, int64_t M, int64_t H, int64_t topk,
+                                         int64_t num_local_experts, void* const* peer_bases, int rank, int world,
+                                         int64_t capacity, int64_t m_max, float eps, void* stream) {
+  SGLB_REQUIRE(in_dtype == SGLB200_BF16 || in_dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "in_dtype=%d: bf16 or f16", in_dtype);
+  SGLB_REQUIRE(ldx >= H && ldx % 8 == 0, SGLB200_ERR_SHAPE, "ldx=%lld must be >= H and a multiple of 8", (long long)ldx);
+  SGLB_REQUIRE(eps >= 0.f, SGLB200_ERR_SHAPE, "eps must be >= 0");
+  EpParams p;
+  if (int rc = fill_params(&p, peer_bases, rank, world, H, topk, num_local_experts, capacity, m_max, 0)) return rc;
+  SGLB_REQUIRE(M >= 0 && M <= m_max, SGLB200_ERR_SHAPE, "M=%lld must be in 0..m_max=%lld", (long long)M, (long long)m_max);
+  SGLB_REQUIRE(M == 0 || (x && topk_ids && topk_weights), SGLB200_ERR_NULL, "x, topk_ids and topk_weights must be given");
+  SGLB_REQUIRE(M == 0 || aligned(x, 16), SGLB200_ERR_ALIGN, "x must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(M);
+  if (in_dtype == SGLB200_BF16)
+    ep_dispatch_quant_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p, static_cast<const __nv_bfloat16*>(x), ldx, topk_ids,
+                                                                    topk_weights, (int32_t)M, eps);
+  else
+    ep_dispatch_quant_kernel<__half><<<grid, 256, 0, st>>>(p, static_cast<const __half*>(x), ldx, topk_ids, topk_weights,
+                                                             (int32_t)M, eps);
+  SGLB_CHECK_LAUNCH("ep_dispatch_quant_kernel");
   return SGLB200_OK;
 }
 

@@ -17,6 +17,7 @@
 
 #include "common.cuh"
 #include "quant_math.cuh"
+#include "quant_vec.cuh"
 
 namespace sglb {
 namespace {
@@ -41,80 +42,6 @@ struct QuantParams {
   uint32_t rows_per_batch, bdiv_mul, bdiv_shift;
   int64_t s_stride_batch;
 };
-
-// ---- element traits: E = elements per 16-byte vector -----------------------------------------
-template <typename T>
-struct Elem;
-
-template <>
-struct Elem<__nv_bfloat16> {
-  static constexpr int E = 8;
-  // |.| maximum over the 8 packed values of a vector, as fp32
-  static __device__ __forceinline__ float vec_absmax(const uint4& u) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-    __nv_bfloat162 m = __hmax2(__habs2(h[0]), __habs2(h[1]));
-    m = __hmax2(m, __hmax2(__habs2(h[2]), __habs2(h[3])));
-    const float2 f = __bfloat1622float2(m);
-    return fmaxf(f.x, f.y);
-  }
-  static __device__ __forceinline__ float2 pair(uint32_t w) {  // two bf16 -> two fp32 (exact)
-    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-  }
-  static __device__ __forceinline__ uint32_t sign_bytes(uint32_t w0, uint32_t w1) {  // bytes 1,3 of each word
-    return __byte_perm(w0, w1, 0x7531);
-  }
-  static __device__ __forceinline__ float round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-};
-
-template <>
-struct Elem<__half> {
-  static constexpr int E = 8;
-  static __device__ __forceinline__ float vec_absmax(const uint4& u) {
-    const __half2* h = reinterpret_cast<const __half2*>(&u);
-    __half2 m = __hmax2(__habs2(h[0]), __habs2(h[1]));
-    m = __hmax2(m, __hmax2(__habs2(h[2]), __habs2(h[3])));
-    const float2 f = __half22float2(m);
-    return fmaxf(f.x, f.y);
-  }
-  static __device__ __forceinline__ float2 pair(uint32_t w) {
-    return __half22float2(*reinterpret_cast<const __half2*>(&w));
-  }
-  static __device__ __forceinline__ uint32_t sign_bytes(uint32_t w0, uint32_t w1) {
-    return __byte_perm(w0, w1, 0x7531);
-  }
-  static __device__ __forceinline__ float round(float x) { return __half2float(__float2half_rn(x)); }
-  static __device__ __forceinline__ uint32_t pack(float a, float b) {
-    __half2 h = __floats2half2_rn(a, b);
-    return *reinterpret_cast<uint32_t*>(&h);
-  }
-};
-
-template <>
-struct Elem<float> {
-  static constexpr int E = 4;
-  static __device__ __forceinline__ float vec_absmax(const uint4& u) {
-    return fmaxf(fmaxf(fabsf(__uint_as_float(u.x)), fabsf(__uint_as_float(u.y))),
-                 fmaxf(fabsf(__uint_as_float(u.z)), fabsf(__uint_as_float(u.w))));
-  }
-  static __device__ __forceinline__ float round(float x) { return x; }
-};
-
-__device__ __forceinline__ float silu_f32(float x) { return __fdiv_rn(x, 1.0f + expf(-x)); }
-
-// Two quotients x / s with the shared reciprocal r = RN(1/s): packed Markstein step.
-__device__ __forceinline__ float2 quotient2(float2 x, float2 rr, float2 neg_ss) {
-  const float2 q0 = __fmul2_rn(x, rr);
-  const float2 rem = __ffma2_rn(q0, neg_ss, x);
-  return __ffma2_rn(rem, rr, q0);
-}
-
-__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
-  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
-}
 
 // 16-bit input types.  LPG = lanes per group = group_size / 16; each lane owns vectors `lane` and
 // `lane + LPG` of its group (group_size 16: one lane, both vectors).

@@ -119,6 +119,16 @@ def ep_dispatch(arr, rank, world, capacity, m_max, a_q, a_s, topk_ids, topk_weig
                                     capacity, m_max, _stream(a_q.device)), "ep_dispatch")
 
 
+def ep_dispatch_quant(arr, rank, world, capacity, m_max, x, topk_ids, topk_weights, e_local, eps=1e-10) -> None:
+    """Quantise ``x [M, H]`` (bf16 / f16, unit column stride) per 128-wide group and dispatch it, in one kernel."""
+    M, H = x.shape
+    assert x.stride(1) == 1 or M <= 1
+    check(lib().sglb200_ep_dispatch_quant(x.data_ptr(), dtype_code(x.dtype), x.stride(0) if M > 1 else H,
+                                          topk_ids.data_ptr(), topk_weights.data_ptr(), M, H, topk_ids.size(1),
+                                          e_local, arr, rank, world, capacity, m_max, eps, _stream(x.device)),
+          "ep_dispatch_quant")
+
+
 def ep_receive(arr, rank, world, H, topk, e_local, capacity, m_max, count, timeout_ns=0) -> None:
     check(lib().sglb200_ep_receive(arr, rank, world, H, topk, e_local, capacity, m_max,
                                    count.data_ptr() if count is not None else None, timeout_ns,
@@ -139,11 +149,12 @@ def ep_combine_reduce(arr, rank, world, topk_ids, out, e_local, capacity, m_max,
 
 def ep_fused_experts_peer(ex: PeerEpExchange, hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
                           w1_scale: torch.Tensor, w2_scale: torch.Tensor, topk_weights: torch.Tensor,
-                          topk_ids: torch.Tensor) -> torch.Tensor:
+                          topk_ids: torch.Tensor, fuse_quant: bool = True) -> torch.Tensor:
     """The expert-parallel MoE layer for the tokens of THIS rank (same contract as
     :func:`sglang_b200.distributed.ep_fused_experts`): ``w1 / w2`` hold this rank's ``E / ep`` experts, ``topk_ids`` are
-    global expert ids.  Five launches around the local expert MLP; nothing synchronises the stream and the exchange counter lives on the
-    device, so the whole layer can be captured in a CUDA graph."""
+    global expert ids.  Four launches around the local expert MLP (the quantiser runs inside the dispatch kernel;
+    ``fuse_quant=False`` keeps it as a launch of its own, with identical results); nothing synchronises the stream and
+    the exchange counter lives on the device, so the whole layer can be captured in a CUDA graph."""
     from ..layers.moe import fused_experts_block_fp8_prequant
     from ..layers.quantization import sglang_per_token_group_quant_fp8
     M, H = hidden_states.shape
@@ -154,12 +165,15 @@ def ep_fused_experts_peer(ex: PeerEpExchange, hidden_states: torch.Tensor, w1: t
     out = torch.empty(M, H, dtype=hidden_states.dtype, device=hidden_states.device)
     args = (ex._arr, ex.rank, ex.world)
     with torch.cuda.device(hidden_states.device):
-        if M > 0:
-            a_q, a_s = sglang_per_token_group_quant_fp8(hidden_states.contiguous(), 128)
+        if fuse_quant:
+            ep_dispatch_quant(*args, ex.capacity, ex.m_max, hidden_states.contiguous(), ids, w, e_local)
         else:
-            a_q = torch.empty(0, H, dtype=torch.float8_e4m3fn, device=hidden_states.device)
-            a_s = torch.empty(0, H // 128, device=hidden_states.device)
-        ep_dispatch(*args, ex.capacity, ex.m_max, a_q, a_s, ids, w, e_local)
+            if M > 0:
+                a_q, a_s = sglang_per_token_group_quant_fp8(hidden_states.contiguous(), 128)
+            else:
+                a_q = torch.empty(0, H, dtype=torch.float8_e4m3fn, device=hidden_states.device)
+                a_s = torch.empty(0, H // 128, device=hidden_states.device)
+            ep_dispatch(*args, ex.capacity, ex.m_max, a_q, a_s, ids, w, e_local)
         ep_receive(*args, H, ex.topk, e_local, ex.capacity, ex.m_max, ex.count)
         partial = fused_experts_block_fp8_prequant(ex.recv_q, ex.recv_s, hidden_states.dtype, w1, w2, w1_scale, w2_scale,
                                                    ex.recv_w, ex.recv_ids)

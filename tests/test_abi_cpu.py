@@ -153,6 +153,9 @@ def test_host_validation_of_routing_and_exchange_entries(built_lib):
     assert L.sglb200_ep_dispatch(None, None, 2, 1, None, None, 4, 200, 2, 4, ptrs, 0, 2, 16, 16, None) == -1
     assert "multiple of 128" in detail()
     assert L.sglb200_ep_dispatch(None, None, 2, 1, None, None, 40, 256, 2, 4, ptrs, 0, 2, 16, 16, None) == -6
+    assert L.sglb200_ep_dispatch_quant(None, 2, 256, None, None, 4, 256, 2, 4, ptrs, 0, 2, 16, 16, 1e-10, None) == -5
+    assert L.sglb200_ep_dispatch_quant(None, 0, 100, None, None, 4, 256, 2, 4, ptrs, 0, 2, 16, 16, 1e-10, None) == -1
+    assert "ldx" in detail()
     assert L.sglb200_ep_combine_reduce(ptrs, 0, 9, None, None, 0, 4, 256, 2, 4, 16, 16, 0, None) == -1
     assert L.sglb200_ep_buffer_bytes(16, 256, 2, 2, 16) > 16 * 256 and L.sglb200_ep_buffer_bytes(0, 256, 2, 2, 16) == 0
     assert L.sglb200_peer_flag_bytes() > 0 and L.sglb200_peer_recv_bytes(1024) == 2 * 8 * 1024 * 2
