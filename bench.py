@@ -402,14 +402,14 @@ def fused_allreduce_section(torch, dist, dev, world, rank, layers, iters=30):
     from sglang_b200.distributed import PeerExchange, fused_row_parallel_linear
     from sglang_b200.layers.quantization import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
     rows = [L for L in layers if L["mode"] == "row"]
-    ex = PeerExchange(slot_elems=256 * max(L["N"] for L in rows))
+    ex = PeerExchange(slot_elems=1024 * max(L["N"] for L in rows))
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     out = {"workload": "row-parallel o_proj / down_proj at decode batch sizes: quant + GEMM + all-reduce as one CUDA "
                        "graph, device us per replay (max over ranks, median), L2 flushed before every replay",
            "cases": []}
     try:
         for L in rows:
-            for m in (16, 64, 128, 256):
+            for m in (16, 64, 128, 256, 512, 1024):
                 x = L["x"][:m].contiguous()
                 w, ws = L["layer"].weight, L["layer"].weight_scale_inv
 
@@ -420,10 +420,16 @@ def fused_allreduce_section(torch, dist, dev, world, rank, layers, iters=30):
                     return y
 
                 def fused_call():  # measured at every size, also where PeerExchange.fits would choose NCCL
-                    return fused_row_parallel_linear(ex, x, w, ws)
+                    return fused_row_parallel_linear(ex, x, w, ws, two_shot=False)
 
+                def two_shot_call():
+                    return fused_row_parallel_linear(ex, x, w, ws, two_shot=True)
+
+                variants = [("nccl", nccl_call), ("fused", fused_call)]
+                if m > 64 and -(-m // 128) * -(-L["N"] // 128) >= world:
+                    variants.append(("two_shot", two_shot_call))
                 res = {}
-                for name, fn in (("nccl", nccl_call), ("fused", fused_call)):
+                for name, fn in variants:
                     # one call captured in a CUDA graph (how a decode step is launched), replayed with the L2 flushed
                     # before every replay; device time of the replay alone
                     side = torch.cuda.Stream()
@@ -453,9 +459,17 @@ def fused_allreduce_section(torch, dist, dev, world, rank, layers, iters=30):
                 y_f, y_n = fused_call(), nccl_call()
                 torch.cuda.synchronize()
                 err = float((y_f.float() - y_n.float()).norm() / y_n.float().norm())
-                out["cases"].append({"layer": L["name"], "M": m, "N": L["N"], "K_local": L["k_loc"],
-                                     "nccl_us": res["nccl"], "fused_us": res["fused"],
-                                     "speedup": res["nccl"] / res["fused"], "rel_l2_vs_nccl": err})
+                case = {"layer": L["name"], "M": m, "N": L["N"], "K_local": L["k_loc"],
+                        "nccl_us": res["nccl"], "fused_us": res["fused"],
+                        "speedup": res["nccl"] / res["fused"], "rel_l2_vs_nccl": err,
+                        "library_choice": "one_shot" if ex.fits(m, L["N"]) else
+                                          "two_shot" if ex.fits_two_shot(m, L["N"]) else "nccl"}
+                if "two_shot" in res:
+                    y_2 = two_shot_call()
+                    torch.cuda.synchronize()
+                    case.update(two_shot_us=res["two_shot"], two_shot_speedup=res["nccl"] / res["two_shot"],
+                                two_shot_equals_one_shot=bool(torch.equal(y_2, y_f)))
+                out["cases"].append(case)
     finally:
         ex.close()
     return out

@@ -384,6 +384,32 @@ int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b, const flo
                                          void* const* peer_recv, void* const* peer_flags, int rank, int world,
                                          int64_t slot_elems, void* workspace, int64_t workspace_bytes, void* stream);
 int64_t sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(int64_t M, int64_t N, int64_t K);
+/*
+ * The same exchange in two shots, for outputs too large to send whole to every rank (three launches per rank, same
+ * buffers, same rules, freely mixed with the one-shot form from one exchange to the next):
+ *   1. sglb200_fp8_blockwise_scaled_mm_push_scatter: the 128-row GEMM whose epilogue stores output tile t only into the
+ *      receive buffer of rank t % world (tiles numbered row-major over the 128 x 128 grid) and flags it there.
+ *   2. sglb200_peer_reduce_scatter: per owned tile waits (bounded) for the `world` partial tiles, adds them in fp32 in
+ *      ascending rank order (the bits the one-shot reduce produces), writes the tile to this rank's `out` and stores it
+ *      into every other rank's slot [epoch & 1][this rank] at the tile's position, then flags it there.
+ *   3. sglb200_peer_gather: waits (bounded) for the tiles this rank does not own and copies them into `out`; its last
+ *      block advances the epoch.
+ * Bytes leaving a rank per exchange: 2 (world - 1) / world x the output instead of (world - 1) x the output.  Needs at
+ * least `world` output tiles (SGLB200_ERR_SHAPE otherwise); `out` is the same [M, N] tensor in 2 and 3.  A wait that
+ * runs out in either kernel sets device status 5 and keeps the epoch, as above.
+ * Replaces: the two-stage path of the reference's custom all-reduce (reduce-scatter, then all-gather:
+ *           sgl-kernel/csrc/allreduce/custom_all_reduce.cuh:225-266, cross_device_reduce_2stage), fused with the GEMM before it.
+ */
+int sglb200_fp8_blockwise_scaled_mm_push_scatter(const void* a, const void* b, const float* sa, const float* sb, int64_t M,
+                                                 int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t sa_stride_m,
+                                                 int64_t sa_stride_k, int64_t sb_stride_n, int64_t sb_stride_k,
+                                                 int out_dtype, void* const* peer_recv, void* const* peer_flags, int rank,
+                                                 int world, int64_t slot_elems, void* stream);
+int sglb200_peer_reduce_scatter(void* const* peer_recv, void* const* peer_flags, void* out, int64_t M, int64_t N,
+                                int64_t ldc, int out_dtype, int rank, int world, int64_t slot_elems, int64_t timeout_ns,
+                                void* stream);
+int sglb200_peer_gather(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N, int64_t ldc,
+                        int out_dtype, int rank, int world, int64_t slot_elems, int64_t timeout_ns, void* stream);
 int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N, int64_t ldc,
                         int out_dtype, int world, int64_t slot_elems, int64_t timeout_ns, void* stream);
 int64_t sglb200_peer_flag_bytes(void);

@@ -47,6 +47,10 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_scaled_mm_push": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _P, _I, _I,
                                              _L, _P, _L, _P],
     "sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes": [_L, _L, _L],
+    "sglb200_fp8_blockwise_scaled_mm_push_scatter": [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _P, _I,
+                                                     _I, _L, _P],
+    "sglb200_peer_reduce_scatter": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _L, _L, _P],
+    "sglb200_peer_gather": [_P, _P, _P, _L, _L, _L, _I, _I, _I, _L, _L, _P],
     "sglb200_peer_reduce": [_P, _P, _P, _L, _L, _L, _I, _I, _L, _L, _P],
     "sglb200_ep_buffer_bytes": [_L, _L, _L, _L, _L],
     "sglb200_ep_buffer_offsets": [_L, _L, _L, _L, _L, _P],

@@ -66,6 +66,7 @@ struct PushParams {
   int32_t world, rank;
   const uint32_t* ctl;  // this rank's control words
   int64_t slot_elems;
+  int32_t scatter;  // 0: every tile goes to every rank (one-shot); 1: tile t goes to rank t % world only (two-shot)
 };
 
 // Push epilogue staging: every promotion warp turns "one output row per lane" into "rows of contiguous bytes per store"
@@ -461,6 +462,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       if constexpr (PUSH) {
         const int32_t n_first = tl.n0 + col0;
         const int32_t tile_id = (tl.row0 / BM) * p.n_tiles + tl.n0 / BN;
+        const int owner = tile_id % p.push.world;
         const int wi = warp - 2 * kIssuers;
         uint32_t* stg = reinterpret_cast<uint32_t*>(smem + kStagingOffset) + wi * 32 * kStageWords;
         const int32_t row_base = tl.row0 + q * 32;  // the warp's rows are row_base + 0..31
@@ -477,10 +479,14 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const int32_t grow = row_base + r, c = n_first + 32 * h + 2 * w;  // 8 columns from c (N % 8 == 0)
             if (grow < tl.row_end && c < p.N) {
               const int64_t off = (slot + (int64_t)grow * p.N + c) * 2;
-              for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
-                int pr = p.push.rank + 1 + i;
-                if (pr >= p.push.world) pr -= p.push.world;
-                *reinterpret_cast<uint4*>(static_cast<char*>(p.push.dst[pr]) + off) = val;
+              if (p.push.scatter) {
+                *reinterpret_cast<uint4*>(static_cast<char*>(p.push.dst[owner]) + off) = val;
+              } else {
+                for (int i = 0; i < p.push.world; ++i) {  // peers first, this rank last
+                  int pr = p.push.rank + 1 + i;
+                  if (pr >= p.push.world) pr -= p.push.world;
+                  *reinterpret_cast<uint4*>(static_cast<char*>(p.push.dst[pr]) + off) = val;
+                }
               }
             }
           });
@@ -488,7 +494,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         // The warp's 32 rows x 64 columns are on their way.  One flag word per (tile, warp) and rank: the warp barrier
         // orders every lane's stores before the release store of the flag (release is cumulative), at system scope.
         __syncwarp();
-        if (lane < p.push.world) {
+        if (p.push.scatter ? lane == owner : lane < p.push.world) {
           uint32_t* f = p.push.flag[lane] +
                         (((int64_t)set * kMaxPeers + p.push.rank) * kPushMaxTiles + tile_id) * kEpiWarps + wi;
           ptx::st_release_sys_u32(f, push_epoch);
@@ -626,6 +632,147 @@ peer_reduce_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT*
   }
   // every block takes a ticket; the last one closes the exchange: the epoch advances only if no block gave up
   // (the epoch was read, and used, before this block's ticket; the counters are only ever touched by atomics)
+  if (threadIdx.x == 0) {
+    if (!s_ok) atomicExch(&ctl[2], 1u);
+    if (atomicAdd(&ctl[1], 1u) == gridDim.x - 1) {
+      const uint32_t failed = atomicExch(&ctl[2], 0u);
+      ctl[1] = 0;
+      if (!failed) *reinterpret_cast<volatile uint32_t*>(ctl) = epoch;
+    }
+  }
+}
+
+// ---- two-shot exchange (reduce-scatter + all-gather) for outputs too large to send whole to every rank -------------
+// The push epilogue in scatter mode sends tile t only to rank t % world.  That rank adds the `world` partial tiles
+// (fp32, ascending rank: the same bits as the one-shot reduce), writes the result to its own output and stores it into
+// every other rank's slot [set][this rank] at the tile's position, which scatter-mode pushes never touch on a rank that
+// does not own the tile; the flag words [set][this rank][tile][quarter] there, equally unused, announce it.  The gather
+// kernel of every rank then waits for the tiles it does not own and copies them out of those slots.  Bytes leaving a
+// rank per exchange: 2 (world - 1) / world of the output instead of (world - 1) times the output.
+
+// spin (bounded) until *f has reached `epoch`; on a time-out clears *ok and records status 5
+__device__ __forceinline__ void wait_flag_word(const uint32_t* f, uint32_t epoch, uint64_t limit_ns, int* ok) {
+  uint64_t t0 = 0;
+  uint32_t polls = 0;
+  while ((int32_t)(ptx::ld_acquire_sys_u32(f) - epoch) < 0) {
+    if ((++polls & 255u) == 0) {
+      const uint64_t now = ptx::global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if ((int64_t)(now - t0) > (int64_t)limit_ns) {
+        *ok = 0;
+        atomicCAS(&g_device_status, 0, 5);
+        break;
+      }
+    }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+peer_reduce_scatter_kernel(const PushParams push, OutT* __restrict__ out, int32_t M, int32_t N, int64_t ldc,
+                           int32_t n_tiles, int32_t total_items, uint64_t limit_ns) {
+  __shared__ int s_ok;
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<const volatile uint32_t*>(push.ctl) + 1u;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch, set = epoch & 1u;
+  const int32_t world = push.world, rank = push.rank;
+  const OutT* recv = static_cast<const OutT*>(push.dst[rank]);
+  const uint32_t* flags = push.flag[rank];
+  // owned work item j = (owned tile j / 4, quarter j % 4); the owned tiles are rank, rank + world, ...
+  for (int32_t item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const int32_t t = (item >> 2) * world + rank, q = item & 3;
+    const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
+    const int32_t row0 = mt * BM + q * 32;
+    if (row0 >= M) continue;  // uniform
+    if ((int)threadIdx.x < world * 2) {
+      const int src = threadIdx.x >> 1, w = q + 4 * (threadIdx.x & 1);
+      wait_flag_word(flags + (((int64_t)set * kMaxPeers + src) * kPushMaxTiles + t) * kEpiWarps + w, epoch, limit_ns, &s_ok);
+    }
+    __syncthreads();
+    if (!s_ok) break;  // uniform: s_ok is only ever cleared before the barrier above
+    const int32_t rows = min(32, M - row0), vecs = min(BN, N - nt * BN) / 8;
+    const int64_t mine = ((int64_t)set * kMaxPeers + rank) * push.slot_elems;
+    for (int32_t i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
+      const int32_t r = i / vecs, c = (i - r * vecs) * 8;
+      const int64_t off = (int64_t)(row0 + r) * N + nt * BN + c;
+      uint4 u[kMaxPeers];
+#pragma unroll
+      for (int src = 0; src < kMaxPeers; ++src) {
+        if (src < world)
+          u[src] = __ldcv(reinterpret_cast<const uint4*>(recv + ((int64_t)set * kMaxPeers + src) * push.slot_elems + off));
+      }
+      float a[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] = 0.f;
+#pragma unroll
+      for (int src = 0; src < kMaxPeers; ++src) {
+        if (src < world) {
+          const OutT* h = reinterpret_cast<const OutT*>(&u[src]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) a[j] += static_cast<float>(h[j]);
+        }
+      }
+      uint4 o;
+      o.x = pack2<OutT>(a[0], a[1]);
+      o.y = pack2<OutT>(a[2], a[3]);
+      o.z = pack2<OutT>(a[4], a[5]);
+      o.w = pack2<OutT>(a[6], a[7]);
+      for (int k = 1; k < world; ++k) {
+        int pr = rank + k;
+        if (pr >= world) pr -= world;
+        *reinterpret_cast<uint4*>(static_cast<OutT*>(push.dst[pr]) + mine + off) = o;
+      }
+      *reinterpret_cast<uint4*>(out + (int64_t)(row0 + r) * ldc + nt * BN + c) = o;
+    }
+    // the block barrier orders every thread's stores before the release stores of the flags (release is cumulative)
+    __syncthreads();
+    if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
+      uint32_t* f = push.flag[threadIdx.x] + (((int64_t)set * kMaxPeers + rank) * kPushMaxTiles + t) * kEpiWarps + q;
+      ptx::st_release_sys_u32(f, epoch);
+    }
+  }
+  if (threadIdx.x == 0 && !s_ok) atomicExch(const_cast<uint32_t*>(push.ctl) + 2, 1u);  // the gather kernel will not advance
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(256)
+peer_gather_kernel(const OutT* recv, const uint32_t* flags, uint32_t* ctl, OutT* __restrict__ out, int32_t M, int32_t N,
+                   int64_t ldc, int32_t n_tiles, int32_t total_items, int32_t world, int32_t rank, int64_t slot_elems,
+                   uint64_t limit_ns) {
+  __shared__ int s_ok;
+  __shared__ uint32_t s_epoch;
+  if (threadIdx.x == 0) {
+    s_epoch = *reinterpret_cast<volatile uint32_t*>(ctl) + 1u;
+    s_ok = 1;
+  }
+  __syncthreads();
+  const uint32_t epoch = s_epoch, set = epoch & 1u;
+  for (int32_t item = blockIdx.x; item < total_items; item += gridDim.x) {
+    const int32_t t = item >> 2, q = item & 3;
+    const int32_t owner = t % world;
+    if (owner == rank) continue;  // written by this rank's reduce-scatter kernel
+    const int32_t mt = t / n_tiles, nt = t - mt * n_tiles;
+    const int32_t row0 = mt * BM + q * 32;
+    if (row0 >= M) continue;  // uniform
+    if (threadIdx.x == 0)
+      wait_flag_word(flags + (((int64_t)set * kMaxPeers + owner) * kPushMaxTiles + t) * kEpiWarps + q, epoch, limit_ns, &s_ok);
+    __syncthreads();
+    if (!s_ok) break;
+    const int32_t rows = min(32, M - row0), vecs = min(BN, N - nt * BN) / 8;
+    const OutT* src = recv + ((int64_t)set * kMaxPeers + owner) * slot_elems;
+    for (int32_t i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
+      const int32_t r = i / vecs, c = (i - r * vecs) * 8;
+      const uint4 v = __ldcv(reinterpret_cast<const uint4*>(src + (int64_t)(row0 + r) * N + nt * BN + c));
+      *reinterpret_cast<uint4*>(out + (int64_t)(row0 + r) * ldc + nt * BN + c) = v;
+    }
+    __syncthreads();
+  }
+  // the last block closes the exchange: the epoch advances only if no block of either kernel gave up
   if (threadIdx.x == 0) {
     if (!s_ok) atomicExch(&ctl[2], 1u);
     if (atomicAdd(&ctl[1], 1u) == gridDim.x - 1) {
@@ -1072,6 +1219,35 @@ int check_push_args(int64_t M, int64_t N, int world, int rank, int64_t slot_elem
 }  // namespace
 }  // namespace sglb
 
+namespace sglb {
+namespace {
+int fill_push(PushParams* push, void* const* peer_recv, void* const* peer_flags, int rank, int world, int64_t slot_elems,
+              int scatter) {
+  SGLB_REQUIRE(peer_recv && peer_flags, SGLB200_ERR_NULL, "peer_recv / peer_flags must not be NULL");
+  for (int i = 0; i < kMaxPeers; ++i) {
+    push->dst[i] = i < world ? peer_recv[i] : nullptr;
+    push->flag[i] = i < world ? static_cast<uint32_t*>(peer_flags[i]) : nullptr;
+    SGLB_REQUIRE(i >= world || (push->dst[i] && push->flag[i] && aligned(push->dst[i], 16) && aligned(push->flag[i], 4)),
+                 SGLB200_ERR_NULL, "peer %d: receive buffer / flags missing or misaligned", i);
+  }
+  push->world = world;
+  push->rank = rank;
+  push->ctl = push->flag[rank] + kFlagWords;
+  push->slot_elems = slot_elems;
+  push->scatter = scatter;
+  return SGLB200_OK;
+}
+
+// the two-shot exchange needs every rank to own a tile (the ranks keep in step through the tiles they exchange)
+int check_scatter_args(int64_t M, int64_t N, int world) {
+  SGLB_REQUIRE(((M + BM - 1) / BM) * ((N + BN - 1) / BN) >= world, SGLB200_ERR_SHAPE,
+               "M=%lld N=%lld: fewer output tiles than ranks (%d); use the one-shot exchange", (long long)M, (long long)N,
+               world);
+  return SGLB200_OK;
+}
+}  // namespace
+}  // namespace sglb
+
 extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b, const float* sa, const float* sb,
                                                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                                                     int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
@@ -1081,22 +1257,102 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_push(const void* a, const void* b
                                                     void* stream) {
   using namespace sglb;
   if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
-  SGLB_REQUIRE(peer_recv && peer_flags, SGLB200_ERR_NULL, "peer_recv / peer_flags must not be NULL");
   PushParams push;
-  for (int i = 0; i < kMaxPeers; ++i) {
-    push.dst[i] = i < world ? peer_recv[i] : nullptr;
-    push.flag[i] = i < world ? static_cast<uint32_t*>(peer_flags[i]) : nullptr;
-    SGLB_REQUIRE(i >= world || (push.dst[i] && push.flag[i] && aligned(push.dst[i], 16) && aligned(push.flag[i], 4)),
-                 SGLB200_ERR_NULL, "peer %d: receive buffer / flags missing or misaligned", i);
-  }
-  push.world = world;
-  push.rank = rank;
-  push.ctl = push.flag[rank] + kFlagWords;
-  push.slot_elems = slot_elems;
+  if (int rc = fill_push(&push, peer_recv, peer_flags, rank, world, slot_elems, 0)) return rc;
   SGLB_REQUIRE(workspace == nullptr || aligned(workspace, 16), SGLB200_ERR_ALIGN, "workspace must be 16-byte aligned");
   return gemm_common(a, b, sa, sb, push.dst[rank], nullptr, nullptr, M, 1, N, K, lda, ldb, 0, N, sa_stride_m, sa_stride_k,
                      0, sb_stride_n, sb_stride_k, out_dtype, stream, static_cast<float*>(workspace),
                      workspace ? workspace_bytes / (int64_t)sizeof(float) : 0, &push);
+}
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm_push_scatter(const void* a, const void* b, const float* sa, const float* sb,
+                                                            int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                                            int64_t sa_stride_m, int64_t sa_stride_k,
+                                                            int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
+                                                            void* const* peer_recv, void* const* peer_flags, int rank,
+                                                            int world, int64_t slot_elems, void* stream) {
+  using namespace sglb;
+  if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
+  if (int rc = check_scatter_args(M, N, world)) return rc;
+  PushParams push;
+  if (int rc = fill_push(&push, peer_recv, peer_flags, rank, world, slot_elems, 1)) return rc;
+  return gemm_common(a, b, sa, sb, push.dst[rank], nullptr, nullptr, M, 1, N, K, lda, ldb, 0, N, sa_stride_m, sa_stride_k,
+                     0, sb_stride_n, sb_stride_k, out_dtype, stream, nullptr, 0, &push);
+}
+
+namespace sglb {
+namespace {
+int check_reduce_out(const void* out, int64_t M, int64_t N, int64_t ldc, int out_dtype, int* sm_count) {
+  SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "out_dtype=%d", out_dtype);
+  SGLB_REQUIRE(out, SGLB200_ERR_NULL, "out must not be NULL");
+  SGLB_REQUIRE(ldc >= N && ldc % 8 == 0 && aligned(out, 16), SGLB200_ERR_ALIGN,
+               "ldc=%lld must be >= N and a multiple of 8; out 16-byte aligned", (long long)ldc);
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
+               di.cc_major, di.cc_minor);
+  *sm_count = di.sm_count;
+  return SGLB200_OK;
+}
+}  // namespace
+}  // namespace sglb
+
+extern "C" int sglb200_peer_reduce_scatter(void* const* peer_recv, void* const* peer_flags, void* out, int64_t M,
+                                           int64_t N, int64_t ldc, int out_dtype, int rank, int world,
+                                           int64_t slot_elems, int64_t timeout_ns, void* stream) {
+  using namespace sglb;
+  SGLB_REQUIRE(M > 0 && N > 0 && N % 8 == 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld (N must be a multiple of 8)", (long long)M,
+               (long long)N);
+  if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
+  if (int rc = check_scatter_args(M, N, world)) return rc;
+  PushParams push;
+  if (int rc = fill_push(&push, peer_recv, peer_flags, rank, world, slot_elems, 1)) return rc;
+  int sms = 0;
+  if (int rc = check_reduce_out(out, M, N, ldc, out_dtype, &sms)) return rc;
+  const int32_t n_tiles = (int32_t)((N + BN - 1) / BN);
+  const int32_t tiles = (int32_t)((M + BM - 1) / BM) * n_tiles;
+  const int32_t items = ((tiles - rank + world - 1) / world) * 4;  // (owned tile, quarter of its rows)
+  const int grid = items < 4 * sms ? items : 4 * sms;
+  const uint64_t limit = timeout_ns > 0 ? (uint64_t)timeout_ns : 2000000000ull;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (out_dtype == SGLB200_BF16)
+    peer_reduce_scatter_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(push, static_cast<__nv_bfloat16*>(out), (int32_t)M,
+                                                                   (int32_t)N, ldc, n_tiles, items, limit);
+  else
+    peer_reduce_scatter_kernel<__half><<<grid, 256, 0, st>>>(push, static_cast<__half*>(out), (int32_t)M, (int32_t)N, ldc,
+                                                            n_tiles, items, limit);
+  SGLB_CHECK_LAUNCH("peer_reduce_scatter_kernel");
+  return SGLB200_OK;
+}
+
+extern "C" int sglb200_peer_gather(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N, int64_t ldc,
+                                   int out_dtype, int rank, int world, int64_t slot_elems, int64_t timeout_ns,
+                                   void* stream) {
+  using namespace sglb;
+  SGLB_REQUIRE(M > 0 && N > 0 && N % 8 == 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld (N must be a multiple of 8)", (long long)M,
+               (long long)N);
+  if (int rc = check_push_args(M, N, world, rank, slot_elems)) return rc;
+  if (int rc = check_scatter_args(M, N, world)) return rc;
+  SGLB_REQUIRE(recv_local && flags_local && aligned(recv_local, 16), SGLB200_ERR_NULL,
+               "recv_local (16-byte aligned) / flags_local must not be NULL");
+  int sms = 0;
+  if (int rc = check_reduce_out(out, M, N, ldc, out_dtype, &sms)) return rc;
+  const int32_t n_tiles = (int32_t)((N + BN - 1) / BN);
+  const int32_t items = (int32_t)((M + BM - 1) / BM) * n_tiles * 4;
+  const int grid = items < 4 * sms ? items : 4 * sms;
+  const uint64_t limit = timeout_ns > 0 ? (uint64_t)timeout_ns : 2000000000ull;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* fl = static_cast<uint32_t*>(flags_local);
+  if (out_dtype == SGLB200_BF16)
+    peer_gather_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(recv_local), fl,
+                                                           fl + kFlagWords, static_cast<__nv_bfloat16*>(out), (int32_t)M,
+                                                           (int32_t)N, ldc, n_tiles, items, world, rank, slot_elems, limit);
+  else
+    peer_gather_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(recv_local), fl, fl + kFlagWords,
+                                                    static_cast<__half*>(out), (int32_t)M, (int32_t)N, ldc, n_tiles, items,
+                                                    world, rank, slot_elems, limit);
+  SGLB_CHECK_LAUNCH("peer_gather_kernel");
+  return SGLB200_OK;
 }
 
 extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, void* out, int64_t M, int64_t N,

@@ -82,7 +82,8 @@ class RowParallelBlockFp8Linear(_ParallelBase):
     With a ``peer_exchange`` (:class:`~sglang_b200.distributed.peer_allreduce.PeerExchange`) and an output that fits
     its receive slot, the GEMM pushes its tiles into every rank's memory and the sum is taken there: no NCCL call
     (the reference switches to its custom all-reduce below a size threshold the same way,
-    ``custom_all_reduce.py: should_custom_ar``).  Larger outputs take the NCCL all-reduce."""
+    ``custom_all_reduce.py: should_custom_ar``); from four ranks up, outputs too large for that take the two-shot form
+    (tile t reduced on rank t % world, results sent round).  Larger outputs still take the NCCL all-reduce."""
 
     def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
                  input_is_parallel: bool = True, reduce_results: bool = True,
@@ -99,7 +100,8 @@ class RowParallelBlockFp8Linear(_ParallelBase):
             x = x.narrow(-1, self.rank * per, per).contiguous()
         ex = self.peer_exchange
         if (ex is not None and self.reduce_results and self.world > 1 and x.is_cuda
-                and ex.fits(x.numel() // x.shape[-1], self.weight.shape[0])):
+                and (ex.fits(x.numel() // x.shape[-1], self.weight.shape[0])
+                     or ex.fits_two_shot(x.numel() // x.shape[-1], self.weight.shape[0]))):
             from .peer_allreduce import fused_row_parallel_linear
             y = fused_row_parallel_linear(ex, x, self.weight, self.weight_scale_inv, None)
             if self.bias is not None:  # held by rank 0 only: every rank needs it after the sum

@@ -6,7 +6,8 @@ The reference runs the row-parallel GEMM and then a separate custom all-reduce o
 ``sgl-kernel/csrc/allreduce/custom_all_reduce.cuh:203-266``).  Here the GEMM's epilogue stores each output tile
 directly into every rank's receive buffer and flags it, and a second kernel per rank waits for the flags and adds the
 ``world`` partial sums in rank order (``include/sglb200.h``: ``sglb200_fp8_blockwise_scaled_mm_push``,
-``sglb200_peer_reduce``).  No NCCL call is on that path; ``torch.distributed`` is used once, to exchange the IPC
+``sglb200_peer_reduce``); for larger outputs the two-shot form sends tile ``t`` to rank ``t % world`` only, which adds
+it up and sends the result round (``..._push_scatter``, ``sglb200_peer_reduce_scatter``, ``sglb200_peer_gather``).  No NCCL call is on that path; ``torch.distributed`` is used once, to exchange the IPC
 handles.  Every bounded wait that runs out is reported through ``sglb200_read_device_status`` (5).
 """
 
@@ -77,12 +78,23 @@ class PeerExchange:
         return n.value
 
     # One-shot exchange: every rank sends its whole partial sum to every other rank.  Measured against NCCL (2 and 8
-    # B200s, N = 7168): ahead up to about 16 MB leaving a rank per call, behind above that.
+    # B200s, N = 7168): ahead up to about 16 MB leaving a rank per call, behind above that.  The two-shot exchange
+    # (tile t reduced on rank t % world, results sent round) moves 2 (world - 1) / world of the output per rank, so from
+    # four ranks up it carries the same byte budget to outputs several times larger.
     MAX_OUT_BYTES = 16 << 20
 
+    def _fits_buffers(self, M: int, N: int) -> bool:
+        return M * N <= self.slot_elems and -(-M // 128) * -(-N // 128) <= 1024
+
     def fits(self, M: int, N: int) -> bool:
-        return (M * N <= self.slot_elems and -(-M // 128) * -(-N // 128) <= 1024
-                and (self.world - 1) * M * N * 2 <= self.MAX_OUT_BYTES)
+        """The one-shot exchange is allowed and worth it for an ``[M, N]`` output."""
+        return self._fits_buffers(M, N) and (self.world - 1) * M * N * 2 <= self.MAX_OUT_BYTES
+
+    def fits_two_shot(self, M: int, N: int) -> bool:
+        """The two-shot exchange is allowed and worth it (a larger output than :meth:`fits` takes, four ranks or more,
+        at least one tile per rank)."""
+        return (self.world >= 4 and self._fits_buffers(M, N) and -(-M // 128) * -(-N // 128) >= self.world
+                and 2 * (self.world - 1) * M * N * 2 <= self.world * self.MAX_OUT_BYTES)
 
     def close(self) -> None:
         """Unmap the peers' buffers and free this rank's (collective: all ranks first stop using them)."""
@@ -129,21 +141,59 @@ def peer_reduce(recv_ptr: int, flag_ptr: int, out: torch.Tensor, world: int, slo
                                     torch.cuda.current_stream(out.device).cuda_stream), "peer_reduce")
 
 
+def push_mm_scatter(ex_recv_arr, ex_flag_arr, rank: int, world: int, slot_elems: int, a_q: torch.Tensor,
+                    a_s: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, out_dtype: torch.dtype) -> None:
+    """First launch of the two-shot exchange: as :func:`push_mm`, but output tile ``t`` goes to rank ``t % world``."""
+    M, K = a_q.shape
+    N = weight.shape[0]
+    check(lib().sglb200_fp8_blockwise_scaled_mm_push_scatter(
+        a_q.data_ptr(), weight.data_ptr(), a_s.data_ptr(), weight_scale.data_ptr(), M, N, K, a_q.stride(0),
+        weight.stride(0), a_s.stride(0), a_s.stride(1), weight_scale.stride(0), weight_scale.stride(1),
+        dtype_code(out_dtype), ex_recv_arr, ex_flag_arr, rank, world, slot_elems,
+        torch.cuda.current_stream(a_q.device).cuda_stream), "fp8_blockwise_scaled_mm_push_scatter")
+
+
+def peer_reduce_scatter(ex_recv_arr, ex_flag_arr, rank: int, world: int, slot_elems: int, out: torch.Tensor,
+                        timeout_ns: int = 0) -> None:
+    """Second launch: add up the tiles this rank owns, write them to ``out`` and send them to the other ranks."""
+    check(lib().sglb200_peer_reduce_scatter(ex_recv_arr, ex_flag_arr, out.data_ptr(), out.size(0), out.size(1),
+                                            out.stride(0), dtype_code(out.dtype), rank, world, slot_elems, timeout_ns,
+                                            torch.cuda.current_stream(out.device).cuda_stream), "peer_reduce_scatter")
+
+
+def peer_gather(recv_ptr: int, flag_ptr: int, rank: int, world: int, slot_elems: int, out: torch.Tensor,
+                timeout_ns: int = 0) -> None:
+    """Third launch: copy the tiles the other ranks reduced into ``out``."""
+    check(lib().sglb200_peer_gather(recv_ptr, flag_ptr, out.data_ptr(), out.size(0), out.size(1), out.stride(0),
+                                    dtype_code(out.dtype), rank, world, slot_elems, timeout_ns,
+                                    torch.cuda.current_stream(out.device).cuda_stream), "peer_gather")
+
+
 def fused_row_parallel_linear(ex: PeerExchange, x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor,
-                              bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+                              bias: Optional[torch.Tensor] = None, two_shot: Optional[bool] = None) -> torch.Tensor:
     """``all_reduce(x_r @ W_r^T)`` for this rank's activation slice ``x [.., K_r]`` (bf16 / f16) and weight slice
     ``[N, K_r]`` with block scales ``[N/128, K_r/128]``: quantise, GEMM with the push epilogue, reduce.  The caller
-    checks ``ex.fits(M, N)`` and takes the NCCL path otherwise (``RowParallelBlockFp8Linear`` does)."""
+    checks ``ex.fits(M, N)`` / ``ex.fits_two_shot(M, N)`` and takes the NCCL path otherwise
+    (``RowParallelBlockFp8Linear`` does).  ``two_shot`` (default: one shot where ``ex.fits`` allows it, else two) selects
+    the exchange; every rank must select the same one."""
     from ..layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
     x2 = x.reshape(-1, x.shape[-1])
     M, N = x2.shape[0], weight.shape[0]
     out = torch.empty(M, N, dtype=x.dtype, device=x.device)
     if M == 0:
         return out.reshape(*x.shape[:-1], N)
+    if two_shot is None:
+        two_shot = not ex.fits(M, N) and ex.fits_two_shot(M, N)
     a_q, a_s = sglang_per_token_group_quant_fp8(x2.contiguous(), 128, column_major_scales=False)
     with torch.cuda.device(x.device):
-        push_mm(ex._recv_arr, ex._flag_arr, ex.rank, ex.world, ex.slot_elems, a_q, a_s, weight, weight_scale, x.dtype)
-        peer_reduce(ex.recv_ptrs[ex.rank], ex.flag_ptrs[ex.rank], out, ex.world, ex.slot_elems)
+        if two_shot:
+            push_mm_scatter(ex._recv_arr, ex._flag_arr, ex.rank, ex.world, ex.slot_elems, a_q, a_s, weight, weight_scale,
+                            x.dtype)
+            peer_reduce_scatter(ex._recv_arr, ex._flag_arr, ex.rank, ex.world, ex.slot_elems, out)
+            peer_gather(ex.recv_ptrs[ex.rank], ex.flag_ptrs[ex.rank], ex.rank, ex.world, ex.slot_elems, out)
+        else:
+            push_mm(ex._recv_arr, ex._flag_arr, ex.rank, ex.world, ex.slot_elems, a_q, a_s, weight, weight_scale, x.dtype)
+            peer_reduce(ex.recv_ptrs[ex.rank], ex.flag_ptrs[ex.rank], out, ex.world, ex.slot_elems)
     if bias is not None:
         out += bias
     return out.reshape(*x.shape[:-1], N)

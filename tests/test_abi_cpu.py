@@ -150,6 +150,11 @@ def test_host_validation_of_routing_and_exchange_entries(built_lib):
     assert L.sglb200_fp8_blockwise_scaled_mm_push(None, None, None, None, 64, 512, 256, 256, 256, 2, 1, 2, 1, 0, ptrs, ptrs,
                                                   3, 2, 64 * 512, None, 0, None) == -1 and "rank" in detail()
     assert L.sglb200_peer_reduce(None, None, None, 64, 500, 512, 0, 2, 64 * 512, 0, None) == -1
+    assert L.sglb200_fp8_blockwise_scaled_mm_push_scatter(None, None, None, None, 64, 128, 256, 256, 256, 2, 1, 2, 1, 0,
+                                                          ptrs, ptrs, 0, 2, 64 * 128, None) == -1
+    assert "fewer output tiles than ranks" in detail()
+    assert L.sglb200_peer_reduce_scatter(ptrs, ptrs, None, 256, 512, 512, 0, 0, 2, 1024, 0, None) == -7
+    assert L.sglb200_peer_gather(None, None, None, 256, 512, 512, 0, 0, 2, 256 * 512, 0, None) == -6
     assert L.sglb200_ep_dispatch(None, None, 2, 1, None, None, 4, 200, 2, 4, ptrs, 0, 2, 16, 16, None) == -1
     assert "multiple of 128" in detail()
     assert L.sglb200_ep_dispatch(None, None, 2, 1, None, None, 40, 256, 2, 4, ptrs, 0, 2, 16, 16, None) == -6

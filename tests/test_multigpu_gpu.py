@@ -79,6 +79,25 @@ def _worker(rank, world, port, q):
             assert big.shape == (512, H) and ex.completed == 7
         finally:
             ex.close()
+        # ---- the two-shot form (tile t reduced on rank t % world, results sent round), alternating with the one-shot form
+        from sglang_b200.distributed import fused_row_parallel_linear
+        ex2 = PeerExchange(slot_elems=300 * H)
+        try:
+            shard = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world)
+            for it, Ms in enumerate([300, 130, 256, 300]):
+                xs = torch.randn(Ms, I, generator=g).bfloat16()
+                xr = xs[:, rank * (I // world):(rank + 1) * (I // world)].contiguous().cuda()
+                y_2 = fused_row_parallel_linear(ex2, xr, shard.weight, shard.weight_scale_inv, two_shot=True)
+                y_1 = fused_row_parallel_linear(ex2, xr, shard.weight, shard.weight_scale_inv, two_shot=False)
+                torch.cuda.synchronize()
+                assert ex2.completed == 2 * (it + 1)
+                assert torch.equal(y_2, y_1), f"two-shot and one-shot bits differ ({it})"
+                both = [torch.empty_like(y_2) for _ in range(world)]
+                dist.all_gather(both, y_2)
+                assert torch.equal(both[0], both[1]), "ranks must hold identical bits"
+            assert_gemm_close(y_2, row_parallel_reference(xs, w_dn, s_dn, world), "two-shot row-parallel")
+        finally:
+            ex2.close()
         # ---- the same expert-parallel layer with dispatch / combine over peer memory (no NCCL, no host sync)
         from sglang_b200.distributed import PeerEpExchange, ep_fused_experts_peer
         epx = PeerEpExchange(capacity=150 + 90, hidden=Hm, topk=topk, m_max=150)

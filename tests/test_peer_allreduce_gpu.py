@@ -92,6 +92,90 @@ def test_push_and_reduce_emulated_ranks(world, M, N, K):
         assert_gemm_close(outs[0], row_parallel_reference(x, wq, ws, world), "push epilogue route")
 
 
+@pytest.mark.parametrize("world,M,N,K", [(2, 130, 640, 1024), (4, 256, 1152, 2048), (8, 300, 7168, 2048),
+                                         (8, 128, 1024, 1024), (4, 100, 576, 512), (3, 515, 384, 768)])
+def test_two_shot_emulated_ranks(world, M, N, K):
+    """Reduce-scatter + all-gather: every rank's scatter push, then every rank's reduce-scatter (its flags are then set),
+    then every rank's gather.  Same bits as the one-shot exchange; one-shot and two-shot exchanges alternate on the same
+    buffers."""
+    from sglang_b200._lib import lib
+    from sglang_b200.distributed.peer_allreduce import (peer_gather, peer_reduce, peer_reduce_scatter, push_mm,
+                                                        push_mm_scatter)
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    slot = -(-M * N // 8) * 8
+    recv, flags, recv_arr, flag_arr = _buffers(world, slot)
+    wq, ws = oracle.block_quant_weight(torch.randn(N, K, generator=torch.Generator().manual_seed(N)) * 0.05)
+    kr = K // world
+    shards = [(wq[:, r * kr:(r + 1) * kr].contiguous().cuda(), ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous().cuda())
+              for r in range(world)]
+    for epoch, two_shot in enumerate((True, True, False, True, True, False, True), start=1):
+        x = make_activations(M, K, seed=epoch, outliers=False)
+        partials = []
+        for r in range(world):
+            a_q, a_s = sglang_per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous().cuda(), 128)
+            (push_mm_scatter if two_shot else push_mm)(recv_arr, flag_arr, r, world, slot, a_q, a_s, shards[r][0],
+                                                       shards[r][1], torch.bfloat16)
+            partials.append(_plain_partial(a_q, a_s, *shards[r]) if M > 64 else None)
+        outs = [torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        if two_shot:
+            for r in range(world):
+                peer_reduce_scatter(recv_arr, flag_arr, r, world, slot, outs[r])
+            for r in range(world):
+                peer_gather(recv[r].data_ptr(), flags[r].data_ptr(), r, world, slot, outs[r])
+        else:
+            for r in range(world):
+                peer_reduce(recv[r].data_ptr(), flags[r].data_ptr(), outs[r], world, slot)
+        torch.cuda.synchronize()
+        assert lib().sglb200_read_device_status() == 0
+        done = ctypes.c_int64(-1)
+        for r in range(world):
+            assert lib().sglb200_peer_completed(flags[r].data_ptr(), ctypes.byref(done)) == 0 and done.value == epoch
+        if M > 64:
+            want = torch.zeros(M, N, dtype=torch.float32, device="cuda")
+            for part in partials:
+                want += part.float()
+            assert torch.equal(outs[0], want.bfloat16()), f"epoch {epoch}"
+        for r in range(1, world):
+            assert torch.equal(outs[r], outs[0]), f"rank {r} epoch {epoch}"
+        assert_gemm_close(outs[0], row_parallel_reference(x, wq, ws, world), f"epoch {epoch}")
+
+
+def test_two_shot_wait_runs_out_and_rejections():
+    from sglang_b200._lib import lib
+    from sglang_b200.distributed.peer_allreduce import peer_gather, peer_reduce_scatter, push_mm_scatter
+    from sglang_b200.layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    M, N, K, world = 130, 256, 256, 2
+    slot = M * N
+    recv, flags, recv_arr, flag_arr = _buffers(world, slot)
+    wq, ws = oracle.block_quant_weight(torch.randn(N, K, generator=torch.Generator().manual_seed(1)) * 0.05)
+    a_q, a_s = sglang_per_token_group_quant_fp8(make_activations(M, K, seed=1, outliers=False).cuda(), 128)
+    out = [torch.full((M, N), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    push_mm_scatter(recv_arr, flag_arr, 0, world, slot, a_q, a_s, wq.cuda(), ws.cuda(), torch.bfloat16)  # rank 1 silent
+    peer_reduce_scatter(recv_arr, flag_arr, 0, world, slot, out[0], timeout_ns=20_000_000)
+    peer_gather(recv[0].data_ptr(), flags[0].data_ptr(), 0, world, slot, out[0], timeout_ns=20_000_000)
+    torch.cuda.synchronize()
+    assert lib().sglb200_read_device_status() == 5 and lib().sglb200_read_device_status() == 0
+    assert (out[0] == 7.0).all()
+    done = ctypes.c_int64(-1)
+    assert lib().sglb200_peer_completed(flags[0].data_ptr(), ctypes.byref(done)) == 0 and done.value == 0
+    # the late rank arrives: the same exchange now completes on both ranks
+    push_mm_scatter(recv_arr, flag_arr, 1, world, slot, a_q, a_s, wq.cuda(), ws.cuda(), torch.bfloat16)
+    for r in range(world):
+        peer_reduce_scatter(recv_arr, flag_arr, r, world, slot, out[r])
+    for r in range(world):
+        peer_gather(recv[r].data_ptr(), flags[r].data_ptr(), r, world, slot, out[r])
+    torch.cuda.synchronize()
+    assert lib().sglb200_read_device_status() == 0
+    for r in range(world):
+        assert lib().sglb200_peer_completed(flags[r].data_ptr(), ctypes.byref(done)) == 0 and done.value == 1
+    assert torch.equal(out[0], (_plain_partial(a_q, a_s, wq.cuda(), ws.cuda()).float() * 2).bfloat16())
+    assert torch.equal(out[1], out[0])
+    # fewer tiles than ranks: refused before anything is launched
+    recv4, flags4, recv_arr4, flag_arr4 = _buffers(4, 64 * 256)
+    with pytest.raises(RuntimeError, match="fewer output tiles than ranks"):
+        push_mm_scatter(recv_arr4, flag_arr4, 0, 4, 64 * 256, a_q[:64], a_s[:64], wq.cuda(), ws.cuda(), torch.bfloat16)
+
+
 def test_reduce_wait_runs_out_and_reports():
     """A rank that never pushes: the bounded wait gives up, the status word says so, the output is left alone and the
     context stays usable."""
