@@ -625,6 +625,12 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    if world > 1:  # set-up, not a step: NCCL builds its channels and buffers for this message size on first use
+        warm = torch.zeros(M, max(L["N"] for L in layers if L["mode"] == "row"), dtype=torch.bfloat16, device=dev)
+        for _ in range(5):
+            dist.all_reduce(warm)
+        del warm
+        fence()
     for _ in range(args.warmup if args.only not in ("quant", "ue8m0") else 0):
         step()
     for L in layers:
