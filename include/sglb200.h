@@ -12,6 +12,12 @@
  * sglb200_status_string() turns a code into text; sglb200_last_error_detail() returns a
  * thread-local message describing the last failed check (which argument, which value).
  *
+ * Threads and devices: the entry points may be called from several host threads, with one exception.  The FIRST call of a
+ * kernel family on a device does per-device set-up (cudaFuncSetAttribute, device properties, the address of the built-in
+ * scratch array) and records it in plain per-device tables; make that first call per device from one thread (a warm-up
+ * call at start-up does it).  Later calls only read those tables.  Device ordinals 0..63 are supported by the tables;
+ * a higher ordinal repeats the set-up on every call, and sglb200_fp8_blockwise_scaled_mm_noalloc refuses it.
+ *
  * Reference files cited below are paths inside the vincent-shop/sglang tree.
  */
 #ifndef SGLB200_H_
@@ -422,8 +428,9 @@ int sglb200_peer_completed(const void* flags_local, int64_t* completed);
  * library and without a host round trip for the row counts.  Every rank owns one exchange buffer of
  * sglb200_ep_buffer_bytes(capacity, H, topk, world, m_max) bytes, zero before the first use, mapped by every rank
  * (sglb200_peer_alloc / sglb200_peer_open); peer_bases is a HOST array of `world` device pointers, entry r = rank r's
- * buffer as mapped in this process.  capacity = rows a rank can receive per exchange (at most the tokens of all ranks),
- * m_max = tokens a rank may send.  sglb200_ep_buffer_offsets returns the byte offsets of {recv_q [capacity, H] e4m3,
+ * buffer as mapped in this process.  capacity = rows a rank can receive per exchange, m_max = tokens a rank may send.
+ * Choose capacity >= world * m_max (a token goes to a rank at most once, so that always fits; the Python wrapper refuses
+ * less): with a smaller one a full buffer DROPS rows (status 23) and the combine adds stale data for them.  sglb200_ep_buffer_offsets returns the byte offsets of {recv_q [capacity, H] e4m3,
  * recv_s [capacity, H/128] f32, recv_meta [capacity, 2] i32, recv_ids [capacity, topk] i32, recv_w [capacity, topk] f32,
  * comb [world, m_max, H] 16-bit, control words} inside a buffer.  One exchange = four launches on one stream per rank,
  * the same sequence on every rank; the exchange counter lives in the control words (read by all four kernels, advanced
@@ -485,9 +492,10 @@ int sglb200_peer_free(void* dev_ptr);
 /*
  * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
  * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce, 11-18 the same
- * roles in the other GEMM kernels, 21-23 the expert-parallel exchange).  Reading clears it.  This call SYNCHRONISES the
- * device (cudaMemcpyFromSymbol); it is for tests and debugging, not for the serving path.  Returns -1 if the
- * read itself failed.  No counterpart in the reference (its kernels have no bounded waits).
+ * roles in the UE8M0 and few-rows kernels, 21-23 the expert-parallel exchange, 31-35 the CTA-pair kernel).  Every
+ * kernel family keeps its own word; each call reads AND clears all of them and returns the first non-zero one, so a
+ * status never surfaces on a later, unrelated read.  This call SYNCHRONISES the device (cudaMemcpyFromSymbol); it is for
+ * tests and debugging, not for the serving path.  Returns -1 if the read itself failed.  No counterpart in the reference (its kernels have no bounded waits).
  */
 int sglb200_read_device_status(void);
 

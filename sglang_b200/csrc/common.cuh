@@ -39,6 +39,11 @@ void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N,
                           int sm_count, void* stream);  // gemm.cu
 int smallm_take_device_status();
 
+// Dense GEMM on CTA pairs (256 x bn tiles, bn = 128 or 256), gemm_pair.cu
+int pair_gemm(int bn, const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N,
+              int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
+              int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, int sm_count, void* stream);
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 #define SGLB_CHECK_LAUNCH(what)                                                                   \

@@ -83,7 +83,9 @@ class RowParallelBlockFp8Linear(_ParallelBase):
     its receive slot, the GEMM pushes its tiles into every rank's memory and the sum is taken there: no NCCL call
     (the reference switches to its custom all-reduce below a size threshold the same way,
     ``custom_all_reduce.py: should_custom_ar``); from four ranks up, outputs too large for that take the two-shot form
-    (tile t reduced on rank t % world, results sent round).  Larger outputs still take the NCCL all-reduce."""
+    (tile t reduced on rank t % world, results sent round).  Larger outputs still take the NCCL all-reduce.
+    On that path the sum is taken by every rank for itself, so every rank keeps the whole bias and adds it once after
+    the sum (decided here, where all ranks see the same arguments, not per rank in ``forward``)."""
 
     def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
                  input_is_parallel: bool = True, reduce_results: bool = True,
@@ -93,6 +95,9 @@ class RowParallelBlockFp8Linear(_ParallelBase):
         self.rank, self.world = rank, world
         self.input_is_parallel, self.reduce_results = input_is_parallel, reduce_results
         self.peer_exchange = peer_exchange
+        self.bias_after_sum = None
+        if peer_exchange is not None and bias is not None:
+            self.bias_after_sum = torch.nn.Parameter(bias, requires_grad=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not self.input_is_parallel:
@@ -103,10 +108,7 @@ class RowParallelBlockFp8Linear(_ParallelBase):
                 and (ex.fits(x.numel() // x.shape[-1], self.weight.shape[0])
                      or ex.fits_two_shot(x.numel() // x.shape[-1], self.weight.shape[0]))):
             from .peer_allreduce import fused_row_parallel_linear
-            y = fused_row_parallel_linear(ex, x, self.weight, self.weight_scale_inv, None)
-            if self.bias is not None:  # held by rank 0 only: every rank needs it after the sum
-                raise RuntimeError("peer_exchange with a bias is not implemented")
-            return y
+            return fused_row_parallel_linear(ex, x, self.weight, self.weight_scale_inv, self.bias_after_sum)
         y = self._apply(self, x, self.bias)
         if self.reduce_results:
             y = tensor_model_parallel_all_reduce(y, self.group)

@@ -44,8 +44,10 @@ def buffer_views(base_ptr: int, device, capacity: int, H: int, topk: int, world:
 
 class PeerEpExchange:
     """This rank's exchange buffer, mapped by every rank of ``group``, and the pointers to the other ranks' buffers.
-    ``capacity`` = rows this rank can receive per call (the tokens of all ranks is always enough), ``m_max`` = tokens a
-    rank may dispatch per call.  Collective: every rank constructs it at the same point."""
+    ``capacity`` = rows this rank can receive per call, ``m_max`` = tokens a rank may dispatch per call.  A token is
+    sent to a rank at most once, so ``world * m_max`` rows always fit; a smaller ``capacity`` is refused here, because a
+    full receive buffer drops rows on the device (status 23 is the only trace) and the combine would then add whatever
+    an earlier exchange left in the dropped row's slot.  Collective: every rank constructs it at the same point."""
 
     def __init__(self, capacity: int, hidden: int, topk: int, m_max: int, group=None,
                  device: Optional[torch.device] = None):
@@ -56,6 +58,9 @@ class PeerEpExchange:
             raise RuntimeError("PeerEpExchange supports at most 8 ranks (one NVLink domain)")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         self.capacity, self.hidden, self.topk, self.m_max = int(capacity), int(hidden), int(topk), int(m_max)
+        if self.capacity < self.world * self.m_max:
+            raise ValueError(f"capacity={self.capacity} rows cannot hold the {self.world} x {self.m_max} tokens the ranks "
+                             "may dispatch to one rank: rows would be dropped")
         L = lib()
         self._opened: List[int] = []
         with torch.cuda.device(self.device):

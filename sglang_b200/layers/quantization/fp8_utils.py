@@ -69,17 +69,47 @@ def ceil_to_ue8m0(x: torch.Tensor) -> torch.Tensor:
     return torch.ldexp(torch.ones_like(mant), torch.where(mant == 0.5, exp - 1, exp))
 
 
-def requant_weight_ue8m0(weight: torch.Tensor, weight_scale: torch.Tensor, block_size: List[int]):
-    """Dequantise a block-FP8 weight and quantise it again with power-of-two block scales
-    (``requant_weight_ue8m0`` / ``per_block_cast_to_fp8``, ``fp8_utils.py:416-507``).  Offline, torch ops."""
-    bn, bk = block_size
+def per_block_cast_to_fp8(x: torch.Tensor):
+    """128x128 block quantisation with power-of-two (UE8M0) scales, the reference's ``per_block_cast_to_fp8``
+    (``fp8_utils.py:494-507``): pad to whole blocks, block amax clamped at 1e-4, scale = the smallest power of two
+    >= amax / 448, codes = e4m3(x * (1 / scale)).  Returns (codes ``[m, n]``, scales fp32 ``[ceil(m/128),
+    ceil(n/128)]``).  Offline, torch ops on ``x``'s device."""
+    assert x.dim() == 2
+    m, n = x.shape
+    m_p, n_p = -(-m // 128) * 128, -(-n // 128) * 128
+    xp = torch.zeros(m_p, n_p, dtype=x.dtype, device=x.device)
+    xp[:m, :n] = x
+    v = xp.view(m_p // 128, 128, n_p // 128, 128)
+    amax = v.abs().float().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
+    # tensor / tensor: a true IEEE division on every device (tensor / python scalar is a multiplication by the
+    # reciprocal in torch's CUDA kernels, one ulp off for some values)
+    sf = ceil_to_ue8m0(amax / torch.full_like(amax, 448.0))
+    q = (v * (1.0 / sf)).to(torch.float8_e4m3fn).view(m_p, n_p)[:m, :n].contiguous()
+    return q, sf.view(m_p // 128, n_p // 128)
+
+
+def block_quant_weight_fp8(weight: torch.Tensor, block_size: Optional[List[int]] = None):
+    """Block quantisation with fp32 scales, the form block-FP8 checkpoints are made with
+    (``convert_weight``, ``test/srt/cpu/utils.py:39-87``): scale = block amax / 448 (1.0 for an all-zero block),
+    codes = e4m3(w / scale) with a true division; ragged edges are zero-padded for the amax and cropped.
+    Returns (codes ``[N, K]`` e4m3, scales fp32 ``[ceil(N/bn), ceil(K/bk)]``).  Offline, torch ops on
+    ``weight``'s device."""
+    bn, bk = block_size if block_size is not None else (128, 128)
     n, k = weight.shape
-    w = block_quant_dequant(weight, weight_scale, block_size, torch.float32)
     n_p, k_p = -(-n // bn) * bn, -(-k // bk) * bk
     wp = torch.zeros(n_p, k_p, dtype=torch.float32, device=weight.device)
-    wp[:n, :k] = w
+    wp[:n, :k] = weight.to(torch.float32)
     v = wp.view(n_p // bn, bn, k_p // bk, bk)
-    amax = v.abs().amax(dim=(1, 3), keepdim=True).clamp(1e-4)
-    sf = ceil_to_ue8m0(amax / 448.0)
-    q = (v * (1.0 / sf)).to(torch.float8_e4m3fn).view(n_p, k_p)[:n, :k].contiguous()
-    return q, sf.view(n_p // bn, k_p // bk).contiguous()
+    amax = v.abs().amax(dim=(1, 3), keepdim=True)
+    s = amax / torch.full_like(amax, 448.0)  # tensor / tensor: a true IEEE division on every device
+    s = torch.where(s == 0, torch.ones_like(s), s)
+    q = (v / s).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(n_p, k_p)[:n, :k].contiguous()
+    return q, s.view(n_p // bn, k_p // bk).contiguous()
+
+
+def requant_weight_ue8m0(weight: torch.Tensor, weight_scale: torch.Tensor, block_size: List[int]):
+    """Dequantise a block-FP8 weight and quantise it again with power-of-two block scales
+    (``_requant_weight_ue8m0``, ``fp8_utils.py:416-491``).  Offline, torch ops."""
+    assert list(block_size) == [128, 128]
+    q, sf = per_block_cast_to_fp8(block_quant_dequant(weight, weight_scale, block_size, torch.float32))
+    return q, sf.contiguous()

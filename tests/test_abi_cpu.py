@@ -168,3 +168,10 @@ def test_host_validation_of_routing_and_exchange_entries(built_lib):
     h = (ctypes.c_ubyte * 64)()
     assert L.sglb200_peer_alloc(0, None, h) == -6 and L.sglb200_peer_open(None, None) == -6
     assert L.sglb200_peer_close(None) == 0 and L.sglb200_peer_free(None) == 0
+
+
+def test_peer_ep_exchange_refuses_a_receive_buffer_that_could_overflow():
+    """capacity < world * m_max is refused before anything is allocated (no GPU needed to see the refusal)."""
+    from sglang_b200.distributed.peer_ep import PeerEpExchange
+    with pytest.raises(ValueError, match="capacity"):
+        PeerEpExchange(capacity=10, hidden=256, topk=2, m_max=11, device="cpu")

@@ -77,6 +77,17 @@ def _worker(rank, world, port, q):
                 assert torch.equal(both[0], both[1]), "ranks must hold identical bits"
             big = fused(torch.randn(512, I // world, generator=g).bfloat16().cuda())  # does not fit: NCCL path
             assert big.shape == (512, H) and ex.completed == 7
+            # a bias with the exchange: every rank adds the whole bias once, after the sum, and the ranks stay in step
+            bias = torch.randn(H, generator=g).bfloat16()
+            fused_b = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, bias=bias.cuda(), peer_exchange=ex)
+            for it in range(2):
+                xs = torch.randn(64, I, generator=g).bfloat16()
+                xr = xs[:, rank * (I // world):(rank + 1) * (I // world)].contiguous().cuda()
+                y_b = fused_b(xr)
+                torch.cuda.synchronize()
+                ref_b = (row_parallel_reference(xs, w_dn, s_dn, world).float() + bias.float()).bfloat16()
+                assert_gemm_close(y_b, ref_b, f"fused row-parallel with bias {it}", allow_one_ulp=True)
+            assert ex.completed == 9
         finally:
             ex.close()
         # ---- the two-shot form (tile t reduced on rank t % world, results sent round), alternating with the one-shot form
@@ -100,7 +111,7 @@ def _worker(rank, world, port, q):
             ex2.close()
         # ---- the same expert-parallel layer with dispatch / combine over peer memory (no NCCL, no host sync)
         from sglang_b200.distributed import PeerEpExchange, ep_fused_experts_peer
-        epx = PeerEpExchange(capacity=150 + 90, hidden=Hm, topk=topk, m_max=150)
+        epx = PeerEpExchange(capacity=2 * 150, hidden=Hm, topk=topk, m_max=150)
         try:
             done = []
             for it in range(6):

@@ -90,3 +90,37 @@ def test_tensor_parallel_two_ranks_gloo():
     for p in procs:
         p.join(timeout=60)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_row_parallel_bias_with_peer_exchange_is_decided_in_the_constructor(monkeypatch):
+    """With a peer exchange every rank takes the sum for itself, so every rank must hold the whole bias and add it after
+    the sum; no rank may raise or skip it on its own (the ranks would leave the exchange out of step)."""
+    import oracle
+    import sglang_b200.distributed.peer_allreduce as pa
+    from sglang_b200.distributed import RowParallelBlockFp8Linear
+
+    class FakeExchange:
+        def fits(self, m, n):
+            return True
+
+        def fits_two_shot(self, m, n):
+            return False
+
+    calls = []
+
+    def fake_fused(ex, x, w, ws, bias=None, two_shot=None):
+        calls.append(bias)
+        return torch.zeros(x.shape[0], w.shape[0]) + (0 if bias is None else bias)
+
+    monkeypatch.setattr(pa, "fused_row_parallel_linear", fake_fused)
+    monkeypatch.setattr(torch.Tensor, "is_cuda", property(lambda self: True))
+    g = torch.Generator().manual_seed(0)
+    w, s = oracle.block_quant_weight(torch.randn(256, 512, generator=g) * 0.05)
+    bias = torch.randn(256, generator=g)
+    outs = []
+    for rank in range(2):
+        layer = RowParallelBlockFp8Linear(w, s, rank, 2, bias=bias, apply_fn=_oracle_apply, peer_exchange=FakeExchange())
+        assert layer.bias_after_sum is not None and torch.equal(layer.bias_after_sum, bias)
+        outs.append(layer(torch.zeros(3, 256)))
+    assert len(calls) == 2 and all(c is not None and torch.equal(c, bias) for c in calls)
+    assert torch.equal(outs[0], outs[1])
