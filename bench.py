@@ -125,11 +125,21 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
+def host_cores() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def cpu_arm(steps: int, warmup: int, m_sample: int):
     """The reference's CPU implementation of the path on this host: sgl-kernel's AMX
     fp8_scaled_mm_cpu (W8A16) built from the reference sources when it loads here, else the
-    torch-native oracle port.  One pass = the five shapes at `m_sample` rows."""
+    torch-native oracle port.  One pass = the five shapes at `m_sample` rows, on every core this
+    process may use (torch.distributed.run exports OMP_NUM_THREADS=1; the thread count is raised
+    here, after import, so the arm is not measured on one core)."""
     import torch
+    torch.set_num_threads(host_cores())
     import oracle
     from oracle.build_ref import load_ref
     ops = load_ref()
@@ -163,6 +173,7 @@ def cpu_arm(steps: int, warmup: int, m_sample: int):
     dt = (time.perf_counter() - t0) / steps
     names = "+".join(s[0] for s in SHAPES if any(l[3] == s[1] and l[4] == s[2] for l in layers))
     return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+            "M_sample": m_sample,
             "sample": f"{names} at M={m_sample} rows, {steps} passes after {warmup} warm-up; "
                       + ("sgl-kernel fp8_scaled_mm_cpu (AMX bf16, W8A16)" if ops is not None
                          else "torch-native oracle (W8A8)"),

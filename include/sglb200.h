@@ -49,6 +49,18 @@ const char* sglb200_last_error_detail(void);
 const char* sglb200_version(void);
 
 /*
+ * Upper bound on the SMs the persistent kernels of this library occupy (GEMM, grouped GEMM, few-rows GEMM and the
+ * grid-sized helpers): their grids are sized from min(num_sms, SMs of the device).  0 lifts the bound.  Process-wide,
+ * read at every launch; set it from the thread that launches.  Use: leave SMs free for a communication kernel that runs
+ * beside a GEMM (a persistent GEMM that fills every SM makes a concurrent kernel wait for one of its CTAs to finish).
+ * Replaces: deep_gemm.set_num_sms / get_num_sms as used by configure_deep_gemm_num_sms,
+ *           python/sglang/srt/layers/deep_gemm_wrapper/entrypoint.py:94-104.
+ * sglb200_get_num_sms returns the bound in force (the device's SM count when none is set).
+ */
+int sglb200_set_num_sms(int num_sms);
+int sglb200_get_num_sms(void);
+
+/*
  * Q — per-token-group quantisation to e4m3.
  * Replaces: sgl_per_token_group_quant_8bit  sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217
  *           (schema sgl-kernel/csrc/common_extension.cc:173-176) for the e4m3 destination type.
@@ -163,6 +175,23 @@ int sglb200_fp8_blockwise_scaled_mm_noalloc(const void* a, const void* b, const 
                                             int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                                             int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
                                             int64_t sb_stride_k, int out_dtype, void* stream);
+/*
+ * G on CTA pairs: the same result contract as sglb200_fp8_blockwise_scaled_mm (dense, any M), computed by clusters of
+ * two CTAs that share one tcgen05.mma.cta_group::2 over a 256 x tile_n output tile (tile_n = 128 or 256).  Each CTA
+ * loads its own 128 rows of A and half of the B rows with its own TMA copies (nothing is broadcast), which lowers the
+ * L2 -> shared-memory bytes per flop to 3/4 (tile_n 128) or 1/2 (tile_n 256) of the single-CTA kernel's.  An explicit
+ * alternative, not the default: measured on B200 it is level with the single-CTA kernel at tile_n = 128 and behind it at
+ * tile_n = 256 on most of the benchmark's shapes (the promotion of the partial sums, not operand delivery, is what bounds
+ * both).  No split-K, no scratch.
+ * Replaces: the 2-SM configuration of the reference's sm_100 kernels
+ *           (KernelPtrArrayTmaWarpSpecializedBlockwise2SmSm100, sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:300-310;
+ *           dense launch sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:39-196).
+ */
+int sglb200_fp8_blockwise_scaled_mm_pair(const void* a, const void* b, const float* sa, const float* sb, void* out,
+                                         int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                                         int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                                         int64_t sb_stride_k, int out_dtype, int tile_n, void* stream);
+
 
 /*
  * G with power-of-two (UE8M0) scales, scaled by the tensor core itself (tcgen05.mma kind::mxf8f6f4.block_scale):

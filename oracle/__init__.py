@@ -21,6 +21,7 @@ from .block_fp8 import (  # noqa: F401
     apply_shuffle_mul_sum,
     block_quant_weight,
     ceil_to_ue8m0,
+    expert_parallel_reference,
     fused_experts_block_fp8,
     moe_align_block_size,
     moe_block_fp8_from_scores,
@@ -29,6 +30,7 @@ from .block_fp8 import (  # noqa: F401
     pack_scales,
     per_token_group_quant_fp8,
     prepare_moe_input,
+    row_parallel_reference,
     shuffle_rows,
     silu_and_mul,
     topk_softmax,

@@ -333,3 +333,33 @@ def moe_fused_gate(x: torch.Tensor, bias: torch.Tensor, num_expert_group: int, t
     if apply_routed_scaling_factor_on_output:
         w = w * torch.tensor(routed_scaling_factor, dtype=torch.float32)
     return w, ids.to(torch.int32)
+
+
+# --------------------------------------------------------------------------------------
+# AR / A2A: the sharded forms, evaluated the way the sharding defines the arithmetic
+# --------------------------------------------------------------------------------------
+def row_parallel_reference(x, wq, ws, world):
+    """Row-parallel linear: every rank quantises its K-slice, rounds its partial product to the output type, and the
+    partial products are added (``python/sglang/srt/layers/linear.py:1361-1386``); fp32 sum here, one cast."""
+    K = x.shape[1]
+    kr = K // world
+    ref = torch.zeros(x.shape[0], wq.shape[0], dtype=torch.float32)
+    for r in range(world):
+        q, s = per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous(), 128)
+        ref += w8a8_block_fp8_matmul(q, wq[:, r * kr:(r + 1) * kr].contiguous(), s,
+                                     ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous(), output_dtype=x.dtype).float()
+    return ref.to(x.dtype)
+
+
+def expert_parallel_reference(x, w1q, w2q, w1s, w2s, topk_w, topk_ids, world):
+    """Expert-parallel MoE: every rank adds up the contributions of ITS experts to a token and returns that partial row
+    in the activation type; the partial rows are added at the source in fp32
+    (``python/sglang/srt/layers/moe/token_dispatcher/deepep.py:466-492``)."""
+    E = w1q.shape[0]
+    el = E // world
+    total = torch.zeros(x.shape[0], w2q.shape[1], dtype=torch.float32)
+    for r in range(world):
+        local = torch.where((topk_ids // el) == r, topk_ids, torch.full_like(topk_ids, -1))
+        if bool((local >= 0).any()):
+            total += fused_experts_block_fp8(x, w1q, w2q, w1s, w2s, topk_w, local).float()
+    return total.to(x.dtype)

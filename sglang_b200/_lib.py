@@ -28,6 +28,7 @@ SIGNATURES = {
     "sglb200_fp8_blockwise_scaled_mm_workspace_bytes": [_L, _L, _L],
     "sglb200_fp8_blockwise_scaled_mm_noalloc": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
     "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": [],
+    "sglb200_fp8_blockwise_scaled_mm_pair": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _I, _P],
     "sglb200_fp8_ue8m0_scaled_mm": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P],
     "sglb200_fp8_ue8m0_scaled_mm_ws": [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P, _L, _P],
     "sglb200_fp8_ue8m0_scaled_grouped_mm": [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L,
@@ -71,6 +72,8 @@ SIGNATURES = {
     "sglb200_status_string": [_I],
     "sglb200_last_error_detail": [],
     "sglb200_version": [],
+    "sglb200_set_num_sms": [_I],
+    "sglb200_get_num_sms": [],
 }
 _RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64,
              "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": c_int64,

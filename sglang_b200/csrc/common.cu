@@ -17,6 +17,8 @@ int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+static int g_num_sms_limit = 0;  // 0: no limit
+
 int device_info(DeviceInfo* out) {
   static DeviceInfo cache[64];
   static bool have[64] = {false};
@@ -38,6 +40,7 @@ int device_info(DeviceInfo* out) {
     have[dev] = true;
   }
   *out = cache[dev];
+  if (g_num_sms_limit > 0 && g_num_sms_limit < out->sm_count) out->sm_count = g_num_sms_limit;
   return SGLB200_OK;
 }
 
@@ -61,6 +64,22 @@ const char* sglb200_status_string(int status) {
 
 const char* sglb200_last_error_detail(void) { return sglb::error_buffer(); }
 
-const char* sglb200_version(void) { return "0.1"; }
+const char* sglb200_version(void) { return "0.2"; }
+
+int sglb200_set_num_sms(int num_sms) {
+  if (num_sms < 0) return sglb::fail(SGLB200_ERR_SHAPE, "num_sms=%d must be >= 0 (0 = every SM)", num_sms);
+  sglb::g_num_sms_limit = num_sms;
+  return SGLB200_OK;
+}
+
+int sglb200_get_num_sms(void) {
+  sglb::DeviceInfo di;
+  const int limit = sglb::g_num_sms_limit;
+  sglb::g_num_sms_limit = 0;
+  const int rc = sglb::device_info(&di);
+  sglb::g_num_sms_limit = limit;
+  if (rc != SGLB200_OK) return limit;
+  return limit > 0 && limit < di.sm_count ? limit : di.sm_count;
+}
 
 }  // extern "C"

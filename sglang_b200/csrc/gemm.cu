@@ -23,7 +23,6 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -76,7 +75,6 @@ constexpr int kStageWords = 20;  // 80-byte row stride: 16-byte aligned, conflic
 constexpr size_t kStagingBytes = (size_t)kEpiWarps * 32 * kStageWords * sizeof(uint32_t);
 constexpr size_t kStagingOffset = (((size_t)kStages * kStageBytes + 256 + (kMaxExperts + 1) * sizeof(int32_t)) + 15) / 16 * 16;
 constexpr size_t kSmemBytesPush = 1024 + kStagingOffset + kStagingBytes;
-static_assert(kSmemBytesPush <= 227 * 1024, "push variant exceeds the shared memory of an SM");
 
 struct GemmParams {
   const float* sa;
@@ -125,6 +123,13 @@ struct SharedCtl {
   volatile int32_t abort_flag;
   int32_t total_tiles;
 };
+
+// bounded wait; fully inlined where the register limit of the warp was changed (no call allowed there)
+template <bool INLINE>
+__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
+  if constexpr (INLINE) return ptx::mbar_wait_inl_a(bar, parity, limit_ns);
+  else return ptx::mbar_wait_a(bar, parity, limit_ns);
+}
 
 template <bool GROUPED>
 __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int32_t* tile_start, int32_t t) {
@@ -236,23 +241,11 @@ __device__ __forceinline__ void warp_rows_via_smem(uint32_t* stg, const uint32_t
   }
 }
 
-// VAR is a bit set of pipeline options (see kVar* below)
-constexpr int kVarPipe = 1;     // promotion warps overlap the TMEM load of the next 32 columns with the FMAs of the last
-constexpr int kVarCommit1 = 2;  // one tcgen05.commit per k-block; a promotion warp hands the smem stage back
-constexpr int kVarLane0 = 4;    // producer and MMA loops are run by lane 0 alone (no warp-wide barrier polling)
-constexpr int kVarIss3 = 8;     // three MMA-issuing warps (416 threads)
-constexpr int kVarNoB = 16;     // DIAGNOSTIC (wrong results): the B tile is not loaded
-constexpr int kVarNoLoad = 32;  // DIAGNOSTIC (wrong results): no tile is loaded
-constexpr int kVarNoFma = 64;   // DIAGNOSTIC (wrong results): the promotion warps skip their FMAs
-__host__ __device__ constexpr int mma_warps_of(int var) { return (var & kVarIss3) ? 3 : 2; }
-__host__ __device__ constexpr int threads_of(int var) { return (kIssuers + mma_warps_of(var) + kEpiWarps) * 32; }
-
-template <bool GROUPED, bool PUSH, int VAR>
-__global__ void __launch_bounds__(threads_of(VAR), 1)
+template <bool GROUPED, bool PUSH>
+__global__ void __launch_bounds__(kThreads, 1)
 fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                       const typename ParamsOf<PUSH>::type p) {
-  constexpr int kMmaWarps = mma_warps_of(VAR);
-  constexpr int kFirstEpiWarp = kIssuers + kMmaWarps;
+  constexpr int kRing = kStages;  // shared-memory stages in the TMA ring
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage_base = smem;
@@ -332,111 +325,101 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     // ===== TMA producers.  Issuing a TMA or an MMA and touching an mbarrier each cost the issuing
     // thread on the order of a hundred cycles, and the tensor pipe does not queue far ahead, so one
     // warp per role cannot feed it: two warps per role take the k-blocks of the CTA alternately.
-    const bool active = (VAR & kVarLane0) ? lane == 0 : true;
     uint32_t stage = 0, phase = 0, g = 0;
-    if (active) {
-      for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        const Tile tl = get_tile<GROUPED>(p, tile_start, t);
-        bool ok = true;
-        for (int32_t kb = tl.kb0; kb < tl.kb1; ++kb, ++g) {
-          if ((g & (kIssuers - 1)) == (uint32_t)warp) {
-            if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
-              record_timeout(ctl, 1);
-              ok = false;
-              break;
-            }
-            if (lane == 0) {
-              const uint32_t dst = stage0 + stage * kStageBytes;
-              if constexpr (VAR & kVarNoLoad) {
-                ptx::mbar_arrive_a(full0 + stage * 8);
-              } else if constexpr (VAR & kVarNoB) {
-                ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kTileABytes);
-                ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.row0);
-              } else {
-                ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
-                ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.row0);
-                ptx::tma_load_3d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, tl.n0, tl.expert);
-              }
-            }
+    uint32_t armed = 0, armed_phase = 0;  // bit i: this warp has armed stage i / the phase bit of its last arming
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+      bool ok = true;
+      for (int32_t kb = tl.kb0; kb < tl.kb1; ++kb, ++g) {
+        if ((g & (kIssuers - 1)) == (uint32_t)warp) {
+          if (!wait_bar<false>(empty0 + stage * 8, phase ^ 1)) {
+            record_timeout(ctl, 1);
+            ok = false;
+            break;
           }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
+          armed |= 1u << stage;
+          armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+          if (lane == 0) {
+            const uint32_t dst = stage0 + stage * kStageBytes;
+            ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, kStageBytes);
+            ptx::tma_load_2d_a(dst, &map_a, full0 + stage * 8, kb * BK, tl.row0);
+            ptx::tma_load_3d_a(dst + kTileABytes, &map_b, full0 + stage * 8, kb * BK, tl.n0, tl.expert);
+          }
         }
-        if (!ok || ctl->abort_flag) break;
+        if (++stage == kRing) { stage = 0; phase ^= 1; }
       }
-      // Tail: the arrivals on the `empty` barriers are asynchronous and nobody waits for the last ones, so the
-      // CTA could exit (and the next kernel's CTA re-initialise barriers at the same shared-memory addresses) while
-      // such an arrival is still in flight.  Acquire every stage once more before leaving.
-      if (warp == 0 && !ctl->abort_flag) {
-        for (int i = 0; i < kStages; ++i) {
-          if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { record_timeout(ctl, 5); break; }
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-        }
+      if (!ok || ctl->abort_flag) break;
+    }
+    // After a time-out somewhere in the CTA: a CTA must not exit while bulk copies into its shared memory are in
+    // flight, so wait (20 ms at most per stage) for the loads this warp issued.
+    if (ctl->abort_flag) {
+      for (uint32_t i = 0; i < (uint32_t)kRing; ++i)
+        if (armed & (1u << i)) wait_bar<true>(full0 + i * 8, (armed_phase >> i) & 1u, 20000000ull);
+    }
+    // Tail: tcgen05.commit arrives on the `empty` barriers asynchronously and nobody waits for the last ones, so the
+    // CTA could exit (and the next kernel's CTA re-initialise barriers at the same shared-memory addresses) while
+    // such an arrival is still in flight.  Acquire every stage once more before leaving.
+    if (warp == 0 && !ctl->abort_flag) {
+      for (int i = 0; i < kRing; ++i) {
+        if (!wait_bar<false>(empty0 + stage * 8, phase ^ 1)) { record_timeout(ctl, 5); break; }
+        if (++stage == kRing) { stage = 0; phase ^= 1; }
       }
     }
-  } else if (warp < kFirstEpiWarp) {
-    // ===== MMA issuers (k-blocks alternate between the warps; each k-block has its own TMEM stage)
+  } else if (warp < 2 * kIssuers) {
+    // ===== MMA issuers (k-blocks alternate between the two warps; each k-block has its own TMEM stage)
     const uint32_t me = warp - kIssuers;
     constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
     const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
-    const bool active = (VAR & kVarLane0) ? lane == 0 : true;
-    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, turn = 0;
-    if (active) {
-      for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
-        bool ok = true;
-        int32_t kb_count = p.k_tiles;
-        if (p.k_splits > 1) {
-          const Tile tl = get_tile<GROUPED>(p, tile_start, t);
-          kb_count = tl.kb1 - tl.kb0;
-        }
-        for (int32_t kb = 0; kb < kb_count; ++kb) {
-          if (turn == me) {
-            if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) {
-              record_timeout(ctl, 2);
-              ok = false;
-              break;
-            }
-            if (!ptx::mbar_wait_a(full0 + stage * 8, phase)) {
-              record_timeout(ctl, 3);
-              ok = false;
-              break;
-            }
-            ptx::tc_fence_after();
-            if (lane == 0) {
-              // descriptors differ from stage 0's only in the 16-byte address field
-              const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
-              const uint64_t b_desc = a_desc + (kTileABytes >> 4);
-              const uint32_t d_tmem = tmem_base + acc * BN;
-              ptx::mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, 0);
-#pragma unroll
-              for (uint32_t k = 1; k < BK / 32; ++k) {
-                // 32 bytes further along K inside the swizzle atom: +2 in the address field
-                ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1);
-              }
-              if constexpr (!(VAR & kVarCommit1)) ptx::mma_commit_a(empty0 + stage * 8);
-              ptx::mma_commit_a(acc_full0 + acc * 8);
-            }
-          }
-          if (++turn == (uint32_t)kMmaWarps) turn = 0;
-          if (++stage == kStages) { stage = 0; phase ^= 1; }
-          if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
-        }
-        if (!ok || ctl->abort_flag) break;
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, g = 0;
+    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+      bool ok = true;
+      int32_t kb_count = p.k_tiles;
+      if (p.k_splits > 1) {
+        const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+        kb_count = tl.kb1 - tl.kb0;
       }
+      for (int32_t kb = 0; kb < kb_count; ++kb, ++g) {
+        if ((g & (kIssuers - 1)) == me) {
+          if (!wait_bar<false>(acc_empty0 + acc * 8, acc_phase ^ 1)) {
+            record_timeout(ctl, 2);
+            ok = false;
+            break;
+          }
+          if (!wait_bar<false>(full0 + stage * 8, phase)) {
+            record_timeout(ctl, 3);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          if (lane == 0) {
+            // descriptors differ from stage 0's only in the 16-byte address field
+            const uint64_t a_desc = desc0 + (uint64_t)(stage * (kStageBytes >> 4));
+            const uint64_t b_desc = a_desc + (kTileABytes >> 4);
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            ptx::mma_f8f6f4(d_tmem, a_desc, b_desc, idesc, 0);
+#pragma unroll
+            for (uint32_t k = 1; k < BK / 32; ++k) {
+              // 32 bytes further along K inside the swizzle atom: +2 in the address field
+              ptx::mma_f8f6f4(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, 1);
+            }
+            ptx::mma_commit_a(empty0 + stage * 8);
+            ptx::mma_commit_a(acc_full0 + acc * 8);
+          }
+        }
+        if (++stage == kRing) { stage = 0; phase ^= 1; }
+        if (++acc == kAccStages) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok || ctl->abort_flag) break;
     }
   } else {
-    // ===== promotion + epilogue; TMEM lane quarter = warp % 4, column half = (warp - first promotion warp) / 4
+    // ===== promotion + epilogue (warps 4..11); TMEM lane quarter = warp % 4, column half = (warp - 4) / 4
     const int q = warp & 3;
-    const int wi = warp - kFirstEpiWarp;
-    const int col0 = (wi >> 2) * kEpiCols;
+    const int col0 = ((warp - 2 * kIssuers) >> 2) * kEpiCols;
     const int r_in_tile = q * 32 + lane;
     uint32_t acc_stage = 0, acc_phase = 0;
-    uint32_t sm_stage = 0;  // kVarCommit1: the shared-memory stage of the k-block being promoted
     float2 acc[kEpiCols / 2];
-    uint32_t va[32], vb[32];
-    bool have_va = false;  // kVarPipe: va already holds (a load in flight of) the first 32 columns of the next k-block
     uint32_t push_epoch = 0;
     if constexpr (PUSH) push_epoch = *reinterpret_cast<const volatile uint32_t*>(p.push.ctl) + 1u;
-    const uint32_t tlane = tmem_base + ((uint32_t)(q * 32) << 16) + col0;
     for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       const int32_t row = tl.row0 + r_in_tile;
@@ -457,7 +440,6 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         sa_ring[u] = __ldg(sa_row + (int64_t)kc * p.sa_stride_k);
         sb_ring[u] = __ldg(sb_blk + (int64_t)kc * p.sb_stride_k);
       }
-      const bool more_tiles = t + (int32_t)gridDim.x < total_tiles;
       bool ok = true;
       for (int32_t kb0 = tl.kb0; kb0 < tl.kb1 && ok; kb0 += kScaleAhead) {
 #pragma unroll
@@ -470,71 +452,28 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             sa_ring[u] = __ldg(sa_row + (int64_t)kn * p.sa_stride_k);
             sb_ring[u] = __ldg(sb_blk + (int64_t)kn * p.sb_stride_k);
           }
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * BN + col0;
           const float2 scale2 = make_float2(scale, scale);
-          if constexpr (VAR & kVarPipe) {
-            if (!have_va) {
-              if (!ptx::mbar_wait_a(acc_full0 + acc_stage * 8, acc_phase)) {
-                record_timeout(ctl, 4);
-                ok = false;
-                break;
-              }
-              ptx::tc_fence_after();
-              if constexpr (VAR & kVarCommit1) {
-                if (wi == 0 && lane == 0) ptx::mbar_arrive_a(empty0 + sm_stage * 8);
-              }
-              ptx::tmem_ld_32x32(tlane + acc_stage * BN, va);
-            }
-            ptx::tmem_ld_wait(va);
-            ptx::tmem_ld_32x32(tlane + acc_stage * BN + 32, vb);
-            if constexpr (!(VAR & kVarNoFma)) fma32(acc, va, scale2);
-            ptx::tmem_ld_wait(vb);
-            // every TMEM read of this stage has landed: hand the stage back to the MMA warps
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_a(acc_empty0 + acc_stage * 8);
-            if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
-            if constexpr (VAR & kVarCommit1) { if (++sm_stage == kStages) sm_stage = 0; }
-            // start on the next k-block of this CTA (of the next tile, after the last one of this tile) if its sums are there
-            have_va = false;
-            if (kb + 1 < tl.kb1 || more_tiles) {
-              have_va = __all_sync(0xffffffffu, ptx::mbar_try_wait_a(acc_full0 + acc_stage * 8, acc_phase));
-              if (have_va) {
-                ptx::tc_fence_after();
-                if constexpr (VAR & kVarCommit1) {
-                  if (wi == 0 && lane == 0) ptx::mbar_arrive_a(empty0 + sm_stage * 8);
-                }
-                ptx::tmem_ld_32x32(tlane + acc_stage * BN, va);
-              }
-            }
-            if constexpr (!(VAR & kVarNoFma)) fma32(acc + 16, vb, scale2);
-          } else {
+          {
             if (!ptx::mbar_wait_a(acc_full0 + acc_stage * 8, acc_phase)) {
               record_timeout(ctl, 4);
               ok = false;
               break;
             }
             ptx::tc_fence_after();
-            if constexpr (VAR & kVarCommit1) {
-              if (wi == 0 && lane == 0) ptx::mbar_arrive_a(empty0 + sm_stage * 8);
-              if (++sm_stage == kStages) sm_stage = 0;
-            }
-            const uint32_t taddr = tlane + acc_stage * BN;
+            uint32_t va[32], vb[32];
             ptx::tmem_ld_32x32(taddr, va);
             ptx::tmem_ld_32x32(taddr + 32, vb);
             ptx::tmem_ld_wait(va);
             ptx::tmem_ld_wait(vb);
-            // every TMEM read of this stage has landed: hand the stage back to the MMA warps
+            // every TMEM read of this stage has landed: hand the stage back to the MMA warp
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_a(acc_empty0 + acc_stage * 8);
-            if constexpr (!(VAR & kVarNoFma)) {
-              fma32(acc, va, scale2);
-              fma32(acc + 16, vb, scale2);
-            } else {
-              acc[0].x += __uint_as_float(va[0] ^ vb[31]);
-            }
-            if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
+            fma32(acc, va, scale2);
+            fma32(acc + 16, vb, scale2);
           }
+          if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1; }
         }
       }
       if (!ok || ctl->abort_flag) break;
@@ -542,6 +481,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int32_t n_first = tl.n0 + col0;
         const int32_t tile_id = (tl.row0 / BM) * p.n_tiles + tl.n0 / BN;
         const int owner = tile_id % p.push.world;
+        const int wi = warp - 2 * kIssuers;
         uint32_t* stg = reinterpret_cast<uint32_t*>(smem + kStagingOffset) + wi * 32 * kStageWords;
         const int32_t row_base = tl.row0 + q * 32;  // the warp's rows are row_base + 0..31
         const uint32_t set = push_epoch & 1u;
@@ -973,15 +913,13 @@ int splitk_choice(int64_t M, int64_t N, int64_t K, int sm_count) {
   return splits < 2 ? 1 : (int)splits;
 }
 
-constexpr int kVarDefault = 0;
-
-template <bool GROUPED, bool PUSH, int VAR = kVarDefault>
+template <bool GROUPED, bool PUSH>
 int set_smem_attr_once() {
   static bool done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<GROUPED, PUSH, VAR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<GROUPED, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)(PUSH ? kSmemBytesPush : kSmemBytes));
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     done[dev] = true;
@@ -1054,14 +992,6 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     return SGLB200_OK;
   }
 
-  if (!grouped && !push) {
-    int pair_bn = 0;
-    if (const char* ev = getenv("SGLB200_GEMM_PAIR")) pair_bn = atoi(ev);
-    if (pair_bn == 128 || pair_bn == 256)
-      return pair_gemm(pair_bn, a, b, sa, sb, out, total_rows, N, K, lda, ldb, ldc, sa_stride_m, sa_stride_k, sb_stride_n,
-                       sb_stride_k, out_dtype, di.sm_count, stream);
-  }
-
   alignas(64) CUtensorMap map_a, map_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)total_rows};
@@ -1117,39 +1047,17 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     // an upper bound on the tile count without reading the device: every expert can add one ragged m-tile
     const int64_t max_tiles = ((total_rows + BM - 1) / BM + num_experts) * p.n_tiles;
     const int grid = (int)(max_tiles < di.sm_count ? max_tiles : di.sm_count);
-    fp8_block_gemm_kernel<true, false, kVarDefault><<<grid, threads_of(kVarDefault), kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
+    fp8_block_gemm_kernel<true, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
   } else if (push) {
     if (int rc = set_smem_attr_once<false, true>()) return rc;
     const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-    fp8_block_gemm_kernel<false, true, kVarDefault><<<grid, threads_of(kVarDefault), kSmemBytesPush, st>>>(map_a, map_b, p);
+    fp8_block_gemm_kernel<false, true><<<grid, kThreads, kSmemBytesPush, st>>>(map_a, map_b, p);
   } else {
     const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles * p.k_splits;
     const int grid = (int)(tiles < di.sm_count ? tiles : di.sm_count);
-    int var = kVarDefault;
-    if (const char* ev = getenv("SGLB200_GEMM_VAR")) var = atoi(ev);
-#define SGLB_DENSE_VAR(V)                                                                                          \
-  case V:                                                                                                          \
-    if (int rc = set_smem_attr_once<false, false, V>()) return rc;                                                 \
-    fp8_block_gemm_kernel<false, false, V><<<grid, threads_of(V), kSmemBytes, st>>>(map_a, map_b,                  \
-                                                                                    static_cast<const GemmParams&>(p)); \
-    break;
-    switch (var) {
-      SGLB_DENSE_VAR(0)
-      SGLB_DENSE_VAR(1)
-      SGLB_DENSE_VAR(3)
-      SGLB_DENSE_VAR(5)
-      SGLB_DENSE_VAR(7)
-      SGLB_DENSE_VAR(16)
-      SGLB_DENSE_VAR(32)
-      SGLB_DENSE_VAR(33)
-      SGLB_DENSE_VAR(64)
-      SGLB_DENSE_VAR(96)
-      SGLB_DENSE_VAR(97)
-      default:
-        return fail(SGLB200_ERR_SHAPE, "SGLB200_GEMM_VAR=%d is not built", var);
-    }
-#undef SGLB_DENSE_VAR
+    if (int rc = set_smem_attr_once<false, false>()) return rc;
+    fp8_block_gemm_kernel<false, false><<<grid, kThreads, kSmemBytes, st>>>(map_a, map_b, static_cast<const GemmParams&>(p));
     if (p.partial != nullptr) {
       SGLB_CHECK_LAUNCH("fp8_block_gemm_kernel");
       launch_splitk_reduce(p.partial, out, total_rows, N, ldc, p.k_splits, out_dtype, di.sm_count, stream);

@@ -2,14 +2,18 @@
 //
 //   out[m, n] = cast( sum_kb ( sum_{k in kb} a[m,k] * b[n,k] ) * sa[m,kb] * sb[n/128,kb] )
 //
-// Why pairs: an SM fills its shared memory from L2 at about 64 bytes per clock.  A 128 x 128 tile needs
-// (128 + 128) x 128 bytes per k-block for 256 clocks of tensor-core work, i.e. 128 B/clk at full rate, so the
-// single-CTA kernel of gemm.cu cannot keep the tensor core more than half busy however its warps are arranged.
-// Here two CTAs of a cluster (two SMs of one TPC) work on one 256 x BN tile: each CTA loads its own 128 rows of A
-// and only HALF of the B rows, and one tcgen05.mma.cta_group::2 issued by the even CTA reads both halves from both
-// shared memories.  Bytes per clock of tensor work per SM: BN = 128: (128 + 64) x 128 / 256 = 96;
-// BN = 256: (128 + 128) x 128 / 512 = 64.  No load is broadcast: every CTA fetches its own tiles with its own TMA
-// copies; only mbarrier arrivals cross between the two CTAs.
+// Why pairs: a 128 x 128 tile needs (128 + 128) x 128 bytes of operands per k-block for 256 clocks of tensor-core work,
+// 128 bytes per clock per SM from L2 at full rate.  Here two CTAs of a cluster (two SMs of one TPC) work on one
+// 256 x BN tile: each CTA loads its own 128 rows of A and only HALF of the B rows, and one tcgen05.mma.cta_group::2
+// issued by the even CTA reads both halves from both shared memories.  Bytes per clock of tensor work per SM:
+// BN = 128: (128 + 64) x 128 / 256 = 96; BN = 256: (128 + 128) x 128 / 512 = 64; BN = 256 also halves the MMA, commit
+// and barrier operations per flop.  No load is broadcast: every CTA fetches its own tiles with its own TMA copies; only
+// mbarrier arrivals cross between the two CTAs.
+// Measured on B200 (M = 8192, the five DeepSeek-V3 shapes): BN = 128 is level with the single-CTA kernel of gemm.cu
+// (1147-1725 against 1150-1717 TFLOP/s), BN = 256 behind it on four of five shapes: with the loads removed altogether
+// the single-CTA kernel gains only 15 %, so operand delivery is not what bounds this family of kernels; the per-k-block
+// hand-over of partial sums through TMEM is, and BN = 256 has only two TMEM stages to hide it.  The kernel is therefore
+// an explicit entry point (sglb200_fp8_blockwise_scaled_mm_pair), not the default.
 //
 // Per CTA, 384 threads, warp-specialised as in gemm.cu:
 //   warps 0-1  TMA producers (k-blocks alternate): A [128 x 128 B] and B [BN/2 x 128 B] per k-block into a ring of
@@ -29,7 +33,6 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
-#include <stdlib.h>
 
 #include "common.cuh"
 #include "ptx.cuh"
@@ -50,6 +53,7 @@ int pair_take_device_status() {
   }
   return v;
 }
+
 
 namespace {
 
@@ -177,6 +181,7 @@ fp8_block_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
   }
   if (warp < kProducers) {
     uint32_t stage = 0, phase = 0, g = 0;
+    uint32_t armed = 0, armed_phase = 0;  // bit i: this warp has armed stage i / the phase bit of its last arming
     for (int32_t t = pair; t < total_tiles; t += pairs) {
       int32_t row0, n0;
       tile_of(t, row0, n0);
@@ -189,6 +194,8 @@ fp8_block_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             ok = false;
             break;
           }
+          armed |= 1u << stage;
+          armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
           if (lane == 0) {
             const uint32_t dst = stage0 + stage * C::kStage;
             if (rank == 0) ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, 2 * C::kStage);  // both CTAs' bytes
@@ -200,6 +207,13 @@ fp8_block_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
         if (++stage == C::kStages) { stage = 0; phase ^= 1; }
       }
       if (!ok || ctl->abort_flag) break;
+    }
+    // After a time-out: no CTA may exit while bulk copies into its shared memory are in flight.  Both CTAs' copies
+    // are counted on the even CTA's `full` barriers, so the even CTA waits (20 ms at most per stage) for the stages it
+    // announced; the cluster barrier at the exit then holds the partner until that is done.
+    if (ctl->abort_flag && rank == 0) {
+      for (uint32_t i = 0; i < (uint32_t)C::kStages; ++i)
+        if (armed & (1u << i)) ptx::mbar_wait_inl_a(full0 + i * 8, (armed_phase >> i) & 1u, 20000000ull);
     }
     // the last arrivals on `empty` come from asynchronous commits: take every stage once more before leaving
     if (warp == 0 && !ctl->abort_flag) {
@@ -301,7 +315,10 @@ fp8_block_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
           if constexpr (C::kCols == 64) {
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(lead_acc_empty0 + acc_stage * 8);
+            if (lane == 0) {
+              if (rank == 0) ptx::mbar_arrive_a(acc_empty0 + acc_stage * 8);
+              else ptx::mbar_arrive_cluster(lead_acc_empty0 + acc_stage * 8);
+            }
             fma32p(acc, va, scale2);
             fma32p(acc + 16, vb, scale2);
           } else {
@@ -313,7 +330,10 @@ fp8_block_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __gr
             ptx::tmem_ld_wait(vb);
             ptx::tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(lead_acc_empty0 + acc_stage * 8);
+            if (lane == 0) {
+              if (rank == 0) ptx::mbar_arrive_a(acc_empty0 + acc_stage * 8);
+              else ptx::mbar_arrive_cluster(lead_acc_empty0 + acc_stage * 8);
+            }
             fma32p(acc + 32, va, scale2);
             fma32p(acc + 48, vb, scale2);
           }
@@ -413,4 +433,35 @@ int pair_gemm(int bn, const void* a, const void* b, const float* sa, const float
                           out_dtype, sm_count, stream);
 }
 
+
 }  // namespace sglb
+
+extern "C" int sglb200_fp8_blockwise_scaled_mm_pair(const void* a, const void* b, const float* sa, const float* sb,
+                                                    void* out, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                                    int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
+                                                    int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype,
+                                                    int tile_n, void* stream) {
+  using namespace sglb;
+  SGLB_REQUIRE(tile_n == 128 || tile_n == 256, SGLB200_ERR_SHAPE, "tile_n=%d: 128 or 256", tile_n);
+  SGLB_REQUIRE(M >= 0 && N >= 0 && K > 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  SGLB_REQUIRE(M < ((int64_t)1 << 31) - 512 && N < ((int64_t)1 << 31) - 512 && K < ((int64_t)1 << 31) - 512,
+               SGLB200_ERR_SHAPE, "a dimension exceeds 2^31");
+  SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE,
+               "out_dtype=%d: only bf16 (0) and f16 (1)", out_dtype);
+  SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, SGLB200_ERR_SHAPE, "K=%lld must be a multiple of 16, N=%lld of 8", (long long)K,
+               (long long)N);
+  if (M == 0 || N == 0) return SGLB200_OK;
+  SGLB_REQUIRE(a && b && sa && sb && out, SGLB200_ERR_NULL, "a/b/sa/sb/out must not be NULL");
+  SGLB_REQUIRE(lda >= K && lda % 16 == 0 && ldb >= K && ldb % 16 == 0 && ldc >= N && ldc % 8 == 0, SGLB200_ERR_ALIGN,
+               "lda=%lld ldb=%lld (>= K, multiples of 16) ldc=%lld (>= N, multiple of 8)", (long long)lda, (long long)ldb,
+               (long long)ldc);
+  SGLB_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(out, 16) && aligned(sa, 4) && aligned(sb, 4), SGLB200_ERR_ALIGN,
+               "a, b and out must be 16-byte aligned, the scales 4-byte aligned");
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
+               di.cc_major, di.cc_minor);
+  SGLB_REQUIRE(di.sm_count >= 2, SGLB200_ERR_SHAPE, "the CTA-pair kernel needs at least two SMs");
+  return pair_gemm(tile_n, a, b, sa, sb, out, M, N, K, lda, ldb, ldc, sa_stride_m, sa_stride_k, sb_stride_n, sb_stride_k,
+                   out_dtype, di.sm_count, stream);
+}

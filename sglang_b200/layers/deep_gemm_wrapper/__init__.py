@@ -5,7 +5,8 @@ unused."""
 
 from __future__ import annotations
 
-from typing import Tuple
+from contextlib import contextmanager
+from typing import Optional, Tuple
 
 import torch
 
@@ -47,3 +48,19 @@ def grouped_gemm_nt_f8f8bf16_masked(lhs: Tuple[torch.Tensor, torch.Tensor], rhs:
             a.stride(1), w.stride(1), w.stride(0), out.stride(1), a_s.stride(0), a_s.stride(1), a_s.stride(2), w_s.stride(0),
             w_s.stride(1), w_s.stride(2), dtype_code(out.dtype), torch.cuda.current_stream(a.device).cuda_stream),
             "grouped_gemm_nt_f8f8bf16_masked")
+
+
+@contextmanager
+def configure_deep_gemm_num_sms(num_sms: Optional[int]):
+    """Run the GEMMs inside the block on at most ``num_sms`` SMs (``entrypoint.py:94-104``): the way the reference keeps
+    SMs free for a communication kernel that overlaps a GEMM.  ``None`` changes nothing."""
+    if num_sms is None:
+        yield
+        return
+    L = lib()
+    original = L.sglb200_get_num_sms()
+    check(L.sglb200_set_num_sms(int(num_sms)), "set_num_sms")
+    try:
+        yield
+    finally:
+        L.sglb200_set_num_sms(original)

@@ -96,29 +96,12 @@ def assert_gemm_close(out, ref, what="", allow_one_ulp=False):
 
 
 def row_parallel_reference(x, wq, ws, world):
-    """Oracle of the row-parallel linear: every rank quantises its K-slice, rounds its partial product to the output
-    type, and the partial products are added (``python/sglang/srt/layers/linear.py:1361-1386``); fp32 sum here."""
+    """Oracle of the row-parallel linear (``oracle.row_parallel_reference``)."""
     import oracle
-    K = x.shape[1]
-    kr = K // world
-    ref = torch.zeros(x.shape[0], wq.shape[0], dtype=torch.float32)
-    for r in range(world):
-        q, s = oracle.per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous(), 128)
-        ref += oracle.w8a8_block_fp8_matmul(q, wq[:, r * kr:(r + 1) * kr].contiguous(), s,
-                                            ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous()).float()
-    return ref.to(x.dtype)
+    return oracle.row_parallel_reference(x, wq, ws, world)
 
 
 def expert_parallel_reference(x, w1q, w2q, w1s, w2s, topk_w, topk_ids, world):
-    """Oracle of the expert-parallel MoE: every rank adds up the contributions of ITS experts to a token and returns
-    that partial row in the activation type; the partial rows are added at the source in fp32
-    (``python/sglang/srt/layers/moe/token_dispatcher/deepep.py:466-492``)."""
+    """Oracle of the expert-parallel MoE (``oracle.expert_parallel_reference``)."""
     import oracle
-    E = w1q.shape[0]
-    el = E // world
-    total = torch.zeros(x.shape[0], w2q.shape[1], dtype=torch.float32)
-    for r in range(world):
-        local = torch.where((topk_ids // el) == r, topk_ids, torch.full_like(topk_ids, -1))
-        if bool((local >= 0).any()):
-            total += oracle.fused_experts_block_fp8(x, w1q, w2q, w1s, w2s, topk_w, local).float()
-    return total.to(x.dtype)
+    return oracle.expert_parallel_reference(x, w1q, w2q, w1s, w2s, topk_w, topk_ids, world)

@@ -36,7 +36,7 @@ def test_library_exports_every_declared_symbol(built_lib):
     for name in declared:
         assert hasattr(handle, name), f"{name} is declared in include/sglb200.h but not exported"
     assert sorted(SIGNATURES) == declared, "ctypes signatures and header are out of step"
-    assert handle.sglb200_version().decode() == "0.1"
+    assert handle.sglb200_version().decode() == "0.2"
     assert handle.sglb200_status_string(0).decode() == "ok"
     assert "alignment" in handle.sglb200_status_string(-2).decode()
 
@@ -175,3 +175,14 @@ def test_peer_ep_exchange_refuses_a_receive_buffer_that_could_overflow():
     from sglang_b200.distributed.peer_ep import PeerEpExchange
     with pytest.raises(ValueError, match="capacity"):
         PeerEpExchange(capacity=10, hidden=256, topk=2, m_max=11, device="cpu")
+
+
+def test_num_sms_limit_round_trip(built_lib):
+    """The SM bound is plain host state: settable and readable without a GPU; a negative value is refused."""
+    from sglang_b200._lib import lib
+    L = lib()
+    assert L.sglb200_set_num_sms(-1) == -1
+    assert L.sglb200_set_num_sms(132) == 0
+    assert L.sglb200_get_num_sms() == 132
+    assert L.sglb200_set_num_sms(0) == 0
+    assert L.sglb200_get_num_sms() != 132
