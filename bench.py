@@ -14,9 +14,13 @@ Synthetic data: activations ~N(0,1) with 1% of entries x50, weights ~N(0, 0.02) 
 Prints ONE JSON line.  `value` = TFLOP/s of the whole step (2*M*N*K summed over the shapes, inputs
 resident in HBM); `e2e` = the same through Fp8LinearMethod.apply from pinned host buffers with the
 result copied back; `roofline` = the GEMM kernel alone (CUDA events around each launch) against
-2 x the measured dense bf16 rate; `quant` = the per-token-group quant kernel on M=16384 x 7168
-against measured HBM bandwidth; `cpu_baseline` = the reference's CPU kernel (or the oracle port)
-on a bounded sample.  `--impl reference` times only that CPU path.
+2 x the measured dense bf16 rate, with the other kernels the path is judged on under `roofline.others`
+(the per-token-group quant kernel on M=16384 x 7168 against measured HBM bandwidth, before and after
+the GEMM sweep; the UE8M0 GEMM; the fused MoE); `breakdown` = device time per kind of kernel and the
+host gap of one step; `cpu_baseline` = the reference's CPU kernel (or the oracle port) on the same five
+shapes.  With N > 1: `parity` = one small tensor-parallel and one small expert-parallel layer checked
+against the CPU oracle on rank 0 before anything is timed, for the NCCL path and for the peer-memory
+paths.  `--impl reference` times only the CPU path.
 """
 
 from __future__ import annotations
@@ -233,7 +237,8 @@ def moe_section(torch, dev, gen, Ms=(256, 4096, 16384), E=256, topk=8, H=7168, I
 def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5):
     """Tensor-parallel decoder projections at the Llama-3-70B shape (hidden 8192, intermediate 28672, 64 q / 8 kv
     heads of 128): column-parallel QKV and gate_up, row-parallel o and down, each followed by an NCCL all-reduce of the
-    [M, 8192] bf16 output.  One step = the four linears of a layer on M tokens; device time, max over ranks."""
+    [M, 8192] bf16 output (none at tp1).  One step = the four linears of a layer on M tokens; device time, max over
+    ranks."""
     from sglang_b200.layers.quantization import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
     layers_ = [("qkv", 10240, 8192, "column"), ("o", 8192, 8192, "row"), ("gate_up", 57344, 8192, "column"),
                ("down", 8192, 28672, "row")]
@@ -246,32 +251,38 @@ def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5):
         built.append((mode, w, ws, x))
         flops += 2.0 * M * N * K
 
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     def step():
         for mode, w, ws, x in built:
             q, sc = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
             y = w8a8_block_fp8_matmul(q, w, sc, ws, [128, 128], torch.bfloat16)
-            if mode == "row":
+            if mode == "row" and world > 1:
                 dist.all_reduce(y)
 
     for _ in range(3):
         step()
-    dist.barrier()
-    torch.cuda.synchronize()
+    sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(iters):
         step()
     e1.record()
-    dist.barrier()
-    torch.cuda.synchronize()
+    sync()
     ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     return {"workload": f"Llama-3-70B layer projections, M={M}, tp{world}: qkv/gate_up column-parallel, o/down "
                         "row-parallel + NCCL all-reduce", "ms_per_layer": float(ms),
-            "tflops": flops / (float(ms) * 1e-3) / 1e12, "allreduce_bytes_per_layer": 2 * M * 8192 * 2}
+            "tflops": flops / (float(ms) * 1e-3) / 1e12,
+            "allreduce_bytes_per_layer": 2 * M * 8192 * 2 if world > 1 else 0}
 
 
-def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk=8, H=7168, I=2048, iters=5):
+def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk=8, H=7168, I=2048, iters=5,
+                   decode_graph=True):
     """Expert-parallel fused MoE at the DeepSeek-V3 layer shape: E / ep experts and M_total / ep tokens per rank,
     all-to-all dispatch of e4m3 rows + scales, local grouped GEMMs, all-to-all combine.  Device time, max over ranks."""
     from sglang_b200.distributed import PeerEpExchange, ep_fused_experts, ep_fused_experts_peer
@@ -325,6 +336,8 @@ def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk
         res["peer"] = {"ms": float(ms_p), "tflops": flops / (float(ms_p) * 1e-3) / 1e12, "rel_l2_vs_nccl": err,
                        "ms_with_separate_quant_launch": float(ms_u),
                        "how": "quantise-and-dispatch / combine kernels over CUDA-IPC peer memory, device-side row counts"}
+        if not decode_graph or m_loc < 64:
+            return res
         # decode size: 64 tokens per rank.  The peer version is one CUDA graph (nothing on its path synchronises); the
         # NCCL version needs the received-row counts on the host and cannot be captured.
         md = 64
@@ -361,6 +374,79 @@ def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk
     finally:
         ex.close()
     return res
+
+
+def parity_section(torch, dist, dev, world, rank):
+    """N > 1: one small row-parallel linear and one small expert-parallel layer on all ranks, checked on rank 0 against
+    the CPU oracle evaluated the way the sharding defines the arithmetic (every rank rounds its partial result to bf16,
+    the partial results are added).  Bars: rel-L2 <= 1e-2 and max-abs <= 2e-2 x RMS(reference).  The oracle is used here
+    as the checker only, outside every timed region."""
+    from sglang_b200._lib import lib
+    from sglang_b200.distributed import (PeerEpExchange, PeerExchange, RowParallelBlockFp8Linear, ep_fused_experts,
+                                         ep_fused_experts_peer, fused_row_parallel_linear)
+    import oracle
+
+    def verdict(out, ref):
+        o, r = out.float().cpu().double(), ref.float().double()
+        rel = float((o - r).norm() / r.norm().clamp(min=1e-30))
+        mx = float((o - r).abs().max() / r.pow(2).mean().sqrt().clamp(min=1e-30))
+        return {"rel_l2": rel, "max_abs_over_rms": mx, "pass": bool(rel <= 1e-2 and mx <= 2e-2)}
+
+    res = {}
+    g = torch.Generator().manual_seed(4321)  # the same inputs on every rank
+    M, N, K = 192, 1024, 2048
+    x = torch.randn(M, K, generator=g).bfloat16()
+    wq, ws = oracle.block_quant_weight(torch.randn(N, K, generator=g) * 0.05)
+    kr = K // world
+    xr = x[:, rank * kr:(rank + 1) * kr].contiguous().to(dev)
+    layer = RowParallelBlockFp8Linear(wq.to(dev), ws.to(dev), rank, world)
+    outs = {"tp_nccl_allreduce": layer(xr)}
+    from sglang_b200.distributed import row_parallel_linear_overlapped
+    outs["tp_nccl_overlapped_chunks"] = row_parallel_linear_overlapped(xr, layer.weight, layer.weight_scale_inv, chunk_rows=128)
+    ex = PeerExchange(slot_elems=M * N)
+    try:
+        outs["tp_peer_one_shot"] = fused_row_parallel_linear(ex, xr, layer.weight, layer.weight_scale_inv, two_shot=False)
+        if -(-M // 128) * -(-N // 128) >= world:
+            outs["tp_peer_two_shot"] = fused_row_parallel_linear(ex, xr, layer.weight, layer.weight_scale_inv, two_shot=True)
+        torch.cuda.synchronize()
+    finally:
+        ex.close()
+    # expert parallel: E experts over the ranks, 48 tokens per rank
+    E, topk, H, I, m_loc = 16, 4, 512, 256, 48
+    w1 = [oracle.block_quant_weight(torch.randn(2 * I, H, generator=g) * 0.05) for _ in range(E)]
+    w2 = [oracle.block_quant_weight(torch.randn(H, I, generator=g) * 0.05) for _ in range(E)]
+    w1q, w1s = torch.stack([w[0] for w in w1]), torch.stack([w[1] for w in w1])
+    w2q, w2s = torch.stack([w[0] for w in w2]), torch.stack([w[1] for w in w2])
+    gr = torch.Generator().manual_seed(100 + rank)
+    xm = torch.randn(m_loc, H, generator=gr).bfloat16()
+    tw, ti = torch.topk(torch.softmax(torch.randn(m_loc, E, generator=gr), -1), topk)
+    el = E // world
+    lo, hi = rank * el, (rank + 1) * el
+    loc = [t[lo:hi].to(dev) for t in (w1q, w2q, w1s, w2s)]
+    ep_outs = {"ep_nccl_all_to_all": ep_fused_experts(xm.to(dev), loc[0], loc[1], loc[2], loc[3], tw.to(dev),
+                                                      ti.to(torch.int32).to(dev), rank, world)}
+    epx = PeerEpExchange(capacity=world * m_loc, hidden=H, topk=topk, m_max=m_loc)
+    try:
+        ep_outs["ep_peer_dispatch_combine"] = ep_fused_experts_peer(epx, xm.to(dev), loc[0], loc[1], loc[2], loc[3],
+                                                                    tw.to(dev), ti.to(torch.int32).to(dev))
+        torch.cuda.synchronize()
+    finally:
+        epx.close()
+    status = lib().sglb200_read_device_status()
+    dist.barrier()
+    if rank == 0:  # the oracle runs after all device work: the peer exchanges assume ranks in step
+        ref = oracle.row_parallel_reference(x, wq, ws, world)
+        for k, v in outs.items():
+            res[k] = verdict(v, ref)
+        ref_ep = oracle.expert_parallel_reference(xm, w1q, w2q, w1s, w2s, tw, ti, world)
+        for k, v in ep_outs.items():
+            res[k] = verdict(v, ref_ep)
+        res["device_status"] = status
+        res["shapes"] = {"tp": [M, N, K], "ep": {"experts": E, "topk": topk, "hidden": H, "intermediate": I,
+                                                "tokens_per_rank": m_loc}}
+        res["pass"] = bool(all(v["pass"] for k, v in res.items() if isinstance(v, dict) and "pass" in v) and status == 0)
+    dist.barrier()
+    return res if rank == 0 else None
 
 
 def decode_section(torch, dev, peaks, shapes=None, ms=(1, 16, 64)):
@@ -493,12 +579,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=8192, help="tokens per step")
-    ap.add_argument("--cpu-m", type=int, default=1024, help="rows of the CPU-baseline sample")
+    ap.add_argument("--cpu-m", type=int, default=0, help="rows of the CPU arm (0: the same M as the GPU arm)")
+    ap.add_argument("--overlap", type=int, default=1, help="N > 1: all-reduce of a row chunk overlaps the next chunk's GEMM")
+    ap.add_argument("--chunk-rows", type=int, default=2048, help="rows per chunk of the overlapped row-parallel linear")
+    ap.add_argument("--comm-sms", type=int, default=16, help="SMs the GEMMs leave free for NCCL while overlapping")
+    ap.add_argument("--nccl-max-ctas", type=int, default=16, help="upper bound on NCCL's CTAs per collective (0: NCCL's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE section (11.3 GB of expert weights)")
-    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant", "ue8m0", "decode"],
-                    help="profiling aid: run only the linear sweep ('gemm'), the quant bandwidth case, the UE8M0 sweep "
-                         "or the decode-size section (with --shape and --m for one case)")
+    ap.add_argument("--only", default="all", choices=["all", "gemm", "quant", "ue8m0", "decode", "moe"],
+                    help="profiling aid: run only the linear sweep ('gemm'), the quant bandwidth case, the UE8M0 sweep, "
+                         "the decode-size section (with --shape and --m for one case) or the fused MoE at --m tokens")
+    ap.add_argument("--moe-experts", type=int, default=256, help="profiling aid for --only moe: number of experts")
     ap.add_argument("--shape", default=None, help="profiling aid: restrict the sweep to one layer name")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -510,10 +601,13 @@ def main():
               "parallelism": f"tp{world}", "block": [128, 128], "group": 128,
               "l2": "working set per step (weights 555 MB + activations) exceeds the 126 MB L2; no explicit flush"}
 
+    cpu_m = args.cpu_m if args.cpu_m > 0 else args.m
     if args.impl == "reference":
         if rank != 0:
             return
-        cb = cpu_arm(args.steps, args.warmup, args.cpu_m)
+        cb = cpu_arm(args.steps, args.warmup, cpu_m)
+        if cb["M_sample"] != args.m:  # the torch-native port is too slow for the full M: say so in the config
+            config["M_sample"] = cb["M_sample"]
         line = {"metric": METRIC, "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": cb["ms_per_pass"], "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config,
@@ -525,29 +619,45 @@ def main():
 
     import torch
     import torch.distributed as dist
-    from sglang_b200.layers.quantization import (Fp8Config, Fp8LinearMethod, pack_ue8m0_scales,
-                                                 sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul,
-                                                 w8a8_block_fp8_matmul_ue8m0)
+    from sglang_b200.layers.quantization import (Fp8Config, Fp8LinearMethod, block_quant_weight_fp8, pack_ue8m0_scales,
+                                                 per_block_cast_to_fp8, sglang_per_token_group_quant_fp8,
+                                                 w8a8_block_fp8_matmul, w8a8_block_fp8_matmul_ue8m0)
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (no CPU fallback exists for the product path)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        opts = None
+        if args.nccl_max_ctas > 0:
+            try:  # fewer, not more, CTAs per collective: the GEMMs running beside it keep the other SMs
+                opts = dist.ProcessGroupNCCL.Options()
+                opts.config.max_ctas = args.nccl_max_ctas
+            except Exception:  # noqa: BLE001 - an older torch without the config field: NCCL's default
+                opts = None
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     peaks = load_peaks()
     M = args.m
+    parity = None
+    if world > 1 and args.only == "all":
+        try:
+            parity = parity_section(torch, dist, dev, world, rank)
+        except Exception as e:  # noqa: BLE001 - reported, never hidden: a failed check shows up as pass = false
+            parity = {"pass": False, "error": f"{type(e).__name__}: {e}"}
+    if args.only == "moe":
+        gen_m = torch.Generator(device=dev).manual_seed(0)
+        print(json.dumps({"metric": METRIC, "only": "moe",
+                          "moe": moe_section(torch, dev, gen_m, Ms=(args.m,), E=args.moe_experts)}))
+        return
     if args.only == "decode":
         sel = [sh for sh in SHAPES if args.shape in (None, sh[0])]
         ms_sel = (args.m,) if args.m <= 64 else (1, 16, 64)
         print(json.dumps({"metric": METRIC, "only": "decode", "decode": decode_section(torch, dev, peaks, sel, ms_sel)}))
         return
 
-    # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed between launches
-    # Runs first, on a GPU that is not yet at its power cap: the kernel is within 15 % of being issue-bound, so right
-    # after the GEMM sweeps (SM clock down to ~1.3 GHz under sw_power_cap) it measures 3.1-4.8 TB/s instead of 5.4-5.5.
-    quant = None
-    if rank == 0 and args.only not in ("gemm", "ue8m0"):
+    # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed between launches.  Measured twice:
+    # before the GEMM sweep (GPU not yet at its power cap) and after it (SM clock pulled down under sw_power_cap).
+    def quant_case(when):
         gen_q = torch.Generator(device=dev).manual_seed(1)
         sampler_q = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
         xq = torch.randn(16384, 7168, device=dev, generator=gen_q)
@@ -567,31 +677,21 @@ def main():
         clocks_q = sampler_q.stop()
         qbytes = 16384 * 7168 * 3 + 16384 * 56 * 4
         qms = statistics.median(times)
-        quant = {"workload": "per_token_group_quant_fp8 M=16384 K=7168 bf16 -> e4m3 + f32 column-major scales",
-                 "bytes": qbytes, "ms": qms, "gbs": qbytes / (qms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
-                 "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                 "l2": "256 MB buffer zeroed between launches", "clocks": clocks_q, "launches": len(times)}
-        del xq, flush
+        mhz = clocks_q.get("sm_mhz")
+        return {"workload": "per_token_group_quant_fp8 M=16384 K=7168 bf16 -> e4m3 + f32 column-major scales",
+                "when": when, "bytes": qbytes, "ms": qms, "gbs": qbytes / (qms * 1e-3) / 1e9,
+                "peak_gbs": peaks["hbm_gbs"], "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                "peak_source": peaks["source"], "l2": "256 MB buffer zeroed between launches", "clocks": clocks_q,
+                "us_x_sm_mhz": qms * 1e3 * mhz if mhz else None, "launches": len(times)}
 
+    quant = None
+    if rank == 0 and args.only not in ("gemm", "ue8m0"):
+        quant = quant_case("before the GEMM sweep")
 
     # ---- synthetic layers, sharded for this rank
     method = Fp8LinearMethod(Fp8Config(), tp_size=world)
     layers = []
     gen = torch.Generator(device=dev).manual_seed(0)
-
-    def block_quant(w, ue8m0=False):
-        n, k = w.shape
-        n_p, k_p = -(-n // 128) * 128, -(-k // 128) * 128
-        wp = torch.zeros(n_p, k_p, device=dev)
-        wp[:n, :k] = w
-        v = wp.view(n_p // 128, 128, k_p // 128, 128)
-        s = v.abs().amax(dim=(1, 3), keepdim=True) / 448.0
-        s = torch.where(s == 0, torch.ones_like(s), s)
-        if ue8m0:  # power-of-two block scales (a UE8M0 checkpoint)
-            mant, exp = torch.frexp(s)
-            s = torch.ldexp(torch.ones_like(s), torch.where(mant == 0.5, exp - 1, exp))
-        q = (v / s).clamp(-448, 448).to(torch.float8_e4m3fn).view(n_p, k_p)[:n, :k].contiguous()
-        return q, s.view(n_p // 128, k_p // 128).contiguous()
 
     total_flops = 0.0
     shapes = [s for s in SHAPES if args.shape in (None, s[0])]
@@ -605,8 +705,9 @@ def main():
         if world > 1 and mode == "row":
             k_loc = K // world
         w = torch.randn(n_loc, k_loc, device=dev, generator=gen) * 0.02
-        wq, ws = block_quant(w)
-        wq_u, ws_u = block_quant(w, ue8m0=True)
+        wq, ws = block_quant_weight_fp8(w)
+        wq_u, ws_u = per_block_cast_to_fp8(w)  # power-of-two block scales (a UE8M0 checkpoint)
+        ws_u = ws_u.contiguous()
         del w
         layer = torch.nn.Module()
         method.create_weights(layer, k_loc, [n_loc], K, N, torch.bfloat16, device=dev)
@@ -617,8 +718,24 @@ def main():
         layers.append({"name": name, "N": N, "K": K, "mode": mode, "n_loc": n_loc, "k_loc": k_loc, "layer": layer,
                        "x": x, "gemm_ms": [], "wq_u": wq_u, "ws_u": pack_ue8m0_scales(ws_u), "ev_u": []})
 
+    overlap = world > 1 and bool(args.overlap)
+    if overlap:
+        from sglang_b200.distributed import row_parallel_linear_overlapped
+        from sglang_b200.layers.deep_gemm_wrapper import configure_deep_gemm_num_sms
+        sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
+        config["step"] = (f"row-parallel layers in chunks of {args.chunk_rows} rows, the NCCL all-reduce of a chunk overlaps "
+                          f"the next chunk's GEMM; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs, NCCL on at most "
+                          f"{args.nccl_max_ctas} CTAs")
+    elif world > 1:
+        config["step"] = "NCCL all-reduce after each row-parallel GEMM, same stream"
+
     def step(record=False):
         for L in layers:
+            if overlap and L["mode"] == "row":
+                with configure_deep_gemm_num_sms(sm_total - args.comm_sms):
+                    y = row_parallel_linear_overlapped(L["x"], L["layer"].weight, L["layer"].weight_scale_inv,
+                                                       chunk_rows=args.chunk_rows)
+                continue
             q, s = sglang_per_token_group_quant_fp8(L["x"], 128, column_major_scales=True, scale_tma_aligned=True)
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -630,6 +747,50 @@ def main():
             if world > 1 and L["mode"] == "row":
                 dist.all_reduce(y)
         return y
+
+    def breakdown_pass(n_steps=3):
+        """Device time per kind of kernel for one step in the plain order (quant, GEMM, then the all-reduce on the same
+        stream), CUDA events around every launch; and the host time to enqueue a step."""
+        evs = {"quant": [], "gemm": [], "allreduce": []}
+
+        def mark(kind, fn):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn()
+            e1.record()
+            evs[kind].append((e0, e1))
+            return out
+
+        def plain_step():
+            for L in layers:
+                q, s = mark("quant", lambda: sglang_per_token_group_quant_fp8(L["x"], 128, column_major_scales=True,
+                                                                              scale_tma_aligned=True))
+                y = mark("gemm", lambda: w8a8_block_fp8_matmul(q, L["layer"].weight, s, L["layer"].weight_scale_inv,
+                                                               [128, 128], torch.bfloat16))
+                if world > 1 and L["mode"] == "row":
+                    mark("allreduce", lambda: dist.all_reduce(y))
+
+        plain_step()
+        fence()
+        for k in evs:
+            evs[k].clear()
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        h0 = time.perf_counter()
+        for _ in range(n_steps):
+            plain_step()
+        host_ms = (time.perf_counter() - h0) * 1e3 / n_steps
+        b1.record()
+        fence()
+        out = {k + "_ms": sum(a.elapsed_time(b) for a, b in v) / n_steps for k, v in evs.items()}
+        t = torch.tensor([b0.elapsed_time(b1) / n_steps, out["quant_ms"], out["gemm_ms"], out["allreduce_ms"], host_ms],
+                         device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms, qm, gm, am, hm = (float(v) for v in t)
+        return {"order": "plain (no overlap), max over ranks", "step_ms": step_ms, "quant_ms": qm, "gemm_ms": gm,
+                "allreduce_ms": am, "host_gap_ms": step_ms - (qm + gm + am), "host_enqueue_ms": hm,
+                "launches_per_step": sum(len(v) for v in evs.values()) // n_steps}
 
     def fence():
         if world > 1:
@@ -663,9 +824,45 @@ def main():
     ms_per_step = float(ms) / main_steps
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
+    breakdown = None
+    if args.only in ("all", "gemm"):
+        breakdown = breakdown_pass()
+        if overlap:
+            breakdown["overlap_saves_ms"] = breakdown["step_ms"] - ms_per_step
+        if world == 1:
+            # the same step as one replayed CUDA graph: what is left of the host gap when nothing is launched from Python
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                step()
+            graph.replay()
+            torch.cuda.synchronize()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record()
+            for _ in range(main_steps):
+                graph.replay()
+            g1.record()
+            torch.cuda.synchronize()
+            breakdown["graph_replay_ms_per_step"] = g0.elapsed_time(g1) / main_steps
+            del graph
+            # host microseconds of one Fp8LinearMethod.apply call (allocation, checks, tensor maps, two launches)
+            torch.cuda.synchronize()
+            h0 = time.perf_counter()
+            for _ in range(20):
+                method.apply(layers[1]["layer"], layers[1]["x"][:256])
+            breakdown["host_us_per_apply_call"] = (time.perf_counter() - h0) * 1e6 / 20
+            torch.cuda.synchronize()
+
     # GEMM kernel alone: CUDA events around every launch in the timed region
     gemm_ms, gemm_flops, per_shape = 0.0, 0.0, {}
     for L in layers:
+        if not L["ev"]:
+            continue
         t = [a.elapsed_time(b) for a, b in L["ev"]]
         f = 2.0 * M * L["n_loc"] * L["k_loc"]
         gemm_ms += sum(t)
@@ -674,16 +871,18 @@ def main():
                                 "gemm_tflops": f / (statistics.median(t) * 1e-3) / 1e12}
     fp8_peak = 2.0 * peaks["bf16_tflops_sustained"]
     achieved = gemm_flops / (gemm_ms * 1e-3) / 1e12
-    # DRAM traffic per launch: algorithmic operand + output bytes x 1.05, the read+write / algorithmic ratio of the
-    # ncu capture in profiles/gemm_fp8_block_gemm_M2048_N7168_K16384.md (189.0 MB measured, 180.4 MB algorithmic)
+    # DRAM traffic per launch: algorithmic operand + output bytes x 1.05, the read + write / algorithmic ratio of one ncu
+    # capture of this kernel at M = 2048, N = 7168, K = 16384 (189.0 MB measured, 180.4 MB algorithmic), scaled up
     alg_bytes = sum(L["n_loc"] * L["k_loc"] + M * L["k_loc"] + 2.0 * M * L["n_loc"] for L in layers) / len(layers)
     roofline = {"bound": "tensor", "achieved": achieved, "peak": fp8_peak, "unit": "TFLOP/s",
                 "frac": achieved / fp8_peak, "traffic": 1.05 * alg_bytes,
                 "traffic_note": "bytes per launch averaged over the layers; ncu ratio 1.05 on a smaller M scaled up",
                 "kernel": "fp8_block_gemm_kernel",
                 "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
-                "frac_of_nominal_fp8": achieved / 4500.0, "launches": main_steps * len(layers),
-                "avg_launch_ms": gemm_ms / (main_steps * len(layers))}
+                "frac_of_nominal_fp8": achieved / 4500.0, "launches": sum(len(L["ev"]) for L in layers),
+                "avg_launch_ms": gemm_ms / max(1, sum(len(L["ev"]) for L in layers)), "others": []}
+    if overlap:
+        roofline["note"] = "column-parallel and replicated layers only: the row-parallel GEMMs run in chunks beside NCCL"
 
     # ---- the same sweep on a UE8M0 checkpoint (power-of-two weight block scales, power-of-two activation group
     # scales): the tensor core applies the scales itself (tcgen05.mma kind::mxf8f6f4.block_scale)
@@ -736,12 +935,26 @@ def main():
                               "frac_of_nominal_fp8": ach_u / 4500.0, "kernel": "fp8_ue8m0_gemm_kernel"},
                  "per_shape": shp, "clocks": clocks_u, "gpu_launches": args.steps * len(layers) * 2}
 
+    quant_after = None
+    if rank == 0 and args.only in ("all", "quant"):
+        quant_after = quant_case("after the GEMM sweeps")
+    for qc in (quant, quant_after):
+        if qc is not None:
+            roofline["others"].append({"kernel": "group_quant16_kernel", "bound": "hbm", "achieved": qc["gbs"],
+                                       "peak": qc["peak_gbs"], "unit": "GB/s", "frac": qc["frac"], "when": qc["when"],
+                                       "us": qc["ms"] * 1e3, "us_x_sm_mhz": qc["us_x_sm_mhz"], "clocks": qc["clocks"],
+                                       "workload": "M=16384 K=7168 bf16 -> e4m3 + f32 scales (355.99 MB)"})
+    if ue8m0 is not None:
+        roofline["others"].append(dict(ue8m0["roofline"], workload="the same sweep on a UE8M0 checkpoint",
+                                       note="outputs may differ from the oracle by one bf16 ulp (the K loop is summed "
+                                            "inside the tensor core); rel-L2 bar unchanged"))
+
     if args.only != "all":
         if rank == 0:
             print(json.dumps({"metric": METRIC, "only": args.only, "value": value, "unit": "TFLOP/s", "n_gpus": world,
                               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "config": config,
                               "clocks": clocks, "roofline": roofline, "quant": quant, "per_shape": per_shape,
-                              "ue8m0": ue8m0}))
+                              "ue8m0": ue8m0, "breakdown": breakdown}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -754,6 +967,34 @@ def main():
         except Exception as e:  # noqa: BLE001 - the headline must not depend on this section
             moe = {"error": f"{type(e).__name__}: {e}"}
         torch.cuda.empty_cache()
+        for case in (moe.get("cases") or []):
+            for ck in ("fp32_scales", "ue8m0"):
+                roofline["others"].append({"kernel": f"fused_experts ({ck}), nine launches", "bound": "tensor",
+                                           "achieved": case[ck]["tflops"], "peak": fp8_peak, "unit": "TFLOP/s",
+                                           "frac": case[ck]["tflops"] / fp8_peak, "ms": case[ck]["ms"],
+                                           "workload": f"E=256 top-8 H=7168 I=2048 M={case['M']}"})
+
+    # ---- the mid sizes of the sweep (M = 128 / 512 / 2048): GEMM kernel alone per shape
+    per_shape_mid = None
+    if rank == 0 and world == 1:
+        per_shape_mid = []
+        for L in layers:
+            for m_mid in (128, 512, 2048):
+                if m_mid >= M:
+                    continue
+                xm = L["x"][:m_mid].contiguous()
+                qm_, sm_ = sglang_per_token_group_quant_fp8(xm, 128, column_major_scales=True, scale_tma_aligned=True)
+                ev = []
+                for i in range(8):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                    w8a8_block_fp8_matmul(qm_, L["layer"].weight, sm_, L["layer"].weight_scale_inv, [128, 128], torch.bfloat16)
+                    e1.record()
+                    ev.append((e0, e1))
+                torch.cuda.synchronize()
+                tms = statistics.median(a.elapsed_time(b) for a, b in ev[3:])
+                per_shape_mid.append({"layer": L["name"], "M": m_mid, "N": L["n_loc"], "K": L["k_loc"], "gemm_us": tms * 1e3,
+                                      "gemm_tflops": 2.0 * m_mid * L["n_loc"] * L["k_loc"] / (tms * 1e-3) / 1e12})
 
     # ---- end to end through the public API from pinned host memory
     host_x = [L["x"].cpu().pin_memory() for L in layers]
@@ -832,24 +1073,38 @@ def main():
             tp_llama = {"error": f"{type(e).__name__}: {e}"}
         torch.cuda.empty_cache()
         if not args.no_moe:
-            try:
-                ep_moe = ep_moe_section(torch, dist, dev, gen, world, rank)
-            except Exception as e:  # noqa: BLE001
-                ep_moe = {"error": f"{type(e).__name__}: {e}"}
-            torch.cuda.empty_cache()
+            ep_moe = []
+            for m_total in (256, 4096, 16384):
+                try:
+                    ep_moe.append(ep_moe_section(torch, dist, dev, gen, world, rank, M_total=m_total,
+                                                 decode_graph=(m_total == 4096)))
+                except Exception as e:  # noqa: BLE001
+                    ep_moe.append({"M_total": m_total, "error": f"{type(e).__name__}: {e}"})
+                torch.cuda.empty_cache()
     else:
         layers_n = len(layers)
+        if rank == 0:
+            for L in layers:
+                L.clear()
+            torch.cuda.empty_cache()
+            try:  # the tp1 point: the base of the tensor-parallel scaling of this layer
+                tp_llama = tp_llama_section(torch, dist, dev, gen, 1, 0)
+            except Exception as e:  # noqa: BLE001
+                tp_llama = {"error": f"{type(e).__name__}: {e}"}
+            torch.cuda.empty_cache()
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_baseline = cpu_arm(3, 1, args.cpu_m)
+        cpu_baseline = cpu_arm(3, 1, cpu_m)
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": config, "clocks": clocks,
                 "e2e": e2e, "gpu_launches": args.steps * layers_n * 2, "roofline": roofline,
-                "cpu_baseline": cpu_baseline, "quant": quant, "moe": moe, "per_shape": per_shape, "ue8m0": ue8m0, "decode": decode, "fused_allreduce": fused_ar, "tp_llama70b": tp_llama, "ep_moe": ep_moe,
+                "cpu_baseline": cpu_baseline, "breakdown": breakdown, "parity": parity, "quant": quant,
+                "quant_after": quant_after, "moe": moe, "per_shape": per_shape, "per_shape_mid": per_shape_mid,
+                "ue8m0": ue8m0, "decode": decode, "fused_allreduce": fused_ar, "tp_llama70b": tp_llama, "ep_moe": ep_moe,
                 "impl": "ours"}
         print(json.dumps(line))
     if world > 1:

@@ -160,13 +160,18 @@ def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     return torch.nn.functional.silu(x[..., :d]) * x[..., d:]
 
 
-def fused_experts_block_fp8(a, w1, w2, w1_s, w2_s, topk_weight, topk_ids, block_shape=(128, 128), scale_ue8m0=False):
+def fused_experts_block_fp8(a, w1, w2, w1_s, w2_s, topk_weight, topk_ids, block_shape=(128, 128), scale_ue8m0=False,
+                            no_combine=False, apply_router_weight_on_input=False):
     """Expert MLP of ``torch_w8a8_block_fp8_moe`` (``test_block_fp8.py:418-447``) with the
     routing result passed in.  a ``[M, H]`` bf16; w1 ``[E, 2I, H]``, w2 ``[E, H, I]`` e4m3;
     w1_s ``[E, 2I/128, H/128]``, w2_s ``[E, H/128, I/128]``; topk_* ``[M, topk]``.
     Experts with id < 0 or >= E contribute zero (non-local experts under expert
     parallelism, ``fused_moe_triton_kernels.py:421-437``).  ``scale_ue8m0`` rounds both activation quantisations'
-    scales up to powers of two (the Blackwell DeepGEMM route, ``fp8_utils.py:511-512``)."""
+    scales up to powers of two (the Blackwell DeepGEMM route, ``fp8_utils.py:511-512``).
+    ``no_combine`` returns the weighted expert outputs ``[M, topk, H]`` without the sum over top-k
+    (``fused_moe_triton/fused_moe.py:452-458,597-598``).  ``apply_router_weight_on_input`` multiplies the gate_up
+    GEMM's fp32 result by the routing weight before it is rounded (the first kernel's ``MUL_ROUTED_WEIGHT``,
+    ``fused_moe.py:523``) and leaves the expert output unweighted."""
     Bt, D = a.shape
     topk = topk_ids.shape[1]
     bk = block_shape[1]
@@ -175,14 +180,22 @@ def fused_experts_block_fp8(a, w1, w2, w1_s, w2_s, topk_weight, topk_ids, block_
     ids = topk_ids.reshape(-1)
     a_q, a_s = per_token_group_quant_fp8(rep, bk, scale_ue8m0=scale_ue8m0)
     a_q = a_q.to(torch.float32)
+    wflat = topk_weight.reshape(-1).to(torch.float32)
     for e in range(w1.shape[0]):
         mask = ids == e
         if mask.sum():
-            h = w8a8_block_fp8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, a.dtype)
+            if apply_router_weight_on_input:
+                h = (w8a8_block_fp8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, torch.float32)
+                     * wflat[mask].unsqueeze(1)).to(a.dtype)
+            else:
+                h = w8a8_block_fp8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, a.dtype)
             act = silu_and_mul(h)
             act_q, act_s = per_token_group_quant_fp8(act.contiguous(), bk, scale_ue8m0=scale_ue8m0)
             out[mask] = w8a8_block_fp8_matmul(act_q, w2[e], act_s, w2_s[e], block_shape, a.dtype)
-    return (out.view(Bt, -1, w2.shape[1]) * topk_weight.view(Bt, -1, 1).to(out.dtype)).sum(dim=1)
+    weighted = out.view(Bt, -1, w2.shape[1])
+    if not apply_router_weight_on_input:
+        weighted = weighted * topk_weight.view(Bt, -1, 1).to(out.dtype)
+    return weighted if no_combine else weighted.sum(dim=1)
 
 
 def moe_block_fp8_from_scores(a, w1, w2, w1_s, w2_s, score, topk, block_shape=(128, 128)):

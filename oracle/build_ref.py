@@ -7,7 +7,10 @@ AVX512-BF16 and AMX at run time (``gemm_fp8.cpp:98,115`` checks).  They are W8A1
 activations, weights dequantised block-wise), so they are the timed CPU baseline and a loose
 cross-check, not the bit-level oracle.
 
-    python oracle/build_ref.py [/path/to/reference]
+    python oracle/build_ref.py /path/to/reference        (or SGLANG_REFERENCE_ROOT=/path/to/reference)
+
+Without an argument :func:`build` looks for the checkout in ``$SGLANG_REFERENCE_ROOT`` and then in a directory named
+``reference`` beside this repository; if there is none it returns None and the prebuilt library (if any) is used.
 
 The result, ``oracle/_ref/libsglb200_ref.so``, is loaded with :func:`load_ref`.
 """
@@ -22,7 +25,20 @@ LIB = os.path.join(OUT, "libsglb200_ref.so")
 FILES = ["gemm.cpp", "gemm_fp8.cpp", "gemm_int8.cpp", "moe.cpp", "moe_fp8.cpp", "moe_int8.cpp"]
 
 
-def build(ref_root="/root/reference", force=False):
+def find_reference():
+    """The reference checkout: ``$SGLANG_REFERENCE_ROOT``, else a directory ``reference`` beside this repository."""
+    cands = [os.environ.get("SGLANG_REFERENCE_ROOT"),
+             os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.isdir(os.path.join(c, "sgl-kernel", "csrc", "cpu")):
+            return c
+    return None
+
+
+def build(ref_root=None, force=False):
+    ref_root = ref_root or find_reference()
+    if ref_root is None:
+        return LIB if os.path.exists(LIB) else None
     src_dir = os.path.join(ref_root, "sgl-kernel", "csrc", "cpu")
     if not os.path.isdir(src_dir):
         return None
@@ -70,4 +86,5 @@ def load_ref():
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    print(build(args[0] if args else None, force="--force" in sys.argv))

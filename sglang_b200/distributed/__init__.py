@@ -8,6 +8,7 @@ from .peer_ep import PeerEpExchange, ep_fused_experts_peer  # noqa: F401
 from .parallel_linear import (  # noqa: F401
     ColumnParallelBlockFp8Linear,
     RowParallelBlockFp8Linear,
+    row_parallel_linear_overlapped,
     shard_block_fp8_weight,
     tensor_model_parallel_all_reduce,
 )

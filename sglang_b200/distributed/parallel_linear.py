@@ -26,6 +26,41 @@ def tensor_model_parallel_all_reduce(x: torch.Tensor, group=None) -> torch.Tenso
     return x
 
 
+def row_parallel_linear_overlapped(x: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, group=None,
+                                   chunk_rows: int = 2048, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``all_reduce(x_r @ W_r^T)`` with the all-reduce of one row chunk running while the GEMM of the next one computes.
+
+    The activations are quantised once; the GEMM then runs per chunk of ``chunk_rows`` rows into a row range of the
+    result, and each range is handed to an asynchronous NCCL all-reduce as soon as its GEMM is enqueued (NCCL orders it
+    after that GEMM on its own stream).  Same result as :class:`RowParallelBlockFp8Linear` without a peer exchange: the
+    chunks only partition the rows.  ``bias`` (rank 0 only, as ``linear.py:1374``) is added before the reduction.
+    The GEMM is a persistent kernel that fills every SM, so a concurrent NCCL kernel would have to wait for its CTAs to
+    finish: callers leave SMs free for it with ``configure_deep_gemm_num_sms`` (``layers.deep_gemm_wrapper``), as the
+    reference does around its overlapped GEMMs (``two_batch_overlap.py:841``)."""
+    from ..layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M, N = x2.shape[0], weight.shape[0]
+    y = torch.empty(M, N, dtype=x.dtype, device=x.device)
+    if M == 0:
+        return y.reshape(*x.shape[:-1], N)
+    q, s = sglang_per_token_group_quant_fp8(x2, BLOCK, column_major_scales=True, scale_tma_aligned=True)
+    multi = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    works = []
+    for r0 in range(0, M, chunk_rows):
+        r1 = min(M, r0 + chunk_rows)
+        part = y[r0:r1]
+        w8a8_block_fp8_matmul(q[r0:r1], weight, s[r0:r1], weight_scale, [BLOCK, BLOCK], x.dtype, out=part)
+        if bias is not None:
+            part += bias
+        if multi:
+            works.append(dist.all_reduce(part, group=group, async_op=True))
+    for w in works:
+        w.wait()
+    return y.reshape(*x.shape[:-1], N)
+
+
 def shard_block_fp8_weight(weight: torch.Tensor, scale: torch.Tensor, rank: int, world: int,
                            dim: int) -> Tuple[torch.Tensor, torch.Tensor]:
     """Slice ``weight [N, K]`` (e4m3) and ``scale [ceil(N/128), ceil(K/128)]`` for one rank along

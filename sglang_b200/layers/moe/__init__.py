@@ -59,7 +59,8 @@ def _grouped_mm(a_q, a_s, w, w_s, out, expert_offsets):
 
 def fused_experts_block_fp8(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, w1_scale: torch.Tensor,
                             w2_scale: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor,
-                            routed_scaling_factor: Optional[float] = None) -> torch.Tensor:
+                            routed_scaling_factor: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                            no_combine: bool = False, apply_router_weight_on_input: bool = False) -> torch.Tensor:
     """Expert MLP with block-FP8 weights.
 
     hidden_states ``[M, H]`` bf16/f16; w1 ``[E, 2I, H]`` (gate rows first, then up), w2 ``[E, H, I]``
@@ -69,19 +70,31 @@ def fused_experts_block_fp8(hidden_states: torch.Tensor, w1: torch.Tensor, w2: t
     ``torch_w8a8_block_fp8_moe`` (``python/sglang/test/test_block_fp8.py:418-447``), including its
     final combine: products with the routing weights are rounded to the activation dtype and
     then summed in fp32.
+
+    ``out``: write the result there (it may be ``hidden_states`` itself: the activations are quantised into their own
+    buffer first, so the in-place form of ``fused_moe.py:280-309`` needs no extra copy).  ``no_combine``: return the
+    weighted expert outputs ``[M, topk, H]`` without the sum over top-k (``fused_moe.py:452-458,597-598``).
+    ``apply_router_weight_on_input``: the routing weight multiplies the gate_up GEMM's fp32 sums instead of the expert
+    output (``fused_moe_triton_kernels.py``, ``MUL_ROUTED_WEIGHT`` on the first kernel); top-1 routing only, as the
+    reference's callers require.
     """
     assert hidden_states.dim() == 2 and hidden_states.is_contiguous()
     if hidden_states.size(0) == 0:
-        return torch.empty_like(hidden_states)
+        if no_combine:
+            return hidden_states.new_empty(0, topk_ids.size(1), hidden_states.size(1))
+        return torch.empty_like(hidden_states) if out is None else out
     a_q, a_s = sglang_per_token_group_quant_fp8(hidden_states, 128)
     return fused_experts_block_fp8_prequant(a_q, a_s, hidden_states.dtype, w1, w2, w1_scale, w2_scale, topk_weights,
-                                            topk_ids, routed_scaling_factor)
+                                            topk_ids, routed_scaling_factor, out=out, no_combine=no_combine,
+                                            apply_router_weight_on_input=apply_router_weight_on_input)
 
 
 def fused_experts_block_fp8_prequant(a_q: torch.Tensor, a_s: torch.Tensor, out_dtype: torch.dtype, w1: torch.Tensor,
                                      w2: torch.Tensor, w1_scale: torch.Tensor, w2_scale: torch.Tensor,
                                      topk_weights: torch.Tensor, topk_ids: torch.Tensor,
-                                     routed_scaling_factor: Optional[float] = None) -> torch.Tensor:
+                                     routed_scaling_factor: Optional[float] = None, out: Optional[torch.Tensor] = None,
+                                     no_combine: bool = False,
+                                     apply_router_weight_on_input: bool = False) -> torch.Tensor:
     """The expert MLP on activations that are already quantised (``a_q [M, H]`` e4m3, ``a_s [M, H/128]`` fp32
     row-major): the form an expert-parallel rank runs on the rows it received from the dispatch, which
     travel as fp8 payload plus scales (``token_dispatcher/deepep.py:360-371``)."""
@@ -96,7 +109,16 @@ def fused_experts_block_fp8_prequant(a_q: torch.Tensor, a_s: torch.Tensor, out_d
     assert topk_weights.shape == topk_ids.shape and topk_ids.size(0) == M
     topk = topk_ids.size(1)
     dev = a_q.device
-    out = torch.empty(M, H, dtype=out_dtype, device=dev)
+    assert not (no_combine and out is not None), "no combine + inplace makes no sense"
+    if apply_router_weight_on_input and topk != 1:
+        raise NotImplementedError("apply_router_weight_on_input is implemented for top-1 routing, as the reference's "
+                                  "callers require")
+    if no_combine:
+        out = torch.empty(M, topk, H, dtype=out_dtype, device=dev)
+    elif out is None:
+        out = torch.empty(M, H, dtype=out_dtype, device=dev)
+    else:
+        assert out.shape == (M, H) and out.dtype == out_dtype and out.is_contiguous() and out.device == dev
     if M == 0:
         return out
     ids = topk_ids.to(torch.int32).contiguous()
@@ -110,13 +132,26 @@ def fused_experts_block_fp8_prequant(a_q: torch.Tensor, a_s: torch.Tensor, out_d
 
     rep_q = shuffle_rows(a_q, a_map, (rows, H))
     rep_s = shuffle_rows(a_s, a_map, (rows, H // 128))
+    if apply_router_weight_on_input:
+        # the gate_up GEMM multiplies its fp32 sums by sa[row, kb] * sb: folding the row's routing weight into its
+        # group scales applies it where the reference's kernel does, before the sums are rounded to the activation type
+        rep_s = rep_s * topk_weights.reshape(-1).to(torch.float32)[a_map.long()].unsqueeze(1)
     c1 = torch.empty(rows, two_i, dtype=out_dtype, device=dev)
     _grouped_mm(rep_q, rep_s, w1, w1_scale, c1, expert_offsets)
     q2, s2 = sglang_per_token_group_quant_fp8(c1, 128, fuse_silu_and_mul=True)
     c2 = torch.empty(rows, H, dtype=out_dtype, device=dev)
     _grouped_mm(q2, s2, w2, w2_scale, c2, expert_offsets)
-    factors = topk_weights if routed_scaling_factor is None else topk_weights * routed_scaling_factor
-    apply_shuffle_mul_sum(c2, out, c_map, factors.to(out_dtype).reshape(-1).contiguous(), round_products=True)
+    factors = None
+    if not apply_router_weight_on_input:
+        factors = topk_weights if routed_scaling_factor is None else topk_weights * routed_scaling_factor
+    elif routed_scaling_factor is not None:
+        factors = torch.full_like(topk_weights, routed_scaling_factor)
+    if factors is not None:
+        factors = factors.to(out_dtype).reshape(-1).contiguous()
+    if no_combine:  # every (token, slot) is its own output row: the combine kernel with one slot per row
+        apply_shuffle_mul_sum(c2, out.view(rows, H), c_map, factors, round_products=True)
+    else:
+        apply_shuffle_mul_sum(c2, out, c_map, factors, round_products=True)
     return out
 
 
@@ -136,15 +171,14 @@ def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tenso
         raise NotImplementedError("biases and static activation scales are not part of the block-FP8 path")
     if moe_runner_config.activation != "silu":
         raise NotImplementedError("only the SiLU-gated MLP is implemented")
-    if moe_runner_config.no_combine or moe_runner_config.apply_router_weight_on_input:
-        raise NotImplementedError("no_combine / apply_router_weight_on_input are not implemented")
     topk_weights, topk_ids = topk_output[0], topk_output[1]
-    out = fused_experts_block_fp8(hidden_states, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids,
-                                  moe_runner_config.routed_scaling_factor)
     if moe_runner_config.inplace:
-        hidden_states.copy_(out)
-        return hidden_states
-    return out
+        assert not moe_runner_config.no_combine, "no combine + inplace makes no sense"
+    return fused_experts_block_fp8(hidden_states, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids,
+                                   moe_runner_config.routed_scaling_factor,
+                                   out=hidden_states if moe_runner_config.inplace else None,
+                                   no_combine=moe_runner_config.no_combine,
+                                   apply_router_weight_on_input=moe_runner_config.apply_router_weight_on_input)
 
 
 def cutlass_fused_experts_fp8(a, w1_q, w2_q, w1_scale, w2_scale, topk_weights, topk_ids, a1_strides=None,

@@ -79,11 +79,14 @@ def per_token_group_quant_fp8(x, group_size, eps: float = 1e-10, column_major_sc
 
 
 def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs: torch.Tensor,
-                          block_size: List[int], output_dtype: torch.dtype = torch.float16) -> torch.Tensor:
+                          block_size: List[int], output_dtype: torch.dtype = torch.float16,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``w8a8_block_fp8_matmul`` (``fp8_kernel.py:1149-1164``; shape rules ``:999-1044``).
 
     A ``[..., K]`` e4m3 contiguous, B ``[N, K]`` e4m3 contiguous, As ``[..., ceil(K/128)]`` fp32
-    (row-major or M-major), Bs ``[ceil(N/128), ceil(K/128)]`` fp32; returns ``[..., N]``."""
+    (row-major or M-major), Bs ``[ceil(N/128), ceil(K/128)]`` fp32; returns ``[..., N]``.  ``out`` (not in the
+    reference's signature) is an optional preallocated ``[M, N]`` result with unit column stride, e.g. a row range of a
+    larger tensor."""
     assert len(block_size) == 2 and block_size[0] == 128 and block_size[1] == 128, "only 128x128 blocks"
     assert A.shape[-1] == B.shape[-1]
     assert A.shape[:-1] == As.shape[:-1] and A.is_contiguous()
@@ -93,11 +96,16 @@ def w8a8_block_fp8_matmul(A: torch.Tensor, B: torch.Tensor, As: torch.Tensor, Bs
     assert -(-N // 128) == Bs.shape[0] and -(-K // 128) == Bs.shape[1]
     M = A.numel() // K
     A2, As2 = A.view(M, K), As.reshape(M, As.shape[-1])
-    C = torch.empty(A.shape[:-1] + (N,), device=A.device, dtype=output_dtype)
+    if out is not None:
+        assert out.shape == (M, N) and out.dtype == output_dtype and out.stride(1) == 1 and out.device == A.device
+        C = out
+    else:
+        C = torch.empty(A.shape[:-1] + (N,), device=A.device, dtype=output_dtype)
     if M == 0:
         return C
+    ldc = C.stride(0) if out is not None and M > 1 else N
     with torch.cuda.device(A.device):
-        blockwise_mm(A2.data_ptr(), B.data_ptr(), As2.data_ptr(), Bs.data_ptr(), C.data_ptr(), M, N, K, K, K, N,
+        blockwise_mm(A2.data_ptr(), B.data_ptr(), As2.data_ptr(), Bs.data_ptr(), C.data_ptr(), M, N, K, K, K, ldc,
                      As2.stride(0), As2.stride(1), Bs.stride(0), Bs.stride(1), dtype_code(output_dtype), A.device,
                      torch.cuda.current_stream(A.device).cuda_stream)
     return C

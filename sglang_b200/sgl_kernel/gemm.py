@@ -20,6 +20,22 @@ def _cuda_check(cond: bool, msg: str) -> None:
         raise RuntimeError(msg)
 
 
+_EPS_CACHE = {}
+
+
+def _eps_in_dtype(eps: float, dtype: torch.dtype) -> float:
+    """``eps`` rounded to the input dtype (what the torch-native reference clamps with); for fp16, where 1e-10 rounds
+    to zero, the fp32 value.  Cached: the rounding is a small CPU tensor op that would otherwise run on every call."""
+    key = (eps, dtype)
+    v = _EPS_CACHE.get(key)
+    if v is None:
+        v = float(eps) if dtype == torch.float32 else float(torch.tensor(eps, dtype=dtype).float())
+        if v == 0.0 and eps > 0.0:
+            v = float(eps)
+        _EPS_CACHE[key] = v
+    return v
+
+
 def fp8_blockwise_scaled_mm(mat_a, mat_b, scales_a, scales_b, out_dtype):
     """Block-scaled FP8 GEMM, same contract as ``fp8_blockwise_scaled_mm``
     (``sgl-kernel/csrc/gemm/fp8_blockwise_gemm_kernel.cu:368-465``).
@@ -111,9 +127,7 @@ def sgl_per_token_group_quant_8bit(
         _cuda_check(output_s.size(0) == rows and output_s.size(1) == G, "output_s shape is not matched")
     if rows == 0 or hidden == 0:
         return
-    eps_eff = float(torch.tensor(eps, dtype=input.dtype).float()) if input.dtype != torch.float32 else float(eps)
-    if eps_eff == 0.0 and eps > 0.0:
-        eps_eff = float(eps)
+    eps_eff = _eps_in_dtype(eps, input.dtype)
     L = lib()
     args = (rows, hidden, group_size, eps_eff, fp8_min, fp8_max, int(bool(scale_ue8m0)),
             output_s.stride(0), output_s.stride(1), _stream(input))
@@ -148,9 +162,7 @@ def _quant_batched(input, output_q, output_s, group_size, eps, fp8_min, fp8_max,
         mptr = masked_m.data_ptr()
     if E == 0 or max_m == 0 or hidden == 0:
         return
-    eps_eff = float(torch.tensor(eps, dtype=input.dtype).float())
-    if eps_eff == 0.0 and eps > 0.0:
-        eps_eff = float(eps)
+    eps_eff = _eps_in_dtype(eps, input.dtype)
     with torch.cuda.device(input.device):
         check(lib().sglb200_group_quant_fp8_batched(
             input.data_ptr(), dtype_code(input.dtype), output_q.data_ptr(), output_s.data_ptr(), E, max_m, hidden,

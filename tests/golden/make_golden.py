@@ -150,4 +150,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit(f"usage: {os.path.basename(__file__)} <reference checkout>")
+    main(sys.argv[1])

@@ -144,3 +144,41 @@ def test_fused_moe_matches_oracle(M, E, topk, H, I):
     with pytest.raises(NotImplementedError):
         fused_experts(a.cuda(), w1q.cuda(), w2q.cuda(), StandardTopKOutput(w.cuda(), ids.cuda(), None), cfg,
                       use_int8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128])
+
+
+def test_fused_experts_options_no_combine_inplace_and_router_weight_on_input():
+    """The options of ``fused_experts`` (``fused_moe_triton/fused_moe.py:254-338``): ``no_combine`` returns the
+    weighted rows per (token, slot); ``inplace`` writes into ``hidden_states`` (no second buffer); with
+    ``apply_router_weight_on_input`` (top-1 routing) the weight scales the gate_up result instead of the expert output."""
+    from sglang_b200.layers.moe import MoeRunnerConfig, StandardTopKOutput, fused_experts
+    M, E, topk, H, I = 150, 8, 2, 512, 256
+    a = make_activations(M, H, seed=3, outliers=False)
+    w1q, w1s, w2q, w2s = _experts(E, H, I, seed=5)
+    w, ids = _routing(M, E, topk, seed=6)
+    dev = [t.cuda() for t in (w1q, w2q, w1s, w2s)]
+
+    def run(cfg, x, tw, ti):
+        return fused_experts(x, dev[0], dev[1], StandardTopKOutput(tw.cuda(), ti.cuda(), None), cfg, use_fp8_w8a8=True,
+                             w1_scale=dev[2], w2_scale=dev[3], block_shape=[128, 128])
+
+    plain = run(MoeRunnerConfig(top_k=topk), a.cuda(), w, ids)
+    # no_combine: [M, topk, H]; summing it in fp32 gives the combined result
+    nc = run(MoeRunnerConfig(top_k=topk, no_combine=True), a.cuda(), w, ids)
+    assert nc.shape == (M, topk, H)
+    ref_nc = oracle.fused_experts_block_fp8(a, w1q, w2q, w1s, w2s, w, ids, no_combine=True)
+    assert_gemm_close(nc.reshape(M * topk, H), ref_nc.reshape(M * topk, H), "no_combine")
+    assert torch.equal(nc.float().sum(dim=1).bfloat16(), plain)
+    # inplace: the result lands in the input tensor, same bits as the out-of-place call
+    x = a.cuda().clone()
+    got = run(MoeRunnerConfig(top_k=topk, inplace=True), x, w, ids)
+    assert got.data_ptr() == x.data_ptr() and torch.equal(x, plain)
+    with pytest.raises(AssertionError):
+        run(MoeRunnerConfig(top_k=topk, inplace=True, no_combine=True), a.cuda().clone(), w, ids)
+    # router weight on the input side, top-1
+    w1_, ids1 = w[:, :1].contiguous(), ids[:, :1].contiguous()
+    rw = run(MoeRunnerConfig(top_k=1, apply_router_weight_on_input=True), a.cuda(), w1_, ids1)
+    ref_rw = oracle.fused_experts_block_fp8(a, w1q, w2q, w1s, w2s, w1_, ids1, apply_router_weight_on_input=True)
+    assert_gemm_close(rw, ref_rw, "apply_router_weight_on_input")
+    with pytest.raises(NotImplementedError):
+        run(MoeRunnerConfig(top_k=topk, apply_router_weight_on_input=True), a.cuda(), w, ids)
+    torch.cuda.synchronize()

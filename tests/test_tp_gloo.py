@@ -124,3 +124,56 @@ def test_row_parallel_bias_with_peer_exchange_is_decided_in_the_constructor(monk
         outs.append(layer(torch.zeros(3, 256)))
     assert len(calls) == 2 and all(c is not None and torch.equal(c, bias) for c in calls)
     assert torch.equal(outs[0], outs[1])
+
+
+def _overlap_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        import sglang_b200.layers.quantization.fp8_kernel as fk
+        from sglang_b200.distributed import row_parallel_linear_overlapped
+
+        # CPU stand-ins for the two CUDA calls, so that the chunking, the row-range outputs and the asynchronous
+        # reductions run for real on two gloo ranks
+        def fake_quant(x, g, column_major_scales=False, scale_tma_aligned=False, **kw):
+            return oracle.per_token_group_quant_fp8(x, g)
+
+        def fake_mm(a, b, a_s, b_s, block, dtype, out=None):
+            y = oracle.w8a8_block_fp8_matmul(a, b, a_s.contiguous(), b_s, output_dtype=dtype)
+            out.copy_(y)
+            return out
+
+        fk.sglang_per_token_group_quant_fp8, fk.w8a8_block_fp8_matmul = fake_quant, fake_mm
+        g = torch.Generator().manual_seed(0)
+        M, N, K = 300, 256, 512
+        x = torch.randn(M, K, generator=g).bfloat16()
+        wq, ws = oracle.block_quant_weight(torch.randn(N, K, generator=g) * 0.05)
+        kr = K // world
+        y = row_parallel_linear_overlapped(x[:, rank * kr:(rank + 1) * kr].contiguous(),
+                                           wq[:, rank * kr:(rank + 1) * kr].contiguous(),
+                                           ws[:, rank * kr // 128:(rank + 1) * kr // 128].contiguous(), chunk_rows=128)
+        ref = oracle.row_parallel_reference(x, wq, ws, world)
+        # gloo adds the bf16 partial products in bf16; two ranks: one addition, the same bits as the fp32 sum rounded
+        assert torch.equal(y, ref), float((y.float() - ref.float()).abs().max())
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, f"{type(e).__name__}: {e}\n{traceback.format_exc()}"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_overlapped_row_parallel_linear_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_overlap_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results
