@@ -31,7 +31,6 @@ import os
 import statistics
 import subprocess
 import sys
-import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -57,75 +56,89 @@ def load_peaks():
 
 
 # --------------------------------------------------------------------------- clock sampling
-class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU while the timed region runs: NVML from a
-    thread every 5 ms (read-only queries), or `nvidia-smi -lms 100` if NVML cannot be imported."""
+_SAMPLER_CHILD = r"""
+import sys, time
+uuid, path = sys.argv[1], sys.argv[2]
+with open(path, "w", buffering=1) as f:
+    try:
+        import pynvml as n
+        n.nvmlInit()
+        h = n.nvmlDeviceGetHandleByUUID(uuid)
+        f.write("max %d\n" % n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM))
+        while True:
+            f.write("%.6f %d %d\n" % (time.time(), n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM),
+                                      n.nvmlDeviceGetCurrentClocksEventReasons(h)))
+            time.sleep(0.004)
+    except Exception as e:
+        f.write("error %r\n" % (e,))
+"""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU while timed regions run.  The NVML polling (read-only queries,
+    every 4 ms) runs in ONE CHILD PROCESS for the whole run, writing to a scratch file: a polling thread inside the
+    benchmark process takes the interpreter lock away from the thread that launches the kernels, which showed as idle GPU
+    time in steps of one or two milliseconds.  start() / stop() mark the wall-clock window whose samples count."""
+
     REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
                ("sw_power_cap", 0x4))
+    _child = None
+    _path = None
 
     def __init__(self, gpu_uuid: str):
-        self.gpu_id, self.rows, self.proc, self.thread = gpu_uuid, [], None, None
-        self.clk, self.mx, self.reasons, self.stop_flag, self.nvml = [], None, set(), False, None
-
-    def _nvml_loop(self):
-        n, h = self.nvml
-        while not self.stop_flag:
+        self.t0 = self.t1 = None
+        if gpu_uuid is None:  # ranks whose line is not printed do not sample
+            return
+        if ClockSampler._child is None:
+            import tempfile
+            fd, ClockSampler._path = tempfile.mkstemp(prefix="sglb200_clocks_", suffix=".txt")
+            os.close(fd)
             try:
-                self.clk.append(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM))
-                r = n.nvmlDeviceGetCurrentClocksEventReasons(h)
-                for name, bit in self.REASONS:
-                    if r & bit:
-                        self.reasons.add(name)
-            except Exception:  # noqa: BLE001
-                pass
-            time.sleep(0.005)
+                ClockSampler._child = subprocess.Popen([sys.executable, "-c", _SAMPLER_CHILD, gpu_uuid, ClockSampler._path],
+                                                       stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL)
+                import atexit
+                atexit.register(ClockSampler.shutdown)
+            except OSError:
+                ClockSampler._child = None
+
+    @staticmethod
+    def shutdown():
+        if ClockSampler._child is not None:
+            ClockSampler._child.terminate()
+            ClockSampler._child = None
+        if ClockSampler._path and os.path.exists(ClockSampler._path):
+            os.remove(ClockSampler._path)
 
     def start(self):
-        try:
-            import pynvml as n
-            n.nvmlInit()
-            h = n.nvmlDeviceGetHandleByUUID(self.gpu_id)
-            self.mx = n.nvmlDeviceGetMaxClockInfo(h, n.NVML_CLOCK_SM)
-            self.nvml = (n, h)
-            self.thread = threading.Thread(target=self._nvml_loop, daemon=True)
-            self.thread.start()
-            return
-        except Exception:  # noqa: BLE001
-            self.nvml = None
-        try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", self.gpu_id, f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
-                                         stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            return
-        self.thread = threading.Thread(target=lambda: [self.rows.append(l) for l in self.proc.stdout], daemon=True)
-        self.thread.start()
+        self.t0 = time.time()
 
     def stop(self):
-        if self.nvml is not None:
-            self.stop_flag = True
-            self.thread.join(timeout=2)
-            return {"sm_mhz": statistics.median(self.clk) if self.clk else None, "sm_max_mhz": self.mx,
-                    "reasons": sorted(self.reasons), "samples": len(self.clk), "source": "nvml"}
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        self.thread.join(timeout=2)
-        clk, mx, reasons = [], None, set()
-        for line in self.rows:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 6 or not f[0].isdigit():
-                continue
-            clk.append(int(f[0]))
-            mx = int(f[1])
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(clk) if clk else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(clk), "source": "nvidia-smi"}
+        self.t1 = time.time()
+        if ClockSampler._child is None or not ClockSampler._path:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock sampler unavailable"]}
+        time.sleep(0.01)
+        clk, near, mx, reasons, err = [], [], None, set(), None
+        with open(ClockSampler._path) as f:
+            for line in f:
+                fld = line.split()
+                if len(fld) == 2 and fld[0] == "max":
+                    mx = int(fld[1])
+                elif fld and fld[0] == "error":
+                    err = line.strip()
+                elif len(fld) == 3:
+                    t, c, r = float(fld[0]), int(fld[1]), int(fld[2])
+                    if self.t0 <= t <= self.t1:
+                        clk.append(c)
+                        for name, bit in self.REASONS:
+                            if r & bit:
+                                reasons.add(name)
+                    elif self.t0 - 0.05 <= t <= self.t1 + 0.05:
+                        near.append(c)
+        if err is not None and not clk:
+            return {"sm_mhz": None, "sm_max_mhz": mx, "reasons": [err]}
+        use = clk or near  # a region shorter than the polling period: the samples right beside it
+        return {"sm_mhz": statistics.median(use) if use else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clk), "source": "nvml (child process)"}
 
 
 # --------------------------------------------------------------------------- CPU arm
@@ -386,11 +399,23 @@ def parity_section(torch, dist, dev, world, rank):
                                          ep_fused_experts_peer, fused_row_parallel_linear)
     import oracle
 
-    def verdict(out, ref):
+    def verdict(out, ref, slack=None):
+        """rel-L2 <= 1e-2 and max-abs <= 2e-2 x RMS(ref); with `slack` (element-wise) an element may instead lie within
+        that distance of the reference: the bound on a sum that the collective library takes in bf16."""
         o, r = out.float().cpu().double(), ref.float().double()
         rel = float((o - r).norm() / r.norm().clamp(min=1e-30))
-        mx = float((o - r).abs().max() / r.pow(2).mean().sqrt().clamp(min=1e-30))
-        return {"rel_l2": rel, "max_abs_over_rms": mx, "pass": bool(rel <= 1e-2 and mx <= 2e-2)}
+        rms = r.pow(2).mean().sqrt().clamp(min=1e-30)
+        diff = (o - r).abs()
+        mx = float(diff.max() / rms)
+        bound = torch.full_like(diff, 2e-2 * float(rms))
+        res = {"rel_l2": rel, "max_abs_over_rms": mx}
+        if slack is not None:
+            bound = torch.maximum(bound, slack)
+            res["bar"] = ("rel-L2 <= 1e-2; max-abs <= 2e-2 x RMS or the rounding of a sum of the ranks' bf16 partial results "
+                          "taken in bf16 (NCCL adds bf16 buffers in bf16; the oracle adds them in fp32)")
+        res["elements_over"] = int((diff > bound).sum())
+        res["pass"] = bool(rel <= 1e-2 and res["elements_over"] == 0)
+        return res
 
     res = {}
     g = torch.Generator().manual_seed(4321)  # the same inputs on every rank
@@ -435,9 +460,11 @@ def parity_section(torch, dist, dev, world, rank):
     status = lib().sglb200_read_device_status()
     dist.barrier()
     if rank == 0:  # the oracle runs after all device work: the peer exchanges assume ranks in step
+        parts = oracle.row_parallel_partials(x, wq, ws, world)
         ref = oracle.row_parallel_reference(x, wq, ws, world)
+        slack = oracle.sum_in_storage_type_bound(parts)
         for k, v in outs.items():
-            res[k] = verdict(v, ref)
+            res[k] = verdict(v, ref, slack if "nccl" in k else None)
         ref_ep = oracle.expert_parallel_reference(xm, w1q, w2q, w1s, w2s, tw, ti, world)
         for k, v in ep_outs.items():
             res[k] = verdict(v, ref_ep)
@@ -580,10 +607,12 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=8192, help="tokens per step")
     ap.add_argument("--cpu-m", type=int, default=0, help="rows of the CPU arm (0: the same M as the GPU arm)")
-    ap.add_argument("--overlap", type=int, default=1, help="N > 1: all-reduce of a row chunk overlaps the next chunk's GEMM")
+    ap.add_argument("--overlap", type=int, default=0,
+                    help="N > 1: 1 = the all-reduce of a row chunk overlaps the next chunk's GEMM (measured: a gain at 2 "
+                         "ranks, a loss at 8; off by default)")
     ap.add_argument("--chunk-rows", type=int, default=2048, help="rows per chunk of the overlapped row-parallel linear")
     ap.add_argument("--comm-sms", type=int, default=16, help="SMs the GEMMs leave free for NCCL while overlapping")
-    ap.add_argument("--nccl-max-ctas", type=int, default=16, help="upper bound on NCCL's CTAs per collective (0: NCCL's own)")
+    ap.add_argument("--nccl-max-ctas", type=int, default=0, help="upper bound on NCCL's CTAs per collective (0: NCCL's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE section (11.3 GB of expert weights)")
     ap.add_argument("--only", default="all", choices=["all", "gemm", "quant", "ue8m0", "decode", "moe"],
@@ -638,6 +667,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     peaks = load_peaks()
     M = args.m
+    gpu_uuid = "GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", "") if rank == 0 else None
+    ClockSampler(gpu_uuid)  # starts the polling child now: it needs a moment to come up
     parity = None
     if world > 1 and args.only == "all":
         try:
@@ -658,8 +689,8 @@ def main():
     # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed between launches.  Measured twice:
     # before the GEMM sweep (GPU not yet at its power cap) and after it (SM clock pulled down under sw_power_cap).
     def quant_case(when):
+        sampler_q = ClockSampler(gpu_uuid)
         gen_q = torch.Generator(device=dev).manual_seed(1)
-        sampler_q = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
         xq = torch.randn(16384, 7168, device=dev, generator=gen_q)
         xq = (xq * 10 ** (torch.rand(16384, 1, device=dev, generator=gen_q) * 4 - 2)).bfloat16()
         flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
@@ -797,6 +828,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(gpu_uuid)  # its child process needs a moment to come up: created before the warm-up
     if world > 1:  # set-up, not a step: NCCL builds its channels and buffers for this message size on first use
         warm = torch.zeros(M, max(L["N"] for L in layers if L["mode"] == "row"), dtype=torch.bfloat16, device=dev)
         for _ in range(5):
@@ -808,7 +840,6 @@ def main():
     for L in layers:
         L["ev"] = []
     main_steps = args.steps if args.only not in ("quant", "ue8m0") else 1
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
     fence()
     sampler.start()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -903,9 +934,9 @@ def main():
 
     ue8m0 = None
     if args.only in ("all", "ue8m0"):
+        sampler_u = ClockSampler(gpu_uuid)
         for _ in range(args.warmup):
             step_u()
-        sampler_u = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid).replace("GPU-", ""))
         fence()
         sampler_u.start()
         u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -998,9 +1029,12 @@ def main():
 
     # ---- end to end through the public API from pinned host memory
     host_x = [L["x"].cpu().pin_memory() for L in layers]
-    host_y = [torch.empty(M, L["n_loc"], dtype=torch.bfloat16).pin_memory() for L in layers]
+    # results that are identical on every rank (all-reduced row-parallel outputs, the replicated layer) go back to the
+    # host once, from rank 0; every rank returns its own column-parallel shard
+    returns = [world == 1 or L["mode"] == "column" or rank == 0 for L in layers]
+    host_y = [torch.empty(M, L["n_loc"], dtype=torch.bfloat16).pin_memory() if r else None for L, r in zip(layers, returns)]
     h2d = sum(t.numel() * 2 for t in host_x)
-    d2h = sum(t.numel() * 2 for t in host_y)
+    d2h = sum(t.numel() * 2 for t in host_y if t is not None)
 
     # Three streams: the upload of layer i + 1 and the download of layer i - 1 run under the compute of layer i (PCIe is
     # full duplex), as a serving loop that owns its copy engines would do it.  Every byte still crosses inside the timed
@@ -1020,6 +1054,8 @@ def main():
             y = method.apply(L["layer"], xd)
             if world > 1 and L["mode"] == "row":
                 dist.all_reduce(y)
+            if hy is None:
+                continue
             ev_out = torch.cuda.Event()
             ev_out.record(cur)
             with torch.cuda.stream(s_out):

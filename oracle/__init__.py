@@ -30,9 +30,11 @@ from .block_fp8 import (  # noqa: F401
     pack_scales,
     per_token_group_quant_fp8,
     prepare_moe_input,
+    row_parallel_partials,
     row_parallel_reference,
     shuffle_rows,
     silu_and_mul,
+    sum_in_storage_type_bound,
     topk_softmax,
     w8a8_block_fp8_matmul,
 )

@@ -351,17 +351,39 @@ def moe_fused_gate(x: torch.Tensor, bias: torch.Tensor, num_expert_group: int, t
 # --------------------------------------------------------------------------------------
 # AR / A2A: the sharded forms, evaluated the way the sharding defines the arithmetic
 # --------------------------------------------------------------------------------------
+def row_parallel_partials(x, wq, ws, world):
+    """The partial products of the row-parallel linear, one per rank, each rounded to the output type as the rank's GEMM
+    leaves it (``python/sglang/srt/layers/linear.py:1361-1378``)."""
+    K = x.shape[1]
+    kr = K // world
+    parts = []
+    for r in range(world):
+        q, s = per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous(), 128)
+        parts.append(w8a8_block_fp8_matmul(q, wq[:, r * kr:(r + 1) * kr].contiguous(), s,
+                                           ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous(), output_dtype=x.dtype))
+    return parts
+
+
 def row_parallel_reference(x, wq, ws, world):
     """Row-parallel linear: every rank quantises its K-slice, rounds its partial product to the output type, and the
     partial products are added (``python/sglang/srt/layers/linear.py:1361-1386``); fp32 sum here, one cast."""
-    K = x.shape[1]
-    kr = K // world
     ref = torch.zeros(x.shape[0], wq.shape[0], dtype=torch.float32)
-    for r in range(world):
-        q, s = per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous(), 128)
-        ref += w8a8_block_fp8_matmul(q, wq[:, r * kr:(r + 1) * kr].contiguous(), s,
-                                     ws[:, r * kr // 128:(r + 1) * kr // 128].contiguous(), output_dtype=x.dtype).float()
+    for part in row_parallel_partials(x, wq, ws, world):
+        ref += part.float()
     return ref.to(x.dtype)
+
+
+def sum_in_storage_type_bound(parts):
+    """How far a sum of ``parts`` taken IN their 16-bit type, in any order (what an all-reduce library does with bf16
+    buffers, ``python/sglang/srt/distributed/device_communicators/pynccl.py:143-160``), can lie from the fp32 sum rounded
+    once: every one of the ``len(parts) - 1`` additions rounds a running sum no larger than ``sum |part|``, half a unit
+    in the last place each, plus half a unit for the final rounding of the reference itself.  Element-wise, fp64."""
+    mant = 8 if parts[0].dtype == torch.bfloat16 else 11
+    mag = torch.zeros(parts[0].shape, dtype=torch.float64)
+    for part in parts:
+        mag += part.double().abs()
+    ulp = torch.ldexp(torch.ones_like(mag), torch.frexp(mag.clamp(min=1e-300))[1] - mant)
+    return 0.5 * ulp * len(parts)
 
 
 def expert_parallel_reference(x, w1q, w2q, w1s, w2s, topk_w, topk_ids, world):
