@@ -607,11 +607,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--m", type=int, default=8192, help="tokens per step")
     ap.add_argument("--cpu-m", type=int, default=0, help="rows of the CPU arm (0: the same M as the GPU arm)")
-    ap.add_argument("--overlap", type=int, default=0,
-                    help="N > 1: 1 = the all-reduce of a row chunk overlaps the next chunk's GEMM (measured: a gain at 2 "
-                         "ranks, a loss at 8; off by default)")
+    ap.add_argument("--overlap", type=int, default=-1,
+                    help="N > 1: 1 = the all-reduce of a row chunk overlaps the next chunk's GEMM; 0 = all-reduce after "
+                         "each row-parallel GEMM on the same stream; -1 (default) = time both during set-up and keep the faster")
     ap.add_argument("--chunk-rows", type=int, default=2048, help="rows per chunk of the overlapped row-parallel linear")
-    ap.add_argument("--comm-sms", type=int, default=16, help="SMs the GEMMs leave free for NCCL while overlapping")
+    ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL while overlapping")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="upper bound on NCCL's CTAs per collective (0: NCCL's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-moe", action="store_true", help="skip the fused-MoE section (11.3 GB of expert weights)")
@@ -686,34 +686,62 @@ def main():
         print(json.dumps({"metric": METRIC, "only": "decode", "decode": decode_section(torch, dev, peaks, sel, ms_sel)}))
         return
 
-    # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed between launches.  Measured twice:
+    # ---- quant kernel on the bandwidth configuration (M=16384 x 7168), L2 flushed before every launch.  Measured twice:
     # before the GEMM sweep (GPU not yet at its power cap) and after it (SM clock pulled down under sw_power_cap).
     def quant_case(when):
+        from sglang_b200.layers.quantization import create_per_token_group_quant_fp8_output_scale
+        from sglang_b200.sgl_kernel import sgl_per_token_group_quant_8bit
         sampler_q = ClockSampler(gpu_uuid)
         gen_q = torch.Generator(device=dev).manual_seed(1)
-        xq = torch.randn(16384, 7168, device=dev, generator=gen_q)
-        xq = (xq * 10 ** (torch.rand(16384, 1, device=dev, generator=gen_q) * 4 - 2)).bfloat16()
-        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-        times = []
+        Mq, Kq, sets = 16384, 7168, 3
+        xs, qs, ss = [], [], []
+        for _ in range(sets):  # three input / output sets used in turn: 1.07 GB in flight, nothing is re-used from L2
+            xq = torch.randn(Mq, Kq, device=dev, generator=gen_q)
+            xs.append((xq * 10 ** (torch.rand(Mq, 1, device=dev, generator=gen_q) * 4 - 2)).bfloat16())
+            qs.append(torch.empty(Mq, Kq, dtype=torch.float8_e4m3fn, device=dev))
+            ss.append(create_per_token_group_quant_fp8_output_scale((Mq, Kq), dev, 128, True, True, False))
+        del xq
+
+        def launch(i):
+            sgl_per_token_group_quant_8bit(xs[i % sets], qs[i % sets], ss[i % sets], 128, 1e-10, -448.0, 448.0, False)
+
+        n = 21
+        for i in range(4):
+            launch(i)
+        torch.cuda.synchronize()
         sampler_q.start()
-        for i in range(24):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize()
+        clocks_q = sampler_q.stop()
+        qms = e0.elapsed_time(e1) / n
+        # the same kernel as a single launch after a 256 MB write flush (the dirty lines of the flush are written back
+        # during the launch, and a launch after an idle gap starts slower): a lower figure, kept for comparison
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+        iso = []
+        for i in range(12):
             flush.zero_()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            sglang_per_token_group_quant_fp8(xq, 128, column_major_scales=True, scale_tma_aligned=True)
-            e1.record()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record()
+            launch(i)
+            f1.record()
             torch.cuda.synchronize()
             if i >= 3:
-                times.append(e0.elapsed_time(e1))
-        clocks_q = sampler_q.stop()
-        qbytes = 16384 * 7168 * 3 + 16384 * 56 * 4
-        qms = statistics.median(times)
+                iso.append(f0.elapsed_time(f1))
+        del flush
+        qbytes = Mq * Kq * 3 + Mq * (Kq // 128) * 4
         mhz = clocks_q.get("sm_mhz")
         return {"workload": "per_token_group_quant_fp8 M=16384 K=7168 bf16 -> e4m3 + f32 column-major scales",
                 "when": when, "bytes": qbytes, "ms": qms, "gbs": qbytes / (qms * 1e-3) / 1e9,
                 "peak_gbs": peaks["hbm_gbs"], "frac": qbytes / (qms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                "peak_source": peaks["source"], "l2": "256 MB buffer zeroed between launches", "clocks": clocks_q,
-                "us_x_sm_mhz": qms * 1e3 * mhz if mhz else None, "launches": len(times)}
+                "peak_source": peaks["source"],
+                "l2": f"inputs larger than L2: {sets} input / output sets of 356 MB used in turn, {n} launches back to back "
+                      "between one pair of CUDA events, no flush",
+                "single_launch_after_write_flush_us": statistics.median(iso) * 1e3,
+                "clocks": clocks_q, "us_x_sm_mhz": qms * 1e3 * mhz if mhz else None, "launches": n}
 
     quant = None
     if rank == 0 and args.only not in ("gemm", "ue8m0"):
@@ -749,21 +777,16 @@ def main():
         layers.append({"name": name, "N": N, "K": K, "mode": mode, "n_loc": n_loc, "k_loc": k_loc, "layer": layer,
                        "x": x, "gemm_ms": [], "wq_u": wq_u, "ws_u": pack_ue8m0_scales(ws_u), "ev_u": []})
 
-    overlap = world > 1 and bool(args.overlap)
-    if overlap:
+    overlap = world > 1 and args.overlap == 1
+    if world > 1:
         from sglang_b200.distributed import row_parallel_linear_overlapped
         from sglang_b200.layers.deep_gemm_wrapper import configure_deep_gemm_num_sms
         sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
-        config["step"] = (f"row-parallel layers in chunks of {args.chunk_rows} rows, the NCCL all-reduce of a chunk overlaps "
-                          f"the next chunk's GEMM; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs, NCCL on at most "
-                          f"{args.nccl_max_ctas} CTAs")
-    elif world > 1:
-        config["step"] = "NCCL all-reduce after each row-parallel GEMM, same stream"
 
     def step(record=False):
         for L in layers:
             if overlap and L["mode"] == "row":
-                with configure_deep_gemm_num_sms(sm_total - args.comm_sms):
+                with configure_deep_gemm_num_sms(sm_total - args.comm_sms if args.comm_sms > 0 else None):
                     y = row_parallel_linear_overlapped(L["x"], L["layer"].weight, L["layer"].weight_scale_inv,
                                                        chunk_rows=args.chunk_rows)
                 continue
@@ -835,6 +858,30 @@ def main():
             dist.all_reduce(warm)
         del warm
         fence()
+    if world > 1 and args.overlap < 0:
+        # set-up, not a step: time both orders of a step (three steps each after one warm-up step, device time, max over
+        # ranks) and keep the faster for the warm-up and the timed region
+        tried = {}
+        for mode in (False, True):
+            overlap = mode
+            step()
+            fence()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(3):
+                step()
+            a1.record()
+            fence()
+            tt = torch.tensor([a0.elapsed_time(a1) / 3], device=dev)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            tried["overlapped" if mode else "plain"] = float(tt)
+        overlap = tried["overlapped"] < tried["plain"]
+        config["step_tried_ms"] = tried
+    if world > 1:
+        config["step"] = ((f"row-parallel layers in chunks of {args.chunk_rows} rows, the NCCL all-reduce of a chunk overlaps "
+                           f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"
+                                                       if args.comm_sms > 0 else "")) if overlap
+                          else "NCCL all-reduce after each row-parallel GEMM, same stream")
     for _ in range(args.warmup if args.only not in ("quant", "ue8m0") else 0):
         step()
     for L in layers:

@@ -44,6 +44,24 @@ int pair_gemm(int bn, const void* a, const void* b, const float* sa, const float
               int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sa_stride_m, int64_t sa_stride_k,
               int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, int sm_count, void* stream);
 
+// Launch with programmatic stream serialization allowed: the kernel may begin before the previous kernel of the stream
+// has finished and must call ptx::grid_dep_wait() before it touches anything that kernel writes or reads.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 #define SGLB_CHECK_LAUNCH(what)                                                                   \

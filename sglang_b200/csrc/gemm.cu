@@ -550,6 +550,8 @@ template <typename OutT>
 __global__ void __launch_bounds__(256)
 splitk_reduce_kernel(const float* __restrict__ partial, OutT* __restrict__ out, int32_t M, int32_t N, int64_t ldc,
                      int32_t splits) {
+  ptx::grid_dep_launch();  // the next kernel may begin its set-up (and a GEMM its weight streaming) beside this one
+  ptx::grid_dep_wait();    // the partial sums come from the kernel before this one
   const int32_t vec_per_row = N / 8;
   const int64_t total = (int64_t)M * vec_per_row;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
@@ -890,11 +892,11 @@ void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N,
   if (rgrid > sm_count * 8) rgrid = sm_count * 8;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (out_dtype == SGLB200_BF16) {
-    splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(partial, static_cast<__nv_bfloat16*>(out), (int32_t)M,
-                                                              (int32_t)N, ldc, splits);
+    launch_pdl(splitk_reduce_kernel<__nv_bfloat16>, dim3(rgrid), dim3(256), 0, st, partial, static_cast<__nv_bfloat16*>(out),
+               (int32_t)M, (int32_t)N, ldc, (int32_t)splits);
   } else {
-    splitk_reduce_kernel<__half><<<rgrid, 256, 0, st>>>(partial, static_cast<__half*>(out), (int32_t)M, (int32_t)N, ldc,
-                                                       splits);
+    launch_pdl(splitk_reduce_kernel<__half>, dim3(rgrid), dim3(256), 0, st, partial, static_cast<__half*>(out), (int32_t)M,
+               (int32_t)N, ldc, (int32_t)splits);
   }
 }
 

@@ -9,6 +9,12 @@
 //
 // warp 0: TMA producer; warp 1: TMEM owner + MMA issuer; warps 2..5: promotion (tcgen05.ld, acc += p * sa[token] * sb)
 // and the transposed store.  All waits are bounded.
+//
+// The kernel is launched with programmatic stream serialization: it may start while the kernel before it (the
+// activation quantiser, or the previous layer's reduce kernel) is still running.  Its set-up and the WEIGHT tiles of the
+// first ring of stages depend on nothing earlier in the stream and are issued at once; the activation tiles, the
+// activation scales and every store come after griddepcontrol.wait.  At decode sizes the fixed cost of a call (launch,
+// set-up, first TMA round trip) is of the order of the streaming time itself, and this hides most of it.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -162,34 +168,54 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
   const uint32_t acc_full0 = ptx::smem_u32(&ctl->acc_full[0]), acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
   const uint32_t stage0 = ptx::smem_u32(smem);
 
+  if (threadIdx.x == 0) ptx::grid_dep_launch();  // the next kernel of the stream may begin its own set-up
+
   if (warp == 0) {
-    // ===== TMA producer
-    uint32_t stage = 0, phase = 0;
-    for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
-      const int32_t split = t / p.n_tiles, nt = t - split * p.n_tiles;
-      const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+    // ===== TMA producer.  Pass 0 runs before griddepcontrol.wait: the weight tiles of the first k-blocks (at most one
+    // ring of stages, whose barriers are fresh) are requested; pass 1 adds their activation tiles and then continues
+    // with whole stages.
+    uint32_t pre = 0;
+    for (int pass = 0; pass < 2; ++pass) {
+      uint32_t stage = 0, phase = 0, idx = 0;
       bool ok = true;
-      for (int32_t kb = kb0; kb < kb1; ++kb) {
-        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
-          timeout(ctl, 11);
-          ok = false;
-          break;
-        }
-        if (lane == 0) {
+      for (int32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
+        const int32_t split = t / p.n_tiles, nt = t - split * p.n_tiles;
+        const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+        for (int32_t kb = kb0; kb < kb1; ++kb, ++idx) {
           const uint32_t dst = stage0 + stage * C::kStageBytes;
-          ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, C::kStageBytes);
-          ptx::tma_load_2d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN);
-          ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, 0);
+          if (pass == 0) {
+            if (idx >= (uint32_t)C::kStages) { ok = false; break; }
+            if (lane == 0) {
+              ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, C::kStageBytes);
+              ptx::tma_load_2d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN);
+            }
+            pre = idx + 1;
+          } else if (idx < pre) {
+            if (lane == 0) ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, 0);
+          } else {
+            if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) {
+              timeout(ctl, 11);
+              ok = false;
+              break;
+            }
+            if (lane == 0) {
+              ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, C::kStageBytes);
+              ptx::tma_load_2d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN);
+              ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, 0);
+            }
+          }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        if (ctl->abort_flag) ok = false;
       }
-      if (!ok || ctl->abort_flag) break;
-    }
-    // the last tcgen05.commit arrivals on `empty` must have landed before the CTA's shared memory is reused
-    if (!ctl->abort_flag) {
-      for (int i = 0; i < C::kStages; ++i) {
-        if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { timeout(ctl, 15); break; }
-        if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+      if (pass == 0) {
+        ptx::grid_dep_wait();  // the activations are written by the kernel before this one
+      } else if (!ctl->abort_flag) {
+        // the last tcgen05.commit arrivals on `empty` must have landed before the CTA's shared memory is reused
+        for (int i = 0; i < C::kStages; ++i) {
+          if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { timeout(ctl, 15); break; }
+          if (++stage == C::kStages) { stage = 0; phase ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
@@ -222,6 +248,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     }
   } else {
     // ===== promotion + transposed store; TMEM lane quarter = warp % 4 (warps 2, 3, 4, 5 -> quarters 2, 3, 0, 1)
+    ptx::grid_dep_wait();  // the activation scales come from the kernel before this one, and it may still read `out` / `partial`
     const int q = warp & 3;
     constexpr int kPerLane = MT / 32 > 0 ? MT / 32 : 1;  // tokens whose activation scale this lane fetches
     uint32_t acc_stage = 0, acc_phase = 0;
@@ -336,8 +363,12 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams
   }
   const int total = p.n_tiles * p.k_splits;
   const int grid = total < sm_count ? total : sm_count;
-  fp8_block_gemm_smallm_kernel<MT, UE><<<grid, kThreads, Cfg<MT>::kSmem, st>>>(map_w, map_a, p);
-  SGLB_CHECK_LAUNCH("fp8_block_gemm_smallm_kernel");
+  const cudaError_t le = launch_pdl(fp8_block_gemm_smallm_kernel<MT, UE>, dim3(grid), dim3(kThreads), Cfg<MT>::kSmem, st,
+                                    map_w, map_a, p);
+  if (le != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SGLB200_ERR_LAUNCH, "fp8_block_gemm_smallm_kernel: %s", cudaGetErrorString(le));
+  }
   return SGLB200_OK;
 }
 

@@ -16,6 +16,15 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-serialization attribute may start while the kernel before it in the stream is
+// still running.  grid_dep_wait() blocks until that kernel has completed and its writes are visible: everything that
+// reads what it produced, or overwrites what it may still read, comes after it; work that depends on neither (barrier
+// set-up, TMEM allocation, streaming the weights) goes before it.  grid_dep_launch() lets the NEXT kernel in the stream
+// start early in the same way.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");

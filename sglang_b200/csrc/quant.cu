@@ -16,6 +16,7 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "ptx.cuh"
 #include "quant_math.cuh"
 #include "quant_vec.cuh"
 
@@ -56,6 +57,10 @@ __global__ void __launch_bounds__(kThreads) group_quant16_kernel(const QuantPara
   const uint32_t base = blockIdx.x * (uint32_t)(kGroupsPerIter * kUnroll) + tg;
   const float inv_max = __frcp_rn(p.fp8_max);
   const bool fast_scale = p.fp8_max == 448.0f;
+  // programmatic dependent launch: the GEMM that follows may begin its set-up and stream its weights beside this
+  // kernel; this kernel's own input comes from the kernel before it
+  ptx::grid_dep_launch();
+  ptx::grid_dep_wait();
 
   uint4 raw[kUnroll][2];
   uint32_t row[kUnroll], grp[kUnroll];
@@ -233,11 +238,11 @@ int launch16(const QuantParams& p, bool ue8m0, bool clamp, cudaStream_t stream) 
   constexpr int kGroupsPerBlock = (kThreads / LPG) * kUnroll;
   const uint32_t blocks = (p.num_groups + kGroupsPerBlock - 1) / kGroupsPerBlock;
   if (ue8m0) {
-    if (clamp) group_quant16_kernel<T, LPG, true, FUSE, true><<<blocks, kThreads, 0, stream>>>(p);
-    else group_quant16_kernel<T, LPG, true, FUSE, false><<<blocks, kThreads, 0, stream>>>(p);
+    if (clamp) launch_pdl(group_quant16_kernel<T, LPG, true, FUSE, true>, dim3(blocks), dim3(kThreads), 0, stream, p);
+    else launch_pdl(group_quant16_kernel<T, LPG, true, FUSE, false>, dim3(blocks), dim3(kThreads), 0, stream, p);
   } else {
-    if (clamp) group_quant16_kernel<T, LPG, false, FUSE, true><<<blocks, kThreads, 0, stream>>>(p);
-    else group_quant16_kernel<T, LPG, false, FUSE, false><<<blocks, kThreads, 0, stream>>>(p);
+    if (clamp) launch_pdl(group_quant16_kernel<T, LPG, false, FUSE, true>, dim3(blocks), dim3(kThreads), 0, stream, p);
+    else launch_pdl(group_quant16_kernel<T, LPG, false, FUSE, false>, dim3(blocks), dim3(kThreads), 0, stream, p);
   }
   SGLB_CHECK_LAUNCH("group_quant16_kernel");
   return SGLB200_OK;
