@@ -80,6 +80,9 @@ int sglb200_get_num_sms(void);
  *   q = RNE_e4m3(clamp(x / s, fp8_min, fp8_max)) with a correctly rounded fp32 quotient.
  * `eps` is used as given, in fp32: a caller that wants the torch-native behaviour for bf16 input
  * passes eps already rounded to bf16 (the Python wrapper does).
+ * UE8M0: the power-of-two rounding is applied to amax / fp8_max as it is; no further floor on the scale (the
+ * torch-native / Triton behaviour).  The reference's v1 CUDA kernel clamps the scale at 1e-10 before rounding, so its
+ * exponent byte for an all-zero group is 94 where this entry point writes the exponent of eps / fp8_max rounded up.
  */
 int sglb200_per_token_group_quant_fp8(const void* input, int in_dtype, void* out_q, void* out_s,
                                       int64_t num_rows, int64_t hidden, int group_size, float eps,

@@ -177,3 +177,28 @@ def test_overlapped_row_parallel_linear_two_ranks():
     for p in procs:
         p.join(timeout=30)
     assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_bf16_sum_bound_covers_any_order_of_a_library_all_reduce():
+    """The bound used for the NCCL paths: a sum of the ranks' bf16 partial results taken in bf16, in ring order from any
+    starting rank or as a pairwise tree, lies within `sum_in_storage_type_bound` of the fp32 sum rounded once."""
+    import oracle
+    g = torch.Generator().manual_seed(0)
+    world = 8
+    x = torch.randn(48, 2048, generator=g).bfloat16()
+    wq, ws = oracle.block_quant_weight(torch.randn(256, 2048, generator=g) * 0.05)
+    parts = oracle.row_parallel_partials(x, wq, ws, world)
+    ref = oracle.row_parallel_reference(x, wq, ws, world).double()
+    slack = oracle.sum_in_storage_type_bound(parts)
+    worst = 0.0
+    for start in range(world):  # ring orders
+        acc = parts[start].clone()
+        for i in range(1, world):
+            acc = (acc.float() + parts[(start + i) % world].float()).bfloat16()
+        assert bool(((acc.double() - ref).abs() <= slack).all())
+        worst = max(worst, float((acc.double() - ref).abs().max() / ref.pow(2).mean().sqrt()))
+    level = list(parts)  # pairwise tree
+    while len(level) > 1:
+        level = [(level[i].float() + level[i + 1].float()).bfloat16() for i in range(0, len(level), 2)]
+    assert bool(((level[0].double() - ref).abs() <= slack).all())
+    assert worst > 2e-2, "with eight bf16 additions the plain 2e-2 x RMS bar is expected to be missed by some element"
