@@ -197,10 +197,11 @@ def cpu_arm(steps: int, warmup: int, m_sample: int):
             "ms_per_pass": dt * 1e3}
 
 
-def moe_section(torch, dev, gen, Ms=(256, 4096, 16384), E=256, topk=8, H=7168, I=2048):
+def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H=7168, I=2048):
     """Block-FP8 fused MoE, DeepSeek-V3 layer shape: 256 experts, top-8 of softmax(random logits), hidden 7168,
     moe_intermediate 2048, M tokens; random e4m3 expert weights (11.3 GB).  Two checkpoints: fp32 block scales
     (software promotion) and power-of-two (UE8M0) scales (grouped GEMMs on the hardware block-scaling path)."""
+    from sglang_b200._lib import lib
     from sglang_b200.layers.moe import fused_experts_block_fp8, fused_experts_block_fp8_ue8m0
     from sglang_b200.layers.quantization import pack_ue8m0_scales
 
@@ -228,26 +229,39 @@ def moe_section(torch, dev, gen, Ms=(256, 4096, 16384), E=256, topk=8, H=7168, I
         tw, ti = torch.topk(torch.softmax(torch.randn(M, E, device=dev, generator=gen), -1), topk)
         ti = ti.to(torch.int32)
         flops = M * topk * (2.0 * H * 2 * I + 2.0 * I * H)
-        case = {"M": M}
-        for name, fn in (("fp32_scales", lambda: fused_experts_block_fp8(a, w1, w2, w1s, w2s, tw, ti)),
-                         ("ue8m0", lambda: fused_experts_block_fp8_ue8m0(a, w1, w2, w1p, w2p, tw, ti))):
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            n = 5
-            e0.record()
-            for _ in range(n):
-                fn()
-            e1.record()
-            torch.cuda.synchronize()
+        # weights of the experts that received a row: what a call has to stream from HBM
+        routed = int(torch.unique(ti).numel())
+        w_bytes = routed * (w1.numel() + w2.numel()) // E
+        case = {"M": M, "experts_with_rows": routed, "routed_weight_bytes": w_bytes}
+        few_rows = M * topk <= lib().sglb200_get_grouped_few_rows() * E  # the fp32-scale grouped GEMMs take the few-rows kernel
+        variants = [("fp32_scales", lambda: fused_experts_block_fp8(a, w1, w2, w1s, w2s, tw, ti), None),
+                    ("ue8m0", lambda: fused_experts_block_fp8_ue8m0(a, w1, w2, w1p, w2p, tw, ti), None)]
+        if few_rows:  # the same calls with the few-rows kernel switched off: the 128 x 128 grouped kernels
+            variants += [("fp32_scales_tile_kernel", variants[0][1], 0)]
+        for name, fn, limit in variants:
+            before = lib().sglb200_get_grouped_few_rows()
+            if limit is not None:
+                lib().sglb200_set_grouped_few_rows(limit)
+            try:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                n = 5
+                e0.record()
+                for _ in range(n):
+                    fn()
+                e1.record()
+                torch.cuda.synchronize()
+            finally:
+                lib().sglb200_set_grouped_few_rows(before)
             ms = e0.elapsed_time(e1) / n
             case[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
-                          "weight_tbs": (w1.numel() + w2.numel()) / (ms * 1e-3) / 1e12}
+                          "weight_tbs": w_bytes / (ms * 1e-3) / 1e12}
         out["cases"].append(case)
     return out
 
 
-def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5):
+def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=None):
     """Tensor-parallel decoder projections at the Llama-3-70B shape (hidden 8192, intermediate 28672, 64 q / 8 kv
     heads of 128): column-parallel QKV and gate_up, row-parallel o and down, each followed by an NCCL all-reduce of the
     [M, 8192] bf16 output (none at tp1).  One step = the four linears of a layer on M tokens; device time, max over
@@ -269,29 +283,42 @@ def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def step():
+    def step(use_mc):
         for mode, w, ws, x in built:
             q, sc = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
-            y = w8a8_block_fp8_matmul(q, w, sc, ws, [128, 128], torch.bfloat16)
-            if mode == "row" and world > 1:
+            row = mode == "row" and world > 1
+            y = w8a8_block_fp8_matmul(q, w, sc, ws, [128, 128], torch.bfloat16,
+                                      out=mc.view((M, w.shape[0])) if row and use_mc else None)
+            if row and use_mc:
+                mc.all_reduce_(y)
+            elif row:
                 dist.all_reduce(y)
 
-    for _ in range(3):
-        step()
-    sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        step()
-    e1.record()
-    sync()
-    ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    return {"workload": f"Llama-3-70B layer projections, M={M}, tp{world}: qkv/gate_up column-parallel, o/down "
-                        "row-parallel + NCCL all-reduce", "ms_per_layer": float(ms),
-            "tflops": flops / (float(ms) * 1e-3) / 1e12,
-            "allreduce_bytes_per_layer": 2 * M * 8192 * 2 if world > 1 else 0}
+    def timed(use_mc):
+        for _ in range(3):
+            step(use_mc)
+        sync()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            step(use_mc)
+        e1.record()
+        sync()
+        ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms)
+
+    ms = timed(False)
+    out = {"workload": f"Llama-3-70B layer projections, M={M}, tp{world}: qkv/gate_up column-parallel, o/down "
+                       "row-parallel + NCCL all-reduce", "ms_per_layer": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+           "allreduce_bytes_per_layer": 2 * M * 8192 * 2 if world > 1 else 0}
+    if mc is not None and world > 1 and 2 * M * 8192 <= mc.max_size:
+        ms_mc = timed(True)
+        out["multicast_allreduce"] = {"ms_per_layer": ms_mc, "tflops": flops / (ms_mc * 1e-3) / 1e12,
+                                      "how": "row-parallel GEMMs write into NVSwitch multicast memory, one multimem "
+                                             "kernel (ld_reduce + st) per all-reduce"}
+    return out
 
 
 def ep_moe_section(torch, dist, dev, gen, world, rank, M_total=4096, E=256, topk=8, H=7168, I=2048, iters=5,
@@ -412,7 +439,8 @@ def parity_section(torch, dist, dev, world, rank):
         if slack is not None:
             bound = torch.maximum(bound, slack)
             res["bar"] = ("rel-L2 <= 1e-2; max-abs <= 2e-2 x RMS or the rounding of a sum of the ranks' bf16 partial results "
-                          "taken in bf16 (NCCL adds bf16 buffers in bf16; the oracle adds them in fp32)")
+                          "taken in bf16 (NCCL adds bf16 buffers in bf16 and the NVSwitch adder does not round to nearest; "
+                          "the oracle adds them in fp32 and rounds once)")
         res["elements_over"] = int((diff > bound).sum())
         res["pass"] = bool(rel <= 1e-2 and res["elements_over"] == 0)
         return res
@@ -428,6 +456,15 @@ def parity_section(torch, dist, dev, world, rank):
     outs = {"tp_nccl_allreduce": layer(xr)}
     from sglang_b200.distributed import row_parallel_linear_overlapped
     outs["tp_nccl_overlapped_chunks"] = row_parallel_linear_overlapped(xr, layer.weight, layer.weight_scale_inv, chunk_rows=128)
+    from sglang_b200.distributed import SymmMemCommunicator, row_parallel_linear_symm_mem
+    mc = SymmMemCommunicator(dist.group.WORLD, dev, max_size=8 << 20)
+    try:
+        if not mc.disabled:
+            outs["tp_multicast_allreduce"] = row_parallel_linear_symm_mem(mc, xr, layer.weight,
+                                                                          layer.weight_scale_inv).clone()
+            torch.cuda.synchronize()
+    finally:
+        mc.close()
     ex = PeerExchange(slot_elems=M * N)
     try:
         outs["tp_peer_one_shot"] = fused_row_parallel_linear(ex, xr, layer.weight, layer.weight_scale_inv, two_shot=False)
@@ -464,7 +501,7 @@ def parity_section(torch, dist, dev, world, rank):
         ref = oracle.row_parallel_reference(x, wq, ws, world)
         slack = oracle.sum_in_storage_type_bound(parts)
         for k, v in outs.items():
-            res[k] = verdict(v, ref, slack if "nccl" in k else None)
+            res[k] = verdict(v, ref, slack if ("nccl" in k or "multicast" in k) else None)
         ref_ep = oracle.expert_parallel_reference(xm, w1q, w2q, w1s, w2s, tw, ti, world)
         for k, v in ep_outs.items():
             res[k] = verdict(v, ref_ep)
@@ -610,7 +647,11 @@ def main():
     ap.add_argument("--overlap", type=int, default=-1,
                     help="N > 1: 1 = the all-reduce of a row chunk overlaps the next chunk's GEMM; 0 = all-reduce after "
                          "each row-parallel GEMM on the same stream; -1 (default) = time both during set-up and keep the faster")
-    ap.add_argument("--chunk-rows", type=int, default=2048, help="rows per chunk of the overlapped row-parallel linear")
+    ap.add_argument("--multicast", type=int, default=-1,
+                    help="N > 1: 1 = row-parallel GEMMs write into NVSwitch multicast memory and this library's "
+                         "multimem kernel adds them; 0 = never; -1 = tried with the other orders, the fastest is kept")
+    ap.add_argument("--chunk-rows", type=int, default=0,
+                    help="rows per chunk of the overlapped row-parallel linear; 0 = M / 4 and M / 2 are both tried")
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL while overlapping")
     ap.add_argument("--nccl-max-ctas", type=int, default=0, help="upper bound on NCCL's CTAs per collective (0: NCCL's own)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -778,31 +819,45 @@ def main():
                        "x": x, "gemm_ms": [], "wq_u": wq_u, "ws_u": pack_ue8m0_scales(ws_u), "ev_u": []})
 
     overlap = world > 1 and args.overlap == 1
+    mc, multicast = None, False
     if world > 1:
-        from sglang_b200.distributed import row_parallel_linear_overlapped
+        from sglang_b200.distributed import SymmMemCommunicator, row_parallel_linear_overlapped
         from sglang_b200.layers.deep_gemm_wrapper import configure_deep_gemm_num_sms
         sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
+        if args.multicast != 0:
+            mc = SymmMemCommunicator(dist.group.WORLD, dev,
+                                     max_size=2 * M * max([L["N"] for L in layers if L["mode"] == "row"] + [8192]))
+            if mc.disabled:
+                mc = None
+        multicast = mc is not None and args.multicast == 1
+        overlap = overlap and not multicast
 
+    chunk_rows = [args.chunk_rows if args.chunk_rows > 0 else max(128, M // 4)]
     own_launches = [0]  # kernels of this library launched by step(): one quantiser + one GEMM per layer (per chunk)
 
     def step(record=False):
         for L in layers:
             if overlap and L["mode"] == "row":
-                own_launches[0] += 1 + -(-M // args.chunk_rows)
+                own_launches[0] += 1 + -(-M // chunk_rows[0])
                 with configure_deep_gemm_num_sms(sm_total - args.comm_sms if args.comm_sms > 0 else None):
                     y = row_parallel_linear_overlapped(L["x"], L["layer"].weight, L["layer"].weight_scale_inv,
-                                                       chunk_rows=args.chunk_rows)
+                                                       chunk_rows=chunk_rows[0])
                 continue
             own_launches[0] += 2
+            use_mc = multicast and L["mode"] == "row"
             q, s = sglang_per_token_group_quant_fp8(L["x"], 128, column_major_scales=True, scale_tma_aligned=True)
             if record:
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-            y = w8a8_block_fp8_matmul(q, L["layer"].weight, s, L["layer"].weight_scale_inv, [128, 128], torch.bfloat16)
+            y = w8a8_block_fp8_matmul(q, L["layer"].weight, s, L["layer"].weight_scale_inv, [128, 128], torch.bfloat16,
+                                      out=mc.view((M, L["n_loc"])) if use_mc else None)
             if record:
                 e1.record()
                 L["ev"].append((e0, e1))
-            if world > 1 and L["mode"] == "row":
+            if use_mc:
+                own_launches[0] += 1
+                mc.all_reduce_(y)
+            elif world > 1 and L["mode"] == "row":
                 dist.all_reduce(y)
         return y
 
@@ -823,9 +878,13 @@ def main():
             for L in layers:
                 q, s = mark("quant", lambda: sglang_per_token_group_quant_fp8(L["x"], 128, column_major_scales=True,
                                                                               scale_tma_aligned=True))
+                use_mc = multicast and L["mode"] == "row"
                 y = mark("gemm", lambda: w8a8_block_fp8_matmul(q, L["layer"].weight, s, L["layer"].weight_scale_inv,
-                                                               [128, 128], torch.bfloat16))
-                if world > 1 and L["mode"] == "row":
+                                                               [128, 128], torch.bfloat16,
+                                                               out=mc.view((M, L["n_loc"])) if use_mc else None))
+                if use_mc:
+                    mark("allreduce", lambda: mc.all_reduce_(y))
+                elif world > 1 and L["mode"] == "row":
                     mark("allreduce", lambda: dist.all_reduce(y))
 
         plain_step()
@@ -846,7 +905,8 @@ def main():
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         step_ms, qm, gm, am, hm = (float(v) for v in t)
-        return {"order": "plain (no overlap), max over ranks", "step_ms": step_ms, "quant_ms": qm, "gemm_ms": gm,
+        return {"order": ("multicast all-reduce kernel after each row-parallel GEMM" if multicast
+                          else "plain (no overlap)") + ", max over ranks", "step_ms": step_ms, "quant_ms": qm, "gemm_ms": gm,
                 "allreduce_ms": am, "host_gap_ms": step_ms - (qm + gm + am), "host_enqueue_ms": hm,
                 "launches_per_step": sum(len(v) for v in evs.values()) // n_steps}
 
@@ -862,12 +922,15 @@ def main():
             dist.all_reduce(warm)
         del warm
         fence()
-    if world > 1 and args.overlap < 0:
-        # set-up, not a step: time both orders of a step (three steps each after one warm-up step, device time, max over
-        # ranks) and keep the faster for the warm-up and the timed region
+    if world > 1 and args.overlap < 0 and args.multicast != 1:
+        # set-up, not a step: time the orders of a step (three steps each after one warm-up step, device time, max over
+        # ranks) and keep the fastest for the warm-up and the timed region
         tried = {}
-        for mode in (False, True):
-            overlap = mode
+        chunk_choices = [args.chunk_rows] if args.chunk_rows > 0 else [max(128, M // 4), max(128, M // 2)]
+        for mode in (["plain"] + [f"overlapped_{c}" for c in chunk_choices] + (["multicast"] if mc is not None else [])):
+            overlap, multicast = mode.startswith("overlapped"), mode == "multicast"
+            if overlap:
+                chunk_rows[0] = int(mode.split("_")[1])
             step()
             fence()
             a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -878,13 +941,18 @@ def main():
             fence()
             tt = torch.tensor([a0.elapsed_time(a1) / 3], device=dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            tried["overlapped" if mode else "plain"] = float(tt)
-        overlap = tried["overlapped"] < tried["plain"]
+            tried[mode] = float(tt)
+        best = min(tried, key=tried.get)
+        overlap, multicast = best.startswith("overlapped"), best == "multicast"
+        if overlap:
+            chunk_rows[0] = int(best.split("_")[1])
         config["step_tried_ms"] = tried
     if world > 1:
-        config["step"] = ((f"row-parallel layers in chunks of {args.chunk_rows} rows, the NCCL all-reduce of a chunk overlaps "
+        config["step"] = ((f"row-parallel layers in chunks of {chunk_rows[0]} rows, the NCCL all-reduce of a chunk overlaps "
                            f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"
                                                        if args.comm_sms > 0 else "")) if overlap
+                          else ("row-parallel GEMMs write into NVSwitch multicast memory; this library's multimem kernel "
+                                "(ld_reduce + st, one launch) adds them in place, same stream") if multicast
                           else "NCCL all-reduce after each row-parallel GEMM, same stream")
     for _ in range(args.warmup if args.only not in ("quant", "ue8m0") else 0):
         step()
@@ -1039,6 +1107,8 @@ def main():
                               "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "config": config,
                               "clocks": clocks, "roofline": roofline, "quant": quant, "per_shape": per_shape,
                               "ue8m0": ue8m0, "breakdown": breakdown}))
+        if mc is not None:
+            mc.close()
         if world > 1:
             dist.destroy_process_group()
         return
@@ -1053,10 +1123,22 @@ def main():
         torch.cuda.empty_cache()
         for case in (moe.get("cases") or []):
             for ck in ("fp32_scales", "ue8m0"):
-                roofline["others"].append({"kernel": f"fused_experts ({ck}), nine launches", "bound": "tensor",
-                                           "achieved": case[ck]["tflops"], "peak": fp8_peak, "unit": "TFLOP/s",
-                                           "frac": case[ck]["tflops"] / fp8_peak, "ms": case[ck]["ms"],
-                                           "workload": f"E=256 top-8 H=7168 I=2048 M={case['M']}"})
+                wl = f"E=256 top-8 H=7168 I=2048 M={case['M']}"
+                if case["M"] <= 256:
+                    # few rows per expert: bound by streaming the weights of the experts that have rows
+                    gbs = case[ck]["weight_tbs"] * 1e3
+                    entry = {"kernel": f"fused_experts ({ck}), nine launches", "bound": "hbm", "achieved": gbs,
+                             "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                             "ms": case[ck]["ms"],
+                             "workload": wl + f", {case['experts_with_rows']} experts with rows"}
+                    if ck + "_tile_kernel" in case:
+                        entry["ms_with_128x128_grouped_kernel"] = case[ck + "_tile_kernel"]["ms"]
+                    roofline["others"].append(entry)
+                else:
+                    roofline["others"].append({"kernel": f"fused_experts ({ck}), nine launches", "bound": "tensor",
+                                               "achieved": case[ck]["tflops"], "peak": fp8_peak, "unit": "TFLOP/s",
+                                               "frac": case[ck]["tflops"] / fp8_peak, "ms": case[ck]["ms"],
+                                               "workload": wl})
 
     # ---- the mid sizes of the sweep (M = 128 / 512 / 2048): GEMM kernel alone per shape
     per_shape_mid = None
@@ -1157,9 +1239,12 @@ def main():
         layers_n = len(layers)
         torch.cuda.empty_cache()
         try:
-            tp_llama = tp_llama_section(torch, dist, dev, gen, world, rank)
+            tp_llama = tp_llama_section(torch, dist, dev, gen, world, rank, mc=mc)
         except Exception as e:  # noqa: BLE001
             tp_llama = {"error": f"{type(e).__name__}: {e}"}
+        if mc is not None:
+            mc.close()
+            mc = None
         torch.cuda.empty_cache()
         if not args.no_moe:
             ep_moe = []

@@ -61,6 +61,23 @@ int sglb200_set_num_sms(int num_sms);
 int sglb200_get_num_sms(void);
 
 /*
+ * Grouped GEMMs with fp32 scales (sglb200_fp8_blockwise_scaled_grouped_mm and its masked form) whose experts hold at
+ * most max_avg_rows rows on average (total rows / experts; the row bound per expert in the masked layout) run on the
+ * few-rows kernel: operands swapped, 128 weight rows x 16 / 32 / 64 activation rows per MMA, only the weights of
+ * experts that have rows are streamed.  This is the decode case of a mixture-of-experts layer, where the 128 x 128
+ * kernel spends a full tile of tensor-core work and promotion on a handful of rows.  Default 20 (measured cross-over
+ * on the DeepSeek-V3 layer shape: faster up to 8 rows per expert, level at 32); 0 = always the 128 x 128 kernel;
+ * at most 64.  The UE8M0 grouped GEMM has no such form: its tile kernel has no promotion to save and streams weights
+ * at the same rate.
+ * The results of the two kernels are bit-identical (same products, same fp32 accumulation order per k-block).
+ * Process-wide, read at every launch.
+ * Replaces: the small-M tile configurations of the reference's grouped kernel,
+ *           sgl-kernel/csrc/moe/fp8_blockwise_moe_kernel.cu:440-560 (dispatch on the row count).
+ */
+int sglb200_set_grouped_few_rows(int max_avg_rows);
+int sglb200_get_grouped_few_rows(void);
+
+/*
  * Q — per-token-group quantisation to e4m3.
  * Replaces: sgl_per_token_group_quant_8bit  sgl-kernel/csrc/gemm/per_token_group_quant_8bit.cu:116-217
  *           (schema sgl-kernel/csrc/common_extension.cc:173-176) for the e4m3 destination type.
@@ -522,9 +539,32 @@ int sglb200_peer_close(void* dev_ptr);
 int sglb200_peer_free(void* dev_ptr);
 
 /*
+ * In-place sum over the ranks of one node of a bf16 / f16 buffer that every rank maps through ONE NVLink multicast
+ * address (NVSwitch in-switch reduction): the all-reduce after a row-parallel linear for outputs too large for the
+ * push epilogues above.  Rank r reduces the r-th slice of the buffer with multimem.ld_reduce (fp32 accumulation in the
+ * switch, ONE rounding of the sum) and writes the sums into every rank's memory with multimem.st, so each GPU sends and
+ * receives the buffer once.  Two bounded cross-rank barriers (flag words in peer memory, per-block epochs kept on the
+ * device: graph-replayable) make the call safe after the producer kernel on every rank's stream and complete on every
+ * rank when it ends.  Every rank must make the same call on its own stream, and the ranks' kernels must be able to run
+ * at the same time (one GPU per rank).
+ *   multicast_addr  address of element 0 of the buffer in the MULTICAST mapping (not the local one), 16-byte aligned.
+ *   flag_blocks     HOST array of `world` device addresses: entry r = rank r's flag block (sglb200_nvls_flag_bytes()
+ *                   bytes, zero before the first call) as mapped in this process.
+ *   numel           elements, a multiple of 8.
+ * The library creates neither the multicast object nor the peer mappings; the Python side (sglang_b200.distributed.nvls)
+ * takes both from torch's symmetric-memory allocator.  A wait that runs out sets status 41 / 42 (first / second barrier).
+ * Replaces: the all-reduce the reference's row-parallel linear calls for large outputs, GroupCoordinator.all_reduce
+ *           python/sglang/srt/distributed/parallel_state.py:513-629 (pynccl / torch.distributed route), and the
+ *           symmetric-memory route device_communicators/torch_symm_mem.py (multimem_all_reduce_).
+ */
+int sglb200_nvls_all_reduce(uint64_t multicast_addr, const uint64_t* flag_blocks, int rank, int world, int64_t numel,
+                            int dtype, void* stream);
+int64_t sglb200_nvls_flag_bytes(void);
+
+/*
  * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
  * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce, 11-18 the same
- * roles in the UE8M0 and few-rows kernels, 21-23 the expert-parallel exchange, 31-35 the CTA-pair kernel).  Every
+ * roles in the UE8M0 and few-rows kernels, 21-23 the expert-parallel exchange, 31-35 the CTA-pair kernel, 41-42 the multicast all-reduce).  Every
  * kernel family keeps its own word; each call reads AND clears all of them and returns the first non-zero one, so a
  * status never surfaces on a later, unrelated read.  This call SYNCHRONISES the device (cudaMemcpyFromSymbol); it is for
  * tests and debugging, not for the serving path.  Returns -1 if the read itself failed.  No counterpart in the reference (its kernels have no bounded waits).

@@ -74,10 +74,14 @@ SIGNATURES = {
     "sglb200_version": [],
     "sglb200_set_num_sms": [_I],
     "sglb200_get_num_sms": [],
+    "sglb200_set_grouped_few_rows": [_I],
+    "sglb200_get_grouped_few_rows": [],
+    "sglb200_nvls_all_reduce": [ctypes.c_uint64, _P, _I, _I, _L, _I, _P],
+    "sglb200_nvls_flag_bytes": [],
 }
 _RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64,
              "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": c_int64,
-             "sglb200_ep_buffer_bytes": c_int64, "sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes": c_int64, "sglb200_peer_flag_bytes": c_int64, "sglb200_peer_recv_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
+             "sglb200_ep_buffer_bytes": c_int64, "sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes": c_int64, "sglb200_peer_flag_bytes": c_int64, "sglb200_nvls_flag_bytes": c_int64, "sglb200_peer_recv_bytes": c_int64, "sglb200_status_string": c_char_p, "sglb200_last_error_detail": c_char_p, "sglb200_version": c_char_p}
 
 _lib = None
 

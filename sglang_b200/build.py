@@ -74,12 +74,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         objs = list(ex.map(lambda s: _compile(s, force, verbose), srcs))
     if force or not os.path.exists(LIB) or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs):
-        cmd = [_nvcc(), "-shared", "-o", LIB, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-ldl",
+        # link beside the target and rename: a reader never sees a half-written library
+        tmp = LIB + f".{os.getpid()}.tmp"
+        cmd = [_nvcc(), "-shared", "-o", tmp, *objs, "-cudart", "static", "-Xlinker", "--no-undefined", "-ldl",
                "-lpthread", "-lrt"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
+            if os.path.exists(tmp):
+                os.remove(tmp)
             raise RuntimeError("link of libsglb200.so failed")
+        os.replace(tmp, LIB)
     return LIB
 
 

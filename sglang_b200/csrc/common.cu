@@ -18,6 +18,7 @@ int fail(int code, const char* fmt, ...) {
 }
 
 static int g_num_sms_limit = 0;  // 0: no limit
+int g_grouped_few_rows_max = 20;  // grouped GEMMs with at most this many rows per expert on average take the few-rows kernel
 
 int device_info(DeviceInfo* out) {
   static DeviceInfo cache[64];
@@ -71,6 +72,15 @@ int sglb200_set_num_sms(int num_sms) {
   sglb::g_num_sms_limit = num_sms;
   return SGLB200_OK;
 }
+
+int sglb200_set_grouped_few_rows(int max_avg_rows) {
+  if (max_avg_rows < 0 || max_avg_rows > 64)
+    return sglb::fail(SGLB200_ERR_SHAPE, "max_avg_rows=%d: 0 (never) .. 64", max_avg_rows);
+  sglb::g_grouped_few_rows_max = max_avg_rows;
+  return SGLB200_OK;
+}
+
+int sglb200_get_grouped_few_rows(void) { return sglb::g_grouped_few_rows_max; }
 
 int sglb200_get_num_sms(void) {
   sglb::DeviceInfo di;

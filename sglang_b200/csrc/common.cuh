@@ -38,6 +38,16 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
 void launch_splitk_reduce(const float* partial, void* out, int64_t M, int64_t N, int64_t ldc, int splits, int out_dtype,
                           int sm_count, void* stream);  // gemm.cu
 int smallm_take_device_status();
+int nvls_take_device_status();  // nvls.cu
+extern int g_grouped_few_rows_max;  // common.cu; sglb200_set_grouped_few_rows
+// The grouped form of the few-rows kernel (one weight matrix per expert, few rows per expert); chunk 0 = do not use it
+int smallm_grouped_chunk(int64_t total_rows, int64_t num_experts, int64_t rows_per_expert);
+int smallm_grouped_gemm(int chunk, const void* a, const void* b, const float* sa, const float* sb, void* out,
+                        const int32_t* expert_offsets, const int32_t* problem_sizes, int count_stride, int64_t total_rows,
+                        int64_t num_experts, int64_t rows_per_expert, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                        int64_t ldb_e, int64_t ldc, int64_t sa_stride_e, int64_t sa_stride_m, int64_t sa_stride_k,
+                        int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, int sm_count,
+                        void* stream);
 
 // Dense GEMM on CTA pairs (256 x bn tiles, bn = 128 or 256), gemm_pair.cu
 int pair_gemm(int bn, const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N,

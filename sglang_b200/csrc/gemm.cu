@@ -994,6 +994,15 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
     return SGLB200_OK;
   }
 
+  if (grouped && !push) {
+    // few rows per expert: the weight-streaming kernel with swapped operands (gemm_smallm.cu)
+    if (const int chunk = smallm_grouped_chunk(total_rows, num_experts, rows_per_expert))
+      return smallm_grouped_gemm(chunk, a, b, sa, sb, out, expert_offsets, problem_sizes, rows_per_expert > 0 ? 1 : 3,
+                                 total_rows, num_experts, rows_per_expert, N, K, lda, ldb, ldb_e, ldc, sa_stride_e,
+                                 sa_stride_m, sa_stride_k, sb_stride_e, sb_stride_n, sb_stride_k, out_dtype, di.sm_count,
+                                 stream);
+  }
+
   alignas(64) CUtensorMap map_a, map_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)total_rows};
@@ -1418,13 +1427,14 @@ int pair_take_device_status();   // gemm_pair.cu
 // timed out (1 producer, 2/3 MMA issuer, 4 promotion warps, 5 peer flags / tail drain; 11-18 the same roles in the
 // UE8M0 and few-rows kernels; 21-23 expert-parallel exchange; 31-35 CTA-pair kernel).  All words are read and cleared on every call, so a
 // status never outlives the call that reports it; when several are set, the first non-zero one in the order UE8M0,
-// few-rows, expert-parallel, CTA-pair, dense is returned.  Synchronises the device: for tests and debugging, not for the
+// few-rows, expert-parallel, CTA-pair, multicast all-reduce, dense is returned.  Synchronises the device: for tests and debugging, not for the
 // serving path.
 extern "C" int sglb200_read_device_status(void) {
   const int u = sglb::ue8m0_take_device_status();
   const int sm = sglb::smallm_take_device_status();
   const int ep = sglb::ep_take_device_status();
   const int pr = sglb::pair_take_device_status();
+  const int nv = sglb::nvls_take_device_status();
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, sglb::g_device_status, sizeof(int)) != cudaSuccess) {
     cudaGetLastError();
@@ -1437,5 +1447,6 @@ extern "C" int sglb200_read_device_status(void) {
   if (sm != 0) return sm;
   if (ep != 0) return ep;
   if (pr != 0) return pr;
+  if (nv != 0) return nv;
   return v;
 }

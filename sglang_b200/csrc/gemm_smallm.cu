@@ -7,6 +7,11 @@
 // kernel is bound by HBM, not by the accumulator hand-off of the 128 x 128 kernel.  K can be cut into ranges that run on
 // different SMs (fp32 partial sums, added by splitk_reduce_kernel) when N / 128 tiles alone cannot occupy the SMs.
 //
+// GROUPED variant (one weight matrix per expert, few rows per expert: the decode case of a mixture-of-experts layer): a
+// work item is (expert, 128 weight rows, chunk of MT of the expert's rows).  The row ranges come from the same device
+// tables as in the 128 x 128 grouped kernel; an expert with more than MT rows gets several chunks (its weight tile is
+// then re-read, from L2), an expert without rows gets no item, so only the weights of routed experts are streamed.
+//
 // warp 0: TMA producer; warp 1: TMEM owner + MMA issuer; warps 2..5: promotion (tcgen05.ld, acc += p * sa[token] * sb)
 // and the transposed store.  All waits are bounded.
 //
@@ -48,6 +53,8 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWBytes = BN * BK;
 constexpr int kScaleAhead = 4;
 
+constexpr int kMaxExperts = 1024;
+
 template <int MT>
 struct Cfg {
   static constexpr int kStages = MT == 64 ? 8 : 10;
@@ -55,6 +62,8 @@ struct Cfg {
   static constexpr uint32_t kABytes = MT * BK;
   static constexpr uint32_t kStageBytes = kWBytes + kABytes;
   static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + 512;
+  // grouped: the table of first work items per expert follows the control block
+  static constexpr size_t kSmemGrouped = kSmem + (kMaxExperts + 1) * sizeof(int32_t) + 12;
 };
 
 struct SmallParams {
@@ -67,7 +76,61 @@ struct SmallParams {
   int64_t ldc;
   int64_t sa_stride_m, sa_stride_k, sb_stride_n, sb_stride_k;
   int32_t out_dtype;
+  // grouped only
+  const int32_t* expert_offsets;  // [E + 1] first row of every expert, or NULL in the masked layout
+  const int32_t* problem_sizes;   // optional: rows of expert e = problem_sizes[count_stride * e]
+  int32_t count_stride, rows_per_expert, num_experts;
+  int64_t sa_stride_e, sb_stride_e;
 };
+
+// one unit of work: rows [row0, row0 + rows) of the activations against weight rows [nt * 128, +128) of expert e,
+// k-blocks [kb0, kb1)
+struct Item {
+  int32_t e, nt, row0, rows, kb0, kb1, split;
+};
+
+__device__ __forceinline__ void expert_rows(const SmallParams& p, int32_t e, int32_t* r0, int32_t* cnt) {
+  if (p.rows_per_expert > 0) {
+    *r0 = e * p.rows_per_expert;
+    *cnt = max(0, min(__ldg(p.problem_sizes + p.count_stride * e), p.rows_per_expert));
+  } else {
+    *r0 = __ldg(p.expert_offsets + e);
+    *cnt = max(0, p.problem_sizes ? __ldg(p.problem_sizes + p.count_stride * e) : __ldg(p.expert_offsets + e + 1) - *r0);
+  }
+}
+
+template <int MT, bool GROUPED>
+__device__ __forceinline__ Item get_item(const SmallParams& p, const int32_t* item_start, int32_t t) {
+  Item it;
+  if constexpr (!GROUPED) {
+    it.split = t / p.n_tiles;
+    it.nt = t - it.split * p.n_tiles;
+    it.kb0 = it.split * p.kb_per_split;
+    it.kb1 = min(it.kb0 + p.kb_per_split, p.k_tiles);
+    it.e = 0;
+    it.row0 = 0;
+    it.rows = p.M;
+  } else {
+    int32_t lo = 0, hi = p.num_experts;  // last e with item_start[e] <= t
+    while (hi - lo > 1) {
+      const int32_t mid = (lo + hi) >> 1;
+      if (item_start[mid] <= t) lo = mid; else hi = mid;
+    }
+    int32_t r0, cnt;
+    expert_rows(p, lo, &r0, &cnt);
+    const int32_t chunks = (cnt + MT - 1) / MT;
+    const int32_t local = t - item_start[lo];
+    it.e = lo;
+    it.nt = local / chunks;
+    const int32_t ch = local - it.nt * chunks;
+    it.row0 = r0 + ch * MT;
+    it.rows = min(MT, cnt - ch * MT);
+    it.kb0 = 0;
+    it.kb1 = p.k_tiles;
+    it.split = 0;
+  }
+  return it;
+}
 
 struct Ctl {
   uint64_t full[10];
@@ -76,6 +139,7 @@ struct Ctl {
   uint64_t acc_empty[16];
   uint32_t tmem_base;
   volatile int32_t abort_flag;
+  int32_t total;
 };
 static_assert(sizeof(Ctl) <= 512, "control block");
 
@@ -130,7 +194,7 @@ __device__ __forceinline__ float load_scale(const float* base, int32_t kc, int64
   }
 }
 
-template <int MT, bool UE>
+template <int MT, bool UE, bool GROUPED>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                              const SmallParams p) {
@@ -138,6 +202,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + (size_t)C::kStages * C::kStageBytes);
+  int32_t* item_start = reinterpret_cast<int32_t*>(smem + (size_t)C::kStages * C::kStageBytes + 512);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
@@ -159,11 +224,41 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish();
   }
+  if constexpr (GROUPED) {
+    // The row tables are written by kernels earlier in the stream: nothing of the work list is known before they end.
+    ptx::grid_dep_wait();
+    if (warp == 2) {  // exclusive prefix sum of work items per expert
+      int32_t running = 0;
+      for (int32_t base = 0; base < p.num_experts; base += 32) {
+        const int32_t e = base + lane;
+        int32_t v = 0;
+        if (e < p.num_experts) {
+          int32_t r0, cnt;
+          expert_rows(p, e, &r0, &cnt);
+          v = ((cnt + MT - 1) / MT) * p.n_tiles;
+        }
+        int32_t incl = v;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+          if (lane >= d) incl += o;
+        }
+        if (e < p.num_experts) item_start[e] = running + incl - v;
+        running += __shfl_sync(0xffffffffu, incl, 31);
+      }
+      if (lane == 0) {
+        item_start[p.num_experts] = running;
+        ctl->total = running;
+      }
+    }
+  } else {
+    if (threadIdx.x == 0) ctl->total = p.n_tiles * p.k_splits;
+  }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
-  const int32_t total = p.n_tiles * p.k_splits;
+  const int32_t total = ctl->total;
   const uint32_t full0 = ptx::smem_u32(&ctl->full[0]), empty0 = ptx::smem_u32(&ctl->empty[0]);
   const uint32_t acc_full0 = ptx::smem_u32(&ctl->acc_full[0]), acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
   const uint32_t stage0 = ptx::smem_u32(smem);
@@ -175,20 +270,23 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     // ring of stages, whose barriers are fresh) are requested; pass 1 adds their activation tiles and then continues
     // with whole stages.
     uint32_t pre = 0;
-    for (int pass = 0; pass < 2; ++pass) {
+    uint32_t armed = 0, armed_phase = 0;  // bit i: stage i was armed / the phase bit of its last arming
+    for (int pass = GROUPED ? 1 : 0; pass < 2; ++pass) {
       uint32_t stage = 0, phase = 0, idx = 0;
       bool ok = true;
       for (int32_t t = blockIdx.x; t < total && ok; t += gridDim.x) {
-        const int32_t split = t / p.n_tiles, nt = t - split * p.n_tiles;
-        const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
-        for (int32_t kb = kb0; kb < kb1; ++kb, ++idx) {
+        const Item it = get_item<MT, GROUPED>(p, item_start, t);
+        const int32_t nt = it.nt;
+        for (int32_t kb = it.kb0; kb < it.kb1; ++kb, ++idx) {
           const uint32_t dst = stage0 + stage * C::kStageBytes;
           if (pass == 0) {
             if (idx >= (uint32_t)C::kStages) { ok = false; break; }
             if (lane == 0) {
               ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, C::kStageBytes);
-              ptx::tma_load_2d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN);
+              ptx::tma_load_3d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN, 0);
             }
+            armed |= 1u << stage;
+            armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
             pre = idx + 1;
           } else if (idx < pre) {
             if (lane == 0) ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, 0);
@@ -200,9 +298,11 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
             }
             if (lane == 0) {
               ptx::mbar_arrive_expect_tx_a(full0 + stage * 8, C::kStageBytes);
-              ptx::tma_load_2d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN);
-              ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, 0);
+              ptx::tma_load_3d_a(dst, &map_w, full0 + stage * 8, kb * BK, nt * BN, it.e);
+              ptx::tma_load_2d_a(dst + kWBytes, &map_a, full0 + stage * 8, kb * BK, it.row0);
             }
+            armed |= 1u << stage;
+            armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
           }
           if (++stage == C::kStages) { stage = 0; phase ^= 1; }
         }
@@ -210,7 +310,11 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
       }
       if (pass == 0) {
         ptx::grid_dep_wait();  // the activations are written by the kernel before this one
-      } else if (!ctl->abort_flag) {
+      } else if (ctl->abort_flag) {
+        // bulk copies must not be in flight when the CTA exits: wait (bounded) for every stage that may still be armed
+        for (int i = 0; i < C::kStages; ++i)
+          if (armed & (1u << i)) ptx::mbar_wait_a(full0 + i * 8, (armed_phase >> i) & 1u, 20000000ull);
+      } else {
         // the last tcgen05.commit arrivals on `empty` must have landed before the CTA's shared memory is reused
         for (int i = 0; i < C::kStages; ++i) {
           if (!ptx::mbar_wait_a(empty0 + stage * 8, phase ^ 1)) { timeout(ctl, 15); break; }
@@ -224,8 +328,12 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
     for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
-      const int32_t split = t / p.n_tiles;
-      const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+      int32_t kb0 = 0, kb1 = p.k_tiles;
+      if constexpr (!GROUPED) {
+        const int32_t split = t / p.n_tiles;
+        kb0 = split * p.kb_per_split;
+        kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+      }
       bool ok = true;
       for (int32_t kb = kb0; kb < kb1; ++kb) {
         if (!ptx::mbar_wait_a(acc_empty0 + acc * 8, acc_phase ^ 1)) { timeout(ctl, 12); ok = false; break; }
@@ -248,16 +356,23 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     }
   } else {
     // ===== promotion + transposed store; TMEM lane quarter = warp % 4 (warps 2, 3, 4, 5 -> quarters 2, 3, 0, 1)
-    ptx::grid_dep_wait();  // the activation scales come from the kernel before this one, and it may still read `out` / `partial`
+    if constexpr (!GROUPED)
+      ptx::grid_dep_wait();  // the activation scales come from the kernel before this one, and it may still read `out` / `partial`
     const int q = warp & 3;
     constexpr int kPerLane = MT / 32 > 0 ? MT / 32 : 1;  // tokens whose activation scale this lane fetches
     uint32_t acc_stage = 0, acc_phase = 0;
     float acc[MT];
     for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
-      const int32_t split = t / p.n_tiles, nt = t - split * p.n_tiles;
-      const int32_t kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.k_tiles);
+      const Item it = get_item<MT, GROUPED>(p, item_start, t);
+      const int32_t split = it.split, nt = it.nt, kb0 = it.kb0, kb1 = it.kb1;
       const int32_t n = nt * BN + q * 32 + lane;
       const float* sb_blk = p.sb + (int64_t)nt * p.sb_stride_n;
+      const float* sa_base = p.sa + (int64_t)it.row0 * p.sa_stride_m;
+      if constexpr (GROUPED) {
+        sb_blk += (int64_t)it.e * p.sb_stride_e;
+        if (p.rows_per_expert > 0)
+          sa_base = p.sa + (int64_t)it.e * p.sa_stride_e + (int64_t)(it.row0 - it.e * p.rows_per_expert) * p.sa_stride_m;
+      }
 #pragma unroll
       for (int j = 0; j < MT; ++j) acc[j] = 0.f;
       // lane l holds the scale of token l (and l + 32); tokens past M get 0 (their products are 0 anyway)
@@ -266,8 +381,8 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
 #pragma unroll
       for (int h = 0; h < kPerLane; ++h) {
         const int32_t tok = lane + 32 * h;
-        tok_ok[h] = tok < p.M && tok < MT;
-        sa_tok[h] = p.sa + (int64_t)(tok_ok[h] ? tok : 0) * p.sa_stride_m;
+        tok_ok[h] = tok < it.rows && tok < MT;
+        sa_tok[h] = sa_base + (int64_t)(tok_ok[h] ? tok : 0) * p.sa_stride_m;
       }
       float sa_ring[kScaleAhead][kPerLane], sb_ring[kScaleAhead];
 #pragma unroll
@@ -326,17 +441,17 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
           float* dst = p.partial + (int64_t)split * p.M * p.N + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            if (j < p.M) dst[(int64_t)j * p.N] = acc[j];
+            if (j < it.rows) dst[(int64_t)j * p.N] = acc[j];
         } else if (p.out_dtype == SGLB200_BF16) {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + n;
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (int64_t)it.row0 * p.ldc + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            if (j < p.M) dst[(int64_t)j * p.ldc] = __float2bfloat16_rn(acc[j]);
+            if (j < it.rows) dst[(int64_t)j * p.ldc] = __float2bfloat16_rn(acc[j]);
         } else {
-          __half* dst = static_cast<__half*>(p.out) + n;
+          __half* dst = static_cast<__half*>(p.out) + (int64_t)it.row0 * p.ldc + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            if (j < p.M) dst[(int64_t)j * p.ldc] = __float2half_rn(acc[j]);
+            if (j < it.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(acc[j]);
         }
       }
     }
@@ -350,20 +465,21 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
   }
 }
 
-template <int MT, bool UE>
-int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams& p, int sm_count, cudaStream_t st) {
+template <int MT, bool UE, bool GROUPED>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams& p, int sm_count, cudaStream_t st,
+           int64_t max_items) {
+  constexpr size_t smem = GROUPED ? Cfg<MT>::kSmemGrouped : Cfg<MT>::kSmem;
   static bool done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT, UE>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<MT>::kSmem);
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT, UE, GROUPED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     done[dev] = true;
   }
-  const int total = p.n_tiles * p.k_splits;
-  const int grid = total < sm_count ? total : sm_count;
-  const cudaError_t le = launch_pdl(fp8_block_gemm_smallm_kernel<MT, UE>, dim3(grid), dim3(kThreads), Cfg<MT>::kSmem, st,
+  const int grid = (int)(max_items < sm_count ? max_items : sm_count);
+  const cudaError_t le = launch_pdl(fp8_block_gemm_smallm_kernel<MT, UE, GROUPED>, dim3(grid), dim3(kThreads), smem, st,
                                     map_w, map_a, p);
   if (le != cudaSuccess) {
     cudaGetLastError();
@@ -409,9 +525,9 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
   const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   alignas(64) CUtensorMap map_w, map_a;
   {
-    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)N};
-    const uint64_t str[1] = {(uint64_t)ldb};
-    if (int rc = make_map_sw128(&map_w, b, 2, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, 1};
+    const uint64_t str[2] = {(uint64_t)ldb, (uint64_t)ldb * (uint64_t)N};
+    if (int rc = make_map_sw128(&map_w, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
   }
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
@@ -436,6 +552,13 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
   p.partial = nullptr;
   p.k_splits = 1;
   p.kb_per_split = p.k_tiles;
+  p.expert_offsets = nullptr;
+  p.problem_sizes = nullptr;
+  p.count_stride = 1;
+  p.rows_per_expert = 0;
+  p.num_experts = 1;
+  p.sa_stride_e = 0;
+  p.sb_stride_e = 0;
   const int splits = smallm_splits(N, K, sm_count);
   if (partial != nullptr && splits > 1 && (int64_t)splits * M * N <= partial_floats) {
     p.partial = partial;
@@ -446,17 +569,81 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
   }
   *splits_used = p.k_splits;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t items = (int64_t)p.n_tiles * p.k_splits;
   if (ue8m0) {
     switch (MT) {
-      case 16: return launch<16, true>(map_w, map_a, p, sm_count, st);
-      case 32: return launch<32, true>(map_w, map_a, p, sm_count, st);
-      default: return launch<64, true>(map_w, map_a, p, sm_count, st);
+      case 16: return launch<16, true, false>(map_w, map_a, p, sm_count, st, items);
+      case 32: return launch<32, true, false>(map_w, map_a, p, sm_count, st, items);
+      default: return launch<64, true, false>(map_w, map_a, p, sm_count, st, items);
     }
   }
   switch (MT) {
-    case 16: return launch<16, false>(map_w, map_a, p, sm_count, st);
-    case 32: return launch<32, false>(map_w, map_a, p, sm_count, st);
-    default: return launch<64, false>(map_w, map_a, p, sm_count, st);
+    case 16: return launch<16, false, false>(map_w, map_a, p, sm_count, st, items);
+    case 32: return launch<32, false, false>(map_w, map_a, p, sm_count, st, items);
+    default: return launch<64, false, false>(map_w, map_a, p, sm_count, st, items);
+  }
+}
+
+// Rows per chunk of the grouped few-rows kernel for `total_rows` rows spread over `num_experts` experts (or
+// rows_per_expert rows at most per expert in the masked layout); 0 = the 128 x 128 grouped kernel is the better choice.
+int smallm_grouped_chunk(int64_t total_rows, int64_t num_experts, int64_t rows_per_expert) {
+  const int64_t avg = rows_per_expert > 0 ? rows_per_expert : (total_rows + num_experts - 1) / num_experts;
+  if (avg > g_grouped_few_rows_max) return 0;
+  if (rows_per_expert > 0) return avg <= 16 ? 16 : (avg <= 32 ? 32 : 64);  // masked layout: the row bound is known
+  return avg <= 8 ? 16 : (avg <= 24 ? 32 : 64);
+}
+
+// Grouped few-rows GEMM (arguments already validated by the caller): chunk = smallm_grouped_chunk(...) != 0.
+int smallm_grouped_gemm(int chunk, const void* a, const void* b, const float* sa, const float* sb, void* out,
+                        const int32_t* expert_offsets, const int32_t* problem_sizes, int count_stride, int64_t total_rows,
+                        int64_t num_experts, int64_t rows_per_expert, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                        int64_t ldb_e, int64_t ldc, int64_t sa_stride_e, int64_t sa_stride_m, int64_t sa_stride_k,
+                        int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, int sm_count,
+                        void* stream) {
+  if (num_experts > kMaxExperts) return fail(SGLB200_ERR_SHAPE, "num_experts=%lld: at most %d", (long long)num_experts, kMaxExperts);
+  alignas(64) CUtensorMap map_w, map_a;
+  {
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)num_experts};
+    const uint64_t str[2] = {(uint64_t)ldb, (uint64_t)ldb_e};
+    if (int rc = make_map_sw128(&map_w, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)total_rows};
+    const uint64_t str[1] = {(uint64_t)lda};
+    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, (uint32_t)chunk, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+  }
+  SmallParams p;
+  p.sa = sa;
+  p.sb = sb;
+  p.out = out;
+  p.partial = nullptr;
+  p.M = (int32_t)total_rows;
+  p.N = (int32_t)N;
+  p.K = (int32_t)K;
+  p.n_tiles = (int32_t)((N + BN - 1) / BN);
+  p.k_tiles = (int32_t)((K + BK - 1) / BK);
+  p.k_splits = 1;
+  p.kb_per_split = p.k_tiles;
+  p.ldc = ldc;
+  p.sa_stride_m = sa_stride_m;
+  p.sa_stride_k = sa_stride_k;
+  p.sb_stride_n = sb_stride_n;
+  p.sb_stride_k = sb_stride_k;
+  p.out_dtype = out_dtype;
+  p.expert_offsets = expert_offsets;
+  p.problem_sizes = problem_sizes;
+  p.count_stride = count_stride;
+  p.rows_per_expert = (int32_t)rows_per_expert;
+  p.num_experts = (int32_t)num_experts;
+  p.sa_stride_e = sa_stride_e;
+  p.sb_stride_e = sb_stride_e;
+  // an upper bound on the work items without reading the device: every expert can add one ragged chunk
+  const int64_t items = ((total_rows + chunk - 1) / chunk + num_experts) * p.n_tiles;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (chunk) {
+    case 16: return launch<16, false, true>(map_w, map_a, p, sm_count, st, items);
+    case 32: return launch<32, false, true>(map_w, map_a, p, sm_count, st, items);
+    default: return launch<64, false, true>(map_w, map_a, p, sm_count, st, items);
   }
 }
 

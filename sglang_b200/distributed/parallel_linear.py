@@ -118,20 +118,23 @@ class RowParallelBlockFp8Linear(_ParallelBase):
     its receive slot, the GEMM pushes its tiles into every rank's memory and the sum is taken there: no NCCL call
     (the reference switches to its custom all-reduce below a size threshold the same way,
     ``custom_all_reduce.py: should_custom_ar``); from four ranks up, outputs too large for that take the two-shot form
-    (tile t reduced on rank t % world, results sent round).  Larger outputs still take the NCCL all-reduce.
+    (tile t reduced on rank t % world, results sent round).  Larger outputs take the multicast all-reduce of a
+    ``symm_mem`` communicator (:class:`~sglang_b200.distributed.symm_mem.SymmMemCommunicator`; the GEMM writes into its
+    symmetric buffer and the returned tensor is a view of it) when one is given and enabled, else the NCCL all-reduce.
     On that path the sum is taken by every rank for itself, so every rank keeps the whole bias and adds it once after
     the sum (decided here, where all ranks see the same arguments, not per rank in ``forward``)."""
 
     def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
                  input_is_parallel: bool = True, reduce_results: bool = True,
-                 apply_fn: Optional[Callable] = None, group=None, peer_exchange=None):
+                 apply_fn: Optional[Callable] = None, group=None, peer_exchange=None, symm_mem=None):
         w, s = shard_block_fp8_weight(weight, scale, rank, world, 1)
         super().__init__(w, s, bias if rank == 0 else None, apply_fn, group)
         self.rank, self.world = rank, world
         self.input_is_parallel, self.reduce_results = input_is_parallel, reduce_results
         self.peer_exchange = peer_exchange
+        self.symm_mem = symm_mem
         self.bias_after_sum = None
-        if peer_exchange is not None and bias is not None:
+        if (peer_exchange is not None or symm_mem is not None) and bias is not None:
             self.bias_after_sum = torch.nn.Parameter(bias, requires_grad=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -144,6 +147,12 @@ class RowParallelBlockFp8Linear(_ParallelBase):
                      or ex.fits_two_shot(x.numel() // x.shape[-1], self.weight.shape[0]))):
             from .peer_allreduce import fused_row_parallel_linear
             return fused_row_parallel_linear(ex, x, self.weight, self.weight_scale_inv, self.bias_after_sum)
+        sm = self.symm_mem
+        if (sm is not None and not sm.disabled and self.reduce_results and self.world > 1 and x.is_cuda
+                and x.dtype in (torch.bfloat16, torch.float16)
+                and (x.numel() // x.shape[-1]) * self.weight.shape[0] * 2 <= sm.max_size):
+            from .symm_mem import row_parallel_linear_symm_mem
+            return row_parallel_linear_symm_mem(sm, x, self.weight, self.weight_scale_inv, self.bias_after_sum)
         y = self._apply(self, x, self.bias)
         if self.reduce_results:
             y = tensor_model_parallel_all_reduce(y, self.group)

@@ -1,0 +1,148 @@
+"""All-reduce through NVSwitch multicast memory ("NVLS") for outputs too large for the push epilogues.
+
+Mirrors ``SymmMemCommunicator`` (``python/sglang/srt/distributed/device_communicators/symm_mem.py:34-200``): one
+symmetric buffer per rank allocated and exchanged by torch's symmetric-memory allocator (plumbing: ``cuMemCreate`` /
+multicast binding / handle exchange), ``disabled`` when the node has no multicast support, ``should_symm_mem_allreduce``
+and ``all_reduce(inp, out=None)`` with the reference's meaning.  The reduction itself is this library's kernel
+(``sglb200_nvls_all_reduce``: ``multimem.ld_reduce`` / ``multimem.st`` on the multicast address, bounded barriers), not
+``torch.ops.symm_mem.multimem_all_reduce_``.
+
+What the reference's wrapper cannot do and this one adds: the producer writes INTO the symmetric buffer
+(:meth:`view` gives the GEMM its ``out=`` tensor), so the two staging copies of ``all_reduce`` (in and out of the
+buffer, ``symm_mem.py:191-199``) disappear; :func:`row_parallel_linear_symm_mem` is the row-parallel linear built that
+way.  The returned tensor is a view of the buffer: it is valid until the next call that writes the same buffer.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Union
+
+import torch
+import torch.distributed as dist
+
+from .._lib import check, dtype_code, lib
+
+BLOCK = 128
+
+
+class SymmMemCommunicator:
+    """Sum over the ranks of one node through a multicast mapping.  Every rank of ``group`` must construct it, call
+    it and close it in step (the kernels of all ranks pair up)."""
+
+    def __init__(self, group, device: Union[int, str, torch.device], max_size: int = 256 << 20):
+        self.disabled = True
+        self.buffer = None
+        try:
+            import torch.distributed._symmetric_memory as tsm
+        except ImportError:
+            return
+        if isinstance(device, int):
+            device = torch.device(f"cuda:{device}")
+        elif isinstance(device, str):
+            device = torch.device(device)
+        self.device, self.group = device, group
+        self.dtype = torch.bfloat16
+        self.max_size = int(max_size)
+        if device.type != "cuda" or not torch.cuda.is_available():
+            return
+        self.world_size = dist.get_world_size(group)
+        if self.world_size < 2 or self.world_size > 8 or torch.cuda.get_device_capability(device)[0] != 10:
+            return
+        torch.cuda.set_device(device)
+        name = group.group_name if group is not None else dist.group.WORLD.group_name
+        self.buffer = tsm.empty(self.max_size // 2, device=device, dtype=self.dtype)
+        handle = tsm.rendezvous(self.buffer, name)
+        if handle.multicast_ptr == 0:  # no NVSwitch multicast on this node (symm_mem.py:103-110)
+            self.buffer = None
+            return
+        flag_words = lib().sglb200_nvls_flag_bytes() // 4
+        self._flags = tsm.empty(flag_words, device=device, dtype=torch.int32)
+        self._flags.zero_()
+        fhandle = tsm.rendezvous(self._flags, name)
+        self._handle, self._fhandle = handle, fhandle
+        self.rank = handle.rank
+        self._flag_blocks = (ctypes.c_uint64 * self.world_size)(*[int(p) for p in fhandle.buffer_ptrs])
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # every rank's flag block is zero before any kernel signals
+        self.disabled = False
+
+    # ------------------------------------------------------------------ the reference's interface
+    def should_symm_mem_allreduce(self, inp: torch.Tensor) -> bool:
+        """``symm_mem.py:113-135``: enabled, a 16-bit dtype this kernel adds, whole 16-byte vectors, fits the buffer."""
+        if self.disabled or inp.dtype not in (torch.bfloat16, torch.float16):
+            return False
+        nbytes = inp.numel() * inp.element_size()
+        return nbytes % 16 == 0 and nbytes <= self.max_size
+
+    def all_reduce(self, inp: torch.Tensor, *, out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Sum of ``inp`` over the ranks into ``out`` (a new tensor if omitted); ``None`` when disabled
+        (``symm_mem.py:137-200``).  Stages through the symmetric buffer; producers that can write into the buffer
+        use :meth:`view` and :meth:`all_reduce_` and skip both copies."""
+        if self.disabled:
+            return None
+        if out is None:
+            out = torch.empty_like(inp)
+        staged = self.view(inp.shape, inp.dtype)
+        staged.copy_(inp)
+        self.all_reduce_(staged)
+        out.copy_(staged)
+        return out
+
+    # ------------------------------------------------------------------ without staging
+    def view(self, shape, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+        """A contiguous tensor of ``shape`` at the start of the symmetric buffer (the ``out=`` of the producer)."""
+        if self.disabled:
+            raise RuntimeError("SymmMemCommunicator is disabled (no multicast support, or not a B200 node)")
+        n = 1
+        for d in shape:
+            n *= int(d)
+        if dtype not in (torch.bfloat16, torch.float16) or n * 2 > self.max_size:
+            raise ValueError(f"view of {tuple(shape)} {dtype}: 16-bit dtypes, at most {self.max_size} bytes")
+        return self.buffer[:n].view(dtype).view(*shape)
+
+    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
+        """In-place sum of a tensor that lives in the symmetric buffer (from :meth:`view`), on the current stream."""
+        if self.disabled:
+            raise RuntimeError("SymmMemCommunicator is disabled")
+        off = t.data_ptr() - self.buffer.data_ptr()
+        nbytes = t.numel() * t.element_size()
+        if not t.is_contiguous() or off < 0 or off + nbytes > self.max_size or off % 16 or nbytes % 16:
+            raise ValueError("all_reduce_ needs a contiguous 16-byte-aligned tensor inside the symmetric buffer")
+        with torch.cuda.device(self.device):
+            check(lib().sglb200_nvls_all_reduce(int(self._handle.multicast_ptr) + off, self._flag_blocks, self.rank,
+                                                self.world_size, t.numel(), dtype_code(t.dtype),
+                                                torch.cuda.current_stream(self.device).cuda_stream),
+                  "nvls_all_reduce")
+        return t
+
+    def close(self) -> None:
+        """Ranks leave together, with no kernel in flight, before the mappings go away."""
+        if self.buffer is not None and not self.disabled:
+            torch.cuda.synchronize(self.device)
+            dist.barrier(self.group)
+        self.disabled = True
+        self._handle = self._fhandle = None
+        self._flags = None
+        self.buffer = None
+
+
+def row_parallel_linear_symm_mem(comm: SymmMemCommunicator, x: torch.Tensor, weight: torch.Tensor,
+                                 weight_scale: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``sum_r x_r @ W_r^T`` (+ bias): quantise, GEMM straight into the symmetric buffer, multicast all-reduce.
+    The counterpart of ``RowParallelLinear.forward`` + ``tensor_model_parallel_all_reduce``
+    (``python/sglang/srt/layers/linear.py:1361-1386``).  The result is a view of ``comm``'s buffer; ``bias`` is the
+    WHOLE bias on every rank and is added once, after the sum (every rank holds the same sum)."""
+    from ..layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M, N = x2.shape[0], weight.shape[0]
+    y = comm.view((M, N), x.dtype)
+    if M:
+        q, s = sglang_per_token_group_quant_fp8(x2, BLOCK, column_major_scales=True, scale_tma_aligned=True)
+        w8a8_block_fp8_matmul(q, weight, s, weight_scale, [BLOCK, BLOCK], x.dtype, out=y)
+        comm.all_reduce_(y)
+        if bias is not None:
+            y += bias
+    return y.reshape(*x.shape[:-1], N)

@@ -186,3 +186,17 @@ def test_num_sms_limit_round_trip(built_lib):
     assert L.sglb200_get_num_sms() == 132
     assert L.sglb200_set_num_sms(0) == 0
     assert L.sglb200_get_num_sms() != 132
+
+
+def test_symm_mem_communicator_is_disabled_without_a_gpu():
+    """The reference's wrapper stays disabled and declines when a prerequisite is missing
+    (``device_communicators/symm_mem.py:46-47,113-123``); so does this one, and the row-parallel layer then takes the
+    collective library's all-reduce."""
+    import torch
+    from sglang_b200.distributed import SymmMemCommunicator
+    comm = SymmMemCommunicator(None, "cpu")
+    assert comm.disabled and comm.all_reduce(torch.zeros(8, dtype=torch.bfloat16)) is None
+    assert not comm.should_symm_mem_allreduce(torch.zeros(8, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        comm.view((8,))
+    comm.close()
