@@ -513,12 +513,12 @@ def parity_section(torch, dist, dev, world, rank):
     return res if rank == 0 else None
 
 
-def decode_section(torch, dev, peaks, shapes=None, ms=(1, 16, 64)):
-    """The five layers at decode batch sizes (M = 1, 16, 64): weight streaming, HBM-bound.  Each measurement is one
+def decode_section(torch, dev, peaks, shapes=None, ms=(1, 16, 64, 128)):
+    """The five layers at decode batch sizes (M = 1, 16, 64, 128): weight streaming, HBM-bound.  Each measurement is one
     CUDA graph holding one GEMM call per weight copy (enough copies that the working set exceeds L2), replayed ten
     times back to back; reported per call."""
     from sglang_b200.layers.quantization import w8a8_block_fp8_matmul
-    out = {"workload": "block-FP8 linear at M = 1 / 16 / 64, per-call device time inside a replayed CUDA graph over "
+    out = {"workload": "block-FP8 linear at M = 1 / 16 / 64 / 128, per-call device time inside a replayed CUDA graph over "
                        "rotating weight copies (working set > L2)", "unit": "us", "peak_gbs": peaks["hbm_gbs"],
            "cases": []}
     for name, N, K, _ in (shapes or SHAPES):

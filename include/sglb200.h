@@ -149,6 +149,8 @@ int sglb200_group_quant_fp8_batched(const void* input, int in_dtype, void* out_q
  * K need not be a multiple of 128 (the tail block is zero-filled), but K % 16 == 0.
  * fp32 accumulation; each 128-deep partial product is scaled and added in registers.
  * Any M >= 0 is accepted with no padding copy (the reference pads M to a multiple of 4).
+ * Up to 128 rows the weight-streaming kernel with swapped operands runs (128 weight rows x 16 / 32 / 64 activation rows
+ * per MMA; from 65 rows two such sub-tiles per work item share every weight stage), above that the 128 x 128 kernel.
  */
 int sglb200_fp8_blockwise_scaled_mm(const void* a, const void* b, const float* sa, const float* sb, void* out,
                                     int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
@@ -421,7 +423,7 @@ int sglb200_moe_sum_reduce(const void* input, void* output, int64_t num_tokens, 
  * and replayed.  Rules: all ranks issue the same sequence of exchanges, each on ONE stream per rank (the two
  * alternating slot sets are safe exactly because a rank's exchange e + 1 is enqueued after its exchange e); at most
  * 1024 output tiles of 128 x 128; world <= 8.
- * workspace / workspace_bytes: scratch for M <= 64 (size from sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes; 0 for
+ * workspace / workspace_bytes: scratch for M <= 128 (size from sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes; 0 for
  * larger M).  With it the few-rows weight-streaming kernel computes fp32 sums (K split over the SMs where that pays) and
  * a second small kernel adds the splits, casts and does the pushing and flagging; without it (NULL) the 128-row kernel
  * with the push epilogue runs.  Both produce the bits of the corresponding plain entry point.

@@ -1,4 +1,4 @@
-// Block-scaled FP8 GEMM for few rows of activations (M <= 64: the decode case), weight-streaming bound.
+// Block-scaled FP8 GEMM for few rows of activations (M <= 128: the decode case), weight-streaming bound.
 //
 // The roles of the operands are swapped: the tensor core computes C^T = W * A^T, a tile being 128 WEIGHT rows (the MMA's
 // M) by MT token columns (the MMA's N, MT = 16 / 32 / 64).  An accumulator stage is then only MT TMEM columns wide, so 8 to
@@ -6,6 +6,9 @@
 // of weights plus MT x 128 bytes of activations, so 8 to 10 stages (128 to 160 KB of weights) are in flight per SM: the
 // kernel is bound by HBM, not by the accumulator hand-off of the 128 x 128 kernel.  K can be cut into ranges that run on
 // different SMs (fp32 partial sums, added by splitk_reduce_kernel) when N / 128 tiles alone cannot occupy the SMs.
+// From 65 to 128 rows the tile is 128 x 128 (4 accumulator stages, 7 shared-memory stages) and eight promotion warps
+// share every accumulator stage, four per 64 token columns: what is left of the advantage over the 128 x 128 kernel is
+// the deeper weight ring and the single role per warp (measured 7-15 % at 96-128 rows).
 //
 // GROUPED variant (one weight matrix per expert, few rows per expert: the decode case of a mixture-of-experts layer): a
 // work item is (expert, 128 weight rows, chunk of MT of the expert's rows).  The row ranges come from the same device
@@ -48,18 +51,22 @@ int smallm_take_device_status() {
 namespace {
 
 constexpr int BN = 128, BK = 128;  // weight rows per tile, K per block
-constexpr int kThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kWBytes = BN * BK;
 constexpr int kScaleAhead = 4;
 
 constexpr int kMaxExperts = 1024;
 
-template <int MT>
+// NSUB = 2 (dense, 64 < M <= 128): the MMA covers MT * NSUB = 128 activation rows (one instruction shape 128 x 128, so
+// the issuing thread's cost per k-block stays that of the narrow tiles) and a second set of four promotion warps takes
+// the second half of every accumulator stage's columns, so the registers per thread stay those of 64 rows.
+template <int MT, int NSUB = 1>
 struct Cfg {
-  static constexpr int kStages = MT == 64 ? 8 : 10;
-  static constexpr int kAcc = (512 / MT) < 16 ? (512 / MT) : 16;
-  static constexpr uint32_t kABytes = MT * BK;
+  static constexpr int kTile = MT * NSUB;  // activation rows per work item = the MMA's N = TMEM columns per stage
+  static constexpr int kStages = kTile == 128 ? 7 : (kTile == 64 ? 8 : 10);
+  static constexpr int kAcc = (512 / kTile) < 16 ? (512 / kTile) : 16;
+  static constexpr int kThreads = 64 + 128 * NSUB;
+  static constexpr uint32_t kABytes = kTile * BK;
   static constexpr uint32_t kStageBytes = kWBytes + kABytes;
   static constexpr size_t kSmem = 1024 + (size_t)kStages * kStageBytes + 512;
   // grouped: the table of first work items per expert follows the control block
@@ -194,11 +201,12 @@ __device__ __forceinline__ float load_scale(const float* base, int32_t kc, int64
   }
 }
 
-template <int MT, bool UE, bool GROUPED>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int MT, bool UE, bool GROUPED, int NSUB>
+__global__ void __launch_bounds__(64 + 128 * NSUB, 1)
 fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                              const SmallParams p) {
-  using C = Cfg<MT>;
+  using C = Cfg<MT, NSUB>;
+  static_assert(!GROUPED || NSUB == 1, "the grouped form has one sub-tile");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   Ctl* ctl = reinterpret_cast<Ctl*>(smem + (size_t)C::kStages * C::kStageBytes);
@@ -212,7 +220,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     }
     for (int i = 0; i < C::kAcc; ++i) {
       ptx::mbar_init(&ctl->acc_full[i], 1);
-      ptx::mbar_init(&ctl->acc_empty[i], 4);  // one arrival per promotion warp
+      ptx::mbar_init(&ctl->acc_empty[i], 4 * NSUB);  // one arrival per promotion warp
     }
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -324,7 +332,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     }
   } else if (warp == 1) {
     // ===== MMA issuer: D[128 weight rows][MT tokens] (+)= W_tile * A_tile^T, one TMEM stage per k-block
-    constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BN, MT);
+    constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BN, C::kTile);
     const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
     for (int32_t t = blockIdx.x; t < total; t += gridDim.x) {
@@ -342,7 +350,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
         if (lane == 0) {
           const uint64_t w_desc = desc0 + (uint64_t)(stage * (C::kStageBytes >> 4));
           const uint64_t a_desc = w_desc + (kWBytes >> 4);
-          const uint32_t d_tmem = tmem_base + acc * MT;
+          const uint32_t d_tmem = tmem_base + acc * C::kTile;
           ptx::mma_f8f6f4(d_tmem, w_desc, a_desc, idesc, 0);
 #pragma unroll
           for (uint32_t k = 1; k < BK / 32; ++k) ptx::mma_f8f6f4(d_tmem, w_desc + 2 * k, a_desc + 2 * k, idesc, 1);
@@ -359,6 +367,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
     if constexpr (!GROUPED)
       ptx::grid_dep_wait();  // the activation scales come from the kernel before this one, and it may still read `out` / `partial`
     const int q = warp & 3;
+    const int sub = NSUB == 1 ? 0 : (warp - 2) >> 2;  // which sub-tile of the item this warp promotes
     constexpr int kPerLane = MT / 32 > 0 ? MT / 32 : 1;  // tokens whose activation scale this lane fetches
     uint32_t acc_stage = 0, acc_phase = 0;
     float acc[MT];
@@ -367,11 +376,12 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
       const int32_t split = it.split, nt = it.nt, kb0 = it.kb0, kb1 = it.kb1;
       const int32_t n = nt * BN + q * 32 + lane;
       const float* sb_blk = p.sb + (int64_t)nt * p.sb_stride_n;
-      const float* sa_base = p.sa + (int64_t)it.row0 * p.sa_stride_m;
+      const int32_t row0 = it.row0 + sub * MT, rows = max(0, min(MT, it.rows - sub * MT));
+      const float* sa_base = p.sa + (int64_t)row0 * p.sa_stride_m;
       if constexpr (GROUPED) {
         sb_blk += (int64_t)it.e * p.sb_stride_e;
         if (p.rows_per_expert > 0)
-          sa_base = p.sa + (int64_t)it.e * p.sa_stride_e + (int64_t)(it.row0 - it.e * p.rows_per_expert) * p.sa_stride_m;
+          sa_base = p.sa + (int64_t)it.e * p.sa_stride_e + (int64_t)(row0 - it.e * p.rows_per_expert) * p.sa_stride_m;
       }
 #pragma unroll
       for (int j = 0; j < MT; ++j) acc[j] = 0.f;
@@ -381,7 +391,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
 #pragma unroll
       for (int h = 0; h < kPerLane; ++h) {
         const int32_t tok = lane + 32 * h;
-        tok_ok[h] = tok < it.rows && tok < MT;
+        tok_ok[h] = tok < rows && tok < MT;
         sa_tok[h] = sa_base + (int64_t)(tok_ok[h] ? tok : 0) * p.sa_stride_m;
       }
       float sa_ring[kScaleAhead][kPerLane], sb_ring[kScaleAhead];
@@ -414,7 +424,7 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
             break;
           }
           ptx::tc_fence_after();
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * MT;
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc_stage * C::kTile + sub * MT;
           uint32_t v[MT];
           if constexpr (MT == 64) {
             tmem_ld_cols<32>(taddr, v);
@@ -438,20 +448,20 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
       // transposed store: for every token the warp writes 32 consecutive outputs
       if (n < p.N) {
         if (p.partial != nullptr) {
-          float* dst = p.partial + (int64_t)split * p.M * p.N + n;
+          float* dst = p.partial + ((int64_t)split * p.M + row0) * p.N + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            if (j < it.rows) dst[(int64_t)j * p.N] = acc[j];
+            if (j < rows) dst[(int64_t)j * p.N] = acc[j];
         } else if (p.out_dtype == SGLB200_BF16) {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (int64_t)it.row0 * p.ldc + n;
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + (int64_t)row0 * p.ldc + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            if (j < it.rows) dst[(int64_t)j * p.ldc] = __float2bfloat16_rn(acc[j]);
+            if (j < rows) dst[(int64_t)j * p.ldc] = __float2bfloat16_rn(acc[j]);
         } else {
-          __half* dst = static_cast<__half*>(p.out) + (int64_t)it.row0 * p.ldc + n;
+          __half* dst = static_cast<__half*>(p.out) + (int64_t)row0 * p.ldc + n;
 #pragma unroll
           for (int j = 0; j < MT; ++j)
-            if (j < it.rows) dst[(int64_t)j * p.ldc] = __float2half_rn(acc[j]);
+            if (j < rows) dst[(int64_t)j * p.ldc] = __float2half_rn(acc[j]);
         }
       }
     }
@@ -465,21 +475,22 @@ fp8_block_gemm_smallm_kernel(const __grid_constant__ CUtensorMap map_w, const __
   }
 }
 
-template <int MT, bool UE, bool GROUPED>
+template <int MT, bool UE, bool GROUPED, int NSUB = 1>
 int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams& p, int sm_count, cudaStream_t st,
            int64_t max_items) {
-  constexpr size_t smem = GROUPED ? Cfg<MT>::kSmemGrouped : Cfg<MT>::kSmem;
+  constexpr size_t smem = GROUPED ? Cfg<MT, NSUB>::kSmemGrouped : Cfg<MT, NSUB>::kSmem;
+  constexpr int kThreads = Cfg<MT, NSUB>::kThreads;
   static bool done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT, UE, GROUPED>,
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_smallm_kernel<MT, UE, GROUPED, NSUB>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     done[dev] = true;
   }
   const int grid = (int)(max_items < sm_count ? max_items : sm_count);
-  const cudaError_t le = launch_pdl(fp8_block_gemm_smallm_kernel<MT, UE, GROUPED>, dim3(grid), dim3(kThreads), smem, st,
+  const cudaError_t le = launch_pdl(fp8_block_gemm_smallm_kernel<MT, UE, GROUPED, NSUB>, dim3(grid), dim3(kThreads), smem, st,
                                     map_w, map_a, p);
   if (le != cudaSuccess) {
     cudaGetLastError();
@@ -490,7 +501,7 @@ int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const SmallParams
 
 }  // namespace
 
-int smallm_max_rows() { return 64; }
+int smallm_max_rows() { return 128; }
 
 // K-splits for a small-M problem.  Cost model in units of one k-block of one work item: a split count s gives
 // ceil(n_tiles * s / SMs) waves of work items, each ceil(k_tiles / s) k-blocks deep plus a fixed cost per item (pipeline
@@ -523,6 +534,7 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
                 int64_t sb_stride_k, int out_dtype, float* partial, int64_t partial_floats, int sm_count, void* stream,
                 int* splits_used, bool always_partial, bool ue8m0) {
   const int MT = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const bool two = M > 64;  // 128 activation rows per work item, two sets of promotion warps
   alignas(64) CUtensorMap map_w, map_a;
   {
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, 1};
@@ -532,7 +544,8 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
     const uint64_t str[1] = {(uint64_t)lda};
-    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, (uint32_t)MT, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, (uint32_t)(M > 64 ? 128 : MT), CU_TENSOR_MAP_L2_PROMOTION_L2_128B))
+      return rc;
   }
   SmallParams p;
   p.sa = sa;
@@ -570,6 +583,10 @@ int smallm_gemm(const void* a, const void* b, const float* sa, const float* sb, 
   *splits_used = p.k_splits;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t items = (int64_t)p.n_tiles * p.k_splits;
+  if (two) {
+    return ue8m0 ? launch<64, true, false, 2>(map_w, map_a, p, sm_count, st, items)
+                 : launch<64, false, false, 2>(map_w, map_a, p, sm_count, st, items);
+  }
   if (ue8m0) {
     switch (MT) {
       case 16: return launch<16, true, false>(map_w, map_a, p, sm_count, st, items);

@@ -475,8 +475,9 @@ int ue8m0_common(const void* a, const void* b, const int32_t* sfa, const int32_t
   SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
                di.cc_major, di.cc_minor);
 
-  if (!grouped && M <= smallm_max_rows()) {
-    // few rows: the weight-streaming kernel with swapped operands decodes the exponent bytes itself (gemm_smallm.cu)
+  if (!grouped && M <= 64) {
+    // few rows: the weight-streaming kernel with swapped operands decodes the exponent bytes itself (gemm_smallm.cu);
+    // from 65 rows up the block-scaled tile kernel below, which has no promotion, is the faster one
     int splits = 1;
     if (int rc = smallm_gemm(a, b, reinterpret_cast<const float*>(sfa), reinterpret_cast<const float*>(sfb), out, M, N, K,
                              lda, ldb, ldc, sfa_stride_m, sfa_ld, sfb_stride_n, sfb_stride_k, out_dtype, workspace,

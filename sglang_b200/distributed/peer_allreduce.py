@@ -121,7 +121,7 @@ def push_mm(ex_recv_arr, ex_flag_arr, rank: int, world: int, slot_elems: int, a_
             a_s: torch.Tensor, weight: torch.Tensor, weight_scale: torch.Tensor, out_dtype: torch.dtype,
             use_workspace: bool = True) -> None:
     """One rank's half of the exchange: ``a_q [M, K_r]`` e4m3 with scales ``a_s [M, K_r/128]`` times the rank's weight
-    slice ``[N, K_r]``, every output tile stored into all ranks' receive buffers.  For ``M <= 64`` a scratch buffer
+    slice ``[N, K_r]``, every output tile stored into all ranks' receive buffers.  For ``M <= 128`` a scratch buffer
     lets the library take the few-rows kernel (``use_workspace=False`` forces the 128-row kernel's push epilogue)."""
     M, K = a_q.shape
     N = weight.shape[0]

@@ -164,7 +164,7 @@ def test_host_validation_of_routing_and_exchange_entries(built_lib):
     assert L.sglb200_ep_combine_reduce(ptrs, 0, 9, None, None, 0, 4, 256, 2, 4, 16, 16, 0, None) == -1
     assert L.sglb200_ep_buffer_bytes(16, 256, 2, 2, 16) > 16 * 256 and L.sglb200_ep_buffer_bytes(0, 256, 2, 2, 16) == 0
     assert L.sglb200_peer_flag_bytes() > 0 and L.sglb200_peer_recv_bytes(1024) == 2 * 8 * 1024 * 2
-    assert L.sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(128, 7168, 8192) == 0
+    assert L.sglb200_fp8_blockwise_scaled_mm_push_workspace_bytes(129, 7168, 8192) == 0
     h = (ctypes.c_ubyte * 64)()
     assert L.sglb200_peer_alloc(0, None, h) == -6 and L.sglb200_peer_open(None, None) == -6
     assert L.sglb200_peer_close(None) == 0 and L.sglb200_peer_free(None) == 0

@@ -141,7 +141,7 @@ def test_small_m_split_k(M, N, K):
     assert lib().sglb200_fp8_blockwise_scaled_mm_workspace_bytes(4096, N, K) == 0
 
 
-@pytest.mark.parametrize("M", [2, 16, 17, 32, 33, 48, 64, 65])
+@pytest.mark.parametrize("M", [2, 16, 17, 32, 33, 48, 64, 65, 96, 127, 128, 129])
 @pytest.mark.parametrize("N,K", [(128, 128), (576, 1024), (1536, 384), (4096, 4096), (7168, 2048)])
 def test_few_rows_kernel_boundaries(M, N, K):
     """The weight-streaming kernel (M <= 64, token columns padded to 16 / 32 / 64) on both sides of every padding
@@ -165,8 +165,9 @@ def test_few_rows_kernel_boundaries(M, N, K):
     assert_gemm_close(out2, ref, f"few rows, plain entry M={M} N={N} K={K}")
 
 
-def test_few_rows_f16_ragged_k_and_strided_output():
-    M, N, K = 24, 384, 320  # K = 2.5 blocks
+@pytest.mark.parametrize("M", [24, 100])  # one sub-tile of 32 rows; two sub-tiles of 64 rows
+def test_few_rows_f16_ragged_k_and_strided_output(M):
+    N, K = 384, 320  # K = 2.5 blocks
     a = make_activations(M, 384, seed=5)[:, :K].contiguous()
     aq, a_s = oracle.per_token_group_quant_fp8(torch.nn.functional.pad(a, (0, 64)), 128)
     aq = aq[:, :K].contiguous()

@@ -24,7 +24,7 @@ def _buffers(world, slot_elems):
 
 
 def _plain_partial(a_q, a_s, w, ws):
-    """The rank's partial product as the plain entry points compute it: for M <= 64 the few-rows kernel with the
+    """The rank's partial product as the plain entry points compute it: for M <= 128 the few-rows kernel with the
     library's own K-split (scratch + reduce kernel), above that the 128-row kernel without a split - in both cases the
     kernel and the order of additions the push variant uses, stored instead of pushed."""
     from sglang_b200._lib import blockwise_mm, check, lib
@@ -33,7 +33,7 @@ def _plain_partial(a_q, a_s, w, ws):
     out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
     args = (a_q.data_ptr(), w.data_ptr(), a_s.data_ptr(), ws.data_ptr(), out.data_ptr(), M, N, K, a_q.stride(0), w.stride(0),
             out.stride(0), a_s.stride(0), a_s.stride(1), ws.stride(0), ws.stride(1), 0)
-    if M <= 64:
+    if M <= 128:
         blockwise_mm(*args, a_q.device, torch.cuda.current_stream().cuda_stream)
     else:
         check(lib().sglb200_fp8_blockwise_scaled_mm(*args, torch.cuda.current_stream().cuda_stream), "mm")
@@ -76,7 +76,7 @@ def test_push_and_reduce_emulated_ranks(world, M, N, K):
         # the tensor-parallel semantic: every rank rounds its partial sum to bf16, then the partial sums are added
         # (python/sglang/srt/layers/linear.py:1361-1386); the oracle does the same on the K-slices
         assert_gemm_close(outs[0], row_parallel_reference(x, wq, ws, world), f"epoch {epoch}")
-    if M <= 64:  # the other route for few rows: the 128-row kernel's push epilogue (no scratch buffer)
+    if M <= 128:  # the other route for few rows: the 128-row kernel's push epilogue (no scratch buffer)
         for r in range(world):
             a_q, a_s = sglang_per_token_group_quant_fp8(x[:, r * kr:(r + 1) * kr].contiguous().cuda(), 128)
             push_mm(recv_arr, flag_arr, r, world, slot, a_q, a_s, shards[r][0], shards[r][1], torch.bfloat16,
