@@ -197,7 +197,7 @@ def cpu_arm(steps: int, warmup: int, m_sample: int):
             "ms_per_pass": dt * 1e3}
 
 
-def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H=7168, I=2048):
+def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H=7168, I=2048, gpu_uuid=None):
     """Block-FP8 fused MoE, DeepSeek-V3 layer shape: 256 experts, top-8 of softmax(random logits), hidden 7168,
     moe_intermediate 2048, M tokens; random e4m3 expert weights (11.3 GB).  Two checkpoints: fp32 block scales
     (software promotion) and power-of-two (UE8M0) scales (grouped GEMMs on the hardware block-scaling path)."""
@@ -224,6 +224,19 @@ def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H
     out = {"workload": f"fused_experts block-FP8 E={E} top{topk} H={H} I={I}", "weight_bytes": w1.numel() + w2.numel(),
            "kernels_per_call": 9, "cases": []}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def board_state():
+        """SM clock and board power right after a timed loop (NVML, read-only)."""
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = (pynvml.nvmlDeviceGetHandleByUUID(gpu_uuid) if gpu_uuid
+                 else pynvml.nvmlDeviceGetHandleByIndex(dev.index or 0))
+            return {"sm_mhz_after": pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
+                    "watts_after": pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0}
+        except Exception:  # noqa: BLE001 - the clock note is optional
+            return {}
+
     for M in Ms:
         a = torch.randn(M, H, device=dev, generator=gen).bfloat16()
         tw, ti = torch.topk(torch.softmax(torch.randn(M, E, device=dev, generator=gen), -1), topk)
@@ -242,11 +255,22 @@ def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H
             before = lib().sglb200_get_grouped_few_rows()
             if limit is not None:
                 lib().sglb200_set_grouped_few_rows(limit)
+            # Sustained figures: a call is milliseconds long and the board needs about a second of load to settle under
+            # its power cap, so a handful of calls would read the clock the PREVIOUS variant left behind (the 128 x 128
+            # kernel on few rows per expert pulls the SM clock to ~1.1 GHz at 1000 W, the few-rows kernel stays at
+            # ~1.75 GHz).  About 0.3 s of untimed calls, then about 0.3 s timed.
             try:
                 for _ in range(3):
                     fn()
                 torch.cuda.synchronize()
-                n = 5
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize()
+                n = max(5, min(150, int(300.0 / max(e0.elapsed_time(e1), 0.05))))
+                for _ in range(n):
+                    fn()
+                torch.cuda.synchronize()
                 e0.record()
                 for _ in range(n):
                     fn()
@@ -256,7 +280,7 @@ def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H
                 lib().sglb200_set_grouped_few_rows(before)
             ms = e0.elapsed_time(e1) / n
             case[name] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
-                          "weight_tbs": w_bytes / (ms * 1e-3) / 1e12}
+                          "weight_tbs": w_bytes / (ms * 1e-3) / 1e12, "calls_timed": n, **board_state()}
         out["cases"].append(case)
     return out
 
@@ -719,7 +743,7 @@ def main():
     if args.only == "moe":
         gen_m = torch.Generator(device=dev).manual_seed(0)
         print(json.dumps({"metric": METRIC, "only": "moe",
-                          "moe": moe_section(torch, dev, gen_m, Ms=(args.m,), E=args.moe_experts)}))
+                          "moe": moe_section(torch, dev, gen_m, Ms=(args.m,), E=args.moe_experts, gpu_uuid=gpu_uuid)}))
         return
     if args.only == "decode":
         sel = [sh for sh in SHAPES if args.shape in (None, sh[0])]
@@ -1117,7 +1141,7 @@ def main():
     moe = None
     if rank == 0 and world == 1 and not args.no_moe:
         try:
-            moe = moe_section(torch, dev, gen)
+            moe = moe_section(torch, dev, gen, gpu_uuid=gpu_uuid)
         except Exception as e:  # noqa: BLE001 - the headline must not depend on this section
             moe = {"error": f"{type(e).__name__}: {e}"}
         torch.cuda.empty_cache()
