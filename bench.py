@@ -285,7 +285,7 @@ def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H
     return out
 
 
-def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=None):
+def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=None, mc_chunk=4096, mc_blocks=32):
     """Tensor-parallel decoder projections at the Llama-3-70B shape (hidden 8192, intermediate 28672, 64 q / 8 kv
     heads of 128): column-parallel QKV and gate_up, row-parallel o and down, each followed by an NCCL all-reduce of the
     [M, 8192] bf16 output (none at tp1).  One step = the four linears of a layer on M tokens; device time, max over
@@ -318,14 +318,14 @@ def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=Non
             elif row:
                 dist.all_reduce(y)
 
-    def timed(use_mc):
+    def timed(fn):
         for _ in range(3):
-            step(use_mc)
+            fn()
         sync()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(iters):
-            step(use_mc)
+            fn()
         e1.record()
         sync()
         ms = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
@@ -333,15 +333,30 @@ def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=Non
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms)
 
-    ms = timed(False)
+    ms = timed(lambda: step(False))
     out = {"workload": f"Llama-3-70B layer projections, M={M}, tp{world}: qkv/gate_up column-parallel, o/down "
                        "row-parallel + NCCL all-reduce", "ms_per_layer": ms, "tflops": flops / (ms * 1e-3) / 1e12,
            "allreduce_bytes_per_layer": 2 * M * 8192 * 2 if world > 1 else 0}
     if mc is not None and world > 1 and 2 * M * 8192 <= mc.max_size:
-        ms_mc = timed(True)
+        ms_mc = timed(lambda: step(True))
         out["multicast_allreduce"] = {"ms_per_layer": ms_mc, "tflops": flops / (ms_mc * 1e-3) / 1e12,
                                       "how": "row-parallel GEMMs write into NVSwitch multicast memory, one multimem "
                                              "kernel (ld_reduce + st) per all-reduce"}
+        from sglang_b200.distributed import row_parallel_linear_symm_mem_overlapped
+
+        def step_ovl():
+            for mode, w, ws, x in built:
+                if mode == "row":
+                    row_parallel_linear_symm_mem_overlapped(mc, x, w, ws, chunk_rows=mc_chunk, ar_blocks=mc_blocks)
+                else:
+                    q, sc = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
+                    w8a8_block_fp8_matmul(q, w, sc, ws, [128, 128], torch.bfloat16)
+
+        ms_ov = timed(step_ovl)
+        out["multicast_allreduce_overlapped"] = {
+            "ms_per_layer": ms_ov, "tflops": flops / (ms_ov * 1e-3) / 1e12,
+            "how": f"the same in chunks of {mc_chunk} rows: the all-reduce of a chunk ({mc_blocks} blocks, side stream) "
+                   "runs beside the next chunk's GEMM"}
     return out
 
 
@@ -674,6 +689,9 @@ def main():
     ap.add_argument("--multicast", type=int, default=-1,
                     help="N > 1: 1 = row-parallel GEMMs write into NVSwitch multicast memory and this library's "
                          "multimem kernel adds them; 0 = never; -1 = tried with the other orders, the fastest is kept")
+    ap.add_argument("--ar-blocks", type=int, default=0,
+                    help="thread blocks of the multicast all-reduce kernel when it overlaps the next row chunk's GEMM; "
+                         "0 = 16, 32 and 64 are tried")
     ap.add_argument("--chunk-rows", type=int, default=0,
                     help="rows per chunk of the overlapped row-parallel linear; 0 = M / 4 and M / 2 are both tried")
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL while overlapping")
@@ -845,7 +863,8 @@ def main():
     overlap = world > 1 and args.overlap == 1
     mc, multicast = None, False
     if world > 1:
-        from sglang_b200.distributed import SymmMemCommunicator, row_parallel_linear_overlapped
+        from sglang_b200.distributed import (SymmMemCommunicator, row_parallel_linear_overlapped,
+                                             row_parallel_linear_symm_mem_overlapped)
         from sglang_b200.layers.deep_gemm_wrapper import configure_deep_gemm_num_sms
         sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
         if args.multicast != 0:
@@ -859,8 +878,16 @@ def main():
     chunk_rows = [args.chunk_rows if args.chunk_rows > 0 else max(128, M // 4)]
     own_launches = [0]  # kernels of this library launched by step(): one quantiser + one GEMM per layer (per chunk)
 
+    mc_chunk = [0]  # > 0: the multicast all-reduce runs per chunk of this many rows beside the next chunk's GEMM
+    ar_blocks = [args.ar_blocks if args.ar_blocks > 0 else 32]
+
     def step(record=False):
         for L in layers:
+            if multicast and mc_chunk[0] > 0 and L["mode"] == "row":
+                own_launches[0] += 1 + 2 * -(-M // mc_chunk[0])
+                y = row_parallel_linear_symm_mem_overlapped(mc, L["x"], L["layer"].weight, L["layer"].weight_scale_inv,
+                                                            chunk_rows=mc_chunk[0], ar_blocks=ar_blocks[0])
+                continue
             if overlap and L["mode"] == "row":
                 own_launches[0] += 1 + -(-M // chunk_rows[0])
                 with configure_deep_gemm_num_sms(sm_total - args.comm_sms if args.comm_sms > 0 else None):
@@ -951,8 +978,14 @@ def main():
         # ranks) and keep the fastest for the warm-up and the timed region
         tried = {}
         chunk_choices = [args.chunk_rows] if args.chunk_rows > 0 else [max(128, M // 4), max(128, M // 2)]
-        for mode in (["plain"] + [f"overlapped_{c}" for c in chunk_choices] + (["multicast"] if mc is not None else [])):
-            overlap, multicast = mode.startswith("overlapped"), mode == "multicast"
+        blocks_choices = [args.ar_blocks] if args.ar_blocks > 0 else [16, 32, 64]
+        for mode in (["plain"] + [f"overlapped_{c}" for c in chunk_choices]
+                     + (["multicast"] + [f"multicast_overlapped_{c}_{b}" for c in chunk_choices for b in blocks_choices]
+                        if mc is not None else [])):
+            overlap, multicast = mode.startswith("overlapped"), mode.startswith("multicast")
+            mc_chunk[0] = int(mode.split("_")[2]) if mode.startswith("multicast_overlapped") else 0
+            if mc_chunk[0]:
+                ar_blocks[0] = int(mode.split("_")[3])
             if overlap:
                 chunk_rows[0] = int(mode.split("_")[1])
             step()
@@ -967,7 +1000,10 @@ def main():
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
             tried[mode] = float(tt)
         best = min(tried, key=tried.get)
-        overlap, multicast = best.startswith("overlapped"), best == "multicast"
+        overlap, multicast = best.startswith("overlapped"), best.startswith("multicast")
+        mc_chunk[0] = int(best.split("_")[2]) if best.startswith("multicast_overlapped") else 0
+        if mc_chunk[0]:
+            ar_blocks[0] = int(best.split("_")[3])
         if overlap:
             chunk_rows[0] = int(best.split("_")[1])
         config["step_tried_ms"] = tried
@@ -975,6 +1011,9 @@ def main():
         config["step"] = ((f"row-parallel layers in chunks of {chunk_rows[0]} rows, the NCCL all-reduce of a chunk overlaps "
                            f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"
                                                        if args.comm_sms > 0 else "")) if overlap
+                          else (f"row-parallel GEMMs in chunks of {mc_chunk[0]} rows on {sm_total - ar_blocks[0]} SMs write "
+                                f"into NVSwitch multicast memory; this library's multimem kernel ({ar_blocks[0]} blocks, side "
+                                "stream) adds a chunk in place while the next chunk's GEMM runs") if multicast and mc_chunk[0]
                           else ("row-parallel GEMMs write into NVSwitch multicast memory; this library's multimem kernel "
                                 "(ld_reduce + st, one launch) adds them in place, same stream") if multicast
                           else "NCCL all-reduce after each row-parallel GEMM, same stream")
@@ -1003,7 +1042,7 @@ def main():
     breakdown = None
     if args.only in ("all", "gemm"):
         breakdown = breakdown_pass()
-        if overlap:
+        if overlap or (multicast and mc_chunk[0] > 0):
             breakdown["overlap_saves_ms"] = breakdown["step_ms"] - ms_per_step
         if world == 1:
             # the same step as one replayed CUDA graph: what is left of the host gap when nothing is launched from Python
@@ -1057,8 +1096,9 @@ def main():
                 "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
                 "frac_of_nominal_fp8": achieved / 4500.0, "launches": sum(len(L["ev"]) for L in layers),
                 "avg_launch_ms": gemm_ms / max(1, sum(len(L["ev"]) for L in layers)), "others": []}
-    if overlap:
-        roofline["note"] = "column-parallel and replicated layers only: the row-parallel GEMMs run in chunks beside NCCL"
+    if overlap or (multicast and mc_chunk[0] > 0):
+        roofline["note"] = ("column-parallel and replicated layers only: the row-parallel GEMMs run in chunks beside "
+                            "the all-reduce")
 
     # ---- the same sweep on a UE8M0 checkpoint (power-of-two weight block scales, power-of-two activation group
     # scales): the tensor core applies the scales itself (tcgen05.mma kind::mxf8f6f4.block_scale)
@@ -1263,7 +1303,8 @@ def main():
         layers_n = len(layers)
         torch.cuda.empty_cache()
         try:
-            tp_llama = tp_llama_section(torch, dist, dev, gen, world, rank, mc=mc)
+            tp_llama = tp_llama_section(torch, dist, dev, gen, world, rank, mc=mc, mc_chunk=mc_chunk[0] or M // 2,
+                                        mc_blocks=ar_blocks[0])
         except Exception as e:  # noqa: BLE001
             tp_llama = {"error": f"{type(e).__name__}: {e}"}
         if mc is not None:

@@ -553,6 +553,8 @@ int sglb200_peer_free(void* dev_ptr);
  *   flag_blocks     HOST array of `world` device addresses: entry r = rank r's flag block (sglb200_nvls_flag_bytes()
  *                   bytes, zero before the first call) as mapped in this process.
  *   numel           elements, a multiple of 8.
+ *   blocks          thread blocks of the kernel, 1..128, 0 = 128; THE SAME ON EVERY RANK for a given call (block b pairs
+ *                   with block b of the peers).  Few blocks leave SMs to a GEMM that runs beside the all-reduce.
  * The library creates neither the multicast object nor the peer mappings; the Python side (sglang_b200.distributed.nvls)
  * takes both from torch's symmetric-memory allocator.  A wait that runs out sets status 41 / 42 (first / second barrier).
  * Replaces: the all-reduce the reference's row-parallel linear calls for large outputs, GroupCoordinator.all_reduce
@@ -560,7 +562,7 @@ int sglb200_peer_free(void* dev_ptr);
  *           symmetric-memory route device_communicators/torch_symm_mem.py (multimem_all_reduce_).
  */
 int sglb200_nvls_all_reduce(uint64_t multicast_addr, const uint64_t* flag_blocks, int rank, int world, int64_t numel,
-                            int dtype, void* stream);
+                            int dtype, int blocks, void* stream);
 int64_t sglb200_nvls_flag_bytes(void);
 
 /*

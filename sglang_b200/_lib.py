@@ -76,7 +76,7 @@ SIGNATURES = {
     "sglb200_get_num_sms": [],
     "sglb200_set_grouped_few_rows": [_I],
     "sglb200_get_grouped_few_rows": [],
-    "sglb200_nvls_all_reduce": [ctypes.c_uint64, _P, _I, _I, _L, _I, _P],
+    "sglb200_nvls_all_reduce": [ctypes.c_uint64, _P, _I, _I, _L, _I, _I, _P],
     "sglb200_nvls_flag_bytes": [],
 }
 _RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64,

@@ -38,7 +38,7 @@ int nvls_take_device_status() {
 
 namespace {
 
-constexpr int kBlocks = 128;     // the same on every rank: block b pairs with block b of the peers
+constexpr int kBlocks = 128;     // most blocks a launch may use (the flag block has a word per block and source rank)
 constexpr int kThreads = 512;
 constexpr int kUnroll = 8;       // 16-byte vectors in flight per thread
 constexpr int kMaxRanks = 8;
@@ -149,11 +149,12 @@ extern "C" int64_t sglb200_nvls_flag_bytes(void) {
 }
 
 extern "C" int sglb200_nvls_all_reduce(uint64_t multicast_addr, const uint64_t* flag_blocks, int rank, int world,
-                                       int64_t numel, int dtype, void* stream) {
+                                       int64_t numel, int dtype, int blocks, void* stream) {
   using namespace sglb;
   SGLB_REQUIRE(world >= 2 && world <= kMaxRanks, SGLB200_ERR_SHAPE, "world=%d: 2..%d", world, kMaxRanks);
   SGLB_REQUIRE(rank >= 0 && rank < world, SGLB200_ERR_SHAPE, "rank=%d of %d", rank, world);
   SGLB_REQUIRE(dtype == SGLB200_BF16 || dtype == SGLB200_F16, SGLB200_ERR_DTYPE, "dtype=%d: only bf16 (0) and f16 (1)", dtype);
+  SGLB_REQUIRE(blocks >= 0 && blocks <= kBlocks, SGLB200_ERR_SHAPE, "blocks=%d: 0 (all %d) .. %d", blocks, kBlocks, kBlocks);
   SGLB_REQUIRE(numel >= 0 && numel % 8 == 0, SGLB200_ERR_SHAPE, "numel=%lld must be a multiple of 8 (16-byte vectors)",
                (long long)numel);
   if (numel == 0) return SGLB200_OK;
@@ -171,10 +172,11 @@ extern "C" int sglb200_nvls_all_reduce(uint64_t multicast_addr, const uint64_t* 
                di.cc_major, di.cc_minor);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const uint64_t limit_ns = 2000000000ull;
+  const int grid = blocks > 0 ? blocks : kBlocks;  // the same on every rank: block b pairs with block b of the peers
   if (dtype == SGLB200_BF16)
-    nvls_all_reduce_kernel<true><<<kBlocks, kThreads, 0, st>>>(multicast_addr, fp, rank, world, numel / 8, limit_ns);
+    nvls_all_reduce_kernel<true><<<grid, kThreads, 0, st>>>(multicast_addr, fp, rank, world, numel / 8, limit_ns);
   else
-    nvls_all_reduce_kernel<false><<<kBlocks, kThreads, 0, st>>>(multicast_addr, fp, rank, world, numel / 8, limit_ns);
+    nvls_all_reduce_kernel<false><<<grid, kThreads, 0, st>>>(multicast_addr, fp, rank, world, numel / 8, limit_ns);
   SGLB_CHECK_LAUNCH("nvls_all_reduce_kernel");
   return SGLB200_OK;
 }

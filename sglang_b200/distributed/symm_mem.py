@@ -63,6 +63,7 @@ class SymmMemCommunicator:
         self._handle, self._fhandle = handle, fhandle
         self.rank = handle.rank
         self._flag_blocks = (ctypes.c_uint64 * self.world_size)(*[int(p) for p in fhandle.buffer_ptrs])
+        self.side_stream = torch.cuda.Stream(device)  # the all-reduces of row chunks that overlap the next chunk's GEMM
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flag block is zero before any kernel signals
         self.disabled = False
@@ -101,8 +102,9 @@ class SymmMemCommunicator:
             raise ValueError(f"view of {tuple(shape)} {dtype}: 16-bit dtypes, at most {self.max_size} bytes")
         return self.buffer[:n].view(dtype).view(*shape)
 
-    def all_reduce_(self, t: torch.Tensor) -> torch.Tensor:
-        """In-place sum of a tensor that lives in the symmetric buffer (from :meth:`view`), on the current stream."""
+    def all_reduce_(self, t: torch.Tensor, blocks: int = 0) -> torch.Tensor:
+        """In-place sum of a tensor that lives in the symmetric buffer (from :meth:`view`), on the current stream.
+        ``blocks`` (0 = all 128) is the kernel's grid and must be the same on every rank."""
         if self.disabled:
             raise RuntimeError("SymmMemCommunicator is disabled")
         off = t.data_ptr() - self.buffer.data_ptr()
@@ -111,7 +113,7 @@ class SymmMemCommunicator:
             raise ValueError("all_reduce_ needs a contiguous 16-byte-aligned tensor inside the symmetric buffer")
         with torch.cuda.device(self.device):
             check(lib().sglb200_nvls_all_reduce(int(self._handle.multicast_ptr) + off, self._flag_blocks, self.rank,
-                                                self.world_size, t.numel(), dtype_code(t.dtype),
+                                                self.world_size, t.numel(), dtype_code(t.dtype), int(blocks),
                                                 torch.cuda.current_stream(self.device).cuda_stream),
                   "nvls_all_reduce")
         return t
@@ -145,4 +147,41 @@ def row_parallel_linear_symm_mem(comm: SymmMemCommunicator, x: torch.Tensor, wei
         comm.all_reduce_(y)
         if bias is not None:
             y += bias
+    return y.reshape(*x.shape[:-1], N)
+
+
+def row_parallel_linear_symm_mem_overlapped(comm: SymmMemCommunicator, x: torch.Tensor, weight: torch.Tensor,
+                                            weight_scale: torch.Tensor, chunk_rows: int = 2048, ar_blocks: int = 32,
+                                            bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`row_parallel_linear_symm_mem` with the all-reduce of one row chunk running while the GEMM of the next
+    chunk computes (the shape of the reference's two-batch overlap, ``two_batch_overlap.py``): the GEMM runs per chunk
+    of ``chunk_rows`` rows into a row range of the symmetric buffer on ``148 - ar_blocks`` SMs
+    (``configure_deep_gemm_num_sms``), and each range goes to the multicast all-reduce kernel with ``ar_blocks`` thread
+    blocks on the communicator's side stream as soon as its GEMM has finished.  Same result as the unchunked form: the
+    chunks only partition the rows.  Every rank must pass the same ``chunk_rows`` and ``ar_blocks``."""
+    from ..layers.deep_gemm_wrapper import configure_deep_gemm_num_sms
+    from ..layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8, w8a8_block_fp8_matmul
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M, N = x2.shape[0], weight.shape[0]
+    y = comm.view((M, N), x.dtype)
+    if M == 0:
+        return y.reshape(*x.shape[:-1], N)
+    q, s = sglang_per_token_group_quant_fp8(x2, BLOCK, column_major_scales=True, scale_tma_aligned=True)
+    main, side = torch.cuda.current_stream(comm.device), comm.side_stream
+    sm_total = torch.cuda.get_device_properties(comm.device).multi_processor_count
+    with configure_deep_gemm_num_sms(max(1, sm_total - ar_blocks)):
+        for r0 in range(0, M, chunk_rows):
+            r1 = min(M, r0 + chunk_rows)
+            part = y[r0:r1]
+            w8a8_block_fp8_matmul(q[r0:r1], weight, s[r0:r1], weight_scale, [BLOCK, BLOCK], x.dtype, out=part)
+            done = torch.cuda.Event()
+            done.record(main)
+            side.wait_event(done)
+            with torch.cuda.stream(side):
+                comm.all_reduce_(part, blocks=ar_blocks)
+    main.wait_stream(side)
+    if bias is not None:
+        y += bias
     return y.reshape(*x.shape[:-1], N)

@@ -28,7 +28,7 @@ def _worker(rank, world, port, q):
         from helpers import assert_gemm_close, row_parallel_reference
         from sglang_b200._lib import lib
         from sglang_b200.distributed import (RowParallelBlockFp8Linear, SymmMemCommunicator,
-                                             row_parallel_linear_symm_mem)
+                                             row_parallel_linear_symm_mem, row_parallel_linear_symm_mem_overlapped)
         dev = torch.device("cuda", rank)
         comm = SymmMemCommunicator(dist.group.WORLD, dev, max_size=64 << 20)
         if comm.disabled:
@@ -110,11 +110,15 @@ def _worker(rank, world, port, q):
             y = layer(xr).clone()
             y_direct = row_parallel_linear_symm_mem(comm, xr, plain.weight, plain.weight_scale_inv).clone()
             y_b = layer_b(xr).clone()
+            # chunks of rows, each chunk's all-reduce (16 blocks, side stream) beside the next chunk's GEMM: same bits
+            y_ovl = row_parallel_linear_symm_mem_overlapped(comm, xr, plain.weight, plain.weight_scale_inv,
+                                                            chunk_rows=512, ar_blocks=16).clone()
             y_n = plain(xr)
             torch.cuda.synchronize()
             ref = row_parallel_reference(xs, w_dn, s_dn, world)
             assert_gemm_close(y, ref, f"symm-mem row-parallel {it}", allow_one_ulp=True)
             assert torch.equal(y, y_direct)
+            assert torch.equal(y, y_ovl), f"chunk-overlapped form differs ({it})"
             # NCCL rounds the same sum to nearest: the two results differ by less than two units in the last place
             d = (y.float() - y_n.float()).abs().cpu().double()
             ulp = torch.ldexp(torch.ones_like(d), torch.frexp(ref.double().abs().clamp(min=1e-30))[1] - 8)
