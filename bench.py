@@ -285,7 +285,7 @@ def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H
     return out
 
 
-def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=None, mc_chunk=4096, mc_blocks=32):
+def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=None, mc_chunk=4096, mc_blocks=16):
     """Tensor-parallel decoder projections at the Llama-3-70B shape (hidden 8192, intermediate 28672, 64 q / 8 kv
     heads of 128): column-parallel QKV and gate_up, row-parallel o and down, each followed by an NCCL all-reduce of the
     [M, 8192] bf16 output (none at tp1).  One step = the four linears of a layer on M tokens; device time, max over
@@ -691,7 +691,7 @@ def main():
                          "multimem kernel adds them; 0 = never; -1 = tried with the other orders, the fastest is kept")
     ap.add_argument("--ar-blocks", type=int, default=0,
                     help="thread blocks of the multicast all-reduce kernel when it overlaps the next row chunk's GEMM; "
-                         "0 = 16, 32 and 64 are tried")
+                         "0 = 4, 8, 16 and 32 are tried")
     ap.add_argument("--chunk-rows", type=int, default=0,
                     help="rows per chunk of the overlapped row-parallel linear; 0 = M / 4 and M / 2 are both tried")
     ap.add_argument("--comm-sms", type=int, default=0, help="SMs the GEMMs leave free for NCCL while overlapping")
@@ -879,7 +879,7 @@ def main():
     own_launches = [0]  # kernels of this library launched by step(): one quantiser + one GEMM per layer (per chunk)
 
     mc_chunk = [0]  # > 0: the multicast all-reduce runs per chunk of this many rows beside the next chunk's GEMM
-    ar_blocks = [args.ar_blocks if args.ar_blocks > 0 else 32]
+    ar_blocks = [args.ar_blocks if args.ar_blocks > 0 else 16]
 
     def step(record=False):
         for L in layers:
@@ -978,7 +978,7 @@ def main():
         # ranks) and keep the fastest for the warm-up and the timed region
         tried = {}
         chunk_choices = [args.chunk_rows] if args.chunk_rows > 0 else [max(128, M // 4), max(128, M // 2)]
-        blocks_choices = [args.ar_blocks] if args.ar_blocks > 0 else [16, 32, 64]
+        blocks_choices = [args.ar_blocks] if args.ar_blocks > 0 else [4, 8, 16, 32]
         for mode in (["plain"] + [f"overlapped_{c}" for c in chunk_choices]
                      + (["multicast"] + [f"multicast_overlapped_{c}_{b}" for c in chunk_choices for b in blocks_choices]
                         if mc is not None else [])):
@@ -1007,6 +1007,12 @@ def main():
         if overlap:
             chunk_rows[0] = int(best.split("_")[1])
         config["step_tried_ms"] = tried
+        # The trials loaded the board for a few hundred milliseconds; at N = 1 the warm-up starts from an idle board.  Give
+        # the power controller the same starting point here (set-up, outside every timed region).
+        fence()
+        time.sleep(1.0)
+        fence()
+        config["after_trials"] = "1 s idle before the warm-up steps"
     if world > 1:
         config["step"] = ((f"row-parallel layers in chunks of {chunk_rows[0]} rows, the NCCL all-reduce of a chunk overlaps "
                            f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"

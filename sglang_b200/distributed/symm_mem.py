@@ -151,7 +151,7 @@ def row_parallel_linear_symm_mem(comm: SymmMemCommunicator, x: torch.Tensor, wei
 
 
 def row_parallel_linear_symm_mem_overlapped(comm: SymmMemCommunicator, x: torch.Tensor, weight: torch.Tensor,
-                                            weight_scale: torch.Tensor, chunk_rows: int = 2048, ar_blocks: int = 32,
+                                            weight_scale: torch.Tensor, chunk_rows: int = 4096, ar_blocks: int = 16,
                                             bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """:func:`row_parallel_linear_symm_mem` with the all-reduce of one row chunk running while the GEMM of the next
     chunk computes (the shape of the reference's two-batch overlap, ``two_batch_overlap.py``): the GEMM runs per chunk

@@ -103,7 +103,8 @@ def _worker(rank, world, port, q):
         plain = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world)
         bias = torch.randn(H, generator=g).bfloat16()
         layer = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, symm_mem=comm)
-        layer_b = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, bias=bias.cuda(), symm_mem=comm)
+        layer_b = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, bias=bias.cuda(), symm_mem=comm,
+                                            symm_mem_chunk_rows=256, symm_mem_blocks=8)  # chunked from 257 rows up
         for it, Ms in enumerate([200, 1, 2048, 333]):
             xs = torch.randn(Ms, I, generator=g).bfloat16()
             xr = xs[:, rank * (I // world):(rank + 1) * (I // world)].contiguous().cuda()
