@@ -246,11 +246,11 @@ def moe_section(torch, dev, gen, Ms=(16, 64, 256, 4096, 16384), E=256, topk=8, H
         routed = int(torch.unique(ti).numel())
         w_bytes = routed * (w1.numel() + w2.numel()) // E
         case = {"M": M, "experts_with_rows": routed, "routed_weight_bytes": w_bytes}
-        few_rows = M * topk <= lib().sglb200_get_grouped_few_rows() * E  # the fp32-scale grouped GEMMs take the few-rows kernel
+        few_rows = M * topk <= lib().sglb200_get_grouped_few_rows() * E  # the grouped GEMMs take the few-rows kernel
         variants = [("fp32_scales", lambda: fused_experts_block_fp8(a, w1, w2, w1s, w2s, tw, ti), None),
                     ("ue8m0", lambda: fused_experts_block_fp8_ue8m0(a, w1, w2, w1p, w2p, tw, ti), None)]
         if few_rows:  # the same calls with the few-rows kernel switched off: the 128 x 128 grouped kernels
-            variants += [("fp32_scales_tile_kernel", variants[0][1], 0)]
+            variants += [("fp32_scales_tile_kernel", variants[0][1], 0), ("ue8m0_tile_kernel", variants[1][1], 0)]
         for name, fn, limit in variants:
             before = lib().sglb200_get_grouped_few_rows()
             if limit is not None:

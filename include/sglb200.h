@@ -61,14 +61,15 @@ int sglb200_set_num_sms(int num_sms);
 int sglb200_get_num_sms(void);
 
 /*
- * Grouped GEMMs with fp32 scales (sglb200_fp8_blockwise_scaled_grouped_mm and its masked form) whose experts hold at
- * most max_avg_rows rows on average (total rows / experts; the row bound per expert in the masked layout) run on the
+ * Grouped GEMMs (sglb200_fp8_blockwise_scaled_grouped_mm, its masked form and sglb200_fp8_ue8m0_scaled_grouped_mm) whose
+ * experts hold at most max_avg_rows rows on average (total rows / experts; the row bound per expert in the masked layout) run on the
  * few-rows kernel: operands swapped, 128 weight rows x 16 / 32 / 64 activation rows per MMA, only the weights of
  * experts that have rows are streamed.  This is the decode case of a mixture-of-experts layer, where the 128 x 128
- * kernel spends a full tile of tensor-core work and promotion on a handful of rows.  Default 20 (measured cross-over
- * on the DeepSeek-V3 layer shape: faster up to 8 rows per expert, level at 32); 0 = always the 128 x 128 kernel;
- * at most 64.  The UE8M0 grouped GEMM has no such form: its tile kernel has no promotion to save and streams weights
- * at the same rate.
+ * kernel spends a full tile of tensor-core work (and, with fp32 scales, of promotion) on a handful of rows: no slower
+ * in a burst, but sustained that work runs the board into its power cap at half the SM clock.  Default 20 (measured
+ * cross-over on the DeepSeek-V3 layer shape under sustained load: faster up to ~24 rows per expert, level at 32-48);
+ * 0 = always the 128 x 128 kernels; at most 64.  With UE8M0 scales the few-rows kernel decodes the exponent bytes and
+ * applies the scales in fp32 after each k-block (exact for powers of two).
  * The results of the two kernels are bit-identical (same products, same fp32 accumulation order per k-block).
  * Process-wide, read at every launch.
  * Replaces: the small-M tile configurations of the reference's grouped kernel,

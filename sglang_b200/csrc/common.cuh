@@ -47,7 +47,7 @@ int smallm_grouped_gemm(int chunk, const void* a, const void* b, const float* sa
                         int64_t num_experts, int64_t rows_per_expert, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                         int64_t ldb_e, int64_t ldc, int64_t sa_stride_e, int64_t sa_stride_m, int64_t sa_stride_k,
                         int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, int sm_count,
-                        void* stream);
+                        void* stream, bool ue8m0);
 
 // Dense GEMM on CTA pairs (256 x bn tiles, bn = 128 or 256), gemm_pair.cu
 int pair_gemm(int bn, const void* a, const void* b, const float* sa, const float* sb, void* out, int64_t M, int64_t N,

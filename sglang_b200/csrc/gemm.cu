@@ -1000,7 +1000,7 @@ int gemm_common(const void* a, const void* b, const float* sa, const float* sb, 
       return smallm_grouped_gemm(chunk, a, b, sa, sb, out, expert_offsets, problem_sizes, rows_per_expert > 0 ? 1 : 3,
                                  total_rows, num_experts, rows_per_expert, N, K, lda, ldb, ldb_e, ldc, sa_stride_e,
                                  sa_stride_m, sa_stride_k, sb_stride_e, sb_stride_n, sb_stride_k, out_dtype, di.sm_count,
-                                 stream);
+                                 stream, false);
   }
 
   alignas(64) CUtensorMap map_a, map_b;

@@ -616,7 +616,7 @@ int smallm_grouped_gemm(int chunk, const void* a, const void* b, const float* sa
                         int64_t num_experts, int64_t rows_per_expert, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                         int64_t ldb_e, int64_t ldc, int64_t sa_stride_e, int64_t sa_stride_m, int64_t sa_stride_k,
                         int64_t sb_stride_e, int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, int sm_count,
-                        void* stream) {
+                        void* stream, bool ue8m0) {
   if (num_experts > kMaxExperts) return fail(SGLB200_ERR_SHAPE, "num_experts=%lld: at most %d", (long long)num_experts, kMaxExperts);
   alignas(64) CUtensorMap map_w, map_a;
   {
@@ -657,6 +657,13 @@ int smallm_grouped_gemm(int chunk, const void* a, const void* b, const float* sa
   // an upper bound on the work items without reading the device: every expert can add one ragged chunk
   const int64_t items = ((total_rows + chunk - 1) / chunk + num_experts) * p.n_tiles;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ue8m0) {
+    switch (chunk) {
+      case 16: return launch<16, true, true>(map_w, map_a, p, sm_count, st, items);
+      case 32: return launch<32, true, true>(map_w, map_a, p, sm_count, st, items);
+      default: return launch<64, true, true>(map_w, map_a, p, sm_count, st, items);
+    }
+  }
   switch (chunk) {
     case 16: return launch<16, false, true>(map_w, map_a, p, sm_count, st, items);
     case 32: return launch<32, false, true>(map_w, map_a, p, sm_count, st, items);

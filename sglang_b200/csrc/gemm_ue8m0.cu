@@ -488,6 +488,16 @@ int ue8m0_common(const void* a, const void* b, const int32_t* sfa, const int32_t
     return SGLB200_OK;
   }
 
+  if (grouped) {
+    // few rows per expert: the weight-streaming kernel decodes the exponent bytes itself (gemm_smallm.cu).  In a burst
+    // the block-scaled tile kernel below is as fast; sustained it runs into the board's power cap at half the clock.
+    if (const int chunk = smallm_grouped_chunk(M, num_experts, 0))
+      return smallm_grouped_gemm(chunk, a, b, reinterpret_cast<const float*>(sfa), reinterpret_cast<const float*>(sfb),
+                                 out, expert_offsets, nullptr, 1, M, num_experts, 0, N, K, lda, ldb, ldb_e, ldc, 0,
+                                 sfa_stride_m, sfa_ld, sfb_stride_e, sfb_stride_n, sfb_stride_k, out_dtype, di.sm_count,
+                                 stream, true);
+  }
+
   alignas(64) CUtensorMap map_a, map_b;
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};

@@ -123,6 +123,37 @@ def test_few_rows_masked_layout(G, max_m):
             assert_gemm_close(outs[0][g, :m], ref, f"group {g}")
 
 
+@pytest.mark.parametrize("counts,N,K", [([3, 0, 17, 1, 9, 0, 40, 2], 448, 512), ([20] * 6, 256, 1152), ([1] * 32, 128, 7168)])
+def test_few_rows_grouped_ue8m0(counts, N, K):
+    """Power-of-two scales: the few-rows kernel decodes the packed exponent words and applies the scales after each
+    k-block, exactly; within the output rounding of the oracle, and within one unit in the last place of the block-scaled
+    tensor-core kernel (which applies the scales inside the MMA, before its fp32 accumulation)."""
+    from sglang_b200.layers.moe import _grouped_mm_ue8m0
+    from sglang_b200.layers.quantization import pack_ue8m0_scales
+    E, rows = len(counts), sum(counts)
+    x = make_activations(rows, K, seed=rows + N, outliers=False)
+    q, s = oracle.per_token_group_quant_fp8(x, 128, scale_ue8m0=True)
+    wq, wsc = _weights(E, N, K, seed=N, ue8m0=True)
+    wp = torch.stack([pack_ue8m0_scales(t) for t in wsc])
+    offs = torch.tensor(np.concatenate([[0], np.cumsum(counts)]), dtype=torch.int32)
+    outs = []
+    for limit in (64, 0):
+        out = torch.full((rows, N), 7.0, dtype=torch.bfloat16, device="cuda")
+        with few_rows_limit(limit):
+            _grouped_mm_ue8m0(q.cuda(), pack_ue8m0_scales(s).cuda(), wq.cuda(), wp.cuda(), out, offs.cuda())
+        torch.cuda.synchronize()
+        from sglang_b200._lib import lib
+        assert lib().sglb200_read_device_status() == 0
+        outs.append(out.cpu())
+    for e in range(E):
+        r0, r1 = int(offs[e]), int(offs[e + 1])
+        if r1 > r0:
+            ref = oracle.w8a8_block_fp8_matmul(q[r0:r1], wq[e], s[r0:r1], wsc[e])
+            assert_gemm_close(outs[0][r0:r1], ref, f"expert {e}, few-rows kernel")
+            assert_gemm_close(outs[1][r0:r1], ref, f"expert {e}, tile kernel", allow_one_ulp=True)
+            assert_gemm_close(outs[0][r0:r1], outs[1][r0:r1], f"expert {e}, kernels against each other", allow_one_ulp=True)
+
+
 def test_few_rows_limit_setter_rejects_bad_values():
     from sglang_b200._lib import lib
     L = lib()
