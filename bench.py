@@ -864,6 +864,7 @@ def main():
     mc, multicast = None, False
     if world > 1:
         from sglang_b200.distributed import (SymmMemCommunicator, row_parallel_linear_overlapped,
+                                             row_parallel_linear_symm_mem_fused,
                                              row_parallel_linear_symm_mem_overlapped)
         from sglang_b200.layers.deep_gemm_wrapper import configure_deep_gemm_num_sms
         sm_total = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -880,9 +881,15 @@ def main():
 
     mc_chunk = [0]  # > 0: the multicast all-reduce runs per chunk of this many rows beside the next chunk's GEMM
     ar_blocks = [args.ar_blocks if args.ar_blocks > 0 else 16]
+    fused_ctas = [0]  # > 0: GEMM and multicast all-reduce in one launch, this many communication CTAs
 
     def step(record=False):
         for L in layers:
+            if multicast and fused_ctas[0] > 0 and L["mode"] == "row":
+                own_launches[0] += 2
+                y = row_parallel_linear_symm_mem_fused(mc, L["x"], L["layer"].weight, L["layer"].weight_scale_inv,
+                                                       comm_ctas=fused_ctas[0])
+                continue
             if multicast and mc_chunk[0] > 0 and L["mode"] == "row":
                 own_launches[0] += 1 + 2 * -(-M // mc_chunk[0])
                 y = row_parallel_linear_symm_mem_overlapped(mc, L["x"], L["layer"].weight, L["layer"].weight_scale_inv,
@@ -981,9 +988,10 @@ def main():
         blocks_choices = [args.ar_blocks] if args.ar_blocks > 0 else [4, 8, 16, 32]
         for mode in (["plain"] + [f"overlapped_{c}" for c in chunk_choices]
                      + (["multicast"] + [f"multicast_overlapped_{c}_{b}" for c in chunk_choices for b in blocks_choices]
-                        if mc is not None else [])):
+                        + [f"multicast_fused_{c}" for c in (8, 16, 24)] if mc is not None else [])):
             overlap, multicast = mode.startswith("overlapped"), mode.startswith("multicast")
             mc_chunk[0] = int(mode.split("_")[2]) if mode.startswith("multicast_overlapped") else 0
+            fused_ctas[0] = int(mode.split("_")[2]) if mode.startswith("multicast_fused") else 0
             if mc_chunk[0]:
                 ar_blocks[0] = int(mode.split("_")[3])
             if overlap:
@@ -1002,6 +1010,7 @@ def main():
         best = min(tried, key=tried.get)
         overlap, multicast = best.startswith("overlapped"), best.startswith("multicast")
         mc_chunk[0] = int(best.split("_")[2]) if best.startswith("multicast_overlapped") else 0
+        fused_ctas[0] = int(best.split("_")[2]) if best.startswith("multicast_fused") else 0
         if mc_chunk[0]:
             ar_blocks[0] = int(best.split("_")[3])
         if overlap:
@@ -1017,6 +1026,9 @@ def main():
         config["step"] = ((f"row-parallel layers in chunks of {chunk_rows[0]} rows, the NCCL all-reduce of a chunk overlaps "
                            f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"
                                                        if args.comm_sms > 0 else "")) if overlap
+                          else (f"row-parallel GEMM and multicast all-reduce in ONE launch: {fused_ctas[0]} CTAs of the GEMM's "
+                                "grid sum every finished block of 2048 output rows through the switch (multimem ld_reduce + "
+                                "st) while the other CTAs compute the next block") if multicast and fused_ctas[0]
                           else (f"row-parallel GEMMs in chunks of {mc_chunk[0]} rows on {sm_total - ar_blocks[0]} SMs write "
                                 f"into NVSwitch multicast memory; this library's multimem kernel ({ar_blocks[0]} blocks, side "
                                 "stream) adds a chunk in place while the next chunk's GEMM runs") if multicast and mc_chunk[0]
@@ -1048,7 +1060,7 @@ def main():
     breakdown = None
     if args.only in ("all", "gemm"):
         breakdown = breakdown_pass()
-        if overlap or (multicast and mc_chunk[0] > 0):
+        if overlap or (multicast and (mc_chunk[0] > 0 or fused_ctas[0] > 0)):
             breakdown["overlap_saves_ms"] = breakdown["step_ms"] - ms_per_step
         if world == 1:
             # the same step as one replayed CUDA graph: what is left of the host gap when nothing is launched from Python
@@ -1102,7 +1114,7 @@ def main():
                 "peak_source": f"2 x bf16_tflops_sustained ({peaks['source']}); nominal dense FP8 is 4500",
                 "frac_of_nominal_fp8": achieved / 4500.0, "launches": sum(len(L["ev"]) for L in layers),
                 "avg_launch_ms": gemm_ms / max(1, sum(len(L["ev"]) for L in layers)), "others": []}
-    if overlap or (multicast and mc_chunk[0] > 0):
+    if overlap or (multicast and (mc_chunk[0] > 0 or fused_ctas[0] > 0)):
         roofline["note"] = ("column-parallel and replicated layers only: the row-parallel GEMMs run in chunks beside "
                             "the all-reduce")
 

@@ -567,8 +567,32 @@ int sglb200_nvls_all_reduce(uint64_t multicast_addr, const uint64_t* flag_blocks
 int64_t sglb200_nvls_flag_bytes(void);
 
 /*
+ * The dense GEMM and the multicast all-reduce of its output in ONE cooperative launch: the row-parallel linear for
+ * large outputs.  The last comm_ctas CTAs of the grid compute no tiles; row block by row block (2048 rows: one raster
+ * group of the tile schedule) they wait until the tile CTAs of the same grid have stored the block (a device counter per
+ * row block), pair up with the same CTAs of the other ranks' kernels (flag words as in sglb200_nvls_all_reduce) and sum
+ * the block through the switch (multimem.ld_reduce / multimem.st) while the tile CTAs compute the next block; only the
+ * last block's reduction is exposed.  Every wait is bounded (status 6: the row block was never finished, 7 / 8: a peer
+ * never arrived).
+ *   out            this rank's mapping of the symmetric buffer, [M, N] contiguous; multicast_out = the multicast
+ *                  address of the same element (0, 0).
+ *   flag_blocks    as for sglb200_nvls_all_reduce (the two calls may share them; all ranks make the same sequence).
+ *   done_counters  64 device words of scratch owned by this rank (zeroed by the call, on the stream).
+ *   comm_ctas      1..64, THE SAME ON EVERY RANK; the GEMM runs on the SMs that are left.
+ * One such call at a time per GPU (the kernel occupies every SM it is given; a cooperative launch fails otherwise).
+ * Replaces: RowParallelLinear.forward + tensor_model_parallel_all_reduce, python/sglang/srt/layers/linear.py:1361-1386,
+ *           for outputs above the custom all-reduce's size limit.
+ */
+int sglb200_fp8_blockwise_scaled_mm_allreduce(const void* a, const void* b, const float* sa, const float* sb, void* out,
+                                              uint64_t multicast_out, const uint64_t* flag_blocks, void* done_counters,
+                                              int rank, int world, int comm_ctas, int64_t M, int64_t N, int64_t K,
+                                              int64_t lda, int64_t ldb, int64_t sa_stride_m, int64_t sa_stride_k,
+                                              int64_t sb_stride_n, int64_t sb_stride_k, int out_dtype, void* stream);
+
+/*
  * Device-side status word of the GEMM kernels: 0, or the code of the first bounded wait that timed out
- * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce, 11-18 the same
+ * (1 TMA producer, 2 or 3 MMA issuer, 4 promotion warps, 5 peer-flag wait of sglb200_peer_reduce, 6-8 the communication
+ * CTAs of sglb200_fp8_blockwise_scaled_mm_allreduce, 11-18 the same
  * roles in the UE8M0 and few-rows kernels, 21-23 the expert-parallel exchange, 31-35 the CTA-pair kernel, 41-42 the multicast all-reduce).  Every
  * kernel family keeps its own word; each call reads AND clears all of them and returns the first non-zero one, so a
  * status never surfaces on a later, unrelated read.  This call SYNCHRONISES the device (cudaMemcpyFromSymbol); it is for

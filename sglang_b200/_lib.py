@@ -78,6 +78,8 @@ SIGNATURES = {
     "sglb200_get_grouped_few_rows": [],
     "sglb200_nvls_all_reduce": [ctypes.c_uint64, _P, _I, _I, _L, _I, _I, _P],
     "sglb200_nvls_flag_bytes": [],
+    "sglb200_fp8_blockwise_scaled_mm_allreduce": [_P, _P, _P, _P, _P, ctypes.c_uint64, _P, _P, _I, _I, _I, _L, _L, _L, _L,
+                                                  _L, _L, _L, _L, _L, _I, _P],
 }
 _RESTYPES = {"sglb200_fp8_blockwise_scaled_mm_workspace_bytes": c_int64,
              "sglb200_fp8_blockwise_scaled_mm_noalloc_max_bytes": c_int64,

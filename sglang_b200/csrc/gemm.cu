@@ -25,6 +25,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "nvls.cuh"
 #include "ptx.cuh"
 
 namespace sglb {
@@ -100,10 +101,28 @@ struct GemmParams {
 struct PushGemmParams : GemmParams {
   PushParams push;
 };
-template <bool PUSH>
+
+// GEMM + all-reduce in one launch (dense, out = a buffer every rank maps through one multicast address): the last
+// comm_ctas CTAs of the grid do not compute tiles.  They wait for the row blocks of `out` (one raster group of kGroupM
+// row tiles each) to be finished by the other CTAs of this grid (`done`, one counter per row block, bumped once per
+// promotion warp and tile), pair up with the same CTAs of the other ranks' kernels through the flag words, and sum the
+// block over the ranks with multimem.ld_reduce / multimem.st (nvls.cuh) while the GEMM CTAs work on the next row block.
+struct ArParams {
+  uint64_t mc_out;       // multicast address of out[0][0]
+  nvls::FlagPtrs fp;     // every rank's flag block (nvls.cuh layout)
+  uint32_t* done;        // [row blocks] counters, zero at launch
+  int32_t rank, world, comm_ctas;
+  uint64_t limit_ns;
+};
+struct ArGemmParams : GemmParams {
+  ArParams ar;
+};
+template <bool PUSH, bool AR = false>
 struct ParamsOf { using type = GemmParams; };
 template <>
-struct ParamsOf<true> { using type = PushGemmParams; };
+struct ParamsOf<true, false> { using type = PushGemmParams; };
+template <>
+struct ParamsOf<false, true> { using type = ArGemmParams; };
 
 struct Tile {
   int32_t row0;     // first row of the tile in a / out
@@ -241,10 +260,11 @@ __device__ __forceinline__ void warp_rows_via_smem(uint32_t* stg, const uint32_t
   }
 }
 
-template <bool GROUPED, bool PUSH>
+template <bool GROUPED, bool PUSH, bool AR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                      const typename ParamsOf<PUSH>::type p) {
+                      const __grid_constant__ typename ParamsOf<PUSH, AR>::type p) {
+  static_assert(!AR || (!GROUPED && !PUSH), "the fused all-reduce is a form of the dense kernel");
   constexpr int kRing = kStages;  // shared-memory stages in the TMA ring
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -310,6 +330,13 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   ptx::tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   const int32_t total_tiles = ctl->total_tiles;
+  // CTAs that compute tiles, and their stride through the tile list
+  int32_t tile_stride = gridDim.x;
+  bool is_comm = false;
+  if constexpr (AR) {
+    tile_stride = (int32_t)gridDim.x - p.ar.comm_ctas;
+    is_comm = (int32_t)blockIdx.x >= tile_stride;
+  }
 
   // ---------------------------------------------------------------- roles
   // The per-k-block loops of the producer and the MMA issuer are a serial chain for one warp, so they
@@ -321,13 +348,65 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
   const uint32_t acc_empty0 = ptx::smem_u32(&ctl->acc_empty[0]);
   const uint32_t stage0 = ptx::smem_u32(stage_base);
 
-  if (warp < kIssuers) {
+  if (is_comm) {
+    if constexpr (AR) {
+      // ===== communication CTA: row block by row block, once the GEMM CTAs of this grid have stored it and the same CTA
+      // of every other rank says the same of theirs, this rank's 1 / world slice of the block is summed through the
+      // switch and written to every rank.  All waits are bounded; after a time-out the CTA skips the data movement but
+      // still advances its epoch.
+      __shared__ int s_ok;
+      __shared__ uint32_t s_epoch;
+      const int cb = (int)blockIdx.x - tile_stride;
+      uint32_t* ctlw = p.ar.fp.p[p.ar.rank] + nvls::kFlagWords + cb;
+      if (threadIdx.x == 0) {
+        s_ok = 1;
+        s_epoch = *reinterpret_cast<volatile uint32_t*>(ctlw);
+      }
+      __syncthreads();
+      const uint32_t epoch0 = s_epoch;
+      const int32_t row_blocks = (p.m_tiles + kGroupM - 1) / kGroupM;
+      bool ok = true;
+      for (int32_t rb = 0; rb < row_blocks && ok; ++rb) {
+        const int32_t mt_rb = min(kGroupM, p.m_tiles - rb * kGroupM);
+        const uint32_t target = (uint32_t)mt_rb * (uint32_t)p.n_tiles * kEpiWarps;
+        if (threadIdx.x == 0) {
+          uint64_t t0 = 0;
+          uint32_t polls = 0;
+          while (ptx::ld_acquire_gpu_u32(p.ar.done + rb) < target) {
+            if ((++polls & 63u) == 0) {
+              const uint64_t now = ptx::global_timer_ns();
+              if (t0 == 0) {
+                t0 = now;
+              } else if ((int64_t)(now - t0) > (int64_t)p.ar.limit_ns) {
+                s_ok = 0;
+                atomicCAS(&g_device_status, 0, 6);
+                break;
+              }
+            }
+          }
+        }
+        ok = nvls::rank_barrier(p.ar.fp, 0, cb, p.ar.rank, p.ar.world, epoch0 + 1u + (uint32_t)rb, p.ar.limit_ns, &s_ok,
+                                &g_device_status, 7);
+        if (!ok) break;
+        const int64_t row0 = (int64_t)rb * kGroupM * BM, rows = min((int64_t)p.total_rows - row0, (int64_t)kGroupM * BM);
+        const int64_t vec0 = row0 * p.N / 8, nvec = rows * p.N / 8;
+        const int64_t per_rank = (nvec + p.ar.world - 1) / p.ar.world;
+        const int64_t v0 = vec0 + (int64_t)p.ar.rank * per_rank, v1 = min(vec0 + nvec, v0 + per_rank);
+        if (p.out_dtype == SGLB200_BF16) nvls::reduce_range<true, 8>(p.ar.mc_out, v0, v1, cb, p.ar.comm_ctas, kThreads);
+        else nvls::reduce_range<false, 8>(p.ar.mc_out, v0, v1, cb, p.ar.comm_ctas, kThreads);
+      }
+      if (ok)
+        nvls::rank_barrier(p.ar.fp, 1, cb, p.ar.rank, p.ar.world, epoch0 + (uint32_t)row_blocks, p.ar.limit_ns, &s_ok,
+                           &g_device_status, 8);
+      if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(ctlw) = epoch0 + (uint32_t)row_blocks;
+    }
+  } else if (warp < kIssuers) {
     // ===== TMA producers.  Issuing a TMA or an MMA and touching an mbarrier each cost the issuing
     // thread on the order of a hundred cycles, and the tensor pipe does not queue far ahead, so one
     // warp per role cannot feed it: two warps per role take the k-blocks of the CTA alternately.
     uint32_t stage = 0, phase = 0, g = 0;
     uint32_t armed = 0, armed_phase = 0;  // bit i: this warp has armed stage i / the phase bit of its last arming
-    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int32_t t = blockIdx.x; t < total_tiles; t += tile_stride) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       bool ok = true;
       for (int32_t kb = tl.kb0; kb < tl.kb1; ++kb, ++g) {
@@ -371,7 +450,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     constexpr uint32_t idesc = ptx::make_idesc_e4m3_f32(BM, BN);
     const uint64_t desc0 = ptx::make_kmajor_sw128_desc(stage0);
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0, g = 0;
-    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int32_t t = blockIdx.x; t < total_tiles; t += tile_stride) {
       bool ok = true;
       int32_t kb_count = p.k_tiles;
       if (p.k_splits > 1) {
@@ -420,7 +499,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     float2 acc[kEpiCols / 2];
     uint32_t push_epoch = 0;
     if constexpr (PUSH) push_epoch = *reinterpret_cast<const volatile uint32_t*>(p.push.ctl) + 1u;
-    for (int32_t t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+    for (int32_t t = blockIdx.x; t < total_tiles; t += tile_stride) {
       const Tile tl = get_tile<GROUPED>(p, tile_start, t);
       const int32_t row = tl.row0 + r_in_tile;
       const int32_t row_c = min(row, p.total_rows - 1);
@@ -531,6 +610,15 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
           store_row<__nv_bfloat16>(acc, static_cast<__nv_bfloat16*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
         } else {
           store_row<__half>(acc, static_cast<__half*>(p.out) + (int64_t)row * p.ldc + n_first, n_first, p.N);
+        }
+      }
+      if constexpr (AR) {
+        // this warp's part of the tile is stored: count it for the tile's row block (the warp barrier orders every
+        // lane's stores before lane 0's fence; the communication CTAs read the counter with acquire)
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          atomicAdd(p.ar.done + (tl.row0 / BM) / kGroupM, 1u);
         }
       }
     }
@@ -1417,6 +1505,119 @@ extern "C" int sglb200_peer_reduce(const void* recv_local, void* flags_local, vo
   SGLB_CHECK_LAUNCH("peer_reduce_kernel");
   return SGLB200_OK;
 }
+
+// GEMM + all-reduce in one cooperative launch (see ArParams).  `out` is this rank's mapping of a buffer that every rank
+// maps through one multicast address (multicast_out = the multicast address of out[0][0]); rows are contiguous
+// (row stride N).  done_counters: at least 64 device words, scratch (zeroed here on the stream).
+extern "C" int sglb200_fp8_blockwise_scaled_mm_allreduce(const void* a, const void* b, const float* sa, const float* sb,
+                                                         void* out, uint64_t multicast_out, const uint64_t* flag_blocks,
+                                                         void* done_counters, int rank, int world, int comm_ctas,
+                                                         int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                                                         int64_t sa_stride_m, int64_t sa_stride_k, int64_t sb_stride_n,
+                                                         int64_t sb_stride_k, int out_dtype, void* stream) {
+  using namespace sglb;
+  SGLB_REQUIRE(M >= 0 && N >= 0 && K > 0, SGLB200_ERR_SHAPE, "M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+  SGLB_REQUIRE(out_dtype == SGLB200_BF16 || out_dtype == SGLB200_F16, SGLB200_ERR_DTYPE,
+               "out_dtype=%d: only bf16 (0) and f16 (1)", out_dtype);
+  SGLB_REQUIRE(M < ((int64_t)1 << 31) - 256 && N < ((int64_t)1 << 31) - 256 && K < ((int64_t)1 << 31) - 256,
+               SGLB200_ERR_SHAPE, "a dimension exceeds 2^31");
+  SGLB_REQUIRE(K % 16 == 0 && N % 8 == 0, SGLB200_ERR_SHAPE, "K=%lld must be a multiple of 16 and N=%lld of 8",
+               (long long)K, (long long)N);
+  SGLB_REQUIRE(world >= 2 && world <= nvls::kMaxRanks && rank >= 0 && rank < world, SGLB200_ERR_SHAPE,
+               "rank=%d world=%d: 2..%d ranks", rank, world, nvls::kMaxRanks);
+  SGLB_REQUIRE(comm_ctas >= 1 && comm_ctas <= 64, SGLB200_ERR_SHAPE, "comm_ctas=%d: 1..64", comm_ctas);
+  if (M == 0 || N == 0) return SGLB200_OK;
+  SGLB_REQUIRE((M + BM - 1) / BM <= 64 * kGroupM, SGLB200_ERR_SHAPE, "M=%lld: at most %d rows (64 row blocks)",
+               (long long)M, 64 * kGroupM * BM);
+  SGLB_REQUIRE(a && b && sa && sb && out && flag_blocks && done_counters && multicast_out, SGLB200_ERR_NULL,
+               "a/b/sa/sb/out/multicast_out/flag_blocks/done_counters must not be NULL");
+  SGLB_REQUIRE(lda >= K && lda % 16 == 0 && ldb >= K && ldb % 16 == 0, SGLB200_ERR_ALIGN,
+               "lda=%lld / ldb=%lld must be >= K and multiples of 16", (long long)lda, (long long)ldb);
+  SGLB_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(out, 16) && multicast_out % 16 == 0 && aligned(sa, 4) &&
+                   aligned(sb, 4) && aligned(done_counters, 4),
+               SGLB200_ERR_ALIGN, "a, b, out and the multicast address must be 16-byte aligned");
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  SGLB_REQUIRE(di.cc_major == 10, SGLB200_ERR_ARCH, "compute capability %d.%d: this library is built for sm_100a only",
+               di.cc_major, di.cc_minor);
+  SGLB_REQUIRE(comm_ctas < di.sm_count, SGLB200_ERR_SHAPE, "comm_ctas=%d leaves no SM for the GEMM", comm_ctas);
+
+  alignas(64) CUtensorMap map_a, map_b;
+  {
+    const uint64_t dims[2] = {(uint64_t)K, (uint64_t)M};
+    const uint64_t str[1] = {(uint64_t)lda};
+    if (int rc = make_map_sw128(&map_a, a, 2, dims, str, BM, CU_TENSOR_MAP_L2_PROMOTION_L2_128B)) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, 1};
+    const uint64_t str[2] = {(uint64_t)ldb, (uint64_t)ldb * (uint64_t)N};
+    if (int rc = make_map_sw128(&map_b, b, 3, dims, str, BN, CU_TENSOR_MAP_L2_PROMOTION_L2_256B)) return rc;
+  }
+  ArGemmParams p;
+  p.sa = sa;
+  p.sb = sb;
+  p.out = out;
+  p.expert_offsets = nullptr;
+  p.problem_sizes = nullptr;
+  p.count_stride = 3;
+  p.rows_per_expert = 0;
+  p.sa_stride_e = 0;
+  p.total_rows = (int32_t)M;
+  p.N = (int32_t)N;
+  p.K = (int32_t)K;
+  p.num_experts = 1;
+  p.m_tiles = (int32_t)((M + BM - 1) / BM);
+  p.n_tiles = (int32_t)((N + BN - 1) / BN);
+  p.k_tiles = (int32_t)((K + BK - 1) / BK);
+  p.ldc = N;
+  p.sa_stride_m = sa_stride_m;
+  p.sa_stride_k = sa_stride_k;
+  p.sb_stride_e = 0;
+  p.sb_stride_n = sb_stride_n;
+  p.sb_stride_k = sb_stride_k;
+  p.out_dtype = out_dtype;
+  p.partial = nullptr;
+  p.k_splits = 1;
+  p.kb_per_split = p.k_tiles;
+  p.ar.mc_out = multicast_out;
+  for (int i = 0; i < nvls::kMaxRanks; ++i) {
+    p.ar.fp.p[i] = i < world ? reinterpret_cast<uint32_t*>(flag_blocks[i]) : nullptr;
+    SGLB_REQUIRE(i >= world || (p.ar.fp.p[i] != nullptr && flag_blocks[i] % 4 == 0), SGLB200_ERR_NULL,
+                 "flag block of rank %d is NULL or misaligned", i);
+  }
+  p.ar.done = static_cast<uint32_t*>(done_counters);
+  p.ar.rank = rank;
+  p.ar.world = world;
+  p.ar.comm_ctas = comm_ctas;
+  p.ar.limit_ns = 2000000000ull;
+
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(fp8_block_gemm_kernel<false, false, true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes);
+    if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    attr_done[dev] = true;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(done_counters, 0, 64 * sizeof(uint32_t), st);
+  if (e != cudaSuccess) return fail(SGLB200_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  // the communication CTAs wait for the tile CTAs of the same grid: every CTA must be resident (cooperative launch),
+  // one CTA per SM
+  const int64_t tiles = (int64_t)p.m_tiles * p.n_tiles;
+  const int64_t gemm_ctas = tiles < di.sm_count - comm_ctas ? tiles : di.sm_count - comm_ctas;
+  const int grid = (int)gemm_ctas + comm_ctas;
+  void* args[] = {(void*)&map_a, (void*)&map_b, (void*)&p};
+  e = cudaLaunchCooperativeKernel((const void*)fp8_block_gemm_kernel<false, false, true>, dim3(grid), dim3(kThreads), args,
+                                  kSmemBytes, st);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(SGLB200_ERR_LAUNCH, "fp8_block_gemm_kernel (fused all-reduce): %s", cudaGetErrorString(e));
+  }
+  return SGLB200_OK;
+}
+
 
 namespace sglb {
 int ue8m0_take_device_status();  // gemm_ue8m0.cu

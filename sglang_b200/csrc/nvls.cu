@@ -17,6 +17,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "nvls.cuh"
 #include "ptx.cuh"
 
 namespace sglb {
@@ -38,74 +39,13 @@ int nvls_take_device_status() {
 
 namespace {
 
-constexpr int kBlocks = 128;     // most blocks a launch may use (the flag block has a word per block and source rank)
+using nvls::FlagPtrs;
+using nvls::kBlocks;
+using nvls::kCtlWords;
+using nvls::kFlagWords;
+using nvls::kMaxRanks;
 constexpr int kThreads = 512;
-constexpr int kUnroll = 8;       // 16-byte vectors in flight per thread
-constexpr int kMaxRanks = 8;
-// flag block of a rank, in 32-bit words: [2 barriers][kMaxRanks sources][kBlocks] flags, then [kBlocks] epochs
-constexpr int kFlagWords = 2 * kMaxRanks * kBlocks;
-constexpr int kCtlWords = kBlocks;
-
-struct FlagPtrs {
-  uint32_t* p[kMaxRanks];  // flag block of every rank, as mapped into this process
-};
-
-template <bool BF16>
-__device__ __forceinline__ uint4 mm_ld_reduce(uint64_t addr) {
-  uint4 v;
-  if constexpr (BF16)
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(addr)
-                 : "memory");
-  else
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(addr)
-                 : "memory");
-  return v;
-}
-
-template <bool BF16>
-__device__ __forceinline__ void mm_st(uint64_t addr, uint4 v) {
-  if constexpr (BF16)
-    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
-                 "r"(v.z), "r"(v.w)
-                 : "memory");
-  else
-    asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y),
-                 "r"(v.z), "r"(v.w)
-                 : "memory");
-}
-
-// Barrier between block blockIdx.x of every rank.  Threads 0 .. world-1 each signal one peer and wait for one peer.
-// Returns false (uniformly over the block) when a wait ran out.
-__device__ __forceinline__ bool rank_barrier(const FlagPtrs& fp, int which, int rank, int world, uint32_t epoch,
-                                             uint64_t limit_ns, int* s_ok) {
-  __syncthreads();  // everything this block did so far is ordered before the signal
-  if ((int)threadIdx.x < world) {
-    const int peer = threadIdx.x;
-    __threadfence_system();
-    ptx::st_release_sys_u32(fp.p[peer] + ((which * kMaxRanks + rank) * kBlocks + blockIdx.x), epoch);
-    const uint32_t* f = fp.p[rank] + ((which * kMaxRanks + peer) * kBlocks + blockIdx.x);
-    uint64_t t0 = 0;
-    uint32_t polls = 0;
-    while ((int32_t)(ptx::ld_acquire_sys_u32(f) - epoch) < 0) {
-      if ((++polls & 255u) == 0) {
-        const uint64_t now = ptx::global_timer_ns();
-        if (t0 == 0) {
-          t0 = now;
-        } else if ((int64_t)(now - t0) > (int64_t)limit_ns) {
-          *s_ok = 0;
-          atomicCAS(&g_nvls_status, 0, 41 + which);
-          break;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  return *s_ok != 0;
-}
+constexpr int kUnroll = 8;  // 16-byte vectors in flight per thread
 
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads)
@@ -119,22 +59,13 @@ nvls_all_reduce_kernel(uint64_t mc_base, const __grid_constant__ FlagPtrs fp, in
   }
   __syncthreads();
   const uint32_t epoch = s_epoch;
-  bool ok = rank_barrier(fp, 0, rank, world, epoch, limit_ns, &s_ok);
+  bool ok = nvls::rank_barrier(fp, 0, blockIdx.x, rank, world, epoch, limit_ns, &s_ok, &g_nvls_status, 41);
   if (ok) {
     // this rank's slice, in 16-byte vectors
     const int64_t per_rank = (vecs + world - 1) / world;
     const int64_t v0 = (int64_t)rank * per_rank, v1 = min(vecs, v0 + per_rank);
-    const int64_t stride = (int64_t)gridDim.x * kThreads;
-    for (int64_t v = v0 + (int64_t)blockIdx.x * kThreads + threadIdx.x; v < v1; v += stride * kUnroll) {
-      uint4 r[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (v + u * stride < v1) r[u] = mm_ld_reduce<BF16>(mc_base + (uint64_t)(v + u * stride) * 16u);
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u)
-        if (v + u * stride < v1) mm_st<BF16>(mc_base + (uint64_t)(v + u * stride) * 16u, r[u]);
-    }
-    ok = rank_barrier(fp, 1, rank, world, epoch, limit_ns, &s_ok);
+    nvls::reduce_range<BF16, kUnroll>(mc_base, v0, v1, blockIdx.x, gridDim.x, kThreads);
+    ok = nvls::rank_barrier(fp, 1, blockIdx.x, rank, world, epoch, limit_ns, &s_ok, &g_nvls_status, 42);
   }
   // the epoch advances even after a time-out, so that the next launch does not pair with stale flags
   if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(ctl) = epoch;

@@ -6,7 +6,7 @@ from .expert_parallel import ep_fused_experts, ep_owner_tables  # noqa: F401
 from .peer_allreduce import PeerExchange, fused_row_parallel_linear  # noqa: F401
 from .peer_ep import PeerEpExchange, ep_fused_experts_peer  # noqa: F401
 from .symm_mem import (SymmMemCommunicator, row_parallel_linear_symm_mem,  # noqa: F401
-                       row_parallel_linear_symm_mem_overlapped)
+                       row_parallel_linear_symm_mem_fused, row_parallel_linear_symm_mem_overlapped)
 from .parallel_linear import (  # noqa: F401
     ColumnParallelBlockFp8Linear,
     RowParallelBlockFp8Linear,

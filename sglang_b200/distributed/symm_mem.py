@@ -63,6 +63,7 @@ class SymmMemCommunicator:
         self._handle, self._fhandle = handle, fhandle
         self.rank = handle.rank
         self._flag_blocks = (ctypes.c_uint64 * self.world_size)(*[int(p) for p in fhandle.buffer_ptrs])
+        self._done = torch.zeros(64, device=device, dtype=torch.int32)  # row-block counters of the fused GEMM
         self.side_stream = torch.cuda.Stream(device)  # the all-reduces of row chunks that overlap the next chunk's GEMM
         torch.cuda.synchronize(device)
         dist.barrier(group)  # every rank's flag block is zero before any kernel signals
@@ -182,6 +183,36 @@ def row_parallel_linear_symm_mem_overlapped(comm: SymmMemCommunicator, x: torch.
             with torch.cuda.stream(side):
                 comm.all_reduce_(part, blocks=ar_blocks)
     main.wait_stream(side)
+    if bias is not None:
+        y += bias
+    return y.reshape(*x.shape[:-1], N)
+
+
+def row_parallel_linear_symm_mem_fused(comm: SymmMemCommunicator, x: torch.Tensor, weight: torch.Tensor,
+                                       weight_scale: torch.Tensor, comm_ctas: int = 16,
+                                       bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`row_parallel_linear_symm_mem` with the GEMM and the all-reduce in ONE kernel launch
+    (``sglb200_fp8_blockwise_scaled_mm_allreduce``): ``comm_ctas`` CTAs of the GEMM's grid sum every finished block of
+    2048 output rows through the switch while the other CTAs compute the next block.  Same bits as the unfused form.
+    Every rank must pass the same ``comm_ctas``; the result is a view of ``comm``'s buffer."""
+    from ..layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    N = weight.shape[0]
+    y = comm.view((M, N), x.dtype)
+    if M == 0:
+        return y.reshape(*x.shape[:-1], N)
+    q, s = sglang_per_token_group_quant_fp8(x2, BLOCK, column_major_scales=True, scale_tma_aligned=True)
+    off = y.data_ptr() - comm.buffer.data_ptr()
+    with torch.cuda.device(comm.device):
+        check(lib().sglb200_fp8_blockwise_scaled_mm_allreduce(
+            q.data_ptr(), weight.data_ptr(), s.data_ptr(), weight_scale.data_ptr(), y.data_ptr(),
+            int(comm._handle.multicast_ptr) + off, comm._flag_blocks, comm._done.data_ptr(), comm.rank, comm.world_size,
+            int(comm_ctas), M, N, K, q.stride(0), weight.stride(0), s.stride(0), s.stride(1), weight_scale.stride(0),
+            weight_scale.stride(1), dtype_code(x.dtype), torch.cuda.current_stream(comm.device).cuda_stream),
+            "fp8_blockwise_scaled_mm_allreduce")
     if bias is not None:
         y += bias
     return y.reshape(*x.shape[:-1], N)

@@ -28,7 +28,8 @@ def _worker(rank, world, port, q):
         from helpers import assert_gemm_close, row_parallel_reference
         from sglang_b200._lib import lib
         from sglang_b200.distributed import (RowParallelBlockFp8Linear, SymmMemCommunicator,
-                                             row_parallel_linear_symm_mem, row_parallel_linear_symm_mem_overlapped)
+                                             row_parallel_linear_symm_mem, row_parallel_linear_symm_mem_fused,
+                                             row_parallel_linear_symm_mem_overlapped)
         dev = torch.device("cuda", rank)
         comm = SymmMemCommunicator(dist.group.WORLD, dev, max_size=64 << 20)
         if comm.disabled:
@@ -105,7 +106,7 @@ def _worker(rank, world, port, q):
         layer = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, symm_mem=comm)
         layer_b = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, bias=bias.cuda(), symm_mem=comm,
                                             symm_mem_chunk_rows=256, symm_mem_blocks=8)  # chunked from 257 rows up
-        for it, Ms in enumerate([200, 1, 2048, 333]):
+        for it, Ms in enumerate([200, 1, 2048 + 2048 + 130, 333]):  # the third: three row blocks, the last one ragged
             xs = torch.randn(Ms, I, generator=g).bfloat16()
             xr = xs[:, rank * (I // world):(rank + 1) * (I // world)].contiguous().cuda()
             y = layer(xr).clone()
@@ -114,12 +115,17 @@ def _worker(rank, world, port, q):
             # chunks of rows, each chunk's all-reduce (16 blocks, side stream) beside the next chunk's GEMM: same bits
             y_ovl = row_parallel_linear_symm_mem_overlapped(comm, xr, plain.weight, plain.weight_scale_inv,
                                                             chunk_rows=512, ar_blocks=16).clone()
+            # GEMM and all-reduce in one launch (communication CTAs inside the GEMM's grid): same bits again
+            y_fused = row_parallel_linear_symm_mem_fused(comm, xr, plain.weight, plain.weight_scale_inv,
+                                                         comm_ctas=[8, 16, 1, 32][it]).clone()
             y_n = plain(xr)
             torch.cuda.synchronize()
+            assert lib().sglb200_read_device_status() == 0
             ref = row_parallel_reference(xs, w_dn, s_dn, world)
             assert_gemm_close(y, ref, f"symm-mem row-parallel {it}", allow_one_ulp=True)
             assert torch.equal(y, y_direct)
             assert torch.equal(y, y_ovl), f"chunk-overlapped form differs ({it})"
+            assert torch.equal(y, y_fused), f"fused GEMM + all-reduce differs ({it})"
             # NCCL rounds the same sum to nearest: the two results differ by less than two units in the last place
             d = (y.float() - y_n.float()).abs().cpu().double()
             ulp = torch.ldexp(torch.ones_like(d), torch.frexp(ref.double().abs().clamp(min=1e-30))[1] - 8)
