@@ -342,7 +342,20 @@ def tp_llama_section(torch, dist, dev, gen, world, rank, M=8192, iters=5, mc=Non
         out["multicast_allreduce"] = {"ms_per_layer": ms_mc, "tflops": flops / (ms_mc * 1e-3) / 1e12,
                                       "how": "row-parallel GEMMs write into NVSwitch multicast memory, one multimem "
                                              "kernel (ld_reduce + st) per all-reduce"}
-        from sglang_b200.distributed import row_parallel_linear_symm_mem_overlapped
+        from sglang_b200.distributed import row_parallel_linear_symm_mem_fused, row_parallel_linear_symm_mem_overlapped
+
+        def step_fused():
+            for mode, w, ws, x in built:
+                if mode == "row":
+                    row_parallel_linear_symm_mem_fused(mc, x, w, ws, comm_ctas=16)
+                else:
+                    q, sc = sglang_per_token_group_quant_fp8(x, 128, column_major_scales=True, scale_tma_aligned=True)
+                    w8a8_block_fp8_matmul(q, w, sc, ws, [128, 128], torch.bfloat16)
+
+        ms_fu = timed(step_fused)
+        out["gemm_allreduce_one_launch"] = {
+            "ms_per_layer": ms_fu, "tflops": flops / (ms_fu * 1e-3) / 1e12,
+            "how": "row-parallel GEMM and multicast all-reduce in one cooperative launch, 16 communication CTAs"}
 
         def step_ovl():
             for mode, w, ws, x in built:
@@ -1027,7 +1040,7 @@ def main():
                            f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"
                                                        if args.comm_sms > 0 else "")) if overlap
                           else (f"row-parallel GEMM and multicast all-reduce in ONE launch: {fused_ctas[0]} CTAs of the GEMM's "
-                                "grid sum every finished block of 2048 output rows through the switch (multimem ld_reduce + "
+                                "grid sum every finished block of 1024 output rows through the switch (multimem ld_reduce + "
                                 "st) while the other CTAs compute the next block") if multicast and fused_ctas[0]
                           else (f"row-parallel GEMMs in chunks of {mc_chunk[0]} rows on {sm_total - ar_blocks[0]} SMs write "
                                 f"into NVSwitch multicast memory; this library's multimem kernel ({ar_blocks[0]} blocks, side "

@@ -48,6 +48,8 @@ constexpr uint32_t kStageBytes = kTileABytes + kTileBBytes;
 constexpr uint32_t kTmemCols = kAccStages * BN;  // 512
 constexpr int kMaxExperts = 1024;
 constexpr int kGroupM = 16;  // m-tiles per raster group (dense)
+constexpr int kGroupMAr = 8;  // the same in the GEMM with the fused all-reduce: a raster group is the unit that is
+                              // reduced over the ranks, and the reduction of the LAST group is not hidden
 constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + 256 /*barriers*/ +
                               (kMaxExperts + 1) * sizeof(int32_t);
 
@@ -103,7 +105,7 @@ struct PushGemmParams : GemmParams {
 };
 
 // GEMM + all-reduce in one launch (dense, out = a buffer every rank maps through one multicast address): the last
-// comm_ctas CTAs of the grid do not compute tiles.  They wait for the row blocks of `out` (one raster group of kGroupM
+// comm_ctas CTAs of the grid do not compute tiles.  They wait for the row blocks of `out` (one raster group of kGroupMAr
 // row tiles each) to be finished by the other CTAs of this grid (`done`, one counter per row block, bumped once per
 // promotion warp and tile), pair up with the same CTAs of the other ranks' kernels through the flag words, and sum the
 // block over the ranks with multimem.ld_reduce / multimem.st (nvls.cuh) while the GEMM CTAs work on the next row block.
@@ -150,7 +152,7 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, uint64_t
   else return ptx::mbar_wait_a(bar, parity, limit_ns);
 }
 
-template <bool GROUPED>
+template <bool GROUPED, int GROUP_M = kGroupM>
 __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int32_t* tile_start, int32_t t) {
   Tile tl;
   tl.kb0 = 0;
@@ -164,10 +166,10 @@ __device__ __forceinline__ Tile get_tile(const GemmParams& p, const int32_t* til
       tl.kb0 = tl.split * p.kb_per_split;
       tl.kb1 = min(tl.kb0 + p.kb_per_split, p.k_tiles);
     }
-    const int32_t per_group = kGroupM * p.n_tiles;
+    const int32_t per_group = GROUP_M * p.n_tiles;
     const int32_t gid = t / per_group;
-    const int32_t first_m = gid * kGroupM;
-    const int32_t gm = min(p.m_tiles - first_m, kGroupM);
+    const int32_t first_m = gid * GROUP_M;
+    const int32_t gm = min(p.m_tiles - first_m, GROUP_M);
     const int32_t local = t - gid * per_group;
     const int32_t nt = local / gm;
     const int32_t mt = first_m + (local - nt * gm);
@@ -364,10 +366,10 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       }
       __syncthreads();
       const uint32_t epoch0 = s_epoch;
-      const int32_t row_blocks = (p.m_tiles + kGroupM - 1) / kGroupM;
+      const int32_t row_blocks = (p.m_tiles + kGroupMAr - 1) / kGroupMAr;
       bool ok = true;
       for (int32_t rb = 0; rb < row_blocks && ok; ++rb) {
-        const int32_t mt_rb = min(kGroupM, p.m_tiles - rb * kGroupM);
+        const int32_t mt_rb = min(kGroupMAr, p.m_tiles - rb * kGroupMAr);
         const uint32_t target = (uint32_t)mt_rb * (uint32_t)p.n_tiles * kEpiWarps;
         if (threadIdx.x == 0) {
           uint64_t t0 = 0;
@@ -388,7 +390,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         ok = nvls::rank_barrier(p.ar.fp, 0, cb, p.ar.rank, p.ar.world, epoch0 + 1u + (uint32_t)rb, p.ar.limit_ns, &s_ok,
                                 &g_device_status, 7);
         if (!ok) break;
-        const int64_t row0 = (int64_t)rb * kGroupM * BM, rows = min((int64_t)p.total_rows - row0, (int64_t)kGroupM * BM);
+        const int64_t row0 = (int64_t)rb * kGroupMAr * BM, rows = min((int64_t)p.total_rows - row0, (int64_t)kGroupMAr * BM);
         const int64_t vec0 = row0 * p.N / 8, nvec = rows * p.N / 8;
         const int64_t per_rank = (nvec + p.ar.world - 1) / p.ar.world;
         const int64_t v0 = vec0 + (int64_t)p.ar.rank * per_rank, v1 = min(vec0 + nvec, v0 + per_rank);
@@ -407,7 +409,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t stage = 0, phase = 0, g = 0;
     uint32_t armed = 0, armed_phase = 0;  // bit i: this warp has armed stage i / the phase bit of its last arming
     for (int32_t t = blockIdx.x; t < total_tiles; t += tile_stride) {
-      const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+      const Tile tl = get_tile<GROUPED, AR ? kGroupMAr : kGroupM>(p, tile_start, t);
       bool ok = true;
       for (int32_t kb = tl.kb0; kb < tl.kb1; ++kb, ++g) {
         if ((g & (kIssuers - 1)) == (uint32_t)warp) {
@@ -454,7 +456,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       bool ok = true;
       int32_t kb_count = p.k_tiles;
       if (p.k_splits > 1) {
-        const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+        const Tile tl = get_tile<GROUPED, AR ? kGroupMAr : kGroupM>(p, tile_start, t);
         kb_count = tl.kb1 - tl.kb0;
       }
       for (int32_t kb = 0; kb < kb_count; ++kb, ++g) {
@@ -500,7 +502,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     uint32_t push_epoch = 0;
     if constexpr (PUSH) push_epoch = *reinterpret_cast<const volatile uint32_t*>(p.push.ctl) + 1u;
     for (int32_t t = blockIdx.x; t < total_tiles; t += tile_stride) {
-      const Tile tl = get_tile<GROUPED>(p, tile_start, t);
+      const Tile tl = get_tile<GROUPED, AR ? kGroupMAr : kGroupM>(p, tile_start, t);
       const int32_t row = tl.row0 + r_in_tile;
       const int32_t row_c = min(row, p.total_rows - 1);
       const float* sa_row = p.sa + (int64_t)row_c * p.sa_stride_m;
@@ -618,7 +620,7 @@ fp8_block_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
         __syncwarp();
         if (lane == 0) {
           __threadfence();
-          atomicAdd(p.ar.done + (tl.row0 / BM) / kGroupM, 1u);
+          atomicAdd(p.ar.done + (tl.row0 / BM) / kGroupMAr, 1u);
         }
       }
     }
@@ -1527,8 +1529,8 @@ extern "C" int sglb200_fp8_blockwise_scaled_mm_allreduce(const void* a, const vo
                "rank=%d world=%d: 2..%d ranks", rank, world, nvls::kMaxRanks);
   SGLB_REQUIRE(comm_ctas >= 1 && comm_ctas <= 64, SGLB200_ERR_SHAPE, "comm_ctas=%d: 1..64", comm_ctas);
   if (M == 0 || N == 0) return SGLB200_OK;
-  SGLB_REQUIRE((M + BM - 1) / BM <= 64 * kGroupM, SGLB200_ERR_SHAPE, "M=%lld: at most %d rows (64 row blocks)",
-               (long long)M, 64 * kGroupM * BM);
+  SGLB_REQUIRE((M + BM - 1) / BM <= 64 * kGroupMAr, SGLB200_ERR_SHAPE, "M=%lld: at most %d rows (64 row blocks)",
+               (long long)M, 64 * kGroupMAr * BM);
   SGLB_REQUIRE(a && b && sa && sb && out && flag_blocks && done_counters && multicast_out, SGLB200_ERR_NULL,
                "a/b/sa/sb/out/multicast_out/flag_blocks/done_counters must not be NULL");
   SGLB_REQUIRE(lda >= K && lda % 16 == 0 && ldb >= K && ldb % 16 == 0, SGLB200_ERR_ALIGN,

@@ -120,15 +120,16 @@ class RowParallelBlockFp8Linear(_ParallelBase):
     ``custom_all_reduce.py: should_custom_ar``); from four ranks up, outputs too large for that take the two-shot form
     (tile t reduced on rank t % world, results sent round).  Larger outputs take the multicast all-reduce of a
     ``symm_mem`` communicator (:class:`~sglang_b200.distributed.symm_mem.SymmMemCommunicator`; the GEMM writes into its
-    symmetric buffer and the returned tensor is a view of it; with ``symm_mem_chunk_rows`` the all-reduce of a row chunk
-    runs beside the next chunk's GEMM) when one is given and enabled, else the NCCL all-reduce.
+    symmetric buffer and the returned tensor is a view of it; with ``symm_mem_fused_ctas`` GEMM and all-reduce are one
+    launch, with ``symm_mem_chunk_rows`` the all-reduce of a row chunk runs beside the next chunk's GEMM) when one is
+    given and enabled, else the NCCL all-reduce.
     On that path the sum is taken by every rank for itself, so every rank keeps the whole bias and adds it once after
     the sum (decided here, where all ranks see the same arguments, not per rank in ``forward``)."""
 
     def __init__(self, weight, scale, rank: int, world: int, bias: Optional[torch.Tensor] = None,
                  input_is_parallel: bool = True, reduce_results: bool = True,
                  apply_fn: Optional[Callable] = None, group=None, peer_exchange=None, symm_mem=None,
-                 symm_mem_chunk_rows: int = 0, symm_mem_blocks: int = 16):
+                 symm_mem_chunk_rows: int = 0, symm_mem_blocks: int = 16, symm_mem_fused_ctas: int = 0):
         w, s = shard_block_fp8_weight(weight, scale, rank, world, 1)
         super().__init__(w, s, bias if rank == 0 else None, apply_fn, group)
         self.rank, self.world = rank, world
@@ -137,6 +138,8 @@ class RowParallelBlockFp8Linear(_ParallelBase):
         self.symm_mem = symm_mem
         # > 0: inputs with more rows run in chunks of this many, a chunk's all-reduce beside the next chunk's GEMM
         self.symm_mem_chunk_rows, self.symm_mem_blocks = int(symm_mem_chunk_rows), int(symm_mem_blocks)
+        # > 0: GEMM and all-reduce in one launch with this many communication CTAs (inputs of more than 1024 rows)
+        self.symm_mem_fused_ctas = int(symm_mem_fused_ctas)
         self.bias_after_sum = None
         if (peer_exchange is not None or symm_mem is not None) and bias is not None:
             self.bias_after_sum = torch.nn.Parameter(bias, requires_grad=False)
@@ -155,7 +158,11 @@ class RowParallelBlockFp8Linear(_ParallelBase):
         if (sm is not None and not sm.disabled and self.reduce_results and self.world > 1 and x.is_cuda
                 and x.dtype in (torch.bfloat16, torch.float16)
                 and (x.numel() // x.shape[-1]) * self.weight.shape[0] * 2 <= sm.max_size):
-            from .symm_mem import row_parallel_linear_symm_mem, row_parallel_linear_symm_mem_overlapped
+            from .symm_mem import (row_parallel_linear_symm_mem, row_parallel_linear_symm_mem_fused,
+                                   row_parallel_linear_symm_mem_overlapped)
+            if self.symm_mem_fused_ctas > 0 and x.numel() // x.shape[-1] > 1024:
+                return row_parallel_linear_symm_mem_fused(sm, x, self.weight, self.weight_scale_inv,
+                                                          self.symm_mem_fused_ctas, self.bias_after_sum)
             if 0 < self.symm_mem_chunk_rows < x.numel() // x.shape[-1]:
                 return row_parallel_linear_symm_mem_overlapped(sm, x, self.weight, self.weight_scale_inv,
                                                                self.symm_mem_chunk_rows, self.symm_mem_blocks,

@@ -104,6 +104,7 @@ def _worker(rank, world, port, q):
         plain = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world)
         bias = torch.randn(H, generator=g).bfloat16()
         layer = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, symm_mem=comm)
+        layer_f = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, symm_mem=comm, symm_mem_fused_ctas=12)
         layer_b = RowParallelBlockFp8Linear(w_dn.cuda(), s_dn.cuda(), rank, world, bias=bias.cuda(), symm_mem=comm,
                                             symm_mem_chunk_rows=256, symm_mem_blocks=8)  # chunked from 257 rows up
         for it, Ms in enumerate([200, 1, 2048 + 2048 + 130, 333]):  # the third: three row blocks, the last one ragged
@@ -118,9 +119,11 @@ def _worker(rank, world, port, q):
             # GEMM and all-reduce in one launch (communication CTAs inside the GEMM's grid): same bits again
             y_fused = row_parallel_linear_symm_mem_fused(comm, xr, plain.weight, plain.weight_scale_inv,
                                                          comm_ctas=[8, 16, 1, 32][it]).clone()
+            y_lf = layer_f(xr).clone()  # one launch from 1025 rows up, the plain multicast form below
             y_n = plain(xr)
             torch.cuda.synchronize()
             assert lib().sglb200_read_device_status() == 0
+            assert torch.equal(y_fused, y_lf)
             ref = row_parallel_reference(xs, w_dn, s_dn, world)
             assert_gemm_close(y, ref, f"symm-mem row-parallel {it}", allow_one_ulp=True)
             assert torch.equal(y, y_direct)
