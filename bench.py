@@ -1040,7 +1040,7 @@ def main():
                            f"the next chunk's GEMM" + (f"; GEMMs on {sm_total - args.comm_sms} of {sm_total} SMs"
                                                        if args.comm_sms > 0 else "")) if overlap
                           else (f"row-parallel GEMM and multicast all-reduce in ONE launch: {fused_ctas[0]} CTAs of the GEMM's "
-                                "grid sum every finished block of 1024 output rows through the switch (multimem ld_reduce + "
+                                "grid sum every finished block of 2048 output rows through the switch (multimem ld_reduce + "
                                 "st) while the other CTAs compute the next block") if multicast and fused_ctas[0]
                           else (f"row-parallel GEMMs in chunks of {mc_chunk[0]} rows on {sm_total - ar_blocks[0]} SMs write "
                                 f"into NVSwitch multicast memory; this library's multimem kernel ({ar_blocks[0]} blocks, side "

@@ -568,7 +568,7 @@ int64_t sglb200_nvls_flag_bytes(void);
 
 /*
  * The dense GEMM and the multicast all-reduce of its output in ONE cooperative launch: the row-parallel linear for
- * large outputs.  The last comm_ctas CTAs of the grid compute no tiles; row block by row block (1024 rows: one raster
+ * large outputs.  The last comm_ctas CTAs of the grid compute no tiles; row block by row block (2048 rows: one raster
  * group of the tile schedule) they wait until the tile CTAs of the same grid have stored the block (a device counter per
  * row block), pair up with the same CTAs of the other ranks' kernels (flag words as in sglb200_nvls_all_reduce) and sum
  * the block through the switch (multimem.ld_reduce / multimem.st) while the tile CTAs compute the next block; only the

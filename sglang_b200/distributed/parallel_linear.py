@@ -138,7 +138,7 @@ class RowParallelBlockFp8Linear(_ParallelBase):
         self.symm_mem = symm_mem
         # > 0: inputs with more rows run in chunks of this many, a chunk's all-reduce beside the next chunk's GEMM
         self.symm_mem_chunk_rows, self.symm_mem_blocks = int(symm_mem_chunk_rows), int(symm_mem_blocks)
-        # > 0: GEMM and all-reduce in one launch with this many communication CTAs (inputs of more than 1024 rows)
+        # > 0: GEMM and all-reduce in one launch with this many communication CTAs (inputs of more than 2048 rows)
         self.symm_mem_fused_ctas = int(symm_mem_fused_ctas)
         self.bias_after_sum = None
         if (peer_exchange is not None or symm_mem is not None) and bias is not None:
@@ -160,7 +160,7 @@ class RowParallelBlockFp8Linear(_ParallelBase):
                 and (x.numel() // x.shape[-1]) * self.weight.shape[0] * 2 <= sm.max_size):
             from .symm_mem import (row_parallel_linear_symm_mem, row_parallel_linear_symm_mem_fused,
                                    row_parallel_linear_symm_mem_overlapped)
-            if self.symm_mem_fused_ctas > 0 and x.numel() // x.shape[-1] > 1024:
+            if self.symm_mem_fused_ctas > 0 and x.numel() // x.shape[-1] > 2048:
                 return row_parallel_linear_symm_mem_fused(sm, x, self.weight, self.weight_scale_inv,
                                                           self.symm_mem_fused_ctas, self.bias_after_sum)
             if 0 < self.symm_mem_chunk_rows < x.numel() // x.shape[-1]:

@@ -193,7 +193,7 @@ def row_parallel_linear_symm_mem_fused(comm: SymmMemCommunicator, x: torch.Tenso
                                        bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     """:func:`row_parallel_linear_symm_mem` with the GEMM and the all-reduce in ONE kernel launch
     (``sglb200_fp8_blockwise_scaled_mm_allreduce``): ``comm_ctas`` CTAs of the GEMM's grid sum every finished block of
-    1024 output rows through the switch while the other CTAs compute the next block.  Same bits as the unfused form.
+    2048 output rows through the switch while the other CTAs compute the next block.  Same bits as the unfused form.
     Every rank must pass the same ``comm_ctas``; the result is a view of ``comm``'s buffer."""
     from ..layers.quantization.fp8_kernel import sglang_per_token_group_quant_fp8
     x2 = x.reshape(-1, x.shape[-1])

@@ -119,7 +119,7 @@ def _worker(rank, world, port, q):
             # GEMM and all-reduce in one launch (communication CTAs inside the GEMM's grid): same bits again
             y_fused = row_parallel_linear_symm_mem_fused(comm, xr, plain.weight, plain.weight_scale_inv,
                                                          comm_ctas=[8, 16, 1, 32][it]).clone()
-            y_lf = layer_f(xr).clone()  # one launch from 1025 rows up, the plain multicast form below
+            y_lf = layer_f(xr).clone()  # one launch from 2049 rows up, the plain multicast form below
             y_n = plain(xr)
             torch.cuda.synchronize()
             assert lib().sglb200_read_device_status() == 0
