@@ -514,6 +514,9 @@ def parity_section(torch, dist, dev, world, rank):
         if not mc.disabled:
             outs["tp_multicast_allreduce"] = row_parallel_linear_symm_mem(mc, xr, layer.weight,
                                                                           layer.weight_scale_inv).clone()
+            from sglang_b200.distributed import row_parallel_linear_symm_mem_fused
+            outs["tp_multicast_gemm_allreduce_one_launch"] = row_parallel_linear_symm_mem_fused(
+                mc, xr, layer.weight, layer.weight_scale_inv, comm_ctas=8).clone()
             torch.cuda.synchronize()
     finally:
         mc.close()
