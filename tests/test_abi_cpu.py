@@ -200,3 +200,38 @@ def test_symm_mem_communicator_is_disabled_without_a_gpu():
     with pytest.raises(RuntimeError):
         comm.view((8,))
     comm.close()
+
+
+def test_host_validation_of_the_multicast_and_few_rows_entries(built_lib):
+    """The multicast all-reduce, the GEMM with the all-reduce in its launch and the kernel-selection setters refuse bad
+    arguments on the host, before any device is touched."""
+    import ctypes
+    from sglang_b200._lib import lib
+    L = lib()
+    detail = lambda: L.sglb200_last_error_detail().decode()
+    flags = (ctypes.c_uint64 * 8)(*([4096] * 8))
+    assert L.sglb200_nvls_flag_bytes() == (2 * 8 * 128 + 128) * 4
+    assert L.sglb200_nvls_all_reduce(4096, flags, 0, 1, 64, 0, 0, None) == -1 and "world" in detail()
+    assert L.sglb200_nvls_all_reduce(4096, flags, 2, 2, 64, 0, 0, None) == -1 and "rank" in detail()
+    assert L.sglb200_nvls_all_reduce(4096, flags, 0, 2, 60, 0, 0, None) == -1 and "multiple of 8" in detail()
+    assert L.sglb200_nvls_all_reduce(4096, flags, 0, 2, 64, 2, 0, None) == -5          # fp32 is not a dtype it adds
+    assert L.sglb200_nvls_all_reduce(4096, flags, 0, 2, 64, 0, 129, None) == -1 and "blocks" in detail()
+    assert L.sglb200_nvls_all_reduce(4096, flags, 0, 2, 0, 0, 0, None) == 0             # nothing to add
+    assert L.sglb200_nvls_all_reduce(0, flags, 0, 2, 64, 0, 0, None) == -6
+    assert L.sglb200_nvls_all_reduce(4104, flags, 0, 2, 64, 0, 0, None) == -2           # not 16-byte aligned
+    mm = L.sglb200_fp8_blockwise_scaled_mm_allreduce
+    args = lambda **kw: [kw.get(k, v) for k, v in dict(a=None, b=None, sa=None, sb=None, out=None, mc=4096, flags=flags,
+                                                       done=None, rank=0, world=2, ctas=16, M=256, N=512, K=1024, lda=1024,
+                                                       ldb=1024, sam=1, sak=256, sbn=8, sbk=1, dt=0, st=None).items()]
+    assert mm(*args(world=9)) == -1 and "ranks" in detail()
+    assert mm(*args(ctas=0)) == -1 and "comm_ctas" in detail()
+    assert mm(*args(ctas=65)) == -1
+    assert mm(*args(K=1000)) == -1 and "multiple of 16" in detail()
+    assert mm(*args(dt=2)) == -5
+    assert mm(*args(M=0)) == 0
+    assert mm(*args(M=64 * 16 * 128 + 1)) == -1 and "row blocks" in detail()
+    assert mm(*args()) == -6                                                          # NULL operands
+    before = L.sglb200_get_grouped_few_rows()
+    assert L.sglb200_set_grouped_few_rows(65) == -1 and L.sglb200_set_grouped_few_rows(-1) == -1
+    assert L.sglb200_set_grouped_few_rows(0) == 0 and L.sglb200_get_grouped_few_rows() == 0
+    assert L.sglb200_set_grouped_few_rows(before) == 0 and L.sglb200_get_grouped_few_rows() == before == 20

@@ -67,6 +67,15 @@ def _worker(rank, world, port, q):
 
         gathered = ColumnParallelBlockFp8Linear(w_up, s_up, rank, world, gather_output=True, apply_fn=_oracle_apply)(x)
         assert torch.equal(gathered, h_ref)
+        # a symmetric-memory communicator that declined (no GPU here) leaves the layer on the collective library's
+        # all-reduce, with the bias on rank 0 before the sum, whatever the one-launch / chunk options say
+        from sglang_b200.distributed import SymmMemCommunicator
+        comm = SymmMemCommunicator(dist.group.WORLD, "cpu")
+        assert comm.disabled
+        down_sm = RowParallelBlockFp8Linear(w_dn, s_dn, rank, world, bias=bias, apply_fn=_oracle_apply, symm_mem=comm,
+                                            symm_mem_fused_ctas=16, symm_mem_chunk_rows=8)
+        assert torch.equal(down_sm(h_local), y)
+        comm.close()
         try:
             shard_block_fp8_weight(w_up[:640], s_up[:5], rank, world, 0)   # 320 rows per rank: not a block multiple
             raise AssertionError("bad split accepted")
