@@ -1012,17 +1012,26 @@ def main():
                 ar_blocks[0] = int(mode.split("_")[3])
             if overlap:
                 chunk_rows[0] = int(mode.split("_")[1])
-            step()
-            fence()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _ in range(3):
+            # an order that the library refuses on this box (a host-side status, nothing launched) is left out on every
+            # rank alike: the ranks agree on the outcome before the next one is tried
+            failed = 0
+            try:
                 step()
-            a1.record()
+                fence()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(3):
+                    step()
+                a1.record()
+            except RuntimeError as e:
+                failed = 1
+                config.setdefault("step_refused", {})[mode] = str(e)[:200]
             fence()
-            tt = torch.tensor([a0.elapsed_time(a1) / 3], device=dev)
+            tt = torch.tensor([a0.elapsed_time(a1) / 3 if not failed else float("inf"), float(failed)], device=dev)
             dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            tried[mode] = float(tt)
+            if float(tt[1]) > 0:
+                continue
+            tried[mode] = float(tt[0])
         best = min(tried, key=tried.get)
         overlap, multicast = best.startswith("overlapped"), best.startswith("multicast")
         mc_chunk[0] = int(best.split("_")[2]) if best.startswith("multicast_overlapped") else 0

@@ -33,6 +33,7 @@ class SymmMemCommunicator:
     def __init__(self, group, device: Union[int, str, torch.device], max_size: int = 256 << 20):
         self.disabled = True
         self.buffer = None
+        self.declined_because = ""
         try:
             import torch.distributed._symmetric_memory as tsm
         except ImportError:
@@ -50,23 +51,34 @@ class SymmMemCommunicator:
         if self.world_size < 2 or self.world_size > 8 or torch.cuda.get_device_capability(device)[0] != 10:
             return
         torch.cuda.set_device(device)
-        name = group.group_name if group is not None else dist.group.WORLD.group_name
-        self.buffer = tsm.empty(self.max_size // 2, device=device, dtype=self.dtype)
-        handle = tsm.rendezvous(self.buffer, name)
-        if handle.multicast_ptr == 0:  # no NVSwitch multicast on this node (symm_mem.py:103-110)
+        # A rank that cannot set the mapping up (no multicast support, an allocator or handle-exchange error) must not
+        # leave the others waiting in a later collective: every rank reports, and all decline together.
+        ok, why = 1, ""
+        try:
+            name = group.group_name if group is not None else dist.group.WORLD.group_name
+            self.buffer = tsm.empty(self.max_size // 2, device=device, dtype=self.dtype)
+            handle = tsm.rendezvous(self.buffer, name)
+            if handle.multicast_ptr == 0:  # no NVSwitch multicast on this node (symm_mem.py:103-110)
+                ok, why = 0, "no multicast mapping"
+            else:
+                flag_words = lib().sglb200_nvls_flag_bytes() // 4
+                self._flags = tsm.empty(flag_words, device=device, dtype=torch.int32)
+                self._flags.zero_()
+                fhandle = tsm.rendezvous(self._flags, name)
+                self._handle, self._fhandle = handle, fhandle
+                self.rank = handle.rank
+                self._flag_blocks = (ctypes.c_uint64 * self.world_size)(*[int(p) for p in fhandle.buffer_ptrs])
+                self._done = torch.zeros(64, device=device, dtype=torch.int32)  # row-block counters of the fused GEMM
+                self.side_stream = torch.cuda.Stream(device)  # all-reduces of row chunks beside the next chunk's GEMM
+        except Exception as e:  # noqa: BLE001 - declined, like the reference's wrapper; the reason is kept
+            ok, why = 0, f"{type(e).__name__}: {e}"
+        agreed = torch.tensor([ok], device=device, dtype=torch.int32)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)  # also: every flag block is zero before any kernel signals
+        torch.cuda.synchronize(device)
+        self.declined_because = why
+        if int(agreed.item()) == 0:
             self.buffer = None
             return
-        flag_words = lib().sglb200_nvls_flag_bytes() // 4
-        self._flags = tsm.empty(flag_words, device=device, dtype=torch.int32)
-        self._flags.zero_()
-        fhandle = tsm.rendezvous(self._flags, name)
-        self._handle, self._fhandle = handle, fhandle
-        self.rank = handle.rank
-        self._flag_blocks = (ctypes.c_uint64 * self.world_size)(*[int(p) for p in fhandle.buffer_ptrs])
-        self._done = torch.zeros(64, device=device, dtype=torch.int32)  # row-block counters of the fused GEMM
-        self.side_stream = torch.cuda.Stream(device)  # the all-reduces of row chunks that overlap the next chunk's GEMM
-        torch.cuda.synchronize(device)
-        dist.barrier(group)  # every rank's flag block is zero before any kernel signals
         self.disabled = False
 
     # ------------------------------------------------------------------ the reference's interface
